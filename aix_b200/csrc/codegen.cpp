@@ -1,0 +1,500 @@
+#include "codegen.hpp"
+
+#include <algorithm>
+#include <sstream>
+
+namespace aixb200
+{
+
+namespace
+{
+
+// Element-type traits and per-op semantics shared by every generated kernel.
+//
+// Semantics follow the reference's CPU device (aixDeviceCPU.cpp:28-255):
+//  * f16 / bf16 compute every op in float and round to the 16-bit type after it (aixFloat16.hpp:104-122, 698-716);
+//  * integers wrap in their storage type; 8/16-bit values are held in int and re-narrowed after each op;
+//  * sqrt/log/exp/pow on integers go through a wide float and a saturating, NaN->0 conversion back
+//    (convertGenericValue, aixDeviceCPU.cpp:96-117); sin/cos/tanh on integers are a plain truncating conversion;
+//  * dtype conversion float-like -> integer saturates and maps NaN to 0, everything else is a C++ static_cast.
+const char* kPrelude = R"PRELUDE(
+typedef unsigned short     u16_t;
+typedef long long          i64_t;
+typedef unsigned long long u64_t;
+
+template <class S, int E> struct alignas((sizeof(S) * E) >= 16 ? 16 : (sizeof(S) * E)) Pack { S v[E]; };
+
+__device__ __forceinline__ float f16_to_f32(u16_t h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+__device__ __forceinline__ u16_t f32_to_f16(float f) { u16_t h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+__device__ __forceinline__ float bf16_to_f32(u16_t h) { return __uint_as_float(((unsigned)h) << 16); }
+__device__ __forceinline__ u16_t f32_to_bf16(float f) { u16_t h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+
+// kind: 0 = IEEE float computed in C, 1 = integer (wraps; C is the register type, U its unsigned twin)
+struct Df64  { typedef double S; typedef double C; typedef double U; static const int kind = 0; static const int id = 0;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return c; }
+    static __device__ __forceinline__ C fix(C c) { return c; } };
+struct Df32  { typedef float S; typedef float C; typedef float U; static const int kind = 0; static const int id = 1;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return c; }
+    static __device__ __forceinline__ C fix(C c) { return c; } };
+struct Df16  { typedef u16_t S; typedef float C; typedef float U; static const int kind = 0; static const int id = 2;
+    static __device__ __forceinline__ C ld(S s) { return f16_to_f32(s); }  static __device__ __forceinline__ S st(C c) { return f32_to_f16(c); }
+    static __device__ __forceinline__ C fix(C c) { return f16_to_f32(f32_to_f16(c)); } };
+struct Dbf16 { typedef u16_t S; typedef float C; typedef float U; static const int kind = 0; static const int id = 3;
+    static __device__ __forceinline__ C ld(S s) { return bf16_to_f32(s); }  static __device__ __forceinline__ S st(C c) { return f32_to_bf16(c); }
+    static __device__ __forceinline__ C fix(C c) { return bf16_to_f32(f32_to_bf16(c)); } };
+struct Di64  { typedef i64_t S; typedef i64_t C; typedef u64_t U; static const int kind = 1; static const int id = 4;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return c; }
+    static __device__ __forceinline__ C fix(C c) { return c; }
+    static __device__ __forceinline__ C sat(double x) { return __double2ll_rz(x); } };
+struct Di32  { typedef int S; typedef int C; typedef unsigned U; static const int kind = 1; static const int id = 5;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return c; }
+    static __device__ __forceinline__ C fix(C c) { return c; }
+    static __device__ __forceinline__ C sat(double x) { return __double2int_rz(x); } };
+struct Di16  { typedef short S; typedef int C; typedef unsigned U; static const int kind = 1; static const int id = 6;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return (short)c; }
+    static __device__ __forceinline__ C fix(C c) { return (int)(short)c; }
+    static __device__ __forceinline__ C sat(double x) { return min(max(__double2int_rz(x), -32768), 32767); } };
+struct Di8   { typedef signed char S; typedef int C; typedef unsigned U; static const int kind = 1; static const int id = 7;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return (signed char)c; }
+    static __device__ __forceinline__ C fix(C c) { return (int)(signed char)c; }
+    static __device__ __forceinline__ C sat(double x) { return min(max(__double2int_rz(x), -128), 127); } };
+struct Du8   { typedef unsigned char S; typedef int C; typedef unsigned U; static const int kind = 1; static const int id = 8;
+    static __device__ __forceinline__ C ld(S s) { return s; }  static __device__ __forceinline__ S st(C c) { return (unsigned char)c; }
+    static __device__ __forceinline__ C fix(C c) { return (int)(unsigned char)c; }
+    static __device__ __forceinline__ C sat(double x) { return min(max(__double2int_rz(x), 0), 255); } };
+
+__device__ __forceinline__ float  m_sqrt(float x)  { return sqrtf(x); }   __device__ __forceinline__ double m_sqrt(double x) { return sqrt(x); }
+__device__ __forceinline__ float  m_sin(float x)   { return sinf(x); }    __device__ __forceinline__ double m_sin(double x)  { return sin(x); }
+__device__ __forceinline__ float  m_cos(float x)   { return cosf(x); }    __device__ __forceinline__ double m_cos(double x)  { return cos(x); }
+__device__ __forceinline__ float  m_tanh(float x)  { return tanhf(x); }   __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
+__device__ __forceinline__ float  m_log(float x)   { return logf(x); }    __device__ __forceinline__ double m_log(double x)  { return log(x); }
+__device__ __forceinline__ float  m_exp(float x)   { return expf(x); }    __device__ __forceinline__ double m_exp(double x)  { return exp(x); }
+__device__ __forceinline__ float  m_pow(float x, float y)   { return powf(x, y); }
+__device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }
+
+#define AIX_C typename D::C
+#define AIX_U typename D::U
+template <class D> __device__ __forceinline__ AIX_C op_add(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(a + b); else return D::fix((AIX_C)((AIX_U)a + (AIX_U)b)); }
+template <class D> __device__ __forceinline__ AIX_C op_sub(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(a - b); else return D::fix((AIX_C)((AIX_U)a - (AIX_U)b)); }
+template <class D> __device__ __forceinline__ AIX_C op_mul(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(a * b); else return D::fix((AIX_C)((AIX_U)a * (AIX_U)b)); }
+template <class D> __device__ __forceinline__ AIX_C op_div(AIX_C a, AIX_C b)
+{
+    if constexpr (D::kind == 0) return D::fix(a / b);
+    else if constexpr (D::id == 4) return (b == 0) ? (AIX_C)0 : ((b == -1) ? (AIX_C)((AIX_U)0 - (AIX_U)a) : a / b);
+    else return (b == 0) ? 0 : D::fix((AIX_C)((i64_t)a / (i64_t)b));
+}
+template <class D> __device__ __forceinline__ AIX_C op_neg(AIX_C a) { if constexpr (D::kind == 0) return D::fix(-a); else return D::fix((AIX_C)((AIX_U)0 - (AIX_U)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_sqrt(AIX_C a) { if constexpr (D::kind == 0) return D::fix(m_sqrt(a)); else return D::sat(sqrt((double)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_log(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_log(a));  else return D::sat(log((double)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_exp(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_exp(a));  else return D::sat(exp((double)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_pow(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(m_pow(a, b)); else return D::sat(pow((double)a, (double)b)); }
+template <class D> __device__ __forceinline__ AIX_C op_sin(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_sin(a));  else return D::fix((AIX_C)sin((double)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_cos(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_cos(a));  else return D::fix((AIX_C)cos((double)a)); }
+template <class D> __device__ __forceinline__ AIX_C op_tanh(AIX_C a) { if constexpr (D::kind == 0) return D::fix(m_tanh(a)); else return D::fix((AIX_C)tanh((double)a)); }
+// SD -> D conversion of a register value
+template <class SD, class D> __device__ __forceinline__ AIX_C op_cast(typename SD::C x)
+{
+    if constexpr (SD::id == D::id) return x;
+    else if constexpr (D::kind == 1 && SD::kind == 0) return D::sat((double)x);
+    else if constexpr (D::kind == 1) return D::fix((AIX_C)x);
+    else if constexpr (D::id == 0) return (double)x;
+    else return D::fix((float)x);
+}
+)PRELUDE";
+
+const char* kTraits[DTYPE_COUNT] = {"Df64", "Df32", "Df16", "Dbf16", "Di64", "Di32", "Di16", "Di8", "Du8"};
+
+enum class Path : uint8_t { DenseWide, DenseElem, Scalar, RowWide, ColWide, General };
+
+Path loadPath(const KernelLoad& l, bool fast)
+{
+    switch (l.access)
+    {
+        case Access::Dense:    return fast ? Path::DenseWide : Path::DenseElem;
+        case Access::Scalar:   return Path::Scalar;
+        case Access::RowBcast: return fast ? Path::RowWide : Path::General;
+        case Access::ColBcast: return fast ? Path::ColWide : Path::General;
+        default:               return Path::General;
+    }
+}
+
+Path storePath(const KernelStore& s, bool fast)
+{
+    if (s.access == Access::Dense) return fast ? Path::DenseWide : Path::DenseElem;
+    return Path::General;
+}
+
+bool aligned(const View& v, size_t bytes) { return (reinterpret_cast<uintptr_t>(v.firstByte()) % bytes) == 0; }
+
+size_t packBytes(uint8_t dtype, int vec) { return std::min<size_t>(16, dtypeSize(dtype) * vec); }
+
+}   // namespace
+
+KernelVariant chooseVariant(const KernelSpec& spec)
+{
+    KernelVariant v;
+    size_t minSize = 8, maxSize = 1;
+    uint64_t maxSpan = spec.count;
+    for (auto& l : spec.loads)
+    {
+        if (l.access != Access::Scalar) { minSize = std::min(minSize, dtypeSize(l.view.dtype)); maxSize = std::max(maxSize, dtypeSize(l.view.dtype)); }
+        maxSpan = std::max(maxSpan, l.view.span());
+    }
+    for (auto& s : spec.stores)
+    {
+        minSize = std::min(minSize, dtypeSize(s.view.dtype));
+        maxSize = std::max(maxSize, dtypeSize(s.view.dtype));
+        maxSpan = std::max(maxSpan, s.view.span());
+    }
+    v.vec = static_cast<int>(std::max<size_t>(1, std::min<size_t>(16 / minSize, 64 / maxSize)));
+    v.index64 = maxSpan >= (uint64_t(1) << 31);
+    for (size_t i = 0; i < spec.loads.size(); ++i)
+    {
+        const KernelLoad& l = spec.loads[i];
+        bool fast = false;
+        switch (l.access)
+        {
+            case Access::Dense:    fast = aligned(l.view, packBytes(l.view.dtype, v.vec)); break;
+            case Access::Scalar:   fast = true; break;
+            case Access::RowBcast: fast = (l.view.shape[1] % v.vec == 0) && aligned(l.view, packBytes(l.view.dtype, v.vec)); break;
+            case Access::ColBcast: fast = (l.view.shape[1] % v.vec == 0); break;
+            default: break;
+        }
+        if (fast) v.fastLoads |= (1u << i);
+    }
+    for (size_t i = 0; i < spec.stores.size(); ++i)
+    {
+        const KernelStore& s = spec.stores[i];
+        if (s.access == Access::Dense && aligned(s.view, packBytes(s.view.dtype, v.vec))) v.fastStores |= (1u << i);
+    }
+    return v;
+}
+
+std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, const CodegenOptions& options)
+{
+    std::string key;
+    key.reserve(64 + spec.nodes.size() * 12);
+    auto put = [&](unsigned x) { key += std::to_string(x); key += '.'; };
+    key += "E"; put(variant.vec); put(variant.index64); put(options.block); put(options.unroll); put(options.strictMath);
+    key += "L";
+    for (size_t i = 0; i < spec.loads.size(); ++i)
+    {
+        const auto& l = spec.loads[i];
+        Path p = loadPath(l, (variant.fastLoads >> i) & 1u);
+        put(l.view.dtype); put(static_cast<unsigned>(p));
+        if (p == Path::General) put(l.view.rank);
+    }
+    key += "N";
+    for (const auto& nd : spec.nodes)
+    {
+        put(static_cast<unsigned>(nd.op)); put(nd.dtype); put(nd.srcDtype);
+        put(nd.a.kind); put(nd.a.index); put(nd.b.kind); put(nd.b.index); put(nd.scalarIndex);
+    }
+    key += "S";
+    for (size_t i = 0; i < spec.stores.size(); ++i)
+    {
+        const auto& s = spec.stores[i];
+        Path p = storePath(s, (variant.fastStores >> i) & 1u);
+        put(s.view.dtype); put(static_cast<unsigned>(p)); put(s.node);
+        if (p == Path::General) put(s.view.rank);
+    }
+    return key;
+}
+
+std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVariant& variant)
+{
+    std::vector<uint64_t> a;
+    a.reserve(spec.loads.size() * 3 + spec.stores.size() * 3 + spec.scalars.size() + 1);
+    for (auto& l : spec.loads) a.push_back(reinterpret_cast<uint64_t>(l.view.firstByte()));
+    for (auto& s : spec.stores) a.push_back(reinterpret_cast<uint64_t>(s.view.firstByte()));
+    a.push_back(spec.count);
+    for (auto& sc : spec.scalars) a.push_back(sc.raw);
+    auto pushLayout = [&](const View& v)
+    {
+        for (int d = 0; d < v.rank; ++d) a.push_back(v.shape[d]);
+        for (int d = 0; d < v.rank; ++d) a.push_back(v.strides[d]);
+    };
+    for (size_t i = 0; i < spec.loads.size(); ++i)
+    {
+        const auto& l = spec.loads[i];
+        switch (loadPath(l, (variant.fastLoads >> i) & 1u))
+        {
+            case Path::RowWide: a.push_back(l.view.shape[1]); break;
+            case Path::ColWide: a.push_back(l.view.shape[1]); a.push_back(l.view.strides[0]); break;
+            case Path::General: pushLayout(l.view); break;
+            default: break;
+        }
+    }
+    for (size_t i = 0; i < spec.stores.size(); ++i)
+        if (storePath(spec.stores[i], (variant.fastStores >> i) & 1u) == Path::General) pushLayout(spec.stores[i].view);
+    return a;
+}
+
+std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& variant, const CodegenOptions& options,
+                                 const std::string& entryName)
+{
+    const int E = variant.vec, U = options.unroll, B = options.block;
+    const size_t nL = spec.loads.size(), nS = spec.stores.size();
+    std::ostringstream o;
+    o << kPrelude << "\n";
+    o << "typedef " << (variant.index64 ? "unsigned long long" : "unsigned int") << " idx_t;\n";
+
+    // ---- argument slots -------------------------------------------------------------------------------------------
+    size_t slot = nL + nS;
+    const size_t slotCount = slot++;
+    const size_t slotScalars = slot;
+    slot += spec.scalars.size();
+    std::vector<size_t> loadAux(nL, 0), storeAux(nS, 0);
+    std::vector<Path> lp(nL), sp(nS);
+    for (size_t i = 0; i < nL; ++i)
+    {
+        lp[i] = loadPath(spec.loads[i], (variant.fastLoads >> i) & 1u);
+        loadAux[i] = slot;
+        if (lp[i] == Path::RowWide) slot += 1;
+        else if (lp[i] == Path::ColWide) slot += 2;
+        else if (lp[i] == Path::General) slot += 2 * spec.loads[i].view.rank;
+    }
+    for (size_t i = 0; i < nS; ++i)
+    {
+        sp[i] = storePath(spec.stores[i], (variant.fastStores >> i) & 1u);
+        storeAux[i] = slot;
+        if (sp[i] == Path::General) slot += 2 * spec.stores[i].view.rank;
+    }
+    o << "struct Params { u64_t a[" << std::max<size_t>(slot, 1) << "]; };\n\n";
+
+    auto T = [&](uint8_t dt) { return std::string(kTraits[dt]); };
+    auto arg = [&](size_t s) { return "p.a[" + std::to_string(s) + "]"; };
+
+    // Offset (in elements) of logical element `i` inside a general strided view whose layout sits at slot `aux`.
+    auto emitGeneralOffset = [&](std::ostream& os, const std::string& var, const std::string& i, int rank, size_t aux,
+                                 const std::string& indent)
+    {
+        os << indent << "idx_t " << var << " = 0;\n";
+        if (rank == 0) return;
+        os << indent << "{ idx_t r_ = " << i << ";\n";
+        for (int d = rank - 1; d >= 1; --d)
+        {
+            os << indent << "  { const idx_t e_ = (idx_t)" << arg(aux + d) << "; const idx_t q_ = r_ / e_; " << var
+               << " += (r_ - q_ * e_) * (idx_t)" << arg(aux + rank + d) << "; r_ = q_; }\n";
+        }
+        os << indent << "  " << var << " += r_ * (idx_t)" << arg(aux + rank) << "; }\n";
+    };
+
+    // The straight-line SSA body for one element. `in(l)` yields the expression of load l's storage value.
+    auto emitNodes = [&](std::ostream& os, const std::string& indent, auto&& in)
+    {
+        auto operand = [&](const OperandRef& r, uint8_t want) -> std::string
+        {
+            if (r.kind == OperandRef::Reg)
+            {
+                uint8_t have = spec.nodes[r.index].dtype;
+                std::string v = "v" + std::to_string(r.index);
+                return have == want ? v : "op_cast<" + T(have) + ", " + T(want) + ">(" + v + ")";
+            }
+            uint8_t have = spec.loads[r.index].view.dtype;
+            std::string v = T(have) + "::ld(" + in(r.index) + ")";
+            return have == want ? v : "op_cast<" + T(have) + ", " + T(want) + ">(" + v + ")";
+        };
+        for (size_t k = 0; k < spec.nodes.size(); ++k)
+        {
+            const KernelNode& nd = spec.nodes[k];
+            const std::string D = T(nd.dtype);
+            os << indent << "const " << D << "::C v" << k << " = ";
+            switch (nd.op)
+            {
+                case Op::Fill:
+                    os << D << "::ld(sc" << nd.scalarIndex << ")";
+                    break;
+                case Op::Cast:
+                {
+                    // operand in its own type, then converted
+                    OperandRef r = nd.a;
+                    uint8_t have = r.kind == OperandRef::Reg ? spec.nodes[r.index].dtype : spec.loads[r.index].view.dtype;
+                    os << "op_cast<" << T(have) << ", " << D << ">(" << operand(r, have) << ")";
+                    break;
+                }
+                case Op::Add: case Op::Sub: case Op::Mul: case Op::Div: case Op::Pow:
+                    os << "op_" << opName(nd.op) << "<" << D << ">(" << operand(nd.a, nd.dtype) << ", " << operand(nd.b, nd.dtype) << ")";
+                    break;
+                default:
+                    os << "op_" << opName(nd.op) << "<" << D << ">(" << operand(nd.a, nd.dtype) << ")";
+                    break;
+            }
+            os << ";\n";
+        }
+    };
+
+    o << "extern \"C\" __global__ void __launch_bounds__(" << B << ") " << entryName
+      << "(const __grid_constant__ Params p)\n{\n";
+    o << "    const idx_t n = (idx_t)" << arg(slotCount) << ";\n";
+    for (size_t i = 0; i < nL; ++i)
+        o << "    const " << T(spec.loads[i].view.dtype) << "::S* const l" << i << " = (const " << T(spec.loads[i].view.dtype)
+          << "::S*)" << arg(i) << ";\n";
+    for (size_t i = 0; i < nS; ++i)
+        o << "    " << T(spec.stores[i].view.dtype) << "::S* const s" << i << " = (" << T(spec.stores[i].view.dtype)
+          << "::S*)" << arg(nL + i) << ";\n";
+    for (size_t i = 0; i < spec.scalars.size(); ++i)
+    {
+        const std::string S = T(spec.scalarDtypes[i]) + "::S";
+        o << "    " << S << " sc" << i << "; { const u64_t raw_ = " << arg(slotScalars + i) << "; sc" << i << " = *(const " << S
+          << "*)&raw_; }\n";
+    }
+    for (size_t i = 0; i < nL; ++i)
+        if (lp[i] == Path::Scalar) o << "    const " << T(spec.loads[i].view.dtype) << "::S x" << i << "s = l" << i << "[0];\n";
+
+    // ---- main loop: U packs of E elements per thread and iteration ----------------------------------------------
+    if (E > 1)
+    {
+        o << "    const idx_t nvec = n / " << E << ";\n";
+        o << "    if (nvec != 0)\n    {\n";
+        o << "        idx_t pk = (idx_t)blockIdx.x * " << (B * U) << " + threadIdx.x;\n";
+        o << "        const idx_t gstep = (idx_t)gridDim.x * " << (B * U) << ";\n";
+        // hoisted broadcast state
+        for (size_t i = 0; i < nL; ++i)
+        {
+            if (lp[i] == Path::RowWide)
+            {
+                o << "        const idx_t cp" << i << " = (idx_t)" << arg(loadAux[i]) << " / " << E << ";          // packs per row\n";
+                o << "        idx_t c" << i << " = pk % cp" << i << ";\n";
+                o << "        const idx_t ct" << i << " = (idx_t)" << B << " % cp" << i << ", cg" << i << " = (gstep - " << (B * U) << ") % cp" << i << ";\n";
+            }
+            else if (lp[i] == Path::ColWide)
+            {
+                o << "        const idx_t cp" << i << " = (idx_t)" << arg(loadAux[i]) << " / " << E << ";\n";
+                o << "        idx_t r" << i << " = pk / cp" << i << ", c" << i << " = pk - r" << i << " * cp" << i << ";\n";
+                o << "        const idx_t qt" << i << " = (idx_t)" << B << " / cp" << i << ", ct" << i << " = (idx_t)" << B << " - qt" << i << " * cp" << i << ";\n";
+                o << "        const idx_t qg" << i << " = (gstep - " << (B * U) << ") / cp" << i << ", cg" << i << " = (gstep - " << (B * U) << ") - qg" << i << " * cp" << i << ";\n";
+            }
+        }
+        o << "        for (; pk < nvec; pk += gstep)\n        {\n";
+        o << "            bool ok[" << U << "];\n";
+        for (size_t i = 0; i < nL; ++i)
+        {
+            const std::string S = T(spec.loads[i].view.dtype) + "::S";
+            if (lp[i] == Path::Scalar) continue;
+            if (lp[i] == Path::ColWide) o << "            " << S << " x" << i << "[" << U << "];\n";
+            else o << "            Pack<" << S << ", " << E << "> x" << i << "[" << U << "];\n";
+        }
+        o << "            #pragma unroll\n            for (int u = 0; u < " << U << "; ++u)\n            {\n";
+        o << "                const idx_t q = pk + (idx_t)u * " << B << ";\n";
+        o << "                ok[u] = q < nvec;\n";
+        o << "                if (ok[u])\n                {\n";
+        for (size_t i = 0; i < nL; ++i)
+        {
+            const std::string S = T(spec.loads[i].view.dtype) + "::S";
+            switch (lp[i])
+            {
+                case Path::DenseWide:
+                    o << "                    x" << i << "[u] = *(const Pack<" << S << ", " << E << ">*)(l" << i << " + q * " << E << ");\n";
+                    break;
+                case Path::DenseElem:
+                    o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e) x" << i << "[u].v[e] = l" << i << "[q * " << E << " + e];\n";
+                    break;
+                case Path::RowWide:
+                    o << "                    x" << i << "[u] = *(const Pack<" << S << ", " << E << ">*)(l" << i << " + c" << i << " * " << E << ");\n";
+                    break;
+                case Path::ColWide:
+                    o << "                    x" << i << "[u] = l" << i << "[r" << i << " * (idx_t)" << arg(loadAux[i] + 1) << "];\n";
+                    break;
+                case Path::General:
+                    o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e)\n                    {\n";
+                    emitGeneralOffset(o, "off_", "(q * " + std::to_string(E) + " + e)", spec.loads[i].view.rank, loadAux[i], "                        ");
+                    o << "                        x" << i << "[u].v[e] = l" << i << "[off_];\n                    }\n";
+                    break;
+                default: break;
+            }
+        }
+        o << "                }\n";
+        for (size_t i = 0; i < nL; ++i)
+        {
+            if (lp[i] == Path::RowWide)
+                o << "                c" << i << " += ct" << i << "; if (c" << i << " >= cp" << i << ") c" << i << " -= cp" << i << ";\n";
+            else if (lp[i] == Path::ColWide)
+                o << "                r" << i << " += qt" << i << "; c" << i << " += ct" << i << "; if (c" << i << " >= cp" << i << ") { c" << i << " -= cp" << i << "; ++r" << i << "; }\n";
+        }
+        o << "            }\n";
+        for (size_t i = 0; i < nL; ++i)
+        {
+            if (lp[i] == Path::RowWide)
+                o << "            c" << i << " += cg" << i << "; if (c" << i << " >= cp" << i << ") c" << i << " -= cp" << i << ";\n";
+            else if (lp[i] == Path::ColWide)
+                o << "            r" << i << " += qg" << i << "; c" << i << " += cg" << i << "; if (c" << i << " >= cp" << i << ") { c" << i << " -= cp" << i << "; ++r" << i << "; }\n";
+        }
+        o << "            #pragma unroll\n            for (int u = 0; u < " << U << "; ++u)\n            {\n";
+        o << "                if (!ok[u]) continue;\n";
+        o << "                const idx_t q = pk + (idx_t)u * " << B << ";\n";
+        for (size_t i = 0; i < nS; ++i)
+            o << "                Pack<" << T(spec.stores[i].view.dtype) << "::S, " << E << "> y" << i << ";\n";
+        o << "                #pragma unroll\n                for (int e = 0; e < " << E << "; ++e)\n                {\n";
+        emitNodes(o, "                    ", [&](size_t l) -> std::string
+        {
+            if (lp[l] == Path::Scalar) return "x" + std::to_string(l) + "s";
+            if (lp[l] == Path::ColWide) return "x" + std::to_string(l) + "[u]";
+            return "x" + std::to_string(l) + "[u].v[e]";
+        });
+        for (size_t i = 0; i < nS; ++i)
+            o << "                    y" << i << ".v[e] = " << T(spec.stores[i].view.dtype) << "::st(" << "v" << spec.stores[i].node << ");\n";
+        o << "                }\n";
+        for (size_t i = 0; i < nS; ++i)
+        {
+            const std::string S = T(spec.stores[i].view.dtype) + "::S";
+            if (sp[i] == Path::DenseWide)
+                o << "                *(Pack<" << S << ", " << E << ">*)(s" << i << " + q * " << E << ") = y" << i << ";\n";
+            else if (sp[i] == Path::DenseElem)
+                o << "                #pragma unroll\n                for (int e = 0; e < " << E << "; ++e) s" << i << "[q * " << E << " + e] = y" << i << ".v[e];\n";
+            else
+            {
+                o << "                #pragma unroll\n                for (int e = 0; e < " << E << "; ++e)\n                {\n";
+                emitGeneralOffset(o, "off_", "(q * " + std::to_string(E) + " + e)", spec.stores[i].view.rank, storeAux[i], "                    ");
+                o << "                    s" << i << "[off_] = y" << i << ".v[e];\n                }\n";
+            }
+        }
+        o << "            }\n        }\n    }\n";
+    }
+
+    // ---- tail (or the whole tensor when E == 1): one element per thread -----------------------------------------
+    if (E > 1) o << "    const idx_t tail0 = nvec * " << E << ";\n";
+    else       o << "    const idx_t tail0 = 0;\n";
+    o << "    for (idx_t i = tail0 + (idx_t)blockIdx.x * " << B << " + threadIdx.x; i < n; i += (idx_t)gridDim.x * " << B << ")\n    {\n";
+    for (size_t l = 0; l < nL; ++l)
+    {
+        const View& v = spec.loads[l].view;
+        const std::string S = T(v.dtype) + "::S";
+        switch (lp[l])
+        {
+            case Path::Scalar: break;
+            case Path::DenseWide: case Path::DenseElem:
+                o << "        const " << S << " t" << l << " = l" << l << "[i];\n";
+                break;
+            case Path::RowWide:
+                o << "        const " << S << " t" << l << " = l" << l << "[i % (idx_t)" << arg(loadAux[l]) << "];\n";
+                break;
+            case Path::ColWide:
+                o << "        const " << S << " t" << l << " = l" << l << "[(i / (idx_t)" << arg(loadAux[l]) << ") * (idx_t)" << arg(loadAux[l] + 1) << "];\n";
+                break;
+            case Path::General:
+                emitGeneralOffset(o, "off" + std::to_string(l), "i", v.rank, loadAux[l], "        ");
+                o << "        const " << S << " t" << l << " = l" << l << "[off" << l << "];\n";
+                break;
+        }
+    }
+    emitNodes(o, "        ", [&](size_t l) -> std::string
+    {
+        return lp[l] == Path::Scalar ? "x" + std::to_string(l) + "s" : "t" + std::to_string(l);
+    });
+    for (size_t i = 0; i < nS; ++i)
+    {
+        const std::string D = T(spec.stores[i].view.dtype);
+        if (sp[i] == Path::General)
+        {
+            emitGeneralOffset(o, "so" + std::to_string(i), "i", spec.stores[i].view.rank, storeAux[i], "        ");
+            o << "        s" << i << "[so" << i << "] = " << D << "::st(v" << spec.stores[i].node << ");\n";
+        }
+        else
+            o << "        s" << i << "[i] = " << D << "::st(v" << spec.stores[i].node << ");\n";
+    }
+    o << "    }\n}\n";
+    return o.str();
+}
+
+}   // namespace aixb200

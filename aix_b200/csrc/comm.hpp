@@ -1,0 +1,28 @@
+// Data-parallel exchange over NCCL (NVLink 5 / NVSwitch). The reference has no multi-device code; this exists for
+// the data-parallel training configuration, where gradients are summed across the GPUs of one node.
+// NCCL is opened with dlopen at first use so that the library loads on machines that have no NCCL or no GPU.
+#pragma once
+
+#include "common.hpp"
+
+typedef struct CUstream_st* cudaStream_t;
+
+namespace aixb200
+{
+
+class Comm
+{
+public:
+    static void uniqueId(void* out128);
+    Comm(int rank, int nranks, const void* id128, int ordinal);
+    ~Comm();
+    void allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream);
+    int rank() const { return m_rank; }
+    int size() const { return m_nranks; }
+
+private:
+    void* m_comm = nullptr;
+    int   m_rank, m_nranks;
+};
+
+}   // namespace aixb200

@@ -1,0 +1,864 @@
+#include "device.hpp"
+
+#include "comm.hpp"
+#include "gemm.hpp"
+#include "kernels.hpp"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <nvrtc.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <sys/stat.h>
+#include <unistd.h>
+
+namespace aixb200
+{
+
+namespace
+{
+
+void check(cudaError_t e, const char* what)
+{
+    if (e != cudaSuccess) failRuntime(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// The few driver-API entry points the device needs, fetched through the runtime so that the library does not link
+// against libcuda (it must load on machines without a driver).
+struct DriverApi
+{
+    CUresult (*moduleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*moduleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*moduleUnload)(CUmodule) = nullptr;
+    CUresult (*launchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
+    CUresult (*getErrorString)(CUresult, const char**) = nullptr;
+    bool loaded = false;
+};
+
+DriverApi& driver()
+{
+    static DriverApi api;
+    if (!api.loaded)
+    {
+        auto get = [](const char* name, void** fn)
+        {
+            cudaDriverEntryPointQueryResult status;
+            check(cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &status), name);
+            if (status != cudaDriverEntryPointSuccess || !*fn) failRuntime(std::string("driver entry point not found: ") + name);
+        };
+        get("cuModuleLoadData", reinterpret_cast<void**>(&api.moduleLoadData));
+        get("cuModuleGetFunction", reinterpret_cast<void**>(&api.moduleGetFunction));
+        get("cuModuleUnload", reinterpret_cast<void**>(&api.moduleUnload));
+        get("cuLaunchKernel", reinterpret_cast<void**>(&api.launchKernel));
+        get("cuGetErrorString", reinterpret_cast<void**>(&api.getErrorString));
+        api.loaded = true;
+    }
+    return api;
+}
+
+void checkDriver(CUresult r, const char* what)
+{
+    if (r == CUDA_SUCCESS) return;
+    const char* msg = nullptr;
+    driver().getErrorString(r, &msg);
+    failRuntime(std::string(what) + ": " + (msg ? msg : "unknown driver error"));
+}
+
+int envInt(const char* name, int fallback)
+{
+    const char* v = std::getenv(name);
+    return (v && *v) ? std::atoi(v) : fallback;
+}
+
+std::string hex64(uint64_t v)
+{
+    char buf[17];
+    std::snprintf(buf, sizeof(buf), "%016llx", static_cast<unsigned long long>(v));
+    return buf;
+}
+
+}   // namespace
+
+// ----------------------------------------------------------------------------------------------------------------
+// construction / destruction
+// ----------------------------------------------------------------------------------------------------------------
+Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
+{
+    if (m_cfg.flush_threshold == 0) m_cfg.flush_threshold = 200;
+    m_limits.fusion = m_cfg.fusion != 0;
+    m_codegen.strictMath = m_cfg.strict_math != 0;
+    m_codegen.block = envInt("AIXB200_EW_BLOCK", 256);
+    m_codegen.unroll = std::max(1, std::min(8, envInt("AIXB200_EW_UNROLL", 2)));
+    m_wavesPerSm = std::max(1, envInt("AIXB200_EW_WAVES", 8));
+
+    if (m_cfg.disk_cache)
+    {
+        const char* dir = std::getenv("AIXB200_CACHE_DIR");
+        if (dir && *dir) m_cacheDir = dir;
+        else
+        {
+            const char* home = std::getenv("HOME");
+            m_cacheDir = std::string(home && *home ? home : "/tmp") + "/.cache/aixb200";
+        }
+        ::mkdir((m_cacheDir.substr(0, m_cacheDir.find_last_of('/'))).c_str(), 0755);
+        ::mkdir(m_cacheDir.c_str(), 0755);
+    }
+
+    if (dryRun())
+    {
+        m_name = "B200 (dry run, no GPU)";
+        RawMemoryOps raw;
+        raw.allocate = [](size_t bytes) { return std::malloc(bytes); };
+        raw.free = [](void* p) { std::free(p); };
+        m_allocator = std::make_unique<CachingAllocator>(raw, uint64_t(1) << 30);
+        return;
+    }
+
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+        throw Error(AIXB200_ERR_NOGPU, "no CUDA device is visible; the B200 device has no CPU fallback");
+    if (m_cfg.ordinal < 0 || m_cfg.ordinal >= count) failInvalid("device ordinal out of range");
+    check(cudaSetDevice(m_cfg.ordinal), "cudaSetDevice");
+    cudaDeviceProp prop{};
+    check(cudaGetDeviceProperties(&prop, m_cfg.ordinal), "cudaGetDeviceProperties");
+    if (prop.major != 10)
+        throw Error(AIXB200_ERR_NOGPU, std::string("device '") + prop.name + "' is not sm_100 (Blackwell B200); kernels are built for sm_100a only");
+    m_name = std::string("B200:") + prop.name;
+    m_smCount = prop.multiProcessorCount;
+    m_totalMemory = prop.totalGlobalMem;
+    driver();
+
+    if (m_cfg.stream) m_stream = static_cast<cudaStream_t>(m_cfg.stream);
+    else
+    {
+        check(cudaStreamCreateWithFlags(&m_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        m_ownStream = true;
+    }
+
+    const bool managed = m_cfg.managed_memory != 0;
+    const int ordinal = m_cfg.ordinal;
+    RawMemoryOps raw;
+    raw.allocate = [managed, ordinal, this](size_t bytes) -> void*
+    {
+        void* p = nullptr;
+        cudaError_t e = managed ? cudaMallocManaged(&p, bytes) : cudaMalloc(&p, bytes);
+        if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return nullptr; }
+        check(e, "cudaMalloc");
+        if (managed)
+        {
+            // Keep the pages on the GPU; the host reads them after synchronize() through on-demand migration.
+            cudaMemLocation loc{};
+            loc.type = cudaMemLocationTypeDevice;
+            loc.id = ordinal;
+            cudaMemAdvise_v2(p, bytes, cudaMemAdviseSetPreferredLocation, loc);
+            cudaMemPrefetchAsync_v2(p, bytes, loc, 0, m_stream);
+            cudaGetLastError();
+        }
+        ++m_stats.cuda_mallocs;
+        return p;
+    };
+    raw.free = [](void* p) { cudaFree(p); };
+    uint64_t limit = m_cfg.cache_limit_bytes ? m_cfg.cache_limit_bytes : m_totalMemory / 4 * 3;
+    m_allocator = std::make_unique<CachingAllocator>(raw, limit);
+
+    m_scratchBytes = size_t(4) << 20;
+    check(cudaMalloc(&m_scratch, m_scratchBytes), "cudaMalloc(scratch)");
+    check(cudaMemsetAsync(m_scratch, 0, m_scratchBytes, m_stream), "cudaMemset(scratch)");
+}
+
+Device::~Device()
+{
+    if (!dryRun())
+    {
+        cudaSetDevice(m_cfg.ordinal);
+        m_comm.reset();
+        if (m_stream) cudaStreamSynchronize(m_stream);
+        for (auto& [key, k] : m_kernels)
+            if (k.module) driver().moduleUnload(k.module);
+        if (m_scratch) cudaFree(m_scratch);
+        if (m_l2Flush) cudaFree(m_l2Flush);
+    }
+    m_allocator.reset();
+    if (!dryRun() && m_ownStream && m_stream) cudaStreamDestroy(m_stream);
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// memory
+// ----------------------------------------------------------------------------------------------------------------
+void* Device::allocate(size_t bytes)
+{
+    // Headroom of one 16-byte pack so that vector tails stay inside the block (the reference pads to 4 elements,
+    // aixDeviceMetal.cpp:245-248).
+    void* p = m_allocator->allocate(bytes + 16);
+    return p;
+}
+
+void* Device::temporary(size_t bytes)
+{
+    void* p = m_allocator->allocate(bytes + 16);
+    m_released.insert(p);
+    m_deferredFrees.push_back(p);
+    m_deferredBytes += m_allocator->blockSize(p);
+    return p;
+}
+
+void Device::deallocate(void* p)
+{
+    if (!p) return;
+    if (!m_allocator->owns(p)) failInvalid("deallocate: pointer was not allocated by this device");
+    if (m_released.count(p)) failInvalid("deallocate: pointer was already deallocated");
+    if (m_pending.empty() && m_deferredFrees.empty())
+    {
+        m_allocator->release(p);       // stream order makes immediate reuse safe
+        return;
+    }
+    m_released.insert(p);
+    m_deferredFrees.push_back(p);
+    m_deferredBytes += m_allocator->blockSize(p);
+    // Memory pressure: do not let dead buffers pile up behind a long recorded chain
+    // (the reference commits when half its working-set budget is queued, aixDeviceMetal.cpp:1438-1444).
+    const uint64_t budget = dryRun() ? (uint64_t(1) << 30) : m_totalMemory / 4;
+    if (m_deferredBytes > budget) flush();
+}
+
+void Device::releaseDeferred()
+{
+    for (void* p : m_deferredFrees) m_allocator->release(p);
+    m_deferredFrees.clear();
+    m_released.clear();
+    m_deferredBytes = 0;
+}
+
+void Device::emptyCache()
+{
+    flush();
+    if (!dryRun()) check(cudaStreamSynchronize(m_stream), "synchronize");
+    m_allocator->trim(0);
+}
+
+void Device::synchronize()
+{
+    flush();
+    if (dryRun()) return;
+    check(cudaStreamSynchronize(m_stream), "cudaStreamSynchronize");
+    check(cudaGetLastError(), "asynchronous kernel failure");
+}
+
+bool Device::isHostPointer(const void* p) const
+{
+    if (dryRun()) return false;
+    cudaPointerAttributes attr{};
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) { cudaGetLastError(); return true; }
+    return attr.type == cudaMemoryTypeUnregistered || attr.type == cudaMemoryTypeHost;
+}
+
+View Device::inputView(const aixb200_tensor* t, const char* what)
+{
+    View v = makeView(t, what);
+    if (v.size == 0 || dryRun()) return v;
+    if (m_allocator->findBlock(v.base)) return v;
+    if (!isHostPointer(v.base)) return v;                 // foreign device memory (another allocator in this process)
+    // Host memory (the reference's getReadOnlyMTLBuffer path, aixDeviceMetal.cpp:1478-1490): copy the touched span
+    // to a temporary device block now; program order on the stream keeps it ahead of the kernels that read it.
+    const size_t es = dtypeSize(v.dtype);
+    const size_t bytes = v.span() * es;
+    char* staged = static_cast<char*>(temporary(bytes));
+    check(cudaMemcpyAsync(staged, v.firstByte(), bytes, cudaMemcpyHostToDevice, m_stream), "host-to-device staging copy");
+    m_stats.h2d_bytes += bytes;
+    v.base = staged;
+    v.offset = 0;
+    return v;
+}
+
+View Device::outputView(const aixb200_tensor* t, const char* what)
+{
+    View v = makeView(t, what);
+    if (v.size == 0 || dryRun()) return v;
+    if (m_allocator->findBlock(v.base)) return v;
+    if (isHostPointer(v.base)) failInvalid(std::string(what) + ": result must be device memory allocated by this device");
+    return v;
+}
+
+void Device::checkLaunch(const char* what)
+{
+    if (dryRun()) return;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) failRuntime(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// recording
+// ----------------------------------------------------------------------------------------------------------------
+void Device::record(OpRecord&& rec)
+{
+    if (rec.out.size == 0) return;
+    m_pending.push_back(std::move(rec));
+    ++m_stats.ops_recorded;
+    if (m_pending.size() >= m_cfg.flush_threshold) flush();
+}
+
+static void checkOperandSize(const View& in, const View& out, const char* what)
+{
+    if (in.size != out.size && in.size != 1)
+        failInvalid(std::string(what) + ": operand has " + std::to_string(in.size) + " elements, result has " + std::to_string(out.size));
+}
+
+void Device::recordBinary(Op op, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* r, const char* what)
+{
+    OpRecord rec;
+    rec.op = op;
+    rec.numInputs = 2;
+    rec.out = outputView(r, what);
+    rec.in[0] = inputView(a, what);
+    rec.in[1] = inputView(b, what);
+    checkOperandSize(rec.in[0], rec.out, what);
+    checkOperandSize(rec.in[1], rec.out, what);
+    record(std::move(rec));
+}
+
+void Device::recordUnary(Op op, const aixb200_tensor* a, const aixb200_tensor* r, const char* what)
+{
+    OpRecord rec;
+    rec.op = op;
+    rec.numInputs = 1;
+    rec.out = outputView(r, what);
+    rec.in[0] = inputView(a, what);
+    checkOperandSize(rec.in[0], rec.out, what);
+    record(std::move(rec));
+}
+
+void Device::recordFill(const void* scalar, uint32_t scalarDtype, const aixb200_tensor* r)
+{
+    if (!scalar) failInvalid("fill: null scalar");
+    dtypeSize(scalarDtype);
+    OpRecord rec;
+    rec.op = Op::Fill;
+    rec.out = outputView(r, "fill");
+    rec.scalar = convertScalar(scalar, scalarDtype, rec.out.dtype);
+    record(std::move(rec));
+}
+
+void Device::recordFillMin(const aixb200_tensor* r)
+{
+    OpRecord rec;
+    rec.op = Op::Fill;
+    rec.out = outputView(r, "fillMin");
+    rec.scalar = lowestValue(rec.out.dtype);
+    record(std::move(rec));
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// flush: plan, generate, compile, launch
+// ----------------------------------------------------------------------------------------------------------------
+void Device::flush()
+{
+    if (m_inFlush) return;
+    if (m_pending.empty()) { releaseDeferred(); return; }
+    m_inFlush = true;
+    struct Reset { bool& f; ~Reset() { f = false; } } reset{m_inFlush};
+    std::vector<OpRecord> ops;
+    ops.swap(m_pending);
+    ++m_stats.flushes;
+    try
+    {
+        std::vector<KernelSpec> kernels = planKernels(ops, m_released, m_limits);
+        for (const KernelSpec& spec : kernels)
+        {
+            launchSpec(spec);
+            ++m_stats.fused_kernels;
+            m_stats.fused_ops += spec.opsFolded;
+            m_stats.fills_absorbed += spec.fillsAbsorbed;
+            m_stats.stores_elided += spec.storesElided;
+        }
+    }
+    catch (...)
+    {
+        releaseDeferred();
+        throw;
+    }
+    releaseDeferred();
+}
+
+std::vector<char> Device::compile(const std::string& source, const std::string& entry)
+{
+    std::vector<const char*> options = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device"};
+    if (m_codegen.strictMath) { options.push_back("--fmad=false"); options.push_back("--prec-div=true"); options.push_back("--prec-sqrt=true"); }
+    else options.push_back("--fmad=true");
+
+    std::string cachePath;
+    if (!m_cacheDir.empty())
+    {
+        uint64_t h = fnv1a(source.data(), source.size());
+        for (auto o : options) h = fnv1a(o, std::strlen(o), h);
+        cachePath = m_cacheDir + "/" + hex64(h) + ".cubin";
+        std::ifstream in(cachePath, std::ios::binary);
+        if (in)
+        {
+            std::vector<char> cubin((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
+            if (!cubin.empty()) return cubin;
+        }
+    }
+
+    const auto t0 = std::chrono::steady_clock::now();
+    nvrtcProgram prog = nullptr;
+    if (nvrtcCreateProgram(&prog, source.c_str(), (entry + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        failRuntime("nvrtcCreateProgram failed");
+    nvrtcResult r = nvrtcCompileProgram(prog, static_cast<int>(options.size()), options.data());
+    if (r != NVRTC_SUCCESS)
+    {
+        size_t logSize = 0;
+        nvrtcGetProgramLogSize(prog, &logSize);
+        std::string log(logSize, '\0');
+        if (logSize) nvrtcGetProgramLog(prog, log.data());
+        nvrtcDestroyProgram(&prog);
+        m_lastSource = source;
+        failRuntime("NVRTC failed to compile a fused kernel: " + log);
+    }
+    size_t size = 0;
+    nvrtcGetCUBINSize(prog, &size);
+    std::vector<char> cubin(size);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    ++m_stats.nvrtc_compiles;
+    m_stats.nvrtc_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+
+    if (!cachePath.empty())
+    {
+        const std::string tmp = cachePath + "." + std::to_string(::getpid());
+        std::ofstream out(tmp, std::ios::binary);
+        if (out)
+        {
+            out.write(cubin.data(), static_cast<std::streamsize>(cubin.size()));
+            out.close();
+            std::rename(tmp.c_str(), cachePath.c_str());
+        }
+    }
+    return cubin;
+}
+
+CompiledKernel& Device::getKernel(const KernelSpec& spec, const KernelVariant& variant, const std::string& key)
+{
+    auto it = m_kernels.find(key);
+    if (it != m_kernels.end()) { ++m_stats.kernel_cache_hits; return it->second; }
+    ++m_stats.kernel_cache_misses;
+    const std::string entry = "aixb200_fused_" + hex64(fnv1a(key.data(), key.size()));
+    CompiledKernel k;
+    k.source = generateKernelSource(spec, variant, m_codegen, entry);
+    std::vector<char> cubin = compile(k.source, entry);
+    if (!dryRun())
+    {
+        checkDriver(driver().moduleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
+        checkDriver(driver().moduleGetFunction(&k.function, k.module, entry.c_str()), "cuModuleGetFunction");
+    }
+    return m_kernels.emplace(key, std::move(k)).first->second;
+}
+
+void Device::launchSpec(const KernelSpec& spec)
+{
+    const KernelVariant variant = chooseVariant(spec);
+    const std::string key = kernelKey(spec, variant, m_codegen);
+    CompiledKernel& k = getKernel(spec, variant, key);
+    m_lastSource = k.source;
+    if (dryRun()) { countLaunch(true); return; }
+
+    std::vector<uint64_t> args = packKernelArguments(spec, variant);
+    if (args.empty()) args.push_back(0);
+    const uint64_t block = static_cast<uint64_t>(m_codegen.block);
+    const uint64_t nvec = variant.vec > 1 ? spec.count / variant.vec : 0;
+    const uint64_t mainBlocks = (nvec + block * m_codegen.unroll - 1) / (block * m_codegen.unroll);
+    const uint64_t tailElems = variant.vec > 1 ? spec.count - nvec * variant.vec : spec.count;
+    const uint64_t tailBlocks = (tailElems + block - 1) / block;
+    uint64_t grid = std::max<uint64_t>(1, std::max(mainBlocks, tailBlocks));
+    grid = std::min<uint64_t>(grid, static_cast<uint64_t>(m_smCount) * m_wavesPerSm);
+    void* params[] = {args.data()};
+    checkDriver(driver().launchKernel(k.function, static_cast<unsigned>(grid), 1, 1, static_cast<unsigned>(block), 1, 1, 0, m_stream, params, nullptr),
+                "cuLaunchKernel(fused)");
+    countLaunch(true);
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// immediate ops
+// ----------------------------------------------------------------------------------------------------------------
+namespace
+{
+
+kernels::LaunchContext makeContext(Device& d, uint64_t* launches)
+{
+    return kernels::LaunchContext{d.stream(), d.smCount(), d.scratch(), d.scratchBytes(), launches};
+}
+
+kernels::Layout layoutOf(const aixb200_tensor* t)
+{
+    kernels::Layout l{};
+    l.rank = static_cast<int>(t->rank);
+    for (uint32_t d = 0; d < t->rank; ++d) { l.shape[d] = t->shape[d]; l.strides[d] = t->strides[d]; }
+    return l;
+}
+
+}   // namespace
+
+#define AIXB200_CTX() uint64_t launched_ = 0; kernels::LaunchContext ctx = makeContext(*this, &launched_)
+#define AIXB200_DONE(what) do { m_stats.static_kernel_launches += launched_; m_stats.total_kernel_launches += launched_; checkLaunch(what); } while (0)
+
+void Device::sum(const aixb200_tensor* a, const aixb200_tensor* r)
+{
+    View src = inputView(a, "sum");
+    View dst = outputView(r, "sum");
+    if (src.dtype != dst.dtype) failInvalid("sum: result must have the element type of the input");
+    if (dst.size != 1) failInvalid("sum: result must have one element");
+    flush();
+    if (dryRun()) return;
+    AIXB200_CTX();
+    kernels::reduceAll(ctx, false, src, dst.firstByte());
+    AIXB200_DONE("sum");
+}
+
+void Device::max(const aixb200_tensor* a, const aixb200_tensor* r)
+{
+    View src = inputView(a, "max");
+    View dst = outputView(r, "max");
+    if (src.dtype != dst.dtype) failInvalid("max: result must have the element type of the input");
+    if (dst.size != 1 || src.size == 0) failInvalid("max: result must have one element and the input at least one");
+    flush();
+    if (dryRun()) return;
+    AIXB200_CTX();
+    kernels::reduceAll(ctx, true, src, dst.firstByte());
+    AIXB200_DONE("max");
+}
+
+void Device::argmax(const aixb200_tensor* a, const aixb200_tensor* r)
+{
+    View src = inputView(a, "argmax");
+    View dst = outputView(r, "argmax");
+    if (dst.dtype != I32) failInvalid("argmax supports only int32 data type for its result");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    AIXB200_CTX();
+    kernels::argmaxAll(ctx, src, reinterpret_cast<int32_t*>(dst.firstByte()), false, src.size);
+    AIXB200_DONE("argmax");
+}
+
+void Device::argmaxIndices(const aixb200_tensor* a, const aixb200_tensor* r)
+{
+    View src = inputView(a, "argmaxIndices");
+    View dst = outputView(r, "argmaxIndices");
+    if (dst.dtype != I32) failInvalid("argmaxIndices supports only int32 data type for its result");
+    if (dst.size != src.size) failInvalid("argmaxIndices: result must have the size of the input");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    AIXB200_CTX();
+    kernels::argmaxAll(ctx, src, reinterpret_cast<int32_t*>(dst.firstByte()), true, src.size);
+    AIXB200_DONE("argmaxIndices");
+}
+
+// Pairs every source dimension with "kept" or "reduced" the way translationIndex does (aixDeviceCPU.cpp:627-649):
+// walking both shapes from the back, a source dimension is kept when the destination has the same extent there.
+static int classifyReduction(const aixb200_tensor* src, const aixb200_tensor* dst, kernels::ReduceDim* dims)
+{
+    int j = static_cast<int>(dst->rank) - 1;
+    for (int i = static_cast<int>(src->rank) - 1; i >= 0; --i)
+    {
+        bool kept = false;
+        if (j >= 0 && dst->shape[j] == src->shape[i]) { kept = true; --j; }
+        else if (j >= 0 && dst->shape[j] == 1) { --j; }
+        dims[i] = {src->shape[i], src->strides[i], kept};
+    }
+    // collapse: drop extent-1 dimensions, merge neighbours of the same kind whose strides chain
+    int rank = 0;
+    for (uint32_t i = 0; i < src->rank; ++i)
+    {
+        if (dims[i].extent == 1) continue;
+        if (rank > 0 && dims[rank - 1].kept == dims[i].kept && dims[rank - 1].stride == dims[i].stride * dims[i].extent)
+        {
+            dims[rank - 1].extent *= dims[i].extent;
+            dims[rank - 1].stride = dims[i].stride;
+        }
+        else dims[rank++] = dims[i];
+    }
+    return rank;
+}
+
+void Device::reduceTo(const aixb200_tensor* s, const aixb200_tensor* d, bool isMax)
+{
+    const char* what = isMax ? "maxTo" : "reduceTo";
+    View src = inputView(s, what);
+    View dst = outputView(d, what);
+    if (src.dtype != dst.dtype) failInvalid(std::string(what) + ": element types differ");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    kernels::ReduceDim dims[MAX_RANK];
+    // inputView may have re-based a staged host tensor: the strides are unchanged, only base/offset moved.
+    int rank = classifyReduction(s, d, dims);
+    uint64_t outputs = 1;
+    for (int i = 0; i < rank; ++i) if (dims[i].kept) outputs *= dims[i].extent;
+    if (outputs != dst.size) failInvalid(std::string(what) + ": destination shape is not a reduction of the source shape");
+    // canonical 2-D forms need an explicit partner dimension
+    kernels::ReduceDim two[2];
+    const kernels::ReduceDim* use = dims;
+    if (rank == 1)
+    {
+        if (dims[0].kept) { two[0] = dims[0]; two[1] = {1, 1, false}; }
+        else              { two[0] = {1, 0, true}; two[1] = dims[0]; }
+        use = two;
+        rank = 2;
+    }
+    else if (rank == 0)
+    {
+        two[0] = {1, 0, true};
+        two[1] = {1, 1, false};
+        use = two;
+        rank = 2;
+    }
+    AIXB200_CTX();
+    kernels::reduceInto(ctx, isMax, src.dtype, src.firstByte(), use, rank, dst.firstByte());
+    AIXB200_DONE(what);
+}
+
+void Device::argmaxTo(const aixb200_tensor* s, const aixb200_tensor* d, size_t dim, bool oneHot)
+{
+    const char* what = oneHot ? "argmaxIndicesTo" : "argmaxTo";
+    View src = inputView(s, what);
+    View dst = outputView(d, what);
+    if (dst.dtype != I32) failInvalid(std::string(what) + " supports only int32 data type for its result");
+    if (dim >= s->rank) failInvalid(std::string(what) + ": dimension out of range");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    kernels::ReduceDim dims[MAX_RANK];
+    for (uint32_t i = 0; i < s->rank; ++i) dims[i] = {s->shape[i], s->strides[i], i != dim};
+    AIXB200_CTX();
+    kernels::argmaxAlong(ctx, src.dtype, src.firstByte(), dims, static_cast<int>(s->rank), static_cast<int>(dim),
+                         reinterpret_cast<int32_t*>(dst.firstByte()), oneHot, src.size);
+    AIXB200_DONE(what);
+}
+
+void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* r)
+{
+    if (a->rank != 2 || b->rank != 2 || r->rank != 2) failInvalid("matmul: operands and result must be 2-D");
+    if (a->shape[1] != b->shape[0] || r->shape[0] != a->shape[0] || r->shape[1] != b->shape[1]) failInvalid("matmul: shapes do not chain");
+    if (a->dtype != r->dtype || b->dtype != r->dtype) failInvalid("matmul: element types differ");
+    View va = inputView(a, "matmul"), vb = inputView(b, "matmul");
+    View vr = outputView(r, "matmul");
+    flush();
+    if (dryRun() || vr.size == 0) return;
+    const uint64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
+    AIXB200_CTX();
+    gemm::Problem p{};
+    p.dtype = r->dtype;
+    p.m = m; p.n = n; p.k = k;
+    p.a = va.firstByte(); p.aRowStride = a->strides[0]; p.aColStride = a->strides[1];
+    p.b = vb.firstByte(); p.bRowStride = b->strides[0]; p.bColStride = b->strides[1];
+    p.c = vr.firstByte();
+    p.splitF32 = m_cfg.tf32x3_matmul != 0;
+    if (!gemm::launchTensorCore(*this, ctx, p))
+        kernels::matmulSimt(ctx, r->dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);
+    AIXB200_DONE("matmul");
+}
+
+void Device::transpose(const aixb200_tensor* a, const aixb200_tensor* r, size_t dim0, size_t dim1)
+{
+    View src = inputView(a, "transpose");
+    View dst = outputView(r, "transpose");
+    if (dim0 >= a->rank || dim1 >= a->rank) failInvalid("transpose: dimension out of range");
+    if (src.dtype != dst.dtype || src.size != dst.size) failInvalid("transpose: result does not match the input");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    AIXB200_CTX();
+    kernels::transposeGeneral(ctx, src.dtype, src.firstByte(), dst.firstByte(), src.size, layoutOf(a), layoutOf(r),
+                              static_cast<int>(dim0), static_cast<int>(dim1));
+    AIXB200_DONE("transpose");
+}
+
+void Device::copy(const void* src, uint32_t srcDtype, void* dst, uint32_t dstDtype, size_t count, bool immediate)
+{
+    const size_t ss = dtypeSize(srcDtype), ds = dtypeSize(dstDtype);
+    if (count == 0) { if (immediate) synchronize(); return; }
+    if (!src || !dst) failInvalid("copy: null pointer");
+    if (dryRun()) { flush(); return; }
+    const bool srcHost = !m_allocator->findBlock(src) && isHostPointer(src);
+    const bool dstHost = !m_allocator->findBlock(dst) && isHostPointer(dst);
+    if (dstHost && !immediate) failInvalid("copy: result must have GPU memory (use copyImmediate to read back to the host)");
+
+    aixb200_tensor ts{}, td{};
+    ts.data = const_cast<void*>(src); ts.size = count; ts.dtype = srcDtype; ts.rank = 1; ts.shape[0] = count; ts.strides[0] = 1;
+    td.data = dst; td.size = count; td.dtype = dstDtype; td.rank = 1; td.shape[0] = count; td.strides[0] = 1;
+
+    if (dstHost)
+    {
+        // device -> host read-back (extension over the reference, whose copy targets device memory only)
+        if (srcHost) failInvalid("copy: source and destination are both host memory");
+        const void* from = src;
+        void* converted = nullptr;
+        if (srcDtype != dstDtype)
+        {
+            converted = m_allocator->allocate(count * ds + 16);
+            td.data = converted;
+            OpRecord rec;
+            rec.op = Op::Cast;
+            rec.numInputs = 1;
+            rec.in[0] = inputView(&ts, "copy");
+            rec.out = makeView(&td, "copy");
+            record(std::move(rec));
+            from = converted;
+        }
+        flush();
+        check(cudaMemcpyAsync(dst, from, count * ds, cudaMemcpyDeviceToHost, m_stream), "device-to-host copy");
+        m_stats.d2h_bytes += count * ds;
+        synchronize();
+        if (converted) m_allocator->release(converted);
+        return;
+    }
+
+    if (srcHost && srcDtype == dstDtype)
+    {
+        flush();                            // ops already recorded against dst must run first
+        check(cudaMemcpyAsync(dst, src, count * ss, cudaMemcpyHostToDevice, m_stream), "host-to-device copy");
+        m_stats.h2d_bytes += count * ss;
+    }
+    else
+    {
+        // device source, or host source with conversion (staged by inputView): a Cast node that fuses like any op
+        OpRecord rec;
+        rec.op = Op::Cast;
+        rec.numInputs = 1;
+        rec.in[0] = inputView(&ts, "copy");
+        rec.out = outputView(&td, "copy");
+        record(std::move(rec));
+    }
+    if (immediate) synchronize();
+}
+
+void Device::contiguous(const aixb200_tensor* s, const aixb200_tensor* d)
+{
+    OpRecord rec;
+    rec.op = Op::Cast;
+    rec.numInputs = 1;
+    rec.out = outputView(d, "contiguous");
+    rec.in[0] = inputView(s, "contiguous");
+    if (rec.in[0].dtype != rec.out.dtype) failInvalid("contiguous: element types differ");
+    checkOperandSize(rec.in[0], rec.out, "contiguous");
+    record(std::move(rec));
+}
+
+void Device::sliceSet(const aixb200_tensor* s, const aixb200_tensor* d, size_t dim, size_t start, size_t end, size_t step)
+{
+    View src = inputView(s, "sliceSet");
+    View dst = outputView(d, "sliceSet");
+    if (dim >= d->rank || step == 0 || end < start) failInvalid("sliceSet: bad slice");
+    if (src.dtype != dst.dtype) failInvalid("sliceSet: element types differ");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    const uint64_t sliceExtent = (end - start + step - 1) / step;
+    AIXB200_CTX();
+    kernels::sliceSet(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), layoutOf(d), src.size, static_cast<int>(dim), start, step, sliceExtent);
+    AIXB200_DONE("sliceSet");
+}
+
+void Device::triangle(const aixb200_tensor* s, const aixb200_tensor* d, int64_t diagonal, bool lower)
+{
+    const char* what = lower ? "tril" : "triu";
+    View src = inputView(s, what);
+    View dst = outputView(d, what);
+    if (s->rank < 2) failInvalid(std::string(what) + ": needs at least two dimensions");
+    if (src.dtype != dst.dtype || src.size != dst.size) failInvalid(std::string(what) + ": result does not match the input");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    AIXB200_CTX();
+    kernels::triangle(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), layoutOf(d), dst.size, s->shape[s->rank - 2],
+                      s->shape[s->rank - 1], diagonal, lower);
+    AIXB200_DONE(what);
+}
+
+void Device::indexSelect(const aixb200_tensor* s, const aixb200_tensor* d, const aixb200_tensor* idx, size_t dim)
+{
+    View src = inputView(s, "indexSelect");
+    View ind = inputView(idx, "indexSelect");
+    View dst = outputView(d, "indexSelect");
+    if (ind.dtype != I32) failInvalid("indexSelect: indices must be int32");
+    if (src.dtype != dst.dtype) failInvalid("indexSelect: element types differ");
+    if (s->rank != 0 && dim >= s->rank) failInvalid("indexSelect: dimension out of range");
+    flush();
+    if (dryRun() || dst.size == 0) return;
+    uint64_t sliceSize = 1;
+    for (size_t i = dim + 1; i < s->rank; ++i) sliceSize *= s->shape[i];
+    const uint64_t dimSize = s->rank ? s->shape[dim] * sliceSize : 0;
+    AIXB200_CTX();
+    kernels::indexSelect(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), reinterpret_cast<const int32_t*>(ind.firstByte()),
+                         ind.size, sliceSize, dimSize, dst.size);
+    AIXB200_DONE("indexSelect");
+}
+
+void Device::indexAdd(const aixb200_tensor* s, const aixb200_tensor* d, const aixb200_tensor* idx, size_t dim)
+{
+    View src = inputView(s, "indexAdd");
+    View ind = inputView(idx, "indexAdd");
+    View dst = outputView(d, "indexAdd");
+    if (ind.dtype != I32) failInvalid("indexAdd: indices must be int32");
+    if (src.dtype != dst.dtype) failInvalid("indexAdd: element types differ");
+    if (d->rank != 0 && dim >= d->rank) failInvalid("indexAdd: dimension out of range");
+    flush();
+    if (dryRun() || src.size == 0) return;
+    uint64_t sliceSize = 1;
+    for (size_t i = dim + 1; i < d->rank; ++i) sliceSize *= d->shape[i];
+    const uint64_t dimSize = d->rank ? d->shape[dim] * sliceSize : 0;
+    AIXB200_CTX();
+    kernels::indexAdd(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), reinterpret_cast<const int32_t*>(ind.firstByte()),
+                      ind.size, sliceSize, dimSize, src.size);
+    AIXB200_DONE("indexAdd");
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// timing helpers, statistics, communication
+// ----------------------------------------------------------------------------------------------------------------
+void Device::flushL2()
+{
+    flush();
+    if (dryRun()) return;
+    if (!m_l2Flush)
+    {
+        m_l2FlushBytes = size_t(256) << 20;       // twice the 126 MB L2
+        check(cudaMalloc(&m_l2Flush, m_l2FlushBytes), "cudaMalloc(L2 flush buffer)");
+    }
+    AIXB200_CTX();
+    kernels::flushL2(ctx, m_l2Flush, m_l2FlushBytes);
+    AIXB200_DONE("flushL2");
+}
+
+void Device::fillStats(aixb200_stats* out) const
+{
+    *out = m_stats;
+    out->bytes_in_use = m_allocator->bytesInUse();
+    out->bytes_cached = m_allocator->bytesCached();
+    out->bytes_reserved = m_allocator->bytesReserved();
+    if (dryRun()) out->cuda_mallocs = m_allocator->rawAllocations();
+}
+
+void Device::commInit(int rank, int nranks, const void* id)
+{
+    if (dryRun()) failInvalid("communication needs a GPU");
+    flush();
+    m_comm = std::make_unique<Comm>(rank, nranks, id, m_cfg.ordinal);
+}
+
+void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
+{
+    if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
+    flush();
+    m_comm->allReduceSum(data, count, dtype, m_stream);
+    if (scale != 1.0)
+    {
+        AIXB200_CTX();
+        kernels::scaleInPlace(ctx, dtype, data, count, scale);
+        AIXB200_DONE("all_reduce scale");
+    }
+}
+
+void Device::commDestroy()
+{
+    if (m_comm) { cudaStreamSynchronize(m_stream); m_comm.reset(); }
+}
+
+}   // namespace aixb200

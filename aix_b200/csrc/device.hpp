@@ -1,0 +1,138 @@
+// The B200 device object behind the C ABI: CUDA context and stream, allocator, lazy recorder, kernel cache.
+// Counterpart of the reference's DeviceMetal (aixDeviceMetal.hpp / .cpp), rebuilt around CUDA's model:
+// one in-order stream instead of command buffers, NVRTC + cubin cache instead of MTL libraries, stream-ordered
+// block reuse instead of completion handlers.
+#pragma once
+
+#include "allocator.hpp"
+#include "codegen.hpp"
+#include "planner.hpp"
+#include "scalar.hpp"
+
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+typedef struct CUstream_st* cudaStream_t;
+typedef struct CUfunc_st* CUfunction;
+typedef struct CUmod_st* CUmodule;
+
+namespace aixb200
+{
+
+class Comm;
+
+struct CompiledKernel
+{
+    CUmodule   module = nullptr;
+    CUfunction function = nullptr;
+    std::string source;
+};
+
+class Device
+{
+public:
+    explicit Device(const aixb200_config& cfg);
+    ~Device();
+    Device(const Device&) = delete;
+    Device& operator=(const Device&) = delete;
+
+    const std::string& name() const { return m_name; }
+    bool dryRun() const { return m_cfg.dry_run != 0; }
+    cudaStream_t stream() const { return m_stream; }
+    int ordinal() const { return m_cfg.ordinal; }
+    int smCount() const { return m_smCount; }
+
+    // memory
+    void* allocate(size_t bytes);
+    void  deallocate(void* p);
+    void  emptyCache();
+    void  synchronize();
+
+    // recorded elementwise ops
+    void recordBinary(Op op, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* r, const char* what);
+    void recordUnary(Op op, const aixb200_tensor* a, const aixb200_tensor* r, const char* what);
+    void recordFill(const void* scalar, uint32_t scalarDtype, const aixb200_tensor* r);
+    void recordFillMin(const aixb200_tensor* r);
+    void flush();
+
+    // immediate ops (flush first, then launch fixed kernels)
+    void sum(const aixb200_tensor* a, const aixb200_tensor* r);
+    void max(const aixb200_tensor* a, const aixb200_tensor* r);
+    void argmax(const aixb200_tensor* a, const aixb200_tensor* r);
+    void argmaxIndices(const aixb200_tensor* a, const aixb200_tensor* r);
+    void reduceTo(const aixb200_tensor* src, const aixb200_tensor* dst, bool isMax);
+    void argmaxTo(const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim, bool oneHot);
+    void matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* r);
+    void transpose(const aixb200_tensor* a, const aixb200_tensor* r, size_t dim0, size_t dim1);
+    void copy(const void* src, uint32_t srcDtype, void* dst, uint32_t dstDtype, size_t count, bool immediate);
+    void contiguous(const aixb200_tensor* src, const aixb200_tensor* dst);
+    void sliceSet(const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim, size_t start, size_t end, size_t step);
+    void triangle(const aixb200_tensor* src, const aixb200_tensor* dst, int64_t diagonal, bool lower);
+    void indexSelect(const aixb200_tensor* src, const aixb200_tensor* dst, const aixb200_tensor* idx, size_t dim);
+    void indexAdd(const aixb200_tensor* src, const aixb200_tensor* dst, const aixb200_tensor* idx, size_t dim);
+
+    // timing / diagnostics
+    void flushL2();
+    void fillStats(aixb200_stats* out) const;
+    const char* lastKernelSource() const { return m_lastSource.empty() ? nullptr : m_lastSource.c_str(); }
+
+    // data-parallel exchange
+    void commInit(int rank, int nranks, const void* id);
+    void allReduce(void* data, size_t count, uint32_t dtype, double scale);
+    void commDestroy();
+
+    // Scratch for fixed kernels (reduction partials, counters); lives as long as the device.
+    void* scratch() const { return m_scratch; }
+    size_t scratchBytes() const { return m_scratchBytes; }
+
+    std::string lastError;
+
+    // A view whose data is guaranteed to be readable by kernels on the stream. Host memory is staged.
+    View inputView(const aixb200_tensor* t, const char* what);
+    // A view that kernels may write: memory from this device's allocator (or foreign *device* memory).
+    View outputView(const aixb200_tensor* t, const char* what);
+    void countLaunch(bool generated) { ++m_stats.total_kernel_launches; if (!generated) ++m_stats.static_kernel_launches; }
+    void checkLaunch(const char* what);
+    // Temporary device block that is returned to the cache after the next flush.
+    void* temporary(size_t bytes);
+
+private:
+    void record(OpRecord&& rec);
+    void launchSpec(const KernelSpec& spec);
+    CompiledKernel& getKernel(const KernelSpec& spec, const KernelVariant& variant, const std::string& key);
+    std::vector<char> compile(const std::string& source, const std::string& entry);
+    bool isHostPointer(const void* p) const;
+    void releaseDeferred();
+
+    aixb200_config m_cfg;
+    std::string    m_name;
+    cudaStream_t   m_stream = nullptr;
+    bool           m_ownStream = false;
+    int            m_smCount = 148;
+    uint64_t       m_totalMemory = 0;
+    std::unique_ptr<CachingAllocator> m_allocator;
+    void*          m_scratch = nullptr;
+    size_t         m_scratchBytes = 0;
+    void*          m_l2Flush = nullptr;
+    size_t         m_l2FlushBytes = 0;
+
+    std::vector<OpRecord> m_pending;
+    std::unordered_set<const void*> m_released;        // storages deallocated while ops were pending
+    std::vector<void*> m_deferredFrees;
+    uint64_t m_deferredBytes = 0;
+    PlannerLimits  m_limits;
+    CodegenOptions m_codegen;
+    int            m_wavesPerSm = 8;
+
+    std::unordered_map<std::string, CompiledKernel> m_kernels;
+    std::string m_cacheDir;
+    std::string m_lastSource;
+    aixb200_stats m_stats{};
+    std::unique_ptr<Comm> m_comm;
+    bool m_inFlush = false;
+};
+
+}   // namespace aixb200

@@ -1,0 +1,29 @@
+// Tensor-core GEMM entry (tcgen05 / TMEM / TMA, sm_100a).
+#pragma once
+
+#include "kernels.hpp"
+
+namespace aixb200
+{
+class Device;
+}
+
+namespace aixb200::gemm
+{
+
+// C[m,n] (dense, row-major) = A[m,k] . B[k,n]; A and B are addressed as base[row * rowStride + col * colStride].
+struct Problem
+{
+    uint32_t    dtype;
+    uint64_t    m, n, k;
+    const void* a; uint64_t aRowStride, aColStride;
+    const void* b; uint64_t bRowStride, bColStride;
+    void*       c;
+    bool        splitF32;      // f32 operands: three-pass split so that the result keeps f32 accuracy
+};
+
+// Runs the problem on the tensor cores when its element type, shape and alignment allow it.
+// Returns false (having launched nothing) when the caller must use the CUDA-core kernel instead.
+bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& problem);
+
+}   // namespace aixb200::gemm

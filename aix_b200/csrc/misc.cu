@@ -1,0 +1,423 @@
+// Fixed kernels off the hot path: argmax family, CUDA-core matmul for shapes and types the tensor-core GEMM does
+// not take, and the data-movement ops of the device interface (transpose, sliceSet, tril/triu, indexSelect,
+// indexAdd). Index arithmetic follows the reference's CPU loops (aixDeviceCPU.cpp:258-622) so results are
+// identical; each kernel is the obvious one-thread-per-element form of the corresponding loop.
+#include "dtypes.cuh"
+#include "kernels.hpp"
+
+#include <algorithm>
+
+namespace aixb200::kernels
+{
+
+using namespace aixb200::dev;
+
+namespace
+{
+
+constexpr int kBlock = 256;
+
+__device__ __forceinline__ uint64_t layoutOffset(uint64_t i, const Layout& l)
+{
+    uint64_t off = 0;
+    for (int d = l.rank - 1; d >= 0; --d)
+    {
+        const uint64_t q = i / l.shape[d];
+        off += (i - q * l.shape[d]) * l.strides[d];
+        i = q;
+    }
+    return off;
+}
+
+inline unsigned int gridFor(uint64_t count, int smCount)
+{
+    const uint64_t blocks = (count + kBlock - 1) / kBlock;
+    return static_cast<unsigned int>(std::max<uint64_t>(1, std::min<uint64_t>(blocks, static_cast<uint64_t>(smCount) * 16)));
+}
+
+// ---- argmax over everything: one CTA, first maximal index wins (aixDeviceCPU.cpp:258-272) -------------------
+template <int DT>
+__global__ void __launch_bounds__(1024) argmaxAllKernel(const typename Elem<DT>::S* __restrict__ src, Layout layout, uint64_t n,
+                                                        int32_t* dst, bool oneHot)
+{
+    typedef Elem<DT> E;
+    typedef typename E::V V;
+    __shared__ V bestV[1024];
+    __shared__ uint64_t bestI[1024];
+    V best = E::lowest();
+    uint64_t bestIdx = ~0ull;
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x)
+    {
+        const V v = E::load(src[layoutOffset(i, layout)]);
+        if (bestIdx == ~0ull || v > best) { best = v; bestIdx = i; }
+    }
+    bestV[threadIdx.x] = best;
+    bestI[threadIdx.x] = bestIdx;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1)
+    {
+        if (threadIdx.x < s)
+        {
+            const V ov = bestV[threadIdx.x + s];
+            const uint64_t oi = bestI[threadIdx.x + s];
+            const uint64_t mi = bestI[threadIdx.x];
+            if (oi != ~0ull && (mi == ~0ull || ov > bestV[threadIdx.x] || (ov == bestV[threadIdx.x] && oi < mi)))
+            {
+                bestV[threadIdx.x] = ov;
+                bestI[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    // The sequential loop of the reference keeps index 0 unless a strictly greater value appears, so NaN-free data
+    // gives the first maximal index; that is what the tie rule above reproduces.
+    const uint64_t winner = bestI[0] == ~0ull ? 0 : bestI[0];
+    if (!oneHot)
+    {
+        if (threadIdx.x == 0) dst[0] = static_cast<int32_t>(winner);
+        return;
+    }
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = (i == winner) ? 1 : 0;
+}
+
+template <int DT>
+void launchArgmaxAll(const LaunchContext& ctx, const View& src, int32_t* dst, bool oneHot, uint64_t count)
+{
+    Layout l{};
+    l.rank = src.rank;
+    for (int d = 0; d < src.rank; ++d) { l.shape[d] = src.shape[d]; l.strides[d] = src.strides[d]; }
+    argmaxAllKernel<DT><<<1, 1024, 0, ctx.stream>>>(reinterpret_cast<const typename Elem<DT>::S*>(src.firstByte()), l, count, dst, oneHot);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+// ---- argmax along one dimension: one thread per output (aixDeviceCPU.cpp:275-352) ---------------------------
+struct AlongDims
+{
+    int      rank, reducedDim;
+    uint64_t extent[MAX_RANK], stride[MAX_RANK];
+    uint64_t outputs;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kBlock) argmaxAlongKernel(const typename Elem<DT>::S* __restrict__ src, AlongDims g, int32_t* dst, bool oneHot)
+{
+    typedef Elem<DT> E;
+    typedef typename E::V V;
+    const uint64_t o = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x;
+    if (o >= g.outputs) return;
+    // decompose the output index over all dimensions except the reduced one
+    uint64_t rem = o, base = 0, flatOuter = 0, flatInnerStride = 1;
+    uint64_t coords[MAX_RANK];
+    for (int d = g.rank - 1; d >= 0; --d)
+    {
+        if (d == g.reducedDim) { coords[d] = 0; continue; }
+        const uint64_t q = rem / g.extent[d];
+        coords[d] = rem - q * g.extent[d];
+        base += coords[d] * g.stride[d];
+        rem = q;
+    }
+    V best = E::load(src[base]);
+    uint64_t bestK = 0;
+    for (uint64_t k = 1; k < g.extent[g.reducedDim]; ++k)
+    {
+        const V v = E::load(src[base + k * g.stride[g.reducedDim]]);
+        if (v > best) { best = v; bestK = k; }
+    }
+    if (!oneHot) { dst[o] = static_cast<int32_t>(bestK); return; }
+    // flat row-major index of the winner in the source shape
+    coords[g.reducedDim] = bestK;
+    for (int d = g.rank - 1; d >= 0; --d) { flatOuter += coords[d] * flatInnerStride; flatInnerStride *= g.extent[d]; }
+    dst[flatOuter] = 1;
+}
+
+template <int DT>
+void launchArgmaxAlong(const LaunchContext& ctx, const void* src, const ReduceDim* dims, int rank, int reducedDim, int32_t* dst, bool oneHot)
+{
+    AlongDims g{};
+    g.rank = rank;
+    g.reducedDim = reducedDim;
+    g.outputs = 1;
+    for (int d = 0; d < rank; ++d)
+    {
+        g.extent[d] = dims[d].extent;
+        g.stride[d] = dims[d].stride;
+        if (d != reducedDim) g.outputs *= dims[d].extent;
+    }
+    const unsigned int grid = static_cast<unsigned int>((g.outputs + kBlock - 1) / kBlock);
+    argmaxAlongKernel<DT><<<grid, kBlock, 0, ctx.stream>>>(static_cast<const typename Elem<DT>::S*>(src), g, dst, oneHot);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+// ---- CUDA-core matmul: 64x64 tile, 16-deep k step, 4x4 outputs per thread, any strides -----------------------
+// Accumulates in float for f32/f16/bf16, double for f64, and wraps for integers (aixDeviceCPU.cpp:355-388 accumulates
+// in the storage type; for 16-bit floats the wider accumulator is deliberate).
+template <int DT> struct MatAcc { typedef typename Elem<DT>::SumA T; };
+
+template <int DT>
+__global__ void __launch_bounds__(256) matmulSimtKernel(const typename Elem<DT>::S* __restrict__ a, uint64_t ars, uint64_t acs,
+                                                        const typename Elem<DT>::S* __restrict__ b, uint64_t brs, uint64_t bcs,
+                                                        typename Elem<DT>::S* __restrict__ c, uint64_t m, uint64_t n, uint64_t k)
+{
+    typedef Elem<DT> E;
+    typedef typename MatAcc<DT>::T A;
+    __shared__ A as[16][64 + 4];
+    __shared__ A bs[16][64 + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const uint64_t row0 = static_cast<uint64_t>(blockIdx.y) * 64, col0 = static_cast<uint64_t>(blockIdx.x) * 64;
+    A acc[4][4];
+    #pragma unroll
+    for (int i = 0; i < 4; ++i)
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = A(0);
+    for (uint64_t k0 = 0; k0 < k; k0 += 16)
+    {
+        for (int t = threadIdx.x; t < 16 * 64; t += 256)
+        {
+            const int kk = t & 15, rr = t >> 4;             // A tile: 64 rows x 16 k
+            const uint64_t r = row0 + rr, kg = k0 + kk;
+            as[kk][rr] = (r < m && kg < k) ? static_cast<A>(E::load(a[r * ars + kg * acs])) : A(0);
+            const int cc = t & 63, kb = t >> 6;             // B tile: 16 k x 64 cols
+            const uint64_t cg = col0 + cc, kg2 = k0 + kb;
+            bs[kb][cc] = (cg < n && kg2 < k) ? static_cast<A>(E::load(b[kg2 * brs + cg * bcs])) : A(0);
+        }
+        __syncthreads();
+        #pragma unroll
+        for (int kk = 0; kk < 16; ++kk)
+        {
+            A av[4], bv[4];
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = as[kk][ty * 4 + i];
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) bv[j] = bs[kk][tx * 4 + j];
+            #pragma unroll
+            for (int i = 0; i < 4; ++i)
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        __syncthreads();
+    }
+    #pragma unroll
+    for (int i = 0; i < 4; ++i)
+        #pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            const uint64_t r = row0 + ty * 4 + i, cidx = col0 + tx * 4 + j;
+            if (r < m && cidx < n) c[r * n + cidx] = E::fromSum(static_cast<typename E::SumW>(acc[i][j]));
+        }
+}
+
+template <int DT>
+void launchMatmulSimt(const LaunchContext& ctx, const void* a, uint64_t ars, uint64_t acs, const void* b, uint64_t brs, uint64_t bcs,
+                      void* c, uint64_t m, uint64_t n, uint64_t k)
+{
+    typedef typename Elem<DT>::S S;
+    dim3 grid(static_cast<unsigned int>((n + 63) / 64), static_cast<unsigned int>((m + 63) / 64));
+    matmulSimtKernel<DT><<<grid, 256, 0, ctx.stream>>>(static_cast<const S*>(a), ars, acs, static_cast<const S*>(b), brs, bcs,
+                                                       static_cast<S*>(c), m, n, k);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+// ---- data movement ----------------------------------------------------------------------------------------------
+// transpose (aixDeviceCPU.cpp:391-405): element i of the dense source goes to the swapped coordinates in the result.
+template <class S>
+__global__ void __launch_bounds__(kBlock) transposeKernel(const S* __restrict__ src, S* __restrict__ dst, uint64_t count, Layout srcCanonical,
+                                                          Layout dstStrides, int dim0, int dim1)
+{
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        uint64_t coords[MAX_RANK], rem = i;
+        for (int d = 0; d < srcCanonical.rank; ++d) { coords[d] = rem / srcCanonical.strides[d]; rem -= coords[d] * srcCanonical.strides[d]; }
+        const uint64_t t = coords[dim0]; coords[dim0] = coords[dim1]; coords[dim1] = t;
+        uint64_t off = 0;
+        for (int d = 0; d < srcCanonical.rank; ++d) off += coords[d] * dstStrides.strides[d];
+        dst[off] = src[i];
+    }
+}
+
+// sliceSet (aixDeviceCPU.cpp:470-499)
+template <class S>
+__global__ void __launch_bounds__(kBlock) sliceSetKernel(const S* __restrict__ src, Layout srcLayout, S* __restrict__ dst, Layout dstLayout,
+                                                         uint64_t count, int dim, uint64_t start, uint64_t step, uint64_t sliceExtent)
+{
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        uint64_t rem = i, off = 0;
+        for (int d = dstLayout.rank - 1; d >= 0; --d)
+        {
+            const uint64_t extent = (d == dim) ? sliceExtent : dstLayout.shape[d];
+            const uint64_t coord = rem % extent;
+            rem /= extent;
+            off += ((d == dim) ? (start + coord * step) : coord) * dstLayout.strides[d];
+        }
+        dst[off] = src[layoutOffset(i, srcLayout)];
+    }
+}
+
+// tril / triu (aixDeviceCPU.cpp:565-622)
+template <class S>
+__global__ void __launch_bounds__(kBlock) triangleKernel(const S* __restrict__ src, Layout srcLayout, S* __restrict__ dst, Layout dstLayout,
+                                                         uint64_t count, uint64_t rows, uint64_t cols, int64_t diagonal, bool lower)
+{
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        const int64_t row = static_cast<int64_t>((i / cols) % rows), col = static_cast<int64_t>(i % cols);
+        const bool zero = lower ? (col > row + diagonal) : (col < row + diagonal);
+        dst[layoutOffset(i, dstLayout)] = zero ? S(0) : src[layoutOffset(i, srcLayout)];
+    }
+}
+
+// indexSelect (aixDeviceCPU.cpp:502-531)
+template <class S>
+__global__ void __launch_bounds__(kBlock) indexSelectKernel(const S* __restrict__ src, Layout srcLayout, S* __restrict__ dst,
+                                                            const int32_t* __restrict__ indices, uint64_t indexCount, uint64_t sliceSize,
+                                                            uint64_t dimSize, uint64_t dstCount)
+{
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < dstCount; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        const uint64_t within = i % sliceSize, idx = (i / sliceSize) % indexCount, outer = i / (indexCount * sliceSize);
+        const uint64_t srcFlat = outer * dimSize + static_cast<uint64_t>(indices[idx]) * sliceSize + within;
+        dst[i] = src[layoutOffset(srcFlat, srcLayout)];
+    }
+}
+
+// indexAdd (aixDeviceCPU.cpp:534-562). Several source slices may land on the same destination slice, so the kernel
+// is parallel over (outer, within) and sequential over the index list: same order as the reference, no atomics.
+template <int DT>
+__global__ void __launch_bounds__(kBlock) indexAddKernel(const typename Elem<DT>::S* __restrict__ src, Layout srcLayout,
+                                                         typename Elem<DT>::S* __restrict__ dst, const int32_t* __restrict__ indices,
+                                                         uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t lanes)
+{
+    typedef Reduce<DT, false> R;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; t < lanes; t += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        const uint64_t within = t % sliceSize, outer = t / sliceSize;
+        for (uint64_t idx = 0; idx < indexCount; ++idx)
+        {
+            const uint64_t dstOff = outer * dimSize + static_cast<uint64_t>(indices[idx]) * sliceSize + within;
+            const uint64_t srcFlat = outer * indexCount * sliceSize + idx * sliceSize + within;
+            dst[dstOff] = R::finish(R::merge(R::liftStored(dst[dstOff]), R::liftStored(src[layoutOffset(srcFlat, srcLayout)])));
+        }
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kBlock) scaleKernel(typename Elem<DT>::S* data, uint64_t count, double scale)
+{
+    typedef Elem<DT> E;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        if (DT == 0) data[i] = E::store(static_cast<typename E::V>(static_cast<double>(E::load(data[i])) * scale));
+        else         data[i] = E::store(static_cast<typename E::V>(static_cast<float>(E::load(data[i])) * static_cast<float>(scale)));
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) flushL2Kernel(uint4* buffer, uint64_t count)
+{
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+        buffer[i] = make_uint4(static_cast<unsigned>(i), 0u, 0u, 0u);
+}
+
+template <int DT> void launchTranspose(const LaunchContext& ctx, const void* src, void* dst, uint64_t count, const Layout& sc, const Layout& ds, int d0, int d1)
+{
+    typedef typename Elem<DT>::S S;
+    transposeKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), count, sc, ds, d0, d1);
+}
+template <int DT> void launchSliceSet(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
+                                      int dim, uint64_t start, uint64_t step, uint64_t sliceExtent)
+{
+    typedef typename Elem<DT>::S S;
+    sliceSetKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, dim, start, step, sliceExtent);
+}
+template <int DT> void launchTriangle(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
+                                      uint64_t rows, uint64_t cols, int64_t diagonal, bool lower)
+{
+    typedef typename Elem<DT>::S S;
+    triangleKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, rows, cols, diagonal, lower);
+}
+template <int DT> void launchIndexSelect(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,
+                                         uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
+{
+    typedef typename Elem<DT>::S S;
+    indexSelectKernel<S><<<gridFor(dstCount, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, indexCount, sliceSize, dimSize, dstCount);
+}
+template <int DT> void launchIndexAdd(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,
+                                      uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
+{
+    typedef typename Elem<DT>::S S;
+    const uint64_t lanes = indexCount ? srcCount / indexCount : 0;
+    if (lanes == 0) return;
+    indexAddKernel<DT><<<gridFor(lanes, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, indexCount, sliceSize, dimSize, lanes);
+}
+template <int DT> void launchScale(const LaunchContext& ctx, void* data, uint64_t count, double scale)
+{
+    scaleKernel<DT><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<typename Elem<DT>::S*>(data), count, scale);
+}
+
+}   // namespace
+
+void argmaxAll(const LaunchContext& ctx, const View& src, int32_t* dst, bool oneHot, uint64_t count)
+{
+    AIXB200_DISPATCH_DTYPE(src.dtype, launchArgmaxAll, ctx, src, dst, oneHot, count);
+}
+
+void argmaxAlong(const LaunchContext& ctx, uint32_t dtype, const void* src, const ReduceDim* dims, int rank, int reducedDim,
+                 int32_t* dst, bool oneHot, uint64_t)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchArgmaxAlong, ctx, src, dims, rank, reducedDim, dst, oneHot);
+}
+
+void matmulSimt(const LaunchContext& ctx, uint32_t dtype, const void* a, uint64_t ars, uint64_t acs, const void* b, uint64_t brs,
+                uint64_t bcs, void* c, uint64_t m, uint64_t n, uint64_t k)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchMatmulSimt, ctx, a, ars, acs, b, brs, bcs, c, m, n, k);
+}
+
+void transposeGeneral(const LaunchContext& ctx, uint32_t dtype, const void* src, void* dst, uint64_t count, const Layout& sc,
+                      const Layout& ds, int dim0, int dim1)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchTranspose, ctx, src, dst, count, sc, ds, dim0, dim1);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void sliceSet(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
+              int dim, uint64_t start, uint64_t step, uint64_t sliceExtent)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchSliceSet, ctx, src, sl, dst, dl, count, dim, start, step, sliceExtent);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void triangle(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
+              uint64_t rows, uint64_t cols, int64_t diagonal, bool lower)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchTriangle, ctx, src, sl, dst, dl, count, rows, cols, diagonal, lower);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void indexSelect(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const int32_t* indices,
+                 uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchIndexSelect, ctx, src, sl, dst, indices, indexCount, sliceSize, dimSize, dstCount);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void indexAdd(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const int32_t* indices,
+              uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchIndexAdd, ctx, src, sl, dst, indices, indexCount, sliceSize, dimSize, srcCount);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void scaleInPlace(const LaunchContext& ctx, uint32_t dtype, void* data, uint64_t count, double scale)
+{
+    AIXB200_DISPATCH_DTYPE(dtype, launchScale, ctx, data, count, scale);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+void flushL2(const LaunchContext& ctx, void* buffer, size_t bytes)
+{
+    const uint64_t count = bytes / 16;
+    flushL2Kernel<<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<uint4*>(buffer), count);
+    if (ctx.launches) ++*ctx.launches;
+}
+
+}   // namespace aixb200::kernels

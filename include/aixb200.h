@@ -1,0 +1,213 @@
+/*
+ * aixb200.h - C ABI of the B200 compute device for the AIX tensor library.
+ *
+ * One opaque handle (aixb200_device) stands for one GPU: a CUDA context, one
+ * in-order stream, a caching allocator, a lazy recorder that fuses elementwise
+ * op chains into runtime-compiled kernels, and fixed reduction / GEMM kernels.
+ *
+ * Every op entry point below replaces exactly one virtual of the reference's
+ * abstract device class (Targets/AIXLib/aixDevice.hpp:30-84): same name, same
+ * argument meaning, same ordering contract (calls take effect in program order;
+ * results are observable by any later call and, on the host, after
+ * aixb200_synchronize). Where the reference throws std::invalid_argument /
+ * std::runtime_error, these functions return AIXB200_ERR_INVALID /
+ * AIXB200_ERR_RUNTIME and leave a message in aixb200_last_error().
+ *
+ * The library never falls back to the CPU: without a usable GPU
+ * aixb200_create() fails.
+ */
+#ifndef AIXB200_H
+#define AIXB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AIXB200_MAX_RANK 8
+
+/* Status codes. 0 is success; everything else leaves a message in aixb200_last_error(). */
+enum
+{
+    AIXB200_OK            = 0,
+    AIXB200_ERR_INVALID   = 1,   /* contract violation (reference: std::invalid_argument) */
+    AIXB200_ERR_RUNTIME   = 2,   /* CUDA / NVRTC / NCCL / allocation failure (reference: std::runtime_error) */
+    AIXB200_ERR_NOGPU     = 3,   /* no CUDA device or driver; there is no CPU fallback */
+    AIXB200_ERR_TIMEOUT   = 4,   /* a bounded device- or host-side wait ran out */
+};
+
+/* Element types; numeric values equal aix::DataType (Targets/AIXLib/aixCore.hpp:44-55).
+ * F16/BF16 are raw IEEE binary16 / bfloat16 bit patterns (Targets/AIXLib/aixFloat16.hpp). */
+enum
+{
+    AIXB200_F64  = 0,
+    AIXB200_F32  = 1,
+    AIXB200_F16  = 2,
+    AIXB200_BF16 = 3,
+    AIXB200_I64  = 4,
+    AIXB200_I32  = 5,
+    AIXB200_I16  = 6,
+    AIXB200_I8   = 7,
+    AIXB200_U8   = 8,
+    AIXB200_DTYPE_COUNT = 9
+};
+
+/* POD image of aix::DeviceTensorParams (Targets/AIXLib/aixCore.hpp:189-198).
+ * `data` is the storage base, the view starts `offset` ELEMENTS into it; strides are in
+ * elements and a stride of 0 is a broadcast dimension; rank 0 is a scalar (size 1).
+ * `data` of an input may be device memory from aixb200_allocate or plain host memory
+ * (it is staged to the GPU at call time); `data` of a result must come from
+ * aixb200_allocate of the same device. isContiguous is derived from the strides. */
+typedef struct aixb200_tensor
+{
+    void*    data;
+    uint64_t offset;
+    uint64_t size;
+    uint32_t dtype;
+    uint32_t rank;
+    uint64_t shape[AIXB200_MAX_RANK];
+    uint64_t strides[AIXB200_MAX_RANK];
+} aixb200_tensor;
+
+typedef struct aixb200_device aixb200_device;
+
+/* Device configuration. Zero-initialise, then override; aixb200_default_config fills the defaults. */
+typedef struct aixb200_config
+{
+    int32_t  ordinal;            /* CUDA device ordinal */
+    int32_t  managed_memory;     /* 1: allocations are host-dereferenceable CUDA managed memory (what the C++
+                                    aix::Device adapter needs, aixCore.hpp:435-440,491-499); 0: plain device memory */
+    uint32_t flush_threshold;    /* pending elementwise ops before the planner runs (reference: 200, aixDeviceMetal.cpp:129) */
+    int32_t  strict_math;        /* 1: no FMA contraction, IEEE div/sqrt, per-op rounding of f16/bf16 */
+    int32_t  fusion;             /* 0 disables fusion: every recorded op becomes its own kernel */
+    int32_t  disk_cache;         /* 1: keep compiled cubins in $AIXB200_CACHE_DIR (default ~/.cache/aixb200) */
+    uint64_t cache_limit_bytes;  /* idle blocks kept by the allocator before it trims (0 = 3/4 of device memory) */
+    void*    stream;             /* cudaStream_t to run on; NULL = the device creates its own non-blocking stream */
+    int32_t  tf32x3_matmul;      /* f32 matmul: 1 = 3xBF16/TF32-class split on tensor cores, 0 = CUDA-core f32 */
+    int32_t  dry_run;            /* 1: no GPU is touched - ops are recorded, planned and compiled with NVRTC but not
+                                    launched, and memory comes from malloc (host-logic tests on machines without a GPU) */
+    int32_t  reserved[6];
+} aixb200_config;
+
+void aixb200_default_config(aixb200_config* cfg);
+
+/* ---- lifecycle ---- (reference: aix::createDevice, Targets/AIXLib/aixDevices.cpp:24-43) */
+int  aixb200_create(int ordinal, aixb200_device** out);
+int  aixb200_create_with_config(const aixb200_config* cfg, aixb200_device** out);
+void aixb200_destroy(aixb200_device* dev);
+/* Message of the last failed call on this device (dev may be NULL for creation failures). */
+const char* aixb200_last_error(const aixb200_device* dev);
+/* "B200" + the CUDA device name (reference: Device::name, aixDevice.hpp:36). */
+const char* aixb200_name(const aixb200_device* dev);
+/* Number of visible CUDA devices, or 0 when there is no driver. Never fails. */
+int  aixb200_device_count(void);
+const char* aixb200_version(void);
+
+/* ---- memory ---- (reference: Device::allocate/deallocate, aixDevice.hpp:40-42; cache and deferred
+ * frees: aixDeviceMetalCache.hpp:28-198, aixDeviceMetal.cpp:251-259) */
+int aixb200_allocate(aixb200_device* dev, size_t bytes, void** out);
+int aixb200_allocate_typed(aixb200_device* dev, size_t count, uint32_t dtype, void** out);
+int aixb200_deallocate(aixb200_device* dev, void* memory);
+int aixb200_empty_cache(aixb200_device* dev);                        /* Device::emptyCache, aixDevice.hpp:82 */
+int aixb200_synchronize(aixb200_device* dev);                        /* Device::synchronize, aixDevice.hpp:83 */
+
+/* ---- elementwise, recorded lazily and fused (aixDevice.hpp:44-48, 57-63) ---- */
+int aixb200_add(aixb200_device* dev, const aixb200_tensor* a1, const aixb200_tensor* a2, const aixb200_tensor* result);
+int aixb200_sub(aixb200_device* dev, const aixb200_tensor* a1, const aixb200_tensor* a2, const aixb200_tensor* result);
+int aixb200_mul(aixb200_device* dev, const aixb200_tensor* a1, const aixb200_tensor* a2, const aixb200_tensor* result);
+int aixb200_div(aixb200_device* dev, const aixb200_tensor* a1, const aixb200_tensor* a2, const aixb200_tensor* result);
+int aixb200_unary(aixb200_device* dev, const aixb200_tensor* a1, const aixb200_tensor* result);   /* negate */
+int aixb200_sqrt(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_sin(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_cos(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_tanh(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_log(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_exp(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_pow(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* exp, const aixb200_tensor* result);
+/* fill: `scalar` points at ONE host value of type scalar_dtype, converted with saturation to the result type
+ * (aixDevice.hpp:50; conversion rule aixDeviceCPU.cpp:96-117). fillMin writes numeric_limits<T>::lowest(). */
+int aixb200_fill(aixb200_device* dev, const void* scalar, uint32_t scalar_dtype, const aixb200_tensor* result);
+int aixb200_fill_min(aixb200_device* dev, const aixb200_tensor* result);                          /* aixDevice.hpp:51 */
+
+/* ---- reductions (aixDevice.hpp:52, 60-62, 70-73) ---- */
+int aixb200_sum(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_max(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_argmax(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+int aixb200_argmax_indices(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+/* dst += sum over the broadcast dimensions of src (dst zeroed by the caller); dst = max(dst, ...) for max_to. */
+int aixb200_reduce_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst);
+int aixb200_max_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst);
+int aixb200_argmax_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim);
+int aixb200_argmax_indices_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim);
+
+/* ---- contraction (aixDevice.hpp:63): result[M,N] = a[M,K] . b[K,N]; a and b may be arbitrary 2-D strided views ---- */
+int aixb200_matmul(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* result);
+
+/* ---- data movement (aixDevice.hpp:64-69, 74-81) ---- */
+int aixb200_transpose(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result, size_t dim0, size_t dim1);
+/* Dtype-converting copy of `count` elements. src may be host or device memory. dst is device memory; as an
+ * extension over the reference, copy_immediate also accepts a host dst (device-to-host read-back). */
+int aixb200_copy(aixb200_device* dev, const void* src, uint32_t src_dtype, void* dst, uint32_t dst_dtype, size_t count);
+int aixb200_copy_immediate(aixb200_device* dev, const void* src, uint32_t src_dtype, void* dst, uint32_t dst_dtype, size_t count);
+int aixb200_contiguous(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst);
+int aixb200_slice_set(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst,
+                      size_t dim, size_t start, size_t end, size_t step);
+int aixb200_tril(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, int64_t diagonal);
+int aixb200_triu(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, int64_t diagonal);
+int aixb200_index_select(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst,
+                         const aixb200_tensor* indices, size_t dim);
+int aixb200_index_add(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst,
+                      const aixb200_tensor* indices, size_t dim);
+
+/* ---- diagnostics (reference: fuse::FlushDiagnostics aixFuse.hpp:144-156; kernel cache counters
+ * aixDeviceMetalKernelGen.hpp:51-53) ---- */
+typedef struct aixb200_stats
+{
+    uint64_t ops_recorded;          /* elementwise ops recorded since creation */
+    uint64_t flushes;
+    uint64_t fused_kernels;         /* generated-kernel launches */
+    uint64_t fused_ops;             /* recorded ops folded into those launches */
+    uint64_t fills_absorbed;        /* fills turned into kernel scalars */
+    uint64_t stores_elided;         /* intermediate results never written to memory */
+    uint64_t kernel_cache_hits;
+    uint64_t kernel_cache_misses;   /* == NVRTC compilations + disk-cache loads */
+    uint64_t nvrtc_compiles;
+    double   nvrtc_ms;              /* total time spent in NVRTC */
+    uint64_t static_kernel_launches;/* reductions, GEMM, copies ... */
+    uint64_t total_kernel_launches; /* every kernel this device put on its stream */
+    uint64_t bytes_in_use;          /* handed out by allocate and not yet deallocated */
+    uint64_t bytes_cached;          /* idle blocks held by the allocator */
+    uint64_t bytes_reserved;        /* obtained from CUDA */
+    uint64_t cuda_mallocs;          /* calls that reached the CUDA allocator */
+    uint64_t h2d_bytes;             /* staged host->device */
+    uint64_t d2h_bytes;
+    uint64_t reserved[6];
+} aixb200_stats;
+int aixb200_get_stats(aixb200_device* dev, aixb200_stats* out);
+/* CUDA C source of the most recently generated kernel (for inspection and tests); NULL if none yet. */
+const char* aixb200_last_kernel_source(const aixb200_device* dev);
+
+/* ---- device-side timing on the device's stream ---- */
+typedef struct aixb200_event aixb200_event;
+int aixb200_event_create(aixb200_device* dev, aixb200_event** out);
+int aixb200_event_record(aixb200_device* dev, aixb200_event* ev);    /* flushes recorded work first */
+int aixb200_event_elapsed_ms(aixb200_device* dev, aixb200_event* start, aixb200_event* stop, float* ms); /* waits for stop */
+int aixb200_event_destroy(aixb200_device* dev, aixb200_event* ev);
+/* Writes `bytes` of device memory so that nothing useful stays in L2 (timing hygiene between iterations). */
+int aixb200_flush_l2(aixb200_device* dev);
+
+/* ---- data-parallel exchange (no reference counterpart: the reference has no multi-device code) ---- */
+#define AIXB200_COMM_ID_BYTES 128
+int aixb200_comm_unique_id(void* id_out /* AIXB200_COMM_ID_BYTES */);
+int aixb200_comm_init(aixb200_device* dev, int rank, int nranks, const void* id);
+/* In-place sum all-reduce over `count` elements of dtype (F32, F64, BF16, F16, I32, I64) followed by a
+ * multiplication by `scale` (1/nranks averages). Ordered after all work recorded so far. */
+int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
+int aixb200_comm_destroy(aixb200_device* dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIXB200_H */
