@@ -245,6 +245,18 @@ void Device::synchronize()
     if (dryRun()) return;
     check(cudaStreamSynchronize(m_stream), "cudaStreamSynchronize");
     check(cudaGetLastError(), "asynchronous kernel failure");
+    if (m_checkErrorWord)
+    {
+        // Kernels with bounded waits (tensor-core GEMM) raise a word in scratch instead of hanging.
+        m_checkErrorWord = false;
+        uint32_t word = 0;
+        check(cudaMemcpy(&word, static_cast<char*>(m_scratch) + 128, 4, cudaMemcpyDeviceToHost), "read error word");
+        if (word)
+        {
+            cudaMemset(static_cast<char*>(m_scratch) + 128, 0, 4);
+            throw Error(AIXB200_ERR_TIMEOUT, "a bounded device-side wait ran out inside the tensor-core matmul; its result is invalid");
+        }
+    }
 }
 
 bool Device::isHostPointer(const void* p) const
@@ -653,7 +665,8 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
     p.b = vb.firstByte(); p.bRowStride = b->strides[0]; p.bColStride = b->strides[1];
     p.c = vr.firstByte();
     p.splitF32 = m_cfg.tf32x3_matmul != 0;
-    if (!gemm::launchTensorCore(*this, ctx, p))
+    if (gemm::launchTensorCore(*this, ctx, p)) m_checkErrorWord = true;
+    else
         kernels::matmulSimt(ctx, r->dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);
     AIXB200_DONE("matmul");
 }

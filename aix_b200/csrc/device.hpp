@@ -133,6 +133,7 @@ private:
     aixb200_stats m_stats{};
     std::unique_ptr<Comm> m_comm;
     bool m_inFlush = false;
+    bool m_checkErrorWord = false;
 };
 
 }   // namespace aixb200

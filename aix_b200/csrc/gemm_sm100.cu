@@ -1,11 +1,552 @@
+// Dense matmul on the 5th-generation tensor cores of sm_100a.
+//
+// Replaces the reference's threadgroup-tiled Metal GEMM (matrixMulStridedTiled<16>, aixDeviceMetalShaders.hpp:1191-1275,
+// selected in aixDeviceMetal.cpp:569-656). Structure of the kernel:
+//   * persistent CTAs (one per SM) walk 128 x 256 output tiles in an L2-friendly order;
+//   * warp 0 streams operand tiles with TMA (cp.async.bulk.tensor, no multicast) into a 4-stage ring of
+//     128-byte-swizzled shared memory, signalling mbarriers;
+//   * warp 1 issues tcgen05.mma (cta_group::1, M=128, N=256, K=16 or 8) from one elected thread; the accumulators
+//     live in tensor memory (TMEM), two buffers of 256 columns so that the epilogue of one tile overlaps the
+//     main loop of the next; tcgen05.commit releases shared-memory stages and publishes finished accumulators;
+//   * warps 2-5 read the accumulator with tcgen05.ld, convert and store C.
+// Operands may be K-major or MN-major (row- or column-major views): the shared-memory matrix descriptors and the
+// TMA boxes are chosen per operand, so forward (A.B), dX (G.B^T) and dW (A^T.G) run without materialised transposes.
+// f32 problems are computed as three TF32 products of a hi/lo split (a = hi + lo): C = Ahi.Bhi + Alo.Bhi + Ahi.Blo,
+// accumulated in f32, which keeps f32-level accuracy; the split pass also makes both operands K-major.
+// Every wait on an mbarrier is bounded in time; on expiry the kernel raises an error word and drains.
 #include "gemm.hpp"
+
+#include "device.hpp"
+#include "dtypes.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
 
 namespace aixb200::gemm
 {
 
-bool launchTensorCore(Device&, const kernels::LaunchContext&, const Problem&)
+namespace
 {
-    return false;
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kStageBytesA = kBlockM * 128;              // 128 rows (or 2 MN atoms x 64 k) x 128 B
+constexpr int kStageBytesB = kBlockN * 128;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kTmemColumns = 512;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;         // 2 s: far beyond any legitimate wait
+
+struct KernelParams
+{
+    uint32_t m, n, k;
+    uint32_t tilesM, tilesN, kBlocks;
+    uint32_t blockK;            // elements of K per stage (64 for 16-bit, 32 for tf32)
+    uint32_t aMnMajor, bMnMajor;
+    uint32_t aBoxes, bBoxes;    // TMA boxes per stage and operand
+    uint32_t aBoxBytes, bBoxBytes;
+    uint32_t aBoxStepMn, bBoxStepMn;   // MN elements covered by one box (MN-major) / unused (K-major)
+    uint32_t idesc;             // tcgen05 instruction descriptor
+    uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
+    uint32_t kAdvanceA, kAdvanceB;     // bytes to advance the descriptor start per MMA along K
+    uint32_t mmasPerStage;
+    uint32_t outDtype;          // F32, F16, BF16
+    uint32_t kPhases;           // 1, or 3 for the split-f32 scheme
+    uint32_t kPerPhase;         // K of the original problem (elements) when kPhases == 3
+    uint32_t vectorStores;      // C rows are 16-byte aligned
+    void*    c;
+    uint32_t* errorWord;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbarExpectTx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbarTest(uint64_t* bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(smemAddr(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ uint64_t globalTimerNs()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: returns false (and raises *abortFlag) when the barrier did not flip within kWaitLimitNs or when
+// another role already gave up.
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag)
+{
+    if (mbarTest(bar, parity)) return true;
+    const uint64_t start = globalTimerNs();
+    uint32_t spins = 0;
+    while (!mbarTest(bar, parity))
+    {
+        if ((++spins & 63u) == 0)
+        {
+            if (*abortFlag) return false;
+            if (globalTimerNs() - start > kWaitLimitNs) { *abortFlag = 1; return false; }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tmaLoad2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smemAddr(dst)), "l"(map), "r"(smemAddr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmemAlloc(uint32_t* resultInSmem, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(resultInSmem)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDealloc(uint32_t taddr, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void fenceBeforeSync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fenceAfterSync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+template <bool Tf32>
+__device__ __forceinline__ void umma(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    if (Tf32)
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ummaCommit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in 16-byte units,
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smemDescriptor(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;       // SWIZZLE_128B
+    return d;
+}
+
+struct SharedStorage
+{
+    alignas(1024) uint8_t a[kStages][kStageBytesA];
+    alignas(1024) uint8_t b[kStages][kStageBytesB];
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmemFull[2];
+    uint64_t tmemEmpty[2];
+    uint32_t tmemBase;
+    uint32_t abortFlag;
+};
+
+__device__ __forceinline__ void tileCoordinates(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t& tm, uint32_t& tn)
+{
+    constexpr uint32_t kGroup = 8;                     // 8 row-tiles share their B columns back to back
+    const uint32_t perGroup = kGroup * tilesN;
+    const uint32_t group = t / perGroup;
+    const uint32_t firstM = group * kGroup;
+    const uint32_t groupRows = min(tilesM - firstM, kGroup);
+    const uint32_t local = t - group * perGroup;
+    tm = firstM + local % groupRows;
+    tn = local / groupRows;
+}
+
+template <bool Tf32>
+__global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                                           const __grid_constant__ KernelParams p)
+{
+    extern __shared__ uint8_t rawSmem[];
+    SharedStorage& s = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile uint32_t* abortFlag = &s.abortFlag;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < kStages; ++i) { mbarInit(&s.full[i], 1); mbarInit(&s.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], 128); }
+        s.abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1)
+    {
+        tmemAlloc(&s.tmemBase, kTmemColumns);
+        tmemRelinquish();
+    }
+    fenceBeforeSync();
+    __syncthreads();
+    fenceAfterSync();
+    const uint32_t tmemBase = s.tmemBase;
+    const uint32_t totalTiles = p.tilesM * p.tilesN;
+    const uint32_t kIters = p.kBlocks * p.kPhases;
+
+    if (warp == 0)
+    {
+        if (lane == 0)
+        {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
+            {
+                uint32_t tm, tn;
+                tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+                const int32_t m0 = static_cast<int32_t>(tm * kBlockM), n0 = static_cast<int32_t>(tn * kBlockN);
+                for (uint32_t it = 0; it < kIters; ++it)
+                {
+                    if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
+                    mbarExpectTx(&s.full[stage], p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes);
+                    // Split-f32: K is laid out as [hi | lo] per operand; the three passes read (hi,hi), (lo,hi), (hi,lo).
+                    const uint32_t pass = it / p.kBlocks, kb = it - pass * p.kBlocks;
+                    const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
+                    const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
+                    for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
+                    {
+                        if (p.aMnMajor) tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], &mapA, &s.full[stage], m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
+                        else            tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], &mapA, &s.full[stage], kA, m0);
+                    }
+                    for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
+                    {
+                        if (p.bMnMajor) tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], &mapB, &s.full[stage], n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
+                        else            tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], &mapB, &s.full[stage], kB, n0);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0)
+        {
+            uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
+            {
+                if (!mbarWait(&s.tmemEmpty[acc], accPhase ^ 1u, abortFlag)) { ok = false; break; }
+                fenceAfterSync();
+                const uint32_t tmemD = tmemBase + acc * kBlockN;
+                for (uint32_t it = 0; it < kIters; ++it)
+                {
+                    if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
+                    fenceAfterSync();
+                    const uint32_t aAddr = smemAddr(&s.a[stage][0]), bAddr = smemAddr(&s.b[stage][0]);
+                    for (uint32_t j = 0; j < p.mmasPerStage; ++j)
+                    {
+                        const uint64_t da = smemDescriptor(aAddr + j * p.kAdvanceA, p.aLbo, 1024);
+                        const uint64_t db = smemDescriptor(bAddr + j * p.kAdvanceB, p.bLbo, 1024);
+                        umma<Tf32>(tmemD, da, db, p.idesc, (it | j) != 0 ? 1u : 0u);
+                    }
+                    ummaCommit(&s.empty[stage]);           // the stage is free once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ummaCommit(&s.tmemFull[acc]);       // accumulator complete
+                acc ^= 1u;
+                if (acc == 0) accPhase ^= 1u;
+            }
+        }
+    }
+    else
+    {
+        // Epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31, i.e. rows of the tile.
+        const uint32_t quarter = warp & 3u;
+        uint32_t acc = 0, accPhase = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
+        {
+            uint32_t tm, tn;
+            tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+            if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
+            fenceAfterSync();
+            const uint32_t row = tm * kBlockM + quarter * 32 + lane;
+            const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
+            #pragma unroll 1
+            for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32)
+            {
+                uint32_t r[32];
+                tmemLoad32(taddr + c0, r);
+                tmemLoadWait();
+                const uint32_t col = tn * kBlockN + c0;
+                if (row < p.m && col < p.n)
+                {
+                    const bool fullRow = col + 32 <= p.n;
+                    if (p.outDtype == F32)
+                    {
+                        float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
+                        if (fullRow && p.vectorStores)
+                        {
+                            #pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                reinterpret_cast<uint4*>(out)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                        else
+                        {
+                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]);
+                        }
+                    }
+                    else
+                    {
+                        uint16_t* out = static_cast<uint16_t*>(p.c) + static_cast<size_t>(row) * p.n + col;
+                        uint32_t packed[16];
+                        #pragma unroll
+                        for (int v = 0; v < 16; ++v)
+                        {
+                            const float lo = __uint_as_float(r[2 * v]), hi = __uint_as_float(r[2 * v + 1]);
+                            const uint32_t l16 = p.outDtype == BF16 ? dev::f32ToBf16(lo) : dev::f32ToF16(lo);
+                            const uint32_t h16 = p.outDtype == BF16 ? dev::f32ToBf16(hi) : dev::f32ToF16(hi);
+                            packed[v] = l16 | (h16 << 16);
+                        }
+                        if (fullRow && p.vectorStores)
+                        {
+                            #pragma unroll
+                            for (int v = 0; v < 4; ++v)
+                                reinterpret_cast<uint4*>(out)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        }
+                        else
+                        {
+                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e)
+                                out[e] = static_cast<uint16_t>((packed[e >> 1] >> ((e & 1) * 16)) & 0xFFFFu);
+                        }
+                    }
+                }
+            }
+            fenceBeforeSync();
+            mbarArrive(&s.tmemEmpty[acc]);
+            acc ^= 1u;
+            if (acc == 0) accPhase ^= 1u;
+        }
+    }
+
+    fenceBeforeSync();
+    __syncthreads();
+    if (warp == 1)
+    {
+        fenceAfterSync();
+        tmemDealloc(tmemBase, kTmemColumns);
+    }
+    if (threadIdx.x == 0 && s.abortFlag) atomicExch(p.errorWord, 1u);
+}
+
+// ---- f32 split pass: src (any 2-D strides) -> dst[rows][2*k] = [hi(k) | lo(k)], K-major, zero padded to kPad ------
+__global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ src, uint64_t rowStride, uint64_t colStride,
+                                                      uint32_t rows, uint32_t k, uint32_t kPad, float* __restrict__ dst)
+{
+    // One CTA handles a 32 x 32 tile through shared memory so that both the strided read and the dense write coalesce
+    // whichever way the source is laid out.
+    __shared__ float tile[32][33];
+    const uint32_t r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
+    const bool colContiguous = colStride == 1;
+    for (uint32_t i = ty; i < 32; i += 8)
+    {
+        // read so that the contiguous source direction maps to tx
+        const uint32_t r = colContiguous ? r0 + i : r0 + tx;
+        const uint32_t c = colContiguous ? c0 + tx : c0 + i;
+        float v = 0.f;
+        if (r < rows && c < k) v = src[static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride];
+        if (colContiguous) tile[i][tx] = v; else tile[tx][i] = v;
+    }
+    __syncthreads();
+    for (uint32_t i = ty; i < 32; i += 8)
+    {
+        const uint32_t r = r0 + i, c = c0 + tx;
+        if (r < rows && c < kPad)
+        {
+            const float v = tile[i][tx];
+            const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);     // exactly representable in TF32
+            float* out = dst + static_cast<uint64_t>(r) * (2ull * kPad);
+            out[c] = hi;
+            out[kPad + c] = v - hi;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []
+    {
+        cudaDriverEntryPointQueryResult status;
+        void* p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess && status == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D tensor map over a matrix whose fast dimension has `inner` elements and whose rows are `pitchBytes` apart.
+bool makeMap(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t outer, uint64_t pitchBytes,
+             uint32_t boxInner, uint32_t boxOuter)
+{
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitchBytes};
+    cuuint32_t box[2] = {boxInner, boxOuter};
+    cuuint32_t elemStrides[2] = {1, 1};
+    EncodeTiledFn fn = encodeTiled();
+    if (!fn) return false;
+    return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Operand
+{
+    const void* base;
+    bool        mnMajor;       // unit stride runs along M (for A) or N (for B) instead of K
+    uint64_t    pitch;         // elements between consecutive lines of the slow dimension
+};
+
+// Classifies a strided 2-D operand (rows x cols, the K dimension being `kIsCols ? cols : rows`).
+bool classify(const void* base, uint64_t rowStride, uint64_t colStride, uint64_t rows, uint64_t cols, bool kIsCols, size_t esize, Operand* out)
+{
+    const bool colsContiguous = colStride == 1 || cols == 1;
+    const bool rowsContiguous = rowStride == 1 || rows == 1;
+    if (colsContiguous && (rows == 1 || rowStride >= cols))
+    {
+        out->base = base; out->pitch = rows == 1 ? cols : rowStride; out->mnMajor = !kIsCols;
+    }
+    else if (rowsContiguous && (cols == 1 || colStride >= rows))
+    {
+        out->base = base; out->pitch = cols == 1 ? rows : colStride; out->mnMajor = kIsCols;
+    }
+    else return false;
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (out->pitch * esize) % 16 != 0) return false;
+    return true;
+}
+
+}   // namespace
+
+bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& q)
+{
+    if (q.dtype != F32 && q.dtype != BF16 && q.dtype != F16) return false;
+    if (q.dtype == F32 && !q.splitF32) return false;
+    if (q.m < 64 || q.n < 64 || q.k < 32) return false;                     // tiny problems: launch-bound, CUDA cores do
+    if (q.m > 0x7FFFFF00ull || q.n > 0x7FFFFF00ull || q.k > 0x3FFFFF00ull) return false;
+    if (!encodeTiled()) return false;
+    static bool disabled = std::getenv("AIXB200_NO_TENSOR_CORE") != nullptr;
+    if (disabled) return false;
+
+    KernelParams p{};
+    p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
+    p.tilesM = (p.m + kBlockM - 1) / kBlockM;
+    p.tilesN = (p.n + kBlockN - 1) / kBlockN;
+    p.c = q.c;
+    p.outDtype = q.dtype;
+    p.vectorStores = (reinterpret_cast<uintptr_t>(q.c) % 16 == 0) && ((q.n * dtypeSize(q.dtype)) % 16 == 0);
+    p.errorWord = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + 128);
+    CUtensorMap mapA, mapB;
+    const bool tf32 = q.dtype == F32;
+
+    if (!tf32)
+    {
+        Operand a, b;
+        if (!classify(q.a, q.aRowStride, q.aColStride, q.m, q.k, true, 2, &a)) return false;
+        if (!classify(q.b, q.bRowStride, q.bColStride, q.k, q.n, false, 2, &b)) return false;
+        p.blockK = 64;
+        p.kBlocks = (p.k + 63) / 64;
+        p.kPhases = 1;
+        p.mmasPerStage = 4;
+        const CUtensorMapDataType type = q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        p.aMnMajor = a.mnMajor; p.bMnMajor = b.mnMajor;
+        if (a.mnMajor)
+        {
+            p.aBoxes = kBlockM / 64; p.aBoxBytes = 64 * 128; p.aBoxStepMn = 64; p.aLbo = 64 * 128; p.kAdvanceA = 16 * 128;
+            if (!makeMap(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, 64)) return false;
+        }
+        else
+        {
+            p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.aLbo = 0; p.kAdvanceA = 32;
+            if (!makeMap(&mapA, type, a.base, q.k, q.m, a.pitch * 2, 64, kBlockM)) return false;
+        }
+        if (b.mnMajor)
+        {
+            p.bBoxes = kBlockN / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
+            if (!makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
+        }
+        else
+        {
+            p.bBoxes = 1; p.bBoxBytes = kStageBytesB; p.bLbo = 0; p.kAdvanceB = 32;
+            if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, kBlockN)) return false;
+        }
+        // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
+        p.idesc = (1u << 4) | ((q.dtype == BF16 ? 1u : 0u) << 7) | ((q.dtype == BF16 ? 1u : 0u) << 10) |
+                  ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+    }
+    else
+    {
+        // hi/lo split into K-major scratch: A' [m][2*kPad], B' [n][2*kPad]
+        const uint32_t kPad = (p.k + 31) & ~31u;
+        const size_t bytesA = static_cast<size_t>(p.m) * 2 * kPad * 4, bytesB = static_cast<size_t>(p.n) * 2 * kPad * 4;
+        float* splitA = static_cast<float*>(device.temporary(bytesA));
+        float* splitB = static_cast<float*>(device.temporary(bytesB));
+        dim3 gridA((kPad + 31) / 32, (p.m + 31) / 32), gridB((kPad + 31) / 32, (p.n + 31) / 32);
+        splitF32Kernel<<<gridA, 256, 0, ctx.stream>>>(static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, splitA);
+        // B is k x n: its "rows" for the split are the n columns
+        splitF32Kernel<<<gridB, 256, 0, ctx.stream>>>(static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, splitB);
+        if (ctx.launches) *ctx.launches += 2;
+        p.blockK = 32;
+        p.kBlocks = kPad / 32;
+        p.kPhases = 3;
+        p.kPerPhase = kPad;
+        p.mmasPerStage = 4;
+        p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
+        p.bBoxes = 1; p.bBoxBytes = kStageBytesB; p.kAdvanceB = 32;
+        if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitA, 2ull * kPad, q.m, 2ull * kPad * 4, 32, kBlockM)) return false;
+        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitB, 2ull * kPad, q.n, 2ull * kPad * 4, 32, kBlockN)) return false;
+        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+    }
+
+    const size_t smemBytes = sizeof(SharedStorage) + 1024;
+    static std::once_flag attrOnce;
+    std::call_once(attrOnce, [&]
+    {
+        cudaFuncSetAttribute(gemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
+        cudaFuncSetAttribute(gemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
+    });
+    const uint32_t tiles = p.tilesM * p.tilesN;
+    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(ctx.smCount));
+    if (tf32) gemmKernel<true><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
+    else      gemmKernel<false><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
+    if (ctx.launches) ++*ctx.launches;
+    return true;
 }
 
 }   // namespace aixb200::gemm

@@ -1,0 +1,75 @@
+"""Secondary measurements printed beside the headline benchmark: the reduction kernels on the broadcast+reduction
+configuration (x [8192,8192] bf16) and the dense matmul configuration (4096^3, bf16 and f32). Device time by CUDA
+events on the device's stream, L2 flushed between iterations when the working set could fit in it."""
+import numpy as np
+
+from . import _capi as C
+from .device import to_storage
+from .tensor import TensorValue
+
+
+def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
+    for _ in range(warmup):
+        fn()
+    dev.synchronize()
+    e0, e1 = dev.createEvent(), dev.createEvent()
+    times = []
+    for _ in range(iters):
+        if flush_l2:
+            dev.flushL2()
+        dev.recordEvent(e0)
+        fn()
+        dev.recordEvent(e1)
+        times.append(dev.elapsedMs(e0, e1))
+    dev.destroyEvent(e0)
+    dev.destroyEvent(e1)
+    return float(np.median(times)), float(np.min(times))
+
+
+def relu(v):
+    return (v + (v * v).sqrt()) * 0.5
+
+
+def measure_reductions(dev, hbm_peak, rows=8192, cols=8192):
+    rng = np.random.default_rng(0)
+    x = TensorValue.from_numpy(rng.normal(0, 1, (rows, cols)).astype(np.float32), dev, C.BF16)
+    g = TensorValue.from_numpy(rng.uniform(0.5, 1.5, cols).astype(np.float32), dev, C.BF16)
+    b = TensorValue.from_numpy(rng.normal(0, 0.1, cols).astype(np.float32), dev, C.BF16)
+    dev.synchronize()
+    n = rows * cols
+    out = {}
+    holder = {}
+
+    y = relu(x * g + b)
+    dev.synchronize()
+    cases = {
+        "relu(x*g+bias) bf16 [fused, y written]": (lambda: holder.__setitem__("y", relu(x * g + b)), 2 * n * 2 + 2 * cols * 2),
+        "row sum bf16 (reduceTo)": (lambda: holder.__setitem__("s", y.sum(1)), n * 2),
+        "row max bf16 (maxTo)": (lambda: holder.__setitem__("m", y.max(1)), n * 2),
+        "global sum bf16": (lambda: holder.__setitem__("t", y.sum()), n * 2),
+    }
+    for name, (fn, nbytes) in cases.items():
+        med, best = _time(dev, fn)
+        out[name] = {"ms": med, "GB/s": nbytes / (med * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (med * 1e-3) / 1e9 / hbm_peak,
+                     "bytes": nbytes}
+    return out
+
+
+def measure_matmul(dev, tensor_peak, size=4096):
+    rng = np.random.default_rng(0)
+    out = {}
+    for name, dtype in (("bf16", C.BF16), ("f32", C.F32)):
+        a = TensorValue.from_numpy(rng.normal(0, 0.02, (size, size)).astype(np.float32), dev, dtype)
+        b = TensorValue.from_numpy(rng.normal(0, 0.02, (size, size)).astype(np.float32), dev, dtype)
+        dev.synchronize()
+        holder = {}
+        forms = {"A.B": lambda: a.matmul(b), "G.B^T": lambda: a.matmul(b.transpose(0, 1)), "A^T.G": lambda: a.transpose(0, 1).matmul(b)}
+        for form, fn in forms.items():
+            med, best = _time(dev, lambda: holder.__setitem__("c", fn()), iters=5, warmup=2, flush_l2=False)
+            tf = 2.0 * size ** 3 / (med * 1e-3) / 1e12
+            out[f"{name} {form} {size}^3"] = {"ms": med, "TFLOP/s": tf, "frac_of_measured_bf16_peak": tf / tensor_peak}
+    return out
+
+
+def measure_extras(dev, hbm_peak, tensor_peak):
+    return {"reductions_8192x8192_bf16": measure_reductions(dev, hbm_peak), "matmul": measure_matmul(dev, tensor_peak)}

@@ -1,0 +1,77 @@
+"""matmul parity with the reference's CPU device (Tests/DeviceTests.cpp:1244-1262, 2200-2360, 2806-2875).
+
+f32 results are compared norm-wise (max |diff| / max |C| <= 1e-5): entries of C come arbitrarily close to zero.
+For f16/bf16 the oracle is the CPU f32 matmul of the same values, rounded once to the 16-bit type (the CPU device's
+own 16-bit accumulator loses everything at large K).
+"""
+import numpy as np
+import pytest
+
+from aix_b200 import BF16, DTYPE_NAMES, F16, F32, F64, I8, I16, I32, I64, U8, TensorValue, from_storage, to_storage
+
+pytestmark = pytest.mark.gpu
+
+
+def quantize(x, dtype):
+    return from_storage(to_storage(x, dtype), dtype)
+
+
+def normwise(got, want):
+    return float(np.max(np.abs(got.astype(np.float64) - want.astype(np.float64))) / max(1e-30, np.max(np.abs(want.astype(np.float64)))))
+
+
+def check(b200, ref, a, b, dtype, transpose_a=False, transpose_b=False, what=""):
+    outs = []
+    for dev, dt in ((b200, dtype), (ref, F32 if dtype in (F16, BF16) else dtype)):
+        ta = TensorValue.from_numpy(a.T.copy() if transpose_a else a, dev, dt)
+        tb = TensorValue.from_numpy(b.T.copy() if transpose_b else b, dev, dt)
+        if transpose_a: ta = ta.transpose(0, 1)
+        if transpose_b: tb = tb.transpose(0, 1)
+        outs.append(ta.matmul(tb).numpy())
+    got, want = outs
+    if dtype in (I64, I32, I16, I8, U8):
+        assert np.array_equal(got, want), what
+    else:
+        tol = {F64: 1e-12, F32: 1e-5, F16: 1e-2, BF16: 1e-2}[dtype]
+        if dtype in (F16, BF16):
+            want = quantize(want, dtype)
+        assert normwise(got, want) <= tol, f"{what}: norm-wise error {normwise(got, want)}"
+
+
+@pytest.mark.parametrize("dtype", [F32, F64, BF16, F16, I32, I64, I16, I8, U8], ids=lambda d: DTYPE_NAMES[d])
+def test_small_and_odd_shapes(b200, ref, dtype):
+    rng = np.random.default_rng(dtype)
+    shapes = [(1, 1, 1), (1, 7, 5), (3, 1, 2), (7, 5, 3), (5, 5, 5), (16, 16, 16), (17, 33, 9), (64, 64, 64), (65, 127, 63), (128, 96, 160)]
+    for m, k, n in shapes:
+        if dtype in (F64, F32, F16, BF16):
+            a, b = quantize(rng.normal(0, 1, (m, k)), dtype), quantize(rng.normal(0, 1, (k, n)), dtype)
+        else:
+            a, b = rng.integers(0, 4, (m, k)), rng.integers(0, 4, (k, n))
+        check(b200, ref, a, b, dtype, what=f"{m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=lambda d: DTYPE_NAMES[d])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_transposed_views_as_operands(b200, ref, dtype, ta, tb):
+    """matmul backward feeds stride-swapped views: dA = G . B^T, dB = A^T . G (aixCore.hpp:2192-2207)."""
+    rng = np.random.default_rng(17)
+    for m, k, n in [(8, 4, 6), (128, 256, 64), (256, 128, 384), (130, 70, 50)]:
+        a, b = quantize(rng.normal(0, 0.5, (m, k)), dtype), quantize(rng.normal(0, 0.5, (k, n)), dtype)
+        check(b200, ref, a, b, dtype, ta, tb, what=f"{m}x{k}x{n} ta={ta} tb={tb}")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16], ids=lambda d: DTYPE_NAMES[d])
+def test_medium_sizes_against_float64(b200, dtype):
+    """Sizes the CPU device cannot finish in seconds: compare with numpy float64 on the same rounded inputs."""
+    rng = np.random.default_rng(23)
+    for m, k, n in [(512, 512, 512), (1024, 768, 640), (1000, 1000, 1000), (2048, 1024, 512)]:
+        a, b = quantize(rng.normal(0, 0.02, (m, k)), dtype), quantize(rng.normal(0, 0.02, (k, n)), dtype)
+        for ta, tb in [(False, False), (False, True), (True, False)]:
+            A = TensorValue.from_numpy(a.T.copy() if ta else a, b200, dtype)
+            B = TensorValue.from_numpy(b.T.copy() if tb else b, b200, dtype)
+            if ta: A = A.transpose(0, 1)
+            if tb: B = B.transpose(0, 1)
+            got = A.matmul(B).numpy()
+            want = a.astype(np.float64) @ b.astype(np.float64)
+            tol = 1e-5 if dtype == F32 else 1e-2
+            assert normwise(got, want) <= tol, f"{m}x{k}x{n} ta={ta} tb={tb}: {normwise(got, want)}"

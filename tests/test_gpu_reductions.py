@@ -1,0 +1,145 @@
+"""Parity of sum / max / reduceTo / maxTo with the reference's CPU device (Tests/DeviceTests.cpp:560-700, 1990-2150).
+
+Floating sums: the CPU device accumulates sequentially in the storage type, so for f32 the comparison is bounded by
+1e-5 * sum(|x|) and additionally checked against the float64 sum; for f16/bf16 the oracle is the CPU device applied
+to the same values widened to f32 (accumulate in f32, round once), because a 16-bit accumulator saturates.
+"""
+import numpy as np
+import pytest
+
+from aix_b200 import BF16, DTYPE_NAMES, F16, F32, F64, I8, I16, I32, I64, U8, TensorValue, to_storage, from_storage
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 2, 3, 5, 8, 17, 33, 64, 127, 255, 1025, 2049, 65537, 1 << 20]
+ALL_DTYPES = [F64, F32, F16, BF16, I64, I32, I16, I8, U8]
+FLOATS = [F64, F32, F16, BF16]
+
+
+def values(rng, shape, dtype):
+    if dtype in FLOATS:
+        x = rng.normal(0, 1, shape)
+        return from_storage(to_storage(x, dtype), dtype).astype(np.float64) if dtype != F64 else x
+    if dtype == U8:
+        return rng.integers(0, 255, shape)
+    return rng.integers(-100, 100, shape)
+
+
+def wide(dtype):
+    return F32 if dtype in (F16, BF16) else dtype
+
+
+def round_to(x, dtype):
+    return from_storage(to_storage(x, dtype), dtype)
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES, ids=lambda d: DTYPE_NAMES[d])
+def test_sum_and_max_of_everything(b200, ref, dtype):
+    rng = np.random.default_rng(100 + dtype)
+    for n in SIZES:
+        x = values(rng, n, dtype)
+        g = TensorValue.from_numpy(x, b200, dtype)
+        r = TensorValue.from_numpy(x, ref, wide(dtype))
+        got_sum, got_max = g.sum().numpy(), g.max().numpy()
+        want_max = r.max().numpy()
+        assert_close(got_max, round_to(want_max, dtype), dtype, f"max n={n}")
+        if dtype in FLOATS:
+            exact = np.sum(np.asarray(x, dtype=np.float64))
+            bound = {F64: 1e-12, F32: 1e-5, F16: 1e-2, BF16: 1e-2}[dtype]
+            assert abs(float(got_sum) - exact) <= bound * max(1.0, float(np.sum(np.abs(x)))), f"sum n={n}"
+            if dtype in (F16, BF16):
+                if np.isfinite(round_to(np.array([exact]), dtype)[0]):
+                    assert_close(got_sum, round_to(r.sum().numpy(), dtype), dtype, f"sum n={n}", scale=max(1.0, abs(exact)))
+        else:
+            assert_close(got_sum, r.sum().numpy(), dtype, f"sum n={n}")
+
+
+def test_sum_of_strided_views(b200, ref):
+    rng = np.random.default_rng(8)
+    x = rng.normal(0, 1, (63, 130)).astype(np.float32)
+    for dev_pair in [(b200, ref)]:
+        outs = []
+        for dev in dev_pair:
+            t = TensorValue.from_numpy(x, dev).transpose(0, 1)
+            row = t.select(0, 5)
+            outs.append((t.sum().numpy(), t.max().numpy(), row.sum().numpy(), row.max().numpy()))
+        for a, b in zip(*outs):
+            assert_close(a, b, F32, "strided", scale=float(np.abs(x).sum()))
+
+
+SHAPES = [((7, 5), 1), ((7, 5), 0), ((64, 1024), 1), ((64, 1024), 0), ((33, 2049), 1), ((1025, 40), 0), ((4, 5, 6), 1),
+          ((4, 5, 6), 0), ((4, 5, 6), 2), ((300, 8192), 1), ((4096, 96), 0), ((2, 3, 4, 5), 2)]
+
+
+@pytest.mark.parametrize("dtype", [F32, F64, BF16, F16, I32, I8, U8, I64, I16], ids=lambda d: DTYPE_NAMES[d])
+def test_reduce_to_and_max_to_along_one_dimension(b200, ref, dtype):
+    rng = np.random.default_rng(200 + dtype)
+    for shape, dim in SHAPES:
+        x = values(rng, shape, dtype)
+        g = TensorValue.from_numpy(x, b200, dtype)
+        r = TensorValue.from_numpy(x, ref, wide(dtype))
+        got_sum, got_max = g.sum(dim).numpy(), g.max(dim).numpy()
+        want_sum, want_max = r.sum(dim).numpy(), r.max(dim).numpy()
+        assert_close(got_max, round_to(want_max, dtype), dtype, f"maxTo {shape} dim {dim}")
+        scale = np.maximum(1.0, np.abs(np.asarray(x, dtype=np.float64)).sum(axis=dim)) if dtype in FLOATS else None
+        assert_close(got_sum, round_to(want_sum, dtype) if dtype in FLOATS else want_sum, dtype, f"reduceTo {shape} dim {dim}", scale=scale)
+
+
+def test_reduce_to_broadcast_shapes(b200, ref):
+    """reduceTo as the backward of broadcasting: arbitrary target shapes incl. lower rank (aixCore.hpp:2029-2036)."""
+    rng = np.random.default_rng(9)
+    cases = [((6, 4, 5), (4, 5)), ((6, 4, 5), (5,)), ((6, 4, 5), (1, 4, 1)), ((6, 4, 5), (6, 1, 5)), ((6, 4, 5), (1,)),
+             ((6, 4, 5), ()), ((128, 256), (1, 256)), ((128, 256), (256,)), ((128, 256), (128, 1))]
+    for src_shape, dst_shape in cases:
+        x = rng.normal(0, 1, src_shape).astype(np.float32)
+        outs = []
+        for dev in (b200, ref):
+            outs.append(TensorValue.from_numpy(x, dev).reduceTo(dst_shape).numpy())
+        assert_close(outs[0], outs[1], F32, f"reduceTo {src_shape} -> {dst_shape}", scale=max(1.0, float(np.abs(x).sum()) / max(1, outs[1].size)))
+
+
+def test_reduce_to_accumulates_into_destination(b200, ref):
+    """The device contract is dst += sum(src): a destination that is not zero keeps its contents."""
+    rng = np.random.default_rng(10)
+    x = rng.normal(0, 1, (50, 70)).astype(np.float32)
+    outs = []
+    for dev in (b200, ref):
+        t = TensorValue.from_numpy(x, dev)
+        dst = TensorValue.full(5.0, (1, 70), dev)
+        dev.reduceTo(t.deviceParams(), dst.deviceParams())
+        mx = TensorValue.full(0.5, (50, 1), dev)
+        dev.maxTo(t.deviceParams(), mx.deviceParams())
+        outs.append((dst.numpy(), mx.numpy()))
+    assert_close(outs[0][0], outs[1][0], F32, "reduceTo accumulate", scale=50.0)
+    assert_close(outs[0][1], outs[1][1], F32, "maxTo accumulate")
+
+
+def relu(v):
+    """relu composed from device ops, identically on every device: (v + sqrt(v*v)) * 0.5."""
+    return (v + (v * v).sqrt()) * 0.5
+
+
+def config1(dev, x, g, bias, dtype):
+    tx, tg, tb = (TensorValue.from_numpy(v, dev, dtype) for v in (x, g, bias))
+    y = relu(tx * tg + tb)
+    return y, y.sum(1), y.max(1), y.mean()
+
+
+@pytest.mark.parametrize("rows,cols", [(256, 512), (1000, 1000)])
+def test_config1_broadcast_and_reductions_bf16(b200, ref, rows, cols):
+    """y = relu(x*g + bias) in bf16; row sums, row maxima and the global mean accumulate in f32."""
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (rows, cols)).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    bias = rng.normal(0, 0.1, cols).astype(np.float32)
+    gy, gsum, gmax, gmean = config1(b200, x, g, bias, BF16)
+    ry, _, rmax, _ = config1(ref, x, g, bias, BF16)
+    y_ref = ry.numpy()
+    assert_close(gy.numpy(), y_ref, BF16, "y")
+    assert_close(gmax.numpy(), rmax.numpy(), BF16, "row max")
+    # 16-bit reductions: oracle = CPU device on the f32-widened y, rounded once to bf16
+    wide_y = TensorValue.from_numpy(y_ref, ref, F32)
+    assert_close(gsum.numpy(), round_to(wide_y.sum(1).numpy(), BF16), BF16, "row sum", scale=np.maximum(1.0, y_ref.sum(axis=1)))
+    want_mean = round_to(np.array(round_to(np.array(y_ref.astype(np.float64).sum()), BF16) / round_to(np.array(float(y_ref.size)), BF16)), BF16)
+    assert_close(gmean.numpy(), want_mean, BF16, "mean")
