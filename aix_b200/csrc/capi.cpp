@@ -48,7 +48,7 @@ void aixb200_default_config(aixb200_config* cfg)
     if (!cfg) return;
     std::memset(cfg, 0, sizeof(*cfg));
     cfg->flush_threshold = 200;
-    cfg->strict_math = 1;
+    cfg->strict_math = 0;
     cfg->fusion = 1;
     cfg->disk_cache = 1;
     cfg->tf32x3_matmul = 1;

@@ -63,14 +63,51 @@ struct Du8   { typedef unsigned char S; typedef int C; typedef unsigned U; stati
     static __device__ __forceinline__ C fix(C c) { return (int)(unsigned char)c; }
     static __device__ __forceinline__ C sat(double x) { return min(max(__double2int_rz(x), 0), 255); } };
 
+// AIX_FAST selects cheaper float routines whose error stays below 1e-6 relative (division and square root come from
+// the compiler flags --prec-div=false / --prec-sqrt=false; exp and tanh below). sin, cos, log and pow keep the
+// accurate library versions in both modes: their fast forms lose relative accuracy near zeros and near 1.
+#if AIX_FAST
+__device__ __forceinline__ float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float fast_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float fast_exp(float x) { return fast_ex2(x * 1.4426950408889634f); }
+__device__ __forceinline__ float fast_tanh(float x)
+{
+    // |x| < 0.6: x + x^3 * p(x^2), a degree-4 fit of (tanh(x) - x) / x^3 (max relative error 9e-8);
+    // otherwise 1 - 2 / (exp(2|x|) + 1) with the sign of x (saturates to +-1 for large |x|).
+    const float t = fabsf(x), u = x * x;
+    float p = -0.006276384927332401f;
+    p = fmaf(p, u, 0.021116212010383606f);
+    p = fmaf(p, u, -0.053875137120485306f);
+    p = fmaf(p, u, 0.13332924246788025f);
+    p = fmaf(p, u, -0.3333333134651184f);
+    const float small = fmaf(x * u, p, x);
+    const float e = fast_ex2(t * 2.885390081777927f);
+    const float large = copysignf(fmaf(-2.0f, fast_rcp(e + 1.0f), 1.0f), x);
+    return t < 0.6f ? small : large;
+}
+#endif
+
 __device__ __forceinline__ float  m_sqrt(float x)  { return sqrtf(x); }   __device__ __forceinline__ double m_sqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float  m_sin(float x)   { return sinf(x); }    __device__ __forceinline__ double m_sin(double x)  { return sin(x); }
 __device__ __forceinline__ float  m_cos(float x)   { return cosf(x); }    __device__ __forceinline__ double m_cos(double x)  { return cos(x); }
-__device__ __forceinline__ float  m_tanh(float x)  { return tanhf(x); }   __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
+#if AIX_FAST
+__device__ __forceinline__ float  m_tanh(float x)  { return fast_tanh(x); }
+#else
+__device__ __forceinline__ float  m_tanh(float x)  { return tanhf(x); }
+#endif   __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
 __device__ __forceinline__ float  m_log(float x)   { return logf(x); }    __device__ __forceinline__ double m_log(double x)  { return log(x); }
-__device__ __forceinline__ float  m_exp(float x)   { return expf(x); }    __device__ __forceinline__ double m_exp(double x)  { return exp(x); }
+#if AIX_FAST
+__device__ __forceinline__ float  m_exp(float x)   { return fast_exp(x); }
+#else
+__device__ __forceinline__ float  m_exp(float x)   { return expf(x); }
+#endif    __device__ __forceinline__ double m_exp(double x)  { return exp(x); }
 __device__ __forceinline__ float  m_pow(float x, float y)   { return powf(x, y); }
 __device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }
+
+// Integer pow goes through double; the reference uses long double, whose result is exact whenever the true power is
+// an integer. A last-place error of pow() must not turn 3 into 2 under truncation, so results that sit within a few
+// ulps of an integer are snapped to it.
+__device__ __forceinline__ double snap_integer(double r) { const double n = rint(r); return (fabs(r - n) <= fabs(n) * 8.9e-16) ? n : r; }
 
 #define AIX_C typename D::C
 #define AIX_U typename D::U
@@ -87,7 +124,7 @@ template <class D> __device__ __forceinline__ AIX_C op_neg(AIX_C a) { if constex
 template <class D> __device__ __forceinline__ AIX_C op_sqrt(AIX_C a) { if constexpr (D::kind == 0) return D::fix(m_sqrt(a)); else return D::sat(sqrt((double)a)); }
 template <class D> __device__ __forceinline__ AIX_C op_log(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_log(a));  else return D::sat(log((double)a)); }
 template <class D> __device__ __forceinline__ AIX_C op_exp(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_exp(a));  else return D::sat(exp((double)a)); }
-template <class D> __device__ __forceinline__ AIX_C op_pow(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(m_pow(a, b)); else return D::sat(pow((double)a, (double)b)); }
+template <class D> __device__ __forceinline__ AIX_C op_pow(AIX_C a, AIX_C b) { if constexpr (D::kind == 0) return D::fix(m_pow(a, b)); else return D::sat(snap_integer(pow((double)a, (double)b))); }
 template <class D> __device__ __forceinline__ AIX_C op_sin(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_sin(a));  else return D::fix((AIX_C)sin((double)a)); }
 template <class D> __device__ __forceinline__ AIX_C op_cos(AIX_C a)  { if constexpr (D::kind == 0) return D::fix(m_cos(a));  else return D::fix((AIX_C)cos((double)a)); }
 template <class D> __device__ __forceinline__ AIX_C op_tanh(AIX_C a) { if constexpr (D::kind == 0) return D::fix(m_tanh(a)); else return D::fix((AIX_C)tanh((double)a)); }
@@ -100,6 +137,45 @@ template <class SD, class D> __device__ __forceinline__ AIX_C op_cast(typename S
     else if constexpr (D::id == 0) return (double)x;
     else return D::fix((float)x);
 }
+
+// ---- two 16-bit floats per 32-bit register --------------------------------------------------------------------
+// add / sub / mul run on the packed half-precision pipes (one instruction for two elements). Their single rounding
+// equals the reference's "compute in float, round to the 16-bit type": the exact product of two 8- or 11-bit
+// significands fits in float, and a float sum of two such values can only be inexact when the smaller operand lies
+// entirely below the rounding position of the 16-bit result. Everything else unpacks to float, computes, and repacks
+// with one round-to-nearest-even conversion for both halves.
+template <class D> struct P2;
+template <> struct P2<Dbf16>
+{
+    static __device__ __forceinline__ unsigned splat(u16_t s) { return (unsigned)s | ((unsigned)s << 16); }
+    static __device__ __forceinline__ unsigned join(u16_t lo, u16_t hi) { return (unsigned)lo | ((unsigned)hi << 16); }
+    static __device__ __forceinline__ float lo(unsigned p) { return __uint_as_float(p << 16); }
+    static __device__ __forceinline__ float hi(unsigned p) { return __uint_as_float(p & 0xffff0000u); }
+    static __device__ __forceinline__ unsigned pack(float l, float h) { unsigned d; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(h), "f"(l)); return d; }
+    static __device__ __forceinline__ unsigned add(unsigned a, unsigned b) { unsigned d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ unsigned sub(unsigned a, unsigned b) { unsigned d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ unsigned mul(unsigned a, unsigned b) { unsigned d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+};
+template <> struct P2<Df16>
+{
+    static __device__ __forceinline__ unsigned splat(u16_t s) { return (unsigned)s | ((unsigned)s << 16); }
+    static __device__ __forceinline__ unsigned join(u16_t lo, u16_t hi) { return (unsigned)lo | ((unsigned)hi << 16); }
+    static __device__ __forceinline__ float lo(unsigned p) { return f16_to_f32((u16_t)(p & 0xffffu)); }
+    static __device__ __forceinline__ float hi(unsigned p) { return f16_to_f32((u16_t)(p >> 16)); }
+    static __device__ __forceinline__ unsigned pack(float l, float h) { unsigned d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(h), "f"(l)); return d; }
+    static __device__ __forceinline__ unsigned add(unsigned a, unsigned b) { unsigned d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ unsigned sub(unsigned a, unsigned b) { unsigned d; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ unsigned mul(unsigned a, unsigned b) { unsigned d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+};
+template <class D> __device__ __forceinline__ unsigned pp_add(unsigned a, unsigned b) { return P2<D>::add(a, b); }
+template <class D> __device__ __forceinline__ unsigned pp_sub(unsigned a, unsigned b) { return P2<D>::sub(a, b); }
+template <class D> __device__ __forceinline__ unsigned pp_mul(unsigned a, unsigned b) { return P2<D>::mul(a, b); }
+template <class D> __device__ __forceinline__ unsigned pp_neg(unsigned a) { return a ^ 0x80008000u; }
+template <class D> __device__ __forceinline__ unsigned pp_cast(unsigned a) { return a; }
+template <class D> __device__ __forceinline__ unsigned pp_div(unsigned a, unsigned b) { return P2<D>::pack(P2<D>::lo(a) / P2<D>::lo(b), P2<D>::hi(a) / P2<D>::hi(b)); }
+template <class D> __device__ __forceinline__ unsigned pp_pow(unsigned a, unsigned b) { return P2<D>::pack(m_pow(P2<D>::lo(a), P2<D>::lo(b)), m_pow(P2<D>::hi(a), P2<D>::hi(b))); }
+#define AIX_PP_UNARY(NAME) template <class D> __device__ __forceinline__ unsigned pp_##NAME(unsigned a) { return P2<D>::pack(m_##NAME(P2<D>::lo(a)), m_##NAME(P2<D>::hi(a))); }
+AIX_PP_UNARY(sqrt) AIX_PP_UNARY(sin) AIX_PP_UNARY(cos) AIX_PP_UNARY(tanh) AIX_PP_UNARY(log) AIX_PP_UNARY(exp)
 )PRELUDE";
 
 const char* kTraits[DTYPE_COUNT] = {"Df64", "Df32", "Df16", "Dbf16", "Di64", "Di32", "Di16", "Di8", "Du8"};
@@ -147,6 +223,16 @@ KernelVariant chooseVariant(const KernelSpec& spec)
         maxSpan = std::max(maxSpan, s.view.span());
     }
     v.vec = static_cast<int>(std::max<size_t>(1, std::min<size_t>(16 / minSize, 64 / maxSize)));
+    // Packed two-per-register arithmetic needs one 16-bit float type throughout the kernel.
+    {
+        int common = -1;
+        bool uniform = true;
+        auto see = [&](uint8_t dt) { if (common < 0) common = dt; else if (common != dt) uniform = false; };
+        for (auto& l : spec.loads) see(l.view.dtype);
+        for (auto& st : spec.stores) see(st.view.dtype);
+        for (auto& nd : spec.nodes) { see(nd.dtype); if (nd.op == Op::Cast) see(nd.srcDtype); }
+        v.packed16 = uniform && (common == F16 || common == BF16) && v.vec >= 2 && v.vec % 2 == 0;
+    }
     v.index64 = maxSpan >= (uint64_t(1) << 31);
     for (size_t i = 0; i < spec.loads.size(); ++i)
     {
@@ -175,7 +261,7 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
     std::string key;
     key.reserve(64 + spec.nodes.size() * 12);
     auto put = [&](unsigned x) { key += std::to_string(x); key += '.'; };
-    key += "E"; put(variant.vec); put(variant.index64); put(options.block); put(options.unroll); put(options.strictMath);
+    key += "E"; put(variant.vec); put(variant.packed16); put(variant.index64); put(options.block); put(options.unroll); put(options.strictMath);
     key += "L";
     for (size_t i = 0; i < spec.loads.size(); ++i)
     {
@@ -236,7 +322,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
     const int E = variant.vec, U = options.unroll, B = options.block;
     const size_t nL = spec.loads.size(), nS = spec.stores.size();
     std::ostringstream o;
-    o << kPrelude << "\n";
+    o << "#define AIX_FAST " << (options.strictMath ? 0 : 1) << "\n" << kPrelude << "\n";
     o << "typedef " << (variant.index64 ? "unsigned long long" : "unsigned int") << " idx_t;\n";
 
     // ---- argument slots -------------------------------------------------------------------------------------------
@@ -318,6 +404,34 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
                     break;
                 default:
                     os << "op_" << opName(nd.op) << "<" << D << ">(" << operand(nd.a, nd.dtype) << ")";
+                    break;
+            }
+            os << ";\n";
+        }
+    };
+
+    // Same body on register pairs (variant.packed16): every value is an `unsigned` holding two 16-bit floats.
+    auto emitNodesPacked = [&](std::ostream& os, const std::string& indent, auto&& in)
+    {
+        auto operand = [&](const OperandRef& r) -> std::string
+        {
+            return r.kind == OperandRef::Reg ? "v" + std::to_string(r.index) : in(r.index);
+        };
+        for (size_t k = 0; k < spec.nodes.size(); ++k)
+        {
+            const KernelNode& nd = spec.nodes[k];
+            const std::string D = T(nd.dtype);
+            os << indent << "const unsigned v" << k << " = ";
+            switch (nd.op)
+            {
+                case Op::Fill:
+                    os << "P2<" << D << ">::splat(sc" << nd.scalarIndex << ")";
+                    break;
+                case Op::Add: case Op::Sub: case Op::Mul: case Op::Div: case Op::Pow:
+                    os << "pp_" << opName(nd.op) << "<" << D << ">(" << operand(nd.a) << ", " << operand(nd.b) << ")";
+                    break;
+                default:
+                    os << "pp_" << opName(nd.op) << "<" << D << ">(" << operand(nd.a) << ")";
                     break;
             }
             os << ";\n";
@@ -425,6 +539,23 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         o << "                const idx_t q = pk + (idx_t)u * " << B << ";\n";
         for (size_t i = 0; i < nS; ++i)
             o << "                Pack<" << T(spec.stores[i].view.dtype) << "::S, " << E << "> y" << i << ";\n";
+        if (variant.packed16)
+        {
+            o << "                #pragma unroll\n                for (int e = 0; e < " << (E / 2) << "; ++e)\n                {\n";
+            emitNodesPacked(o, "                    ", [&](size_t l) -> std::string
+            {
+                const std::string P = "P2<" + T(spec.loads[l].view.dtype) + ">::";
+                if (lp[l] == Path::Scalar) return P + "splat(x" + std::to_string(l) + "s)";
+                if (lp[l] == Path::ColWide) return P + "splat(x" + std::to_string(l) + "[u])";
+                return P + "join(x" + std::to_string(l) + "[u].v[2 * e], x" + std::to_string(l) + "[u].v[2 * e + 1])";
+            });
+            for (size_t i = 0; i < nS; ++i)
+                o << "                    y" << i << ".v[2 * e] = (u16_t)(v" << spec.stores[i].node << " & 0xffffu); y" << i
+                  << ".v[2 * e + 1] = (u16_t)(v" << spec.stores[i].node << " >> 16);\n";
+            o << "                }\n";
+        }
+        else
+        {
         o << "                #pragma unroll\n                for (int e = 0; e < " << E << "; ++e)\n                {\n";
         emitNodes(o, "                    ", [&](size_t l) -> std::string
         {
@@ -435,6 +566,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         for (size_t i = 0; i < nS; ++i)
             o << "                    y" << i << ".v[e] = " << T(spec.stores[i].view.dtype) << "::st(" << "v" << spec.stores[i].node << ");\n";
         o << "                }\n";
+        }
         for (size_t i = 0; i < nS; ++i)
         {
             const std::string S = T(spec.stores[i].view.dtype) + "::S";

@@ -27,6 +27,7 @@ struct CodegenOptions
 struct KernelVariant
 {
     int      vec = 1;          // elements per pack (16 bytes of the narrowest element type)
+    bool     packed16 = false; // one f16/bf16 type throughout: two elements per register on the packed pipes
     bool     index64 = false;  // element count does not fit 32 bits
     uint32_t fastLoads = 0;    // bit l: load l may use the wide / hoisted path
     uint32_t fastStores = 0;   // bit s: store s may use 128-bit stores

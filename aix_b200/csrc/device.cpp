@@ -399,7 +399,7 @@ std::vector<char> Device::compile(const std::string& source, const std::string& 
 {
     std::vector<const char*> options = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device"};
     if (m_codegen.strictMath) { options.push_back("--fmad=false"); options.push_back("--prec-div=true"); options.push_back("--prec-sqrt=true"); }
-    else options.push_back("--fmad=true");
+    else { options.push_back("--fmad=true"); options.push_back("--prec-div=false"); options.push_back("--prec-sqrt=false"); }
 
     std::string cachePath;
     if (!m_cacheDir.empty())

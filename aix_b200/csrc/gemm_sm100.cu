@@ -57,6 +57,8 @@ struct KernelParams
     uint32_t outDtype;          // F32, F16, BF16
     uint32_t kPhases;           // 1, or 3 for the split-f32 scheme
     uint32_t kPerPhase;         // K of the original problem (elements) when kPhases == 3
+    uint32_t chunkBlocks;       // k-blocks folded inside TMEM before the partial result is added to C in f32
+    uint32_t chunks;            // number of such partial results per tile (1: plain store)
     uint32_t vectorStores;      // C rows are 16-byte aligned
     void*    c;
     uint32_t* errorWord;
@@ -214,7 +216,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
     fenceAfterSync();
     const uint32_t tmemBase = s.tmemBase;
     const uint32_t totalTiles = p.tilesM * p.tilesN;
-    const uint32_t kIters = p.kBlocks * p.kPhases;
 
     if (warp == 0)
     {
@@ -227,12 +228,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 uint32_t tm, tn;
                 tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
                 const int32_t m0 = static_cast<int32_t>(tm * kBlockM), n0 = static_cast<int32_t>(tn * kBlockN);
-                for (uint32_t it = 0; it < kIters; ++it)
+                for (uint32_t c = 0; c < p.chunks && ok; ++c)
+                {
+                const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
+                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
                 {
                     if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
                     mbarExpectTx(&s.full[stage], p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes);
-                    // Split-f32: K is laid out as [hi | lo] per operand; the three passes read (hi,hi), (lo,hi), (hi,lo).
-                    const uint32_t pass = it / p.kBlocks, kb = it - pass * p.kBlocks;
+                    // Split-f32: K is laid out as [hi | lo] per operand. Per chunk the two small products (lo.hi, hi.lo)
+                    // go first, while the accumulator is still tiny, then hi.hi.
+                    const uint32_t passIndex = it / kbCount, kb = kbBegin + (it - passIndex * kbCount);
+                    const uint32_t pass = p.kPhases == 3 ? (passIndex + 1) % 3 : 0;
                     const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
                     const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
                     for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
@@ -247,6 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
+                }
             }
         }
     }
@@ -257,11 +264,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
+            for (uint32_t c = 0; c < p.chunks && ok; ++c)
             {
                 if (!mbarWait(&s.tmemEmpty[acc], accPhase ^ 1u, abortFlag)) { ok = false; break; }
                 fenceAfterSync();
                 const uint32_t tmemD = tmemBase + acc * kBlockN;
-                for (uint32_t it = 0; it < kIters; ++it)
+                const uint32_t kbCount = min(p.kBlocks - c * p.chunkBlocks, p.chunkBlocks);
+                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
@@ -291,6 +300,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
         {
             uint32_t tm, tn;
             tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+            for (uint32_t c = 0; c < p.chunks && ok; ++c)
+            {
             if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
             fenceAfterSync();
             const uint32_t row = tm * kBlockM + quarter * 32 + lane;
@@ -308,15 +319,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                     if (p.outDtype == F32)
                     {
                         float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
+                        // Partial results after the first are added to C with IEEE f32 additions: the tensor core's own
+                        // accumulation truncates, and that bias grows with the number of MMAs folded into one accumulator.
                         if (fullRow && p.vectorStores)
                         {
                             #pragma unroll
                             for (int v = 0; v < 8; ++v)
-                                reinterpret_cast<uint4*>(out)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                            {
+                                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                                if (c > 0)
+                                {
+                                    const float4 old = reinterpret_cast<const float4*>(out)[v];
+                                    x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                                }
+                                reinterpret_cast<float4*>(out)[v] = x;
+                            }
                         }
                         else
                         {
-                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]);
+                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]) + (c > 0 ? out[e] : 0.f);
                         }
                     }
                     else
@@ -349,6 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             mbarArrive(&s.tmemEmpty[acc]);
             acc ^= 1u;
             if (acc == 0) accPhase ^= 1u;
+            }
         }
     }
 
@@ -483,6 +505,8 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.blockK = 64;
         p.kBlocks = (p.k + 63) / 64;
         p.kPhases = 1;
+        p.chunkBlocks = p.kBlocks;
+        p.chunks = 1;
         p.mmasPerStage = 4;
         const CUtensorMapDataType type = q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         p.aMnMajor = a.mnMajor; p.bMnMajor = b.mnMajor;
@@ -526,6 +550,8 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.kBlocks = kPad / 32;
         p.kPhases = 3;
         p.kPerPhase = kPad;
+        p.chunkBlocks = 8;                                   // 256 elements of K per in-TMEM partial sum
+        p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
         p.mmasPerStage = 4;
         p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
         p.bBoxes = 1; p.bBoxBytes = kStageBytesB; p.kAdvanceB = 32;

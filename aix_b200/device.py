@@ -19,21 +19,24 @@ NUMPY_STORAGE = [np.float64, np.float32, np.float16, np.uint16, np.int64, np.int
 
 def float32_to_bfloat16_bits(x: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even f32 -> bf16 bit patterns, NaN kept NaN (aixFloat16.hpp:775-805)."""
-    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    x = np.asarray(x, dtype=np.float32)
+    bits = np.ascontiguousarray(x).reshape(x.shape).view(np.uint32)
     nan = (bits & 0x7F800000 == 0x7F800000) & (bits & 0x007FFFFF != 0)
     rounded = (bits + (0x7FFF + ((bits >> 16) & 1))) >> 16
     return np.where(nan, (bits >> 16) | 0x0040, rounded).astype(np.uint16)
 
 
 def bfloat16_bits_to_float32(b: np.ndarray) -> np.ndarray:
-    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+    b = np.asarray(b, dtype=np.uint16)
+    return (np.ascontiguousarray(b).reshape(b.shape).astype(np.uint32) << 16).view(np.float32)
 
 
 def to_storage(values: np.ndarray, dtype: int) -> np.ndarray:
     """Converts an array of ordinary numpy numbers into the storage representation of `dtype`."""
     if dtype == C.BF16:
         return float32_to_bfloat16_bits(np.asarray(values, dtype=np.float32))
-    return np.ascontiguousarray(values, dtype=NUMPY_STORAGE[dtype])
+    values = np.asarray(values)
+    return np.ascontiguousarray(values, dtype=NUMPY_STORAGE[dtype]).reshape(values.shape)
 
 
 def from_storage(raw: np.ndarray, dtype: int) -> np.ndarray:

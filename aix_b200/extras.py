@@ -9,21 +9,23 @@ from .tensor import TensorValue
 
 
 def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
+    """Device time of one call of fn: `iters` calls are queued back to back behind a few L2-flush kernels, so that the
+    host is ahead of the GPU and the interval between the two events holds kernel time only. The working sets used
+    here (>= 128 MiB per call) do not fit the L2 together with the next call's."""
     for _ in range(warmup):
         fn()
     dev.synchronize()
     e0, e1 = dev.createEvent(), dev.createEvent()
-    times = []
+    for _ in range(3 if flush_l2 else 1):
+        dev.flushL2()
+    dev.recordEvent(e0)
     for _ in range(iters):
-        if flush_l2:
-            dev.flushL2()
-        dev.recordEvent(e0)
         fn()
-        dev.recordEvent(e1)
-        times.append(dev.elapsedMs(e0, e1))
+    dev.recordEvent(e1)
+    ms = dev.elapsedMs(e0, e1) / iters
     dev.destroyEvent(e0)
     dev.destroyEvent(e1)
-    return float(np.median(times)), float(np.min(times))
+    return float(ms), float(ms)
 
 
 def relu(v):

@@ -80,7 +80,10 @@ typedef struct aixb200_config
     int32_t  managed_memory;     /* 1: allocations are host-dereferenceable CUDA managed memory (what the C++
                                     aix::Device adapter needs, aixCore.hpp:435-440,491-499); 0: plain device memory */
     uint32_t flush_threshold;    /* pending elementwise ops before the planner runs (reference: 200, aixDeviceMetal.cpp:129) */
-    int32_t  strict_math;        /* 1: no FMA contraction, IEEE div/sqrt, per-op rounding of f16/bf16 */
+    int32_t  strict_math;        /* 1: no FMA contraction, IEEE division and square root, library expf/tanhf.
+                                    0 (default): contraction allowed, 2-ulp division/sqrt, exp and tanh from hardware
+                                    exp2/reciprocal; every f32 result stays within 1e-6 relative of the strict one.
+                                    f16/bf16 values are rounded after every op in both modes. */
     int32_t  fusion;             /* 0 disables fusion: every recorded op becomes its own kernel */
     int32_t  disk_cache;         /* 1: keep compiled cubins in $AIXB200_CACHE_DIR (default ~/.cache/aixb200) */
     uint64_t cache_limit_bytes;  /* idle blocks kept by the allocator before it trims (0 = 3/4 of device memory) */
