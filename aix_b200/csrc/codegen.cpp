@@ -94,13 +94,15 @@ __device__ __forceinline__ float  m_cos(float x)   { return cosf(x); }    __devi
 __device__ __forceinline__ float  m_tanh(float x)  { return fast_tanh(x); }
 #else
 __device__ __forceinline__ float  m_tanh(float x)  { return tanhf(x); }
-#endif   __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
+#endif
+__device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
 __device__ __forceinline__ float  m_log(float x)   { return logf(x); }    __device__ __forceinline__ double m_log(double x)  { return log(x); }
 #if AIX_FAST
 __device__ __forceinline__ float  m_exp(float x)   { return fast_exp(x); }
 #else
 __device__ __forceinline__ float  m_exp(float x)   { return expf(x); }
-#endif    __device__ __forceinline__ double m_exp(double x)  { return exp(x); }
+#endif
+__device__ __forceinline__ double m_exp(double x)  { return exp(x); }
 __device__ __forceinline__ float  m_pow(float x, float y)   { return powf(x, y); }
 __device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }
 

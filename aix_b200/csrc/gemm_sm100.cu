@@ -310,9 +310,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32)
             {
                 uint32_t r[32];
+                const uint32_t col = tn * kBlockN + c0;
+                // Later partial results are added to what C already holds: fetch that first so the global loads and the
+                // TMEM load are in flight together.
+                float4 old[8];
+                const bool fastF32 = p.outDtype == F32 && p.vectorStores && row < p.m && col + 32 <= p.n;
+                if (fastF32 && c > 0)
+                {
+                    const float4* in = reinterpret_cast<const float4*>(static_cast<const float*>(p.c) + static_cast<size_t>(row) * p.n + col);
+                    #pragma unroll
+                    for (int v = 0; v < 8; ++v) old[v] = in[v];
+                }
                 tmemLoad32(taddr + c0, r);
                 tmemLoadWait();
-                const uint32_t col = tn * kBlockN + c0;
                 if (row < p.m && col < p.n)
                 {
                     const bool fullRow = col + 32 <= p.n;
@@ -327,11 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                             for (int v = 0; v < 8; ++v)
                             {
                                 float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                                if (c > 0)
-                                {
-                                    const float4 old = reinterpret_cast<const float4*>(out)[v];
-                                    x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
-                                }
+                                if (c > 0) { x.x += old[v].x; x.y += old[v].y; x.z += old[v].z; x.w += old[v].w; }
                                 reinterpret_cast<float4*>(out)[v] = x;
                             }
                         }
@@ -550,7 +556,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.kBlocks = kPad / 32;
         p.kPhases = 3;
         p.kPerPhase = kPad;
-        p.chunkBlocks = 8;                                   // 256 elements of K per in-TMEM partial sum
+        p.chunkBlocks = 16;                                  // 512 elements of K per in-TMEM partial sum
         p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
         p.mmasPerStage = 4;
         p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;

@@ -24,7 +24,7 @@ constexpr size_t kMaxReduceBlocks     = 4096;       // upper bound of partials a
 // ---- full reductions (Device::sum / Device::max, aixDevice.hpp:52,60) -----------------------------------------
 // dst[0] = sum or max of all elements of src, in src's element type.
 void reduceAll(const LaunchContext& ctx, bool isMax, const View& src, void* dst);
-// Same kernel with caller-provided scratch (partials + ticket counter); used by the allocation-free entry point.
+// Same kernel with caller-provided scratch (partials + ticket counter).
 void reduceAllWithScratch(const LaunchContext& ctx, bool isMax, const View& src, void* dst, void* scratch, size_t scratchBytes);
 
 // ---- partial reductions (Device::reduceTo / maxTo, aixDevice.hpp:70-71) ----------------------------------------

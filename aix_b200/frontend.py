@@ -1,0 +1,295 @@
+"""Host-side mirror of the callers of the device on the training path: aix::Tensor with autograd, nn::Linear / Tanh /
+Sequential / MSELoss and optim::Adam / SGD.
+
+Only what the MLP training configuration needs is mirrored, and it is mirrored literally: every method issues the
+device calls of the reference method it cites, in the same order, so that a training step drives the device with
+the op stream of the reference front end (4 Linear layers: 17 forward ops, 8 zero-fills, 39 backward ops, 22 ops per
+parameter in Adam). Nothing here computes; all arithmetic happens in device calls.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from . import _capi as C
+from .tensor import _TO_FLOAT, TensorValue, promote
+
+
+class TensorNode:
+    """aix::TensorNode (aixCore.hpp:1790-1857)."""
+
+    def __init__(self, value: TensorValue, requireGrad: bool = False):
+        self.value = value
+        self.requireGrad = requireGrad
+        self.retainGrad = False
+        self.isLeaf = True
+        self.inputs: List["TensorNode"] = []
+        self.backwardFunc: Callable = defaultBackward
+        self._grad: Optional[TensorValue] = None
+
+    def grad(self) -> TensorValue:
+        if self._grad is None:
+            self._grad = TensorValue.empty(self.value.shape, self.value.device, self.value.dtype)
+            self._grad.fill(0)
+        return self._grad
+
+    def backward(self, seed: TensorValue):
+        if self.retainGrad:
+            g = self.grad()
+            g += seed
+        if self.requireGrad or self.retainGrad:
+            self.backwardFunc(self, seed)
+
+    def setBackward(self, inputs, func):
+        if self.requireGrad or self.retainGrad:
+            self.inputs = list(inputs)
+            self.backwardFunc = func
+
+
+def _wants(node: TensorNode) -> bool:
+    return node.requireGrad or node.retainGrad
+
+
+# ---- backward functions (aixCore.hpp:2014-2247) ---------------------------------------------------------------------
+def defaultBackward(node: TensorNode, seed: TensorValue):
+    if node.requireGrad and not node.retainGrad:
+        g = node.grad()
+        g += seed                                  # in-place Device::add into the gradient buffer
+
+
+def broadcastBackwardFunc(node, seed):
+    if node.inputs:
+        node.inputs[0].backward(seed.reduceTo(node.inputs[0].value.shape))
+
+
+def addBackwardFunc(node, seed):
+    if len(node.inputs) < 2: return
+    if node.inputs[0] is node.inputs[1]:
+        node.inputs[0].backward(seed + seed)
+        return
+    if _wants(node.inputs[0]): node.inputs[0].backward(seed)
+    if _wants(node.inputs[1]): node.inputs[1].backward(seed)
+
+
+def subBackwardFunc(node, seed):
+    if len(node.inputs) < 2 or node.inputs[0] is node.inputs[1]: return
+    if _wants(node.inputs[0]): node.inputs[0].backward(seed)
+    if _wants(node.inputs[1]): node.inputs[1].backward(-seed)
+
+
+def mulBackwardFunc(node, seed):
+    if len(node.inputs) < 2: return
+    if node.inputs[0] is node.inputs[1]:
+        grad = node.inputs[0].value * seed
+        node.inputs[0].backward(grad + grad)
+        return
+    if _wants(node.inputs[0]): node.inputs[0].backward(node.inputs[1].value * seed)
+    if _wants(node.inputs[1]): node.inputs[1].backward(node.inputs[0].value * seed)
+
+
+def divBackwardFunc(node, seed):
+    if len(node.inputs) < 2: return
+    if _wants(node.inputs[0]): node.inputs[0].backward(seed / node.inputs[1].value)
+    if _wants(node.inputs[1]):
+        b = node.inputs[1].value
+        node.inputs[1].backward(-node.inputs[0].value * seed / (b * b))
+
+
+def unaryBackwardFunc(node, seed):
+    if node.inputs: node.inputs[0].backward(-seed)
+
+
+def tanhBackwardFunc(node, seed):
+    if node.inputs:
+        t = node.value
+        node.inputs[0].backward((1.0 - t * t) * seed)
+
+
+def matmulBackwardFunc(node, seed):
+    if len(node.inputs) < 2: return
+    a, b = node.inputs
+    if a is b:
+        xT = a.value.transpose(0, 1)
+        a.backward(seed.matmul(xT) + xT.matmul(seed))
+        return
+    if _wants(a): a.backward(seed.matmul(b.value.transpose(0, 1)))
+    if _wants(b): b.backward(a.value.transpose(0, 1).matmul(seed))
+
+
+def sumBackwardFunc(node, seed):
+    if node.inputs: node.inputs[0].backward(seed.broadcastTo(node.inputs[0].value.shape))
+
+
+class Tensor:
+    """aix::Tensor (aixCore.hpp:1879-2893), the subset on the MLP training path."""
+
+    def __init__(self, value: TensorValue, requireGrad: bool = False):
+        self.node = TensorNode(value, requireGrad)
+
+    @staticmethod
+    def _result(value: TensorValue, anyRequiresGrad: bool, anyNonLeaf: bool = False) -> "Tensor":
+        t = Tensor(value, anyRequiresGrad)           # makeResult (aixCore.hpp:2788-2796)
+        t.node.isLeaf = not anyRequiresGrad and not anyNonLeaf
+        return t
+
+    # accessors
+    @property
+    def value(self) -> TensorValue: return self.node.value
+    @property
+    def shape(self): return self.node.value.shape
+    @property
+    def dtype(self): return self.node.value.dtype
+    @property
+    def device(self): return self.node.value.device
+    def grad(self) -> TensorValue: return self.node.grad()
+    def isRequireGrad(self) -> bool: return self.node.requireGrad
+    def zeroGrad(self): self.node.grad().fill(0)
+
+    def backward(self):
+        """aixCore.hpp:1921-1931: seed of ones in the tensor's own shape."""
+        v = self.node.value
+        seed = TensorValue.full(1, v.shape, v.device, v.dtype)
+        self.node.backward(seed)
+
+    # views / conversions
+    def broadcastTo(self, shape) -> "Tensor":
+        if tuple(shape) == tuple(self.shape): return self
+        r = Tensor._result(self.value.broadcastTo(shape), self.isRequireGrad())
+        r.node.setBackward([self.node], broadcastBackwardFunc)
+        return r
+
+    def _binary(self, other, op: str, backward) -> "Tensor":
+        if not isinstance(other, Tensor):
+            one = TensorValue.full(float(other), (), self.device, _TO_FLOAT[self.dtype])
+            other = Tensor(one).broadcastTo(self.shape)         # aixCore.hpp:2384-2406
+        dtype = promote(self.dtype, other.dtype)
+        shape = self.shape if tuple(self.shape) == tuple(other.shape) else tuple(np.broadcast_shapes(self.shape, other.shape))
+        lhs, rhs = self.broadcastTo(shape), other.broadcastTo(shape)
+        assert lhs.dtype == dtype and rhs.dtype == dtype, "mixed element types are not on the mirrored path"
+        value = getattr(lhs.value, op)(rhs.value)
+        r = Tensor._result(value, self.isRequireGrad() or other.isRequireGrad(), not lhs.node.isLeaf or not rhs.node.isLeaf)
+        r.node.setBackward([lhs.node, rhs.node], backward)
+        return r
+
+    def __add__(self, o): return self._binary(o, "__add__", addBackwardFunc)
+    def __sub__(self, o): return self._binary(o, "__sub__", subBackwardFunc)
+    def __mul__(self, o): return self._binary(o, "__mul__", mulBackwardFunc)
+    def __truediv__(self, o): return self._binary(o, "__truediv__", divBackwardFunc)
+
+    def __neg__(self) -> "Tensor":
+        r = Tensor._result(-self.value, self.isRequireGrad())
+        r.node.setBackward([self.node], unaryBackwardFunc)
+        return r
+
+    def tanh(self) -> "Tensor":
+        r = Tensor._result(self.value.tanh(), self.isRequireGrad())
+        r.node.setBackward([self.node], tanhBackwardFunc)
+        return r
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        r = Tensor._result(self.value.matmul(other.value), self.isRequireGrad() or other.isRequireGrad(),
+                           not self.node.isLeaf or not other.node.isLeaf)
+        r.node.setBackward([self.node, other.node], matmulBackwardFunc)
+        return r
+
+    def sum(self) -> "Tensor":
+        r = Tensor._result(self.value.sum(), self.isRequireGrad())
+        r.node.setBackward([self.node], sumBackwardFunc)
+        return r
+
+    def mean(self) -> "Tensor":
+        return self.sum() / float(self.value.size)             # aixCore.hpp:2498-2501
+
+
+# ---- nn (aixNeuralNetwork.hpp) ---------------------------------------------------------------------------------------
+class Linear:
+    """nn::Linear (aixNeuralNetwork.hpp:132-157): W is {in, out}, b is {1, out}, forward = matmul(x, W) + b."""
+
+    def __init__(self, weight: np.ndarray, bias: np.ndarray, device, dtype: int = C.F32):
+        self.w = Tensor(TensorValue.from_numpy(weight, device, dtype), requireGrad=True)
+        self.b = Tensor(TensorValue.from_numpy(bias.reshape(1, -1), device, dtype), requireGrad=True)
+
+    def parameters(self): return [self.w, self.b]
+    def forward(self, x: Tensor) -> Tensor: return x.matmul(self.w) + self.b
+
+
+class Tanh:
+    def parameters(self): return []
+    def forward(self, x: Tensor) -> Tensor: return x.tanh()
+
+
+class Sequential:
+    def __init__(self, *modules): self.modules = list(modules)
+    def parameters(self): return [p for m in self.modules for p in m.parameters()]
+
+    def forward(self, x: Tensor) -> Tensor:
+        for m in self.modules:
+            x = m.forward(x)
+        return x
+
+
+class MSELoss:
+    """nn::MSELoss (aixNeuralNetwork.hpp:222-231): mean(diff * diff)."""
+
+    def __call__(self, predictions: Tensor, targets: Tensor) -> Tensor:
+        diff = predictions - targets
+        return (diff * diff).mean()
+
+
+# ---- optim (aixOptimizer.hpp) ------------------------------------------------------------------------------------------
+class SGD:
+    def __init__(self, parameters: Sequence[Tensor], lr: float = 0.01):
+        self.parameters, self.lr = list(parameters), lr
+
+    def zeroGrad(self):
+        for p in self.parameters: p.zeroGrad()
+
+    def step(self):                                  # aixOptimizer.hpp:76-86
+        for p in self.parameters:
+            if p.isRequireGrad():
+                v = p.value
+                v -= p.grad() * self.lr
+
+
+class Adam:
+    """optim::Adam (aixOptimizer.hpp:93-159); state tensors live on the parameters' device."""
+
+    def __init__(self, parameters: Sequence[Tensor], lr=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8):
+        self.parameters = list(parameters)
+        self.lr, self.beta1, self.beta2, self.epsilon = lr, beta1, beta2, epsilon
+        self.timestep = 0
+        self.m = [TensorValue.full(0.0, p.shape, p.device, C.F32) for p in self.parameters]
+        self.v = [TensorValue.full(0.0, p.shape, p.device, C.F32) for p in self.parameters]
+
+    def zeroGrad(self):
+        for p in self.parameters: p.zeroGrad()
+
+    def step(self):
+        self.timestep += 1
+        # The reference's members are floats and its expressions are evaluated in double, then narrowed:
+        # float(1.0 - m_beta1), float(1.0 - std::pow(m_beta1, m_timestep)) (aixOptimizer.hpp:124-133).
+        b1, b2 = float(np.float32(self.beta1)), float(np.float32(self.beta2))
+        narrow = lambda x: float(np.float32(x))
+        for i, p in enumerate(self.parameters):
+            if not p.isRequireGrad():
+                continue
+            g = p.grad().to(C.F32)
+            self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
+            self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
+            mHat = self.m[i] / narrow(1.0 - math.pow(b1, self.timestep))
+            vHat = self.v[i] / narrow(1.0 - math.pow(b2, self.timestep))
+            value = p.value
+            value -= (self.lr * mHat / (vHat.sqrt() + self.epsilon)).to(p.dtype)
+
+
+def all_reduce_gradients(device, parameters: Sequence[Tensor], world_size: int):
+    """Data-parallel exchange between backward() and step(): sums every gradient over the ranks and divides by the
+    number of ranks, so that each rank holds the gradient of the mean loss over the global batch. The reference has no
+    such hook; gradients are plain tensor values reachable through Tensor::grad() (aixCore.hpp:1946-1956)."""
+    if world_size <= 1:
+        return
+    for p in parameters:
+        g = p.grad()
+        device.allReduce(g.storage.data, g.size, g.dtype, 1.0 / world_size)

@@ -1,0 +1,66 @@
+"""The MLP training configuration: 4 Linear layers 1024 -> 4096 -> 4096 -> 4096 -> 1024 with tanh between them,
+float32, Xavier-uniform weights, MSE loss, Adam(1e-3, 0.9, 0.999); one step = forward + backward + (gradient
+all-reduce over the ranks) + optimizer step, issued through the mirrored front end (aix_b200/frontend.py)."""
+import numpy as np
+
+from . import _capi as C
+from .frontend import Adam, Linear, MSELoss, Sequential, Tanh, Tensor, all_reduce_gradients
+from .tensor import TensorValue
+
+DEFAULT_DIMS = (1024, 4096, 4096, 4096, 1024)
+
+
+def xavier_parameters(dims, seed=0):
+    """U(-sqrt(6/(in+out)), +sqrt(6/(in+out))) weights and zero biases, identical on every rank."""
+    rng = np.random.default_rng(seed)
+    weights, biases = [], []
+    for fan_in, fan_out in zip(dims[:-1], dims[1:]):
+        bound = np.sqrt(6.0 / (fan_in + fan_out))
+        weights.append(rng.uniform(-bound, bound, (fan_in, fan_out)).astype(np.float32))
+        biases.append(np.zeros((1, fan_out), dtype=np.float32))
+    return weights, biases
+
+
+def synthetic_batch(dims, batch, rank=0, seed=0):
+    """Inputs and targets ~ N(0,1); rank r draws from the seed-0 stream offset by r."""
+    rng = np.random.default_rng([seed, rank])
+    x = rng.normal(0, 1, (batch, dims[0])).astype(np.float32)
+    y = rng.normal(0, 1, (batch, dims[-1])).astype(np.float32)
+    return x, y
+
+
+class MlpTrainer:
+    def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None):
+        self.device, self.dims, self.world_size = device, tuple(dims), world_size
+        if weights is None:
+            weights, biases = xavier_parameters(dims, seed)
+        layers = []
+        for i, (w, b) in enumerate(zip(weights, biases)):
+            layers.append(Linear(w, b, device))
+            if i + 1 < len(weights):
+                layers.append(Tanh())
+        self.model = Sequential(*layers)
+        x, y = synthetic_batch(dims, batch, rank, seed)
+        self.x = Tensor(TensorValue.from_numpy(x, device))
+        self.y = Tensor(TensorValue.from_numpy(y, device))
+        self.optimizer = Adam(self.model.parameters(), lr=lr)      # created after the parameters live on the device
+        self.loss_fn = MSELoss()
+        self.flops_per_step = 2.0 * batch * sum(a * b for a, b in zip(dims[:-1], dims[1:])) * 3 \
+            - 2.0 * batch * dims[0] * dims[1]                        # forward + dW + dX (no dX for the first layer)
+
+    def set_batch(self, x_ptr, y_ptr):
+        """Copies a new batch from (pinned) host memory into the resident input tensors."""
+        self.device.copy(x_ptr, C.F32, self.x.value.storage.data, C.F32, self.x.value.size)
+        self.device.copy(y_ptr, C.F32, self.y.value.storage.data, C.F32, self.y.value.size)
+
+    def step(self) -> Tensor:
+        pred = self.model.forward(self.x)
+        loss = self.loss_fn(pred, self.y)
+        self.optimizer.zeroGrad()
+        loss.backward()
+        all_reduce_gradients(self.device, self.model.parameters(), self.world_size)
+        self.optimizer.step()
+        return loss
+
+    def parameters_numpy(self):
+        return [p.value.numpy() for p in self.model.parameters()]
