@@ -37,6 +37,32 @@ def build(force: bool = False) -> str | None:
     return OUT
 
 
+ADAPTER_OUT = os.path.join(OUT_DIR, "adapter_check")
+
+
+def build_adapter_check(force: bool = False) -> str | None:
+    """Builds the drop-in check: the reference's unmodified front end + aix_b200/adapter/aixDeviceB200.hpp, linked
+    against libaixb200.so. Needs the reference headers, hence lives with the oracle artefacts."""
+    if not reference_available():
+        return ADAPTER_OUT if os.path.isfile(ADAPTER_OUT) else None
+    root = os.path.join(HERE, "..")
+    adapter_dir = os.path.join(root, "aix_b200", "adapter")
+    lib_dir = os.path.join(root, "aix_b200", "lib")
+    src = os.path.join(adapter_dir, "adapter_check.cpp")
+    deps = [src, os.path.join(adapter_dir, "aixDeviceB200.hpp"), os.path.join(root, "include", "aixb200.h")]
+    if not os.path.isfile(os.path.join(lib_dir, "libaixb200.so")):
+        return None
+    if not force and os.path.isfile(ADAPTER_OUT) and all(os.path.getmtime(ADAPTER_OUT) >= os.path.getmtime(d) for d in deps):
+        return ADAPTER_OUT
+    os.makedirs(OUT_DIR, exist_ok=True)
+    cmd = ["g++", "-std=c++20", "-O2", "-w", "-I", LIB_DIR, "-I", os.path.join(root, "include"), "-I", adapter_dir, src]
+    cmd += [os.path.join(LIB_DIR, s) for s in REF_SOURCES]
+    cmd += ["-L", lib_dir, "-laixb200", "-Wl,-rpath,$ORIGIN/../../aix_b200/lib", "-o", ADAPTER_OUT]
+    subprocess.run(cmd, check=True)
+    return ADAPTER_OUT
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv)
     print(path if path else "reference sources not found; nothing built")
+    print(build_adapter_check(force="--force" in sys.argv))
