@@ -101,7 +101,7 @@ SIGNATURES = {
 }
 for _name in ("add", "sub", "mul", "div", "pow"):
     SIGNATURES["aixb200_" + _name] = ([_D, _T, _T, _T], ctypes.c_int)
-for _name in ("unary", "sqrt", "sin", "cos", "tanh", "log", "exp", "sum", "max", "argmax", "argmax_indices",
+for _name in ("unary", "sqrt", "sin", "cos", "tanh", "log", "exp", "sum", "sum_static_scratch", "max", "argmax", "argmax_indices",
               "reduce_to", "max_to", "contiguous"):
     SIGNATURES["aixb200_" + _name] = ([_D, _T, _T], ctypes.c_int)
 

@@ -136,6 +136,8 @@ int aixb200_fill(aixb200_device* dev, const void* scalar, uint32_t scalarDtype, 
 int aixb200_fill_min(aixb200_device* dev, const aixb200_tensor* r) { return guarded(dev, [&](Device& d) { d.recordFillMin(r); }); }
 
 int aixb200_sum(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* r) { return guarded(dev, [&](Device& d) { d.sum(a, r); }); }
+int aixb200_sum_static_scratch(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* r)
+{ return guarded(dev, [&](Device& d) { d.sumStaticScratch(a, r); }); }
 int aixb200_max(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* r) { return guarded(dev, [&](Device& d) { d.max(a, r); }); }
 int aixb200_argmax(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* r) { return guarded(dev, [&](Device& d) { d.argmax(a, r); }); }
 int aixb200_argmax_indices(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* r)

@@ -529,6 +529,30 @@ void Device::sum(const aixb200_tensor* a, const aixb200_tensor* r)
     AIXB200_DONE("sum");
 }
 
+// Sum for callers that must not allocate: no staging of host inputs, no flush of recorded work (a flush may
+// compile and load a kernel), scratch in the library's static device array.
+void Device::sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r)
+{
+    if (dryRun()) failInvalid("sum_static_scratch needs a GPU");
+    if (!m_pending.empty() || !m_deferredFrees.empty())
+        failInvalid("sum_static_scratch: recorded work is pending; call aixb200_synchronize() first (flushing here could allocate)");
+    View src = makeView(a, "sum_static_scratch");
+    View dst = makeView(r, "sum_static_scratch");
+    if (src.dtype != dst.dtype) failInvalid("sum_static_scratch: result must have the element type of the input");
+    if (dst.size != 1) failInvalid("sum_static_scratch: result must have one element");
+    if (src.size > kernels::kStaticScratchMaxElements)
+        failInvalid("sum_static_scratch: input has " + std::to_string(src.size) + " elements, the static scratch variant takes at most " +
+                    std::to_string(kernels::kStaticScratchMaxElements));
+    if (src.size == 0) failInvalid("sum_static_scratch: empty input");
+    if ((!m_allocator->findBlock(src.base) && isHostPointer(src.base)) || (!m_allocator->findBlock(dst.base) && isHostPointer(dst.base)))
+        failInvalid("sum_static_scratch: input and result must be device memory (host inputs would need a staging allocation)");
+    AIXB200_CTX();
+    const char* error = kernels::sumWithStaticScratch(ctx, m_cfg.ordinal, src, dst.firstByte());
+    m_stats.static_kernel_launches += launched_;
+    m_stats.total_kernel_launches += launched_;
+    if (error) failRuntime(std::string("sum_static_scratch: ") + error);
+}
+
 void Device::max(const aixb200_tensor* a, const aixb200_tensor* r)
 {
     View src = inputView(a, "max");

@@ -61,6 +61,7 @@ public:
     // immediate ops (flush first, then launch fixed kernels)
     void sum(const aixb200_tensor* a, const aixb200_tensor* r);
     void max(const aixb200_tensor* a, const aixb200_tensor* r);
+    void sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r);
     void argmax(const aixb200_tensor* a, const aixb200_tensor* r);
     void argmaxIndices(const aixb200_tensor* a, const aixb200_tensor* r);
     void reduceTo(const aixb200_tensor* src, const aixb200_tensor* dst, bool isMax);

@@ -26,6 +26,11 @@ constexpr size_t kMaxReduceBlocks     = 4096;       // upper bound of partials a
 void reduceAll(const LaunchContext& ctx, bool isMax, const View& src, void* dst);
 // Same kernel with caller-provided scratch (partials + ticket counter).
 void reduceAllWithScratch(const LaunchContext& ctx, bool isMax, const View& src, void* dst, void* scratch, size_t scratchBytes);
+// Sum with the scratch in a static __device__ array of the library (no allocation anywhere on the path).
+// Inputs above kStaticScratchMaxElements are refused by the caller. Returns a CUDA error string or nullptr.
+constexpr uint64_t kStaticScratchMaxElements = uint64_t(1) << 30;
+constexpr size_t   kStaticScratchBytes = 32768;
+const char* sumWithStaticScratch(const LaunchContext& ctx, int ordinal, const View& src, void* dst);
 
 // ---- partial reductions (Device::reduceTo / maxTo, aixDevice.hpp:70-71) ----------------------------------------
 // One (extent, source stride, kept?) triple per collapsed source dimension, outermost first. Kept dimensions index

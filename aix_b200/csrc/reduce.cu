@@ -383,6 +383,35 @@ void launchReduceInto(const LaunchContext& ctx, bool isMax, const void* srcRaw, 
 
 }   // namespace
 
+// ------------------------------------------------------------------------------------------------------------
+// Scratch that is part of the library image instead of the heap: one ticket word (first 256 bytes) and 4064 partial
+// slots. Every GPU that loads the library carries these 32 KiB until the process exits. In host code the array's
+// name is only a stand-in; the device address comes from cudaGetSymbolAddress, once per device.
+// ------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_staticReduceScratch[kStaticScratchBytes];
+
+const char* sumWithStaticScratch(const LaunchContext& ctx, int ordinal, const View& src, void* dst)
+{
+    constexpr int kMaxDevices = 64;
+    static void* addresses[kMaxDevices] = {};
+    if (ordinal < 0 || ordinal >= kMaxDevices) return "device ordinal out of range for the static scratch table";
+    if (!addresses[ordinal])
+    {
+        // First call on this device (the device is current): resolve the array's device address.
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_staticReduceScratch);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        addresses[ordinal] = p;
+    }
+    void* scratch = addresses[ordinal];
+    // The ticket must start at zero; a launch that was cut short could have left it raised.
+    cudaError_t e = cudaMemsetAsync(scratch, 0, kScratchCounterBytes, ctx.stream);
+    if (e != cudaSuccess) return cudaGetErrorString(e);
+    reduceAllWithScratch(ctx, false, src, dst, scratch, kStaticScratchBytes);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
 void reduceAllWithScratch(const LaunchContext& ctx, bool isMax, const View& src, void* dst, void* scratch, size_t scratchBytes)
 {
     AIXB200_DISPATCH_DTYPE(src.dtype, launchReduceAll, ctx, isMax, src, dst, scratch, scratchBytes);

@@ -198,6 +198,12 @@ class DeviceB200:
     def synchronize(self):  self._check(self._lib.aixb200_synchronize(self._h))
 
     # ---- additions over the reference interface ----------------------------------------------------------------
+    def sumStaticScratch(self, a, result):
+        """Device::sum without any allocation on the way: partials go to a static device array of the library.
+        For callers that cannot allocate when they call (fixed memory budget, allocation-free regions). Inputs must be
+        device memory, at most 2**30 elements, and recorded work must have been synchronised before."""
+        self._check(self._lib.aixb200_sum_static_scratch(self._h, self._t(a), self._t(result)))
+
     def stats(self) -> dict:
         s = C.Stats()
         self._check(self._lib.aixb200_get_stats(self._h, ctypes.byref(s)))

@@ -137,6 +137,21 @@ int aixb200_fill_min(aixb200_device* dev, const aixb200_tensor* result);        
 /* ---- reductions (aixDevice.hpp:52, 60-62, 70-73) ---- */
 int aixb200_sum(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
 int aixb200_max(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
+/* Same result as aixb200_sum, for callers that may not allocate GPU or host memory at the moment of the call - code
+ * running under a fixed memory budget, inside a region where cudaMalloc is forbidden or would synchronise, or next to
+ * another allocator that owns the whole device. No counterpart in the reference (its devices always allocate their
+ * reduction temporaries, aixDeviceMetal.cpp:329-350). The partial sums live in a 32 KiB static __device__ array that is
+ * part of this library's image: every GPU that loads the library holds it until the process exits.
+ *  - `a` and `result` must already be device memory; host pointers are refused (staging would allocate).
+ *  - at most AIXB200_SUM_STATIC_SCRATCH_MAX_ELEMENTS elements; larger inputs return AIXB200_ERR_INVALID.
+ *  - recorded elementwise work must have been flushed (aixb200_synchronize) - otherwise AIXB200_ERR_INVALID, because
+ *    flushing may compile and load a kernel.
+ *  - the first call on a device resolves the array's address (cudaGetSymbolAddress); make that first call before any
+ *    stream capture begins.
+ *  - all calls on one GPU share the array: calls that overlap on the GPU (two streams, two device handles, two
+ *    threads) race on it. Calls on one device handle are ordered by its stream and are safe. */
+#define AIXB200_SUM_STATIC_SCRATCH_MAX_ELEMENTS (1ull << 30)
+int aixb200_sum_static_scratch(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
 int aixb200_argmax(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
 int aixb200_argmax_indices(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
 /* dst += sum over the broadcast dimensions of src (dst zeroed by the caller); dst = max(dst, ...) for max_to. */
