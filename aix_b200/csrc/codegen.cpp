@@ -174,10 +174,27 @@ template <class D> __device__ __forceinline__ unsigned pp_sub(unsigned a, unsign
 template <class D> __device__ __forceinline__ unsigned pp_mul(unsigned a, unsigned b) { return P2<D>::mul(a, b); }
 template <class D> __device__ __forceinline__ unsigned pp_neg(unsigned a) { return a ^ 0x80008000u; }
 template <class D> __device__ __forceinline__ unsigned pp_cast(unsigned a) { return a; }
+#if AIX_FAST
+// The quotient is rounded to 8 or 11 significant bits right away: a reciprocal good to 1 ulp of float is plenty.
+template <class D> __device__ __forceinline__ unsigned pp_div(unsigned a, unsigned b) { return P2<D>::pack(P2<D>::lo(a) * fast_rcp(P2<D>::lo(b)), P2<D>::hi(a) * fast_rcp(P2<D>::hi(b))); }
+#else
 template <class D> __device__ __forceinline__ unsigned pp_div(unsigned a, unsigned b) { return P2<D>::pack(P2<D>::lo(a) / P2<D>::lo(b), P2<D>::hi(a) / P2<D>::hi(b)); }
+#endif
 template <class D> __device__ __forceinline__ unsigned pp_pow(unsigned a, unsigned b) { return P2<D>::pack(m_pow(P2<D>::lo(a), P2<D>::lo(b)), m_pow(P2<D>::hi(a), P2<D>::hi(b))); }
 #define AIX_PP_UNARY(NAME) template <class D> __device__ __forceinline__ unsigned pp_##NAME(unsigned a) { return P2<D>::pack(m_##NAME(P2<D>::lo(a)), m_##NAME(P2<D>::hi(a))); }
-AIX_PP_UNARY(sqrt) AIX_PP_UNARY(sin) AIX_PP_UNARY(cos) AIX_PP_UNARY(tanh) AIX_PP_UNARY(log) AIX_PP_UNARY(exp)
+AIX_PP_UNARY(sqrt) AIX_PP_UNARY(sin) AIX_PP_UNARY(cos) AIX_PP_UNARY(log) AIX_PP_UNARY(exp)
+#if AIX_FAST
+// bfloat16 keeps 8 significant bits: the hardware tanh (relative error 2^-11) is exact to a quarter of the last place
+// of the result, so it differs from the rounded exact value by at most one bfloat16 ulp, and only near rounding ties.
+__device__ __forceinline__ float hw_tanh(float x) { float y; asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+template <class D> __device__ __forceinline__ unsigned pp_tanh(unsigned a)
+{
+    if constexpr (D::id == 3) return P2<D>::pack(hw_tanh(P2<D>::lo(a)), hw_tanh(P2<D>::hi(a)));
+    else return P2<D>::pack(m_tanh(P2<D>::lo(a)), m_tanh(P2<D>::hi(a)));
+}
+#else
+AIX_PP_UNARY(tanh)
+#endif
 )PRELUDE";
 
 const char* kTraits[DTYPE_COUNT] = {"Df64", "Df32", "Df16", "Dbf16", "Di64", "Di32", "Di16", "Di8", "Du8"};

@@ -73,5 +73,37 @@ def measure_matmul(dev, tensor_peak, size=4096):
     return out
 
 
+def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batch=4096, barrier=None, reduce_max=None):
+    """MLP training configuration: device time of `steps` steps (forward, backward, gradient all-reduce when
+    world_size > 1, Adam), loss not read inside the timed region."""
+    from .mlp import MlpTrainer
+    trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size)
+    for _ in range(warmup):
+        loss = trainer.step()
+    first = float(loss.value.item())
+    e0, e1 = dev.createEvent(), dev.createEvent()
+    if barrier: barrier()
+    dev.synchronize()
+    s0 = dev.stats()
+    dev.recordEvent(e0)
+    for _ in range(steps):
+        loss = trainer.step()
+    dev.recordEvent(e1)
+    ms = dev.elapsedMs(e0, e1)
+    if barrier: barrier()
+    if reduce_max: ms = reduce_max(ms)
+    s1 = dev.stats()
+    last = float(loss.value.item())
+    per_step = ms / steps
+    tf = trainer.flops_per_step / (per_step * 1e-3) / 1e12
+    return {"config": "4 Linear 1024-4096-4096-4096-1024, tanh, f32, batch %d per GPU, MSE, Adam(1e-3)" % batch,
+            "ms_per_step": per_step, "steps_per_s": 1e3 / per_step, "samples_per_s": world_size * batch * 1e3 / per_step,
+            "gemm_TFLOP/s_per_gpu": tf, "frac_of_measured_bf16_peak": tf / tensor_peak, "world_size": world_size,
+            "kernel_launches_per_step": (s1["total_kernel_launches"] - s0["total_kernel_launches"]) / steps,
+            "fused_kernels_per_step": (s1["fused_kernels"] - s0["fused_kernels"]) / steps,
+            "device_calls_per_step": (s1["ops_recorded"] - s0["ops_recorded"]) / steps,
+            "loss_after_warmup": first, "loss_at_end": last}
+
+
 def measure_extras(dev, hbm_peak, tensor_peak):
     return {"reductions_8192x8192_bf16": measure_reductions(dev, hbm_peak), "matmul": measure_matmul(dev, tensor_peak)}

@@ -7,6 +7,8 @@ reported beside it.
 A step is one evaluation of  z = (a*b + c) * sigmoid(a) - tanh(b) / (1 + exp(-c));  s = z.sum()  over n = 2**L
 elements per GPU (synthetic U(-1,1) inputs, seed 0), issued op by op through the C ABI exactly as the AIX core would
 issue it: 16 recorded device calls that the device fuses into one generated kernel, plus the sum kernel.
+The line also carries `mlp_train` (steps/s of the data-parallel MLP configuration at this N) and, at N = 1, `extras`
+(reductions at 8192^2 bf16, matmul 4096^3) and `cpu_baseline`.
 `value` counts the algorithmic bytes of the step (3 reads + 1 write for the chain, 1 read for the sum: 20*n for
 f32) over the device time of K steps with inputs resident in HBM; `e2e` is the same step with the inputs copied from
 pinned host memory and the sum read back every step. Rank 0 prints one JSON line.
@@ -137,6 +139,7 @@ def main():
     ap.add_argument("--log2n", type=int, default=28)
     ap.add_argument("--dtype", default="f32", choices=list(DT))
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary kernel-class measurements")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -256,6 +259,24 @@ def main():
         "fusion": {k: stats1[k] - stats0[k] for k in ("ops_recorded", "fused_kernels", "fused_ops", "fills_absorbed", "stores_elided",
                                                       "kernel_cache_hits", "kernel_cache_misses")},
     }
+
+    # ---- the data-parallel MLP training configuration, at every N (gradient all-reduce over NCCL for N > 1) --------------
+    if not args.no_mlp:
+        # free the sweep tensors first: the MLP step needs its own few GB
+        del a, b, c
+        dev.emptyCache()
+        try:
+            if world > 1:
+                ids = [DeviceB200.commUniqueId() if rank == 0 else None]
+                dist.broadcast_object_list(ids, src=0)
+                dev.commInit(rank, world, ids[0])
+            from aix_b200.extras import measure_mlp
+            line["mlp_train"] = measure_mlp(dev, tensor_peak, steps=max(3, min(args.steps, 10)), warmup=3, rank=rank, world_size=world,
+                                            barrier=barrier, reduce_max=max_over_ranks)
+            if world > 1:
+                dev.commDestroy()
+        except Exception as exc:
+            line["mlp_train"] = {"error": str(exc)}
 
     if rank == 0 and world == 1:
         try:
