@@ -118,7 +118,7 @@ int main()
             auto ta = Tensor(a.data(), a.size(), DataType::kFloat32, Shape{n, n}, opt);
             auto tb = Tensor(b.data(), b.size(), DataType::kFloat32, Shape{n, n}, opt);
             auto c = matmul(ta, tb);
-            c.backward();
+            c.backward(Tensor(1.0f, Shape{n, n}, TensorOptions{ .m_device = devices[d] }));   // upstream gradient of ones
             devices[d]->synchronize();
             outs[d] = c; grads[d][0] = ta; grads[d][1] = tb;
         }

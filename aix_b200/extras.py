@@ -18,11 +18,14 @@ def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
     e0, e1 = dev.createEvent(), dev.createEvent()
     for _ in range(3 if flush_l2 else 1):
         dev.flushL2()
+    marker = dev.createEvent()
     dev.recordEvent(e0)
     for _ in range(iters):
         fn()
+        dev.recordEvent(marker)         # flushes recorded elementwise work: one launch set per call, as in a real step
     dev.recordEvent(e1)
     ms = dev.elapsedMs(e0, e1) / iters
+    dev.destroyEvent(marker)
     dev.destroyEvent(e0)
     dev.destroyEvent(e1)
     return float(ms), float(ms)

@@ -21,9 +21,12 @@ def test_loss_curve_and_parameters_follow_the_reference_front_end(b200, ref):
     assert np.allclose(got_losses, want_losses, rtol=2e-5), (got_losses, want_losses)
     params = trainer.parameters_numpy()
     for i in range(4):
-        # Adam moves every weight by ~lr per step regardless of the gradient's size, so compare on the scale of the update
-        assert np.max(np.abs(params[2 * i] - ref_w[i])) <= 2e-5 * max(1.0, np.max(np.abs(ref_w[i]))) + 1e-3 * 10 * 1e-2
-        assert np.max(np.abs(params[2 * i + 1] - ref_b[i])) <= 2e-5 + 1e-3 * 10 * 1e-2
+        # Adam moves every weight by about lr per step whatever the gradient's size, and for weights whose gradient is
+        # rounding noise the direction itself is noise: bound single weights by a fraction of the total movement
+        # (steps * lr = 1e-2) and the average weight tightly.
+        for got, want in ((params[2 * i], ref_w[i]), (params[2 * i + 1], ref_b[i])):
+            assert np.max(np.abs(got - want)) <= 0.1 * steps * 1e-3
+            assert np.mean(np.abs(got - want)) <= 2e-6
 
 
 def test_full_width_step_runs_and_reduces_the_loss(b200):
