@@ -189,6 +189,60 @@ __device__ __forceinline__ void tileCoordinates(uint32_t t, uint32_t tilesM, uin
     tn = local / groupRows;
 }
 
+// Epilogue of one 32-column strip of one accumulator row: convert and store (first chunk) or add to what C already
+// holds (later chunks of the split-f32 scheme; `old` was fetched before the TMEM load).
+__device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const uint32_t (&r)[32], const float4 (&old)[8], uint32_t row, uint32_t col, uint32_t c)
+{
+    if (row < p.m && col < p.n)
+    {
+        const bool fullRow = col + 32 <= p.n;
+        if (p.outDtype == F32)
+        {
+            float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
+            // Partial results after the first are added to C with IEEE f32 additions: the tensor core's own
+            // accumulation truncates, and that bias grows with the number of MMAs folded into one accumulator.
+            if (fullRow && p.vectorStores)
+            {
+                #pragma unroll
+                for (int v = 0; v < 8; ++v)
+                {
+                    float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    if (c > 0) { x.x += old[v].x; x.y += old[v].y; x.z += old[v].z; x.w += old[v].w; }
+                    reinterpret_cast<float4*>(out)[v] = x;
+                }
+            }
+            else
+            {
+                for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]) + (c > 0 ? out[e] : 0.f);
+            }
+        }
+        else
+        {
+            uint16_t* out = static_cast<uint16_t*>(p.c) + static_cast<size_t>(row) * p.n + col;
+            uint32_t packed[16];
+            #pragma unroll
+            for (int v = 0; v < 16; ++v)
+            {
+                const float lo = __uint_as_float(r[2 * v]), hi = __uint_as_float(r[2 * v + 1]);
+                const uint32_t l16 = p.outDtype == BF16 ? dev::f32ToBf16(lo) : dev::f32ToF16(lo);
+                const uint32_t h16 = p.outDtype == BF16 ? dev::f32ToBf16(hi) : dev::f32ToF16(hi);
+                packed[v] = l16 | (h16 << 16);
+            }
+            if (fullRow && p.vectorStores)
+            {
+                #pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    reinterpret_cast<uint4*>(out)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+            else
+            {
+                for (uint32_t e = 0; e < 32 && col + e < p.n; ++e)
+                    out[e] = static_cast<uint16_t>((packed[e >> 1] >> ((e & 1) * 16)) & 0xFFFFu);
+            }
+        }
+    }
+}
+
 template <bool Tf32>
 __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                            const __grid_constant__ KernelParams p)
@@ -323,54 +377,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 }
                 tmemLoad32(taddr + c0, r);
                 tmemLoadWait();
-                if (row < p.m && col < p.n)
-                {
-                    const bool fullRow = col + 32 <= p.n;
-                    if (p.outDtype == F32)
-                    {
-                        float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
-                        // Partial results after the first are added to C with IEEE f32 additions: the tensor core's own
-                        // accumulation truncates, and that bias grows with the number of MMAs folded into one accumulator.
-                        if (fullRow && p.vectorStores)
-                        {
-                            #pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                            {
-                                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                                if (c > 0) { x.x += old[v].x; x.y += old[v].y; x.z += old[v].z; x.w += old[v].w; }
-                                reinterpret_cast<float4*>(out)[v] = x;
-                            }
-                        }
-                        else
-                        {
-                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]) + (c > 0 ? out[e] : 0.f);
-                        }
-                    }
-                    else
-                    {
-                        uint16_t* out = static_cast<uint16_t*>(p.c) + static_cast<size_t>(row) * p.n + col;
-                        uint32_t packed[16];
-                        #pragma unroll
-                        for (int v = 0; v < 16; ++v)
-                        {
-                            const float lo = __uint_as_float(r[2 * v]), hi = __uint_as_float(r[2 * v + 1]);
-                            const uint32_t l16 = p.outDtype == BF16 ? dev::f32ToBf16(lo) : dev::f32ToF16(lo);
-                            const uint32_t h16 = p.outDtype == BF16 ? dev::f32ToBf16(hi) : dev::f32ToF16(hi);
-                            packed[v] = l16 | (h16 << 16);
-                        }
-                        if (fullRow && p.vectorStores)
-                        {
-                            #pragma unroll
-                            for (int v = 0; v < 4; ++v)
-                                reinterpret_cast<uint4*>(out)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                        }
-                        else
-                        {
-                            for (uint32_t e = 0; e < 32 && col + e < p.n; ++e)
-                                out[e] = static_cast<uint16_t>((packed[e >> 1] >> ((e & 1) * 16)) & 0xFFFFu);
-                        }
-                    }
-                }
+                storeAccumulatorRow(p, r, old, row, col, c);
             }
             fenceBeforeSync();
             mbarArrive(&s.tmemEmpty[acc]);
@@ -386,6 +393,225 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
     {
         fenceAfterSync();
         tmemDealloc(tmemBase, kTmemColumns);
+    }
+    if (threadIdx.x == 0 && s.abortFlag) atomicExch(p.errorWord, 1u);
+}
+
+// ==================================================================================================================
+// CTA-pair variant (cta_group::2). Two CTAs of a cluster own one 256 x 256 tile: CTA r holds rows r*128.. of A and of
+// the accumulator, and columns r*128.. of B; the leader CTA (rank 0) issues M=256 MMAs that read both CTAs' shared
+// memory. Each CTA therefore loads 32 KiB per stage instead of 48 KiB, which buys a 6-stage ring: the single-CTA
+// kernel stalls on TMA latency with its 4 stages (tensor pipe 56 % busy at 4096^3). No TMA multicast is used: every
+// CTA loads its own operand slices and signals the leader's `full` barrier (cp.async.bulk.tensor ... .cta_group::2).
+// ==================================================================================================================
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytesB = 128 * 128;
+
+struct PairStorage
+{
+    alignas(1024) uint8_t a[kPairStages][kStageBytesA];
+    alignas(1024) uint8_t b[kPairStages][kPairStageBytesB];
+    uint64_t full[kPairStages];        // used in the leader CTA: both CTAs' loads land here
+    uint64_t empty[kPairStages];       // one per CTA, released by the leader's multicast commit
+    uint64_t tmemFull[2];              // one per CTA, multicast commit
+    uint64_t tmemEmpty[2];             // used in the leader CTA: 256 epilogue threads of the pair arrive
+    uint32_t tmemBase;
+    uint32_t abortFlag;
+};
+
+__device__ __forceinline__ uint32_t clusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t mapToCta(uint32_t sharedAddr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(sharedAddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void clusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbarExpectTxCluster(uint32_t clusterAddr, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(clusterAddr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ void tmaLoad2dPair(void* dst, const CUtensorMap* map, uint32_t leaderBar, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smemAddr(dst)), "l"(map), "r"(leaderBar), "r"(c0), "r"(c1) : "memory");
+}
+template <bool Tf32>
+__device__ __forceinline__ void ummaPair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    if (Tf32)
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ummaCommitPair(uint64_t* bar)
+{
+    // arrives on the barrier at this offset in BOTH CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smemAddr(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
+template <bool Tf32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ KernelParams p)
+{
+    extern __shared__ uint8_t rawSmem[];
+    PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = clusterRank();
+    const bool leader = rank == 0;
+    volatile uint32_t* abortFlag = &s.abortFlag;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < kPairStages; ++i) { mbarInit(&s.full[i], 2); mbarInit(&s.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], 256); }
+        s.abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1)
+    {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&s.tmemBase)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    fenceBeforeSync();
+    __syncthreads();
+    clusterSync();                      // barriers of both CTAs are initialised before anyone signals across
+    fenceAfterSync();
+    const uint32_t tmemBase = s.tmemBase;
+    const uint32_t totalTiles = p.tilesM * p.tilesN;                 // tiles of 256 x 256
+    const uint32_t clusterId = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+
+    if (warp == 0)
+    {
+        if (lane == 0)
+        {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+            {
+                uint32_t tm, tn;
+                tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+                const int32_t m0 = static_cast<int32_t>(tm * 256 + rank * 128), n0 = static_cast<int32_t>(tn * 256 + rank * 128);
+                for (uint32_t c = 0; c < p.chunks && ok; ++c)
+                {
+                    const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
+                    for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                    {
+                        if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
+                        const uint32_t leaderFull = mapToCta(smemAddr(&s.full[stage]), 0);
+                        mbarExpectTxCluster(leaderFull, p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes);
+                        const uint32_t passIndex = it / kbCount, kb = kbBegin + (it - passIndex * kbCount);
+                        const uint32_t pass = p.kPhases == 3 ? (passIndex + 1) % 3 : 0;
+                        const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
+                        const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
+                        for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
+                        {
+                            if (p.aMnMajor) tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], &mapA, leaderFull, m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
+                            else            tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], &mapA, leaderFull, kA, m0);
+                        }
+                        for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
+                        {
+                            if (p.bMnMajor) tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], &mapB, leaderFull, n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
+                            else            tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], &mapB, leaderFull, kB, n0);
+                        }
+                        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0 && leader)
+        {
+            uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
+            bool ok = true;
+            for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+            for (uint32_t c = 0; c < p.chunks && ok; ++c)
+            {
+                if (!mbarWait(&s.tmemEmpty[acc], accPhase ^ 1u, abortFlag)) { ok = false; break; }
+                fenceAfterSync();
+                const uint32_t tmemD = tmemBase + acc * kBlockN;
+                const uint32_t kbCount = min(p.kBlocks - c * p.chunkBlocks, p.chunkBlocks);
+                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                {
+                    if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
+                    fenceAfterSync();
+                    const uint32_t aAddr = smemAddr(&s.a[stage][0]), bAddr = smemAddr(&s.b[stage][0]);
+                    for (uint32_t j = 0; j < p.mmasPerStage; ++j)
+                    {
+                        const uint64_t da = smemDescriptor(aAddr + j * p.kAdvanceA, p.aLbo, 1024);
+                        const uint64_t db = smemDescriptor(bAddr + j * p.kAdvanceB, p.bLbo, 1024);
+                        ummaPair<Tf32>(tmemD, da, db, p.idesc, (it | j) != 0 ? 1u : 0u);
+                    }
+                    ummaCommitPair(&s.empty[stage]);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ummaCommitPair(&s.tmemFull[acc]);
+                acc ^= 1u;
+                if (acc == 0) accPhase ^= 1u;
+            }
+        }
+    }
+    else
+    {
+        const uint32_t quarter = warp & 3u;
+        uint32_t acc = 0, accPhase = 0;
+        bool ok = true;
+        for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+        {
+            uint32_t tm, tn;
+            tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+            for (uint32_t c = 0; c < p.chunks && ok; ++c)
+            {
+                if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
+                fenceAfterSync();
+                const uint32_t row = tm * 256 + rank * 128 + quarter * 32 + lane;
+                const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
+                #pragma unroll 1
+                for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32)
+                {
+                    uint32_t r[32];
+                    const uint32_t col = tn * kBlockN + c0;
+                    float4 old[8];
+                    const bool fastF32 = p.outDtype == F32 && p.vectorStores && row < p.m && col + 32 <= p.n;
+                    if (fastF32 && c > 0)
+                    {
+                        const float4* in = reinterpret_cast<const float4*>(static_cast<const float*>(p.c) + static_cast<size_t>(row) * p.n + col);
+                        #pragma unroll
+                        for (int v = 0; v < 8; ++v) old[v] = in[v];
+                    }
+                    tmemLoad32(taddr + c0, r);
+                    tmemLoadWait();
+                    storeAccumulatorRow(p, r, old, row, col, c);
+                }
+                fenceBeforeSync();
+                mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
+                acc ^= 1u;
+                if (acc == 0) accPhase ^= 1u;
+            }
+        }
+    }
+
+    fenceBeforeSync();
+    __syncthreads();
+    clusterSync();                      // the leader's MMAs read the peer's shared memory until the very end
+    if (warp == 1)
+    {
+        fenceAfterSync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(kTmemColumns) : "memory");
     }
     if (threadIdx.x == 0 && s.abortFlag) atomicExch(p.errorWord, 1u);
 }
@@ -492,9 +718,13 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     static bool disabled = std::getenv("AIXB200_NO_TENSOR_CORE") != nullptr;
     if (disabled) return false;
 
+    // CTA pairs (256 x 256 tiles) unless switched off or the problem has a single row of 128-row tiles.
+    static const bool pairEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_PAIR"); return !(v && v[0] == '0'); }();
+    const bool pair = pairEnabled && q.m > 128;
+    const uint32_t bRows = pair ? 128u : static_cast<uint32_t>(kBlockN);      // B rows (N) each CTA loads per stage
     KernelParams p{};
     p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
-    p.tilesM = (p.m + kBlockM - 1) / kBlockM;
+    p.tilesM = pair ? (p.m + 255) / 256 : (p.m + kBlockM - 1) / kBlockM;
     p.tilesN = (p.n + kBlockN - 1) / kBlockN;
     p.c = q.c;
     p.outDtype = q.dtype;
@@ -528,17 +758,17 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         }
         if (b.mnMajor)
         {
-            p.bBoxes = kBlockN / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
+            p.bBoxes = bRows / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
             if (!makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
         }
         else
         {
-            p.bBoxes = 1; p.bBoxBytes = kStageBytesB; p.bLbo = 0; p.kAdvanceB = 32;
-            if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, kBlockN)) return false;
+            p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.bLbo = 0; p.kAdvanceB = 32;
+            if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, bRows)) return false;
         }
         // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
         p.idesc = (1u << 4) | ((q.dtype == BF16 ? 1u : 0u) << 7) | ((q.dtype == BF16 ? 1u : 0u) << 10) |
-                  ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+                  ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((kBlockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
     }
     else
     {
@@ -560,10 +790,10 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
         p.mmasPerStage = 4;
         p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
-        p.bBoxes = 1; p.bBoxBytes = kStageBytesB; p.kAdvanceB = 32;
+        p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.kAdvanceB = 32;
         if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitA, 2ull * kPad, q.m, 2ull * kPad * 4, 32, kBlockM)) return false;
-        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitB, 2ull * kPad, q.n, 2ull * kPad * 4, 32, kBlockN)) return false;
-        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kBlockN >> 3) << 17) | ((kBlockM >> 4) << 24);
+        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitB, 2ull * kPad, q.n, 2ull * kPad * 4, 32, bRows)) return false;
+        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kBlockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
     }
 
     const size_t smemBytes = sizeof(SharedStorage) + 1024;
@@ -574,6 +804,36 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         cudaFuncSetAttribute(gemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
     });
     const uint32_t tiles = p.tilesM * p.tilesN;
+    if (pair)
+    {
+        const size_t pairSmem = sizeof(PairStorage) + 1024;
+        static int maxClusters = 0;
+        static std::once_flag pairOnce;
+        std::call_once(pairOnce, [&]
+        {
+            cudaFuncSetAttribute(gemmPairKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(static_cast<unsigned>(ctx.smCount) & ~1u);
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = pairSmem;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&maxClusters, gemmPairKernel<false>, &cfg) != cudaSuccess || maxClusters <= 0)
+            {
+                cudaGetLastError();
+                maxClusters = ctx.smCount / 2;
+            }
+        });
+        const uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
+        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, p);
+        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, p);
+        if (ctx.launches) ++*ctx.launches;
+        return true;
+    }
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(ctx.smCount));
     if (tf32) gemmKernel<true><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
     else      gemmKernel<false><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
