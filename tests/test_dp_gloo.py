@@ -1,0 +1,83 @@
+"""Data-parallel host logic on CPU: two gloo ranks, each with a CPU device (the numpy oracle) and the mirrored front
+end, exchange gradients through the same `all_reduce_gradients` call the GPU path uses (the device's allReduce is
+served by gloo here instead of NCCL). After three Adam steps on per-rank batches every rank must hold the parameters
+a single process gets from the concatenated batch, and both ranks must agree bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from aix_b200 import _capi as C
+from aix_b200.mlp import MlpTrainer, synthetic_batch, xavier_parameters
+from aix_b200.frontend import Tensor
+from aix_b200.tensor import TensorValue
+from oracle.numpy_oracle import DeviceNumpyOracle
+
+DIMS = (8, 16, 16, 4)
+BATCH = 6
+STEPS = 3
+
+
+class GlooDevice(DeviceNumpyOracle):
+    """CPU device whose allReduce goes through torch.distributed (gloo): sum over ranks, then scale."""
+
+    def allReduce(self, data, count, dtype, scale=1.0):
+        assert dtype == C.F32
+        view = self._raw(data, dtype, count)
+        t = torch.from_numpy(view.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        view[:] = (t.numpy() * np.float32(scale)).astype(np.float32)
+
+
+def set_batch(trainer, dev, x, y):
+    trainer.x = Tensor(TensorValue.from_numpy(x, dev))
+    trainer.y = Tensor(TensorValue.from_numpy(y, dev))
+
+
+def worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dev = GlooDevice()
+    weights, biases = xavier_parameters(DIMS, seed=0)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases)
+    x, y = synthetic_batch(DIMS, BATCH, rank)
+    set_batch(trainer, dev, x, y)
+    for _ in range(STEPS):
+        trainer.step()
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *trainer.parameters_numpy())
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = np.load(tmp_path / "rank0.npz")
+    r1 = np.load(tmp_path / "rank1.npz")
+    for k in r0.files:
+        assert np.array_equal(r0[k], r1[k]), "ranks diverged"
+
+    dev = DeviceNumpyOracle()
+    weights, biases = xavier_parameters(DIMS, seed=0)
+    single = MlpTrainer(dev, DIMS, 2 * BATCH, weights=weights, biases=biases)
+    xs, ys = zip(*(synthetic_batch(DIMS, BATCH, r) for r in range(2)))
+    set_batch(single, dev, np.concatenate(xs), np.concatenate(ys))
+    for _ in range(STEPS):
+        single.step()
+    for got, want in zip((r0[k] for k in r0.files), single.parameters_numpy()):
+        assert np.allclose(got, want, rtol=1e-4, atol=2e-5), np.max(np.abs(got - want))
+
+
+def test_shards_are_disjoint_and_deterministic():
+    a0, _ = synthetic_batch(DIMS, BATCH, rank=0)
+    a1, _ = synthetic_batch(DIMS, BATCH, rank=1)
+    b0, _ = synthetic_batch(DIMS, BATCH, rank=0)
+    assert np.array_equal(a0, b0) and not np.array_equal(a0, a1)
+    w0, _ = xavier_parameters(DIMS, seed=0)
+    w1, _ = xavier_parameters(DIMS, seed=0)
+    assert all(np.array_equal(x, y) for x, y in zip(w0, w1))          # identical replicas on every rank
