@@ -12,7 +12,7 @@ namespace
 // Minimal slice of the NCCL C API (stable since NCCL 2.0).
 typedef struct { char internal[128]; } NcclUniqueId;
 typedef void* NcclComm;
-enum { kNcclSum = 0 };
+enum { kNcclSum = 0, kNcclAvg = 4 };
 enum { kNcclInt32 = 2, kNcclInt64 = 4, kNcclHalf = 6, kNcclFloat = 7, kNcclDouble = 8, kNcclBfloat16 = 9 };
 
 struct NcclApi
@@ -76,7 +76,7 @@ Comm::~Comm()
     if (m_comm) nccl().commDestroy(m_comm);
 }
 
-void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream)
+void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average)
 {
     int type;
     switch (dtype)
@@ -89,7 +89,7 @@ void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t s
         case I32: type = kNcclInt32; break;
         default: failInvalid("all_reduce: unsupported element type");
     }
-    checkNccl(nccl().allReduce(data, data, count, type, kNcclSum, m_comm, stream), "ncclAllReduce");
+    checkNccl(nccl().allReduce(data, data, count, type, average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclAllReduce");
 }
 
 }   // namespace aixb200

@@ -16,7 +16,8 @@ public:
     static void uniqueId(void* out128);
     Comm(int rank, int nranks, const void* id128, int ordinal);
     ~Comm();
-    void allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream);
+    // Sum over the ranks; with `average` the sum is divided by the number of ranks inside the collective.
+    void allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average = false);
     int rank() const { return m_rank; }
     int size() const { return m_nranks; }
 

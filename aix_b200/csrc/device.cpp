@@ -884,8 +884,10 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
     flush();
-    m_comm->allReduceSum(data, count, dtype, m_stream);
-    if (scale != 1.0)
+    // A scale of exactly 1/ranks on a floating type is the collective's own averaging: no extra pass over the data.
+    const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
+    m_comm->allReduceSum(data, count, dtype, m_stream, average);
+    if (scale != 1.0 && !average)
     {
         AIXB200_CTX();
         kernels::scaleInPlace(ctx, dtype, data, count, scale);

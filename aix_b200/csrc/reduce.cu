@@ -72,13 +72,13 @@ __global__ void __launch_bounds__(kBlock) reduceAllKernel(const typename Elem<DT
         const uint64_t nvec = n / VEC;
         const Pack<S, VEC>* vsrc = reinterpret_cast<const Pack<S, VEC>*>(src);
         uint64_t i = tid;
-        for (; i + threads < nvec; i += 2 * threads)          // two packs in flight
+        for (; i + 3 * threads < nvec; i += 4 * threads)      // four packs (64 bytes) in flight per thread
         {
-            const Pack<S, VEC> p0 = vsrc[i], p1 = vsrc[i + threads];
+            const Pack<S, VEC> p0 = vsrc[i], p1 = vsrc[i + threads], p2 = vsrc[i + 2 * threads], p3 = vsrc[i + 3 * threads];
             #pragma unroll
-            for (int e = 0; e < VEC; ++e) acc[e] = R::step(R::step(acc[e], p0.v[e]), p1.v[e]);
+            for (int e = 0; e < VEC; ++e) acc[e] = R::step(R::step(R::step(R::step(acc[e], p0.v[e]), p1.v[e]), p2.v[e]), p3.v[e]);
         }
-        if (i < nvec)
+        for (; i < nvec; i += threads)
         {
             const Pack<S, VEC> p0 = vsrc[i];
             #pragma unroll
@@ -133,7 +133,7 @@ void launchReduceAll(const LaunchContext& ctx, bool isMax, const View& src, void
     StridedSrc layout{};
     layout.rank = src.rank;
     for (int d = 0; d < src.rank; ++d) { layout.shape[d] = src.shape[d]; layout.strides[d] = src.strides[d]; }
-    const uint64_t perBlock = static_cast<uint64_t>(kBlock) * (dense ? 2 * (16 / sizeof(S)) : 1);
+    const uint64_t perBlock = static_cast<uint64_t>(kBlock) * (dense ? 4 * (16 / sizeof(S)) : 1);
     uint64_t blocks = (src.size + perBlock - 1) / perBlock;
     blocks = std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::min<uint64_t>(maxBlocks, static_cast<uint64_t>(ctx.smCount) * 8)));
     auto out = static_cast<S*>(dst);
@@ -184,7 +184,14 @@ __global__ void __launch_bounds__(kBlock) reduceRowsKernel(const typename Elem<D
             if (static_cast<uint64_t>(lane) < head) acc[0] = R::step(acc[0], p[lane]);
             const uint64_t nvec = (cols - head) / VEC;
             const Pack<S, VEC>* vp = reinterpret_cast<const Pack<S, VEC>*>(p + head);
-            for (uint64_t i = lane; i < nvec; i += lanes)
+            uint64_t i = lane;
+            for (; i + 3 * lanes < nvec; i += 4 * lanes)         // four independent 128-bit loads per thread
+            {
+                const Pack<S, VEC> p0 = vp[i], p1 = vp[i + lanes], p2 = vp[i + 2 * lanes], p3 = vp[i + 3 * lanes];
+                #pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[e] = R::step(R::step(R::step(R::step(acc[e], p0.v[e]), p1.v[e]), p2.v[e]), p3.v[e]);
+            }
+            for (; i < nvec; i += lanes)
             {
                 const Pack<S, VEC> pk = vp[i];
                 #pragma unroll
@@ -234,13 +241,14 @@ __global__ void __launch_bounds__(kBlock) reduceColsKernel(const typename Elem<D
     if (col < cols)
     {
         uint64_t r = rowBegin + warp;
-        for (; r + kWarps < rowEnd; r += 2 * kWarps)
+        for (; r + 3 * kWarps < rowEnd; r += 4 * kWarps)      // four rows in flight per thread
         {
             const S a = src[r * rowStride + col], b = src[(r + kWarps) * rowStride + col];
-            acc0 = R::step(acc0, a);
-            acc1 = R::step(acc1, b);
+            const S c = src[(r + 2 * kWarps) * rowStride + col], d = src[(r + 3 * kWarps) * rowStride + col];
+            acc0 = R::step(R::step(acc0, a), c);
+            acc1 = R::step(R::step(acc1, b), d);
         }
-        if (r < rowEnd) acc0 = R::step(acc0, src[r * rowStride + col]);
+        for (; r < rowEnd; r += kWarps) acc0 = R::step(acc0, src[r * rowStride + col]);
     }
     tile[warp][lane] = R::merge(R::widen(acc0), R::widen(acc1));
     __syncthreads();

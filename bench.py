@@ -130,7 +130,18 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def emit(line):
+    """Prints the JSON line on the real stdout (libraries such as NCCL write banners to fd 1, which main() points at
+    stderr for the duration of the run)."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = os.dup(1)
+
+
 def main():
+    sys.stdout.flush()
+    os.dup2(2, 1)                        # anything a library prints goes to stderr; the JSON line goes to _REAL_STDOUT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -293,7 +304,7 @@ def main():
             except Exception as exc:
                 line["extras"] = {"error": str(exc)}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     dev.close()
     if dist is not None:
         dist.destroy_process_group()
