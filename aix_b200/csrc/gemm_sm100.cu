@@ -277,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
         {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint32_t stageBytes = p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes;
             for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
             {
                 uint32_t tm, tn;
@@ -285,14 +286,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
                 const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
-                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
+                for (uint32_t kb = kbBegin; kb < kbBegin + kbCount; ++kb)
                 {
                     if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
-                    mbarExpectTx(&s.full[stage], p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes);
+                    mbarExpectTx(&s.full[stage], stageBytes);
                     // Split-f32: K is laid out as [hi | lo] per operand. Per chunk the two small products (lo.hi, hi.lo)
                     // go first, while the accumulator is still tiny, then hi.hi.
-                    const uint32_t passIndex = it / kbCount, kb = kbBegin + (it - passIndex * kbCount);
-                    const uint32_t pass = p.kPhases == 3 ? (passIndex + 1) % 3 : 0;
+                    const uint32_t pass = p.kPhases == 3 ? (passIndex == 2 ? 0u : passIndex + 1u) : 0u;
                     const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
                     const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
                     for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
@@ -315,6 +316,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
     {
         if (lane == 0)
         {
+            // Descriptor halves that never change: the high word (stride offsets, version, swizzle) and the low word of
+            // stage 0; per stage and per MMA only a 32-bit add remains.
+            const uint64_t descHiA = smemDescriptor(0, p.aLbo, 1024), descHiB = smemDescriptor(0, p.bLbo, 1024);
+            const uint32_t descLoA = (smemAddr(&s.a[0][0]) & 0x3FFFFu) >> 4, descLoB = (smemAddr(&s.b[0][0]) & 0x3FFFFu) >> 4;
+            const uint32_t aStageBytes = sizeof(s.a[0]), bStageBytes = sizeof(s.b[0]);
+            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc;
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
@@ -328,12 +335,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
-                    const uint32_t aAddr = smemAddr(&s.a[stage][0]), bAddr = smemAddr(&s.b[stage][0]);
-                    for (uint32_t j = 0; j < p.mmasPerStage; ++j)
+                    const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j)
                     {
-                        const uint64_t da = smemDescriptor(aAddr + j * p.kAdvanceA, p.aLbo, 1024);
-                        const uint64_t db = smemDescriptor(bAddr + j * p.kAdvanceB, p.bLbo, 1024);
-                        umma<Tf32>(tmemD, da, db, p.idesc, (it | j) != 0 ? 1u : 0u);
+                        const uint64_t da = descHiA | static_cast<uint64_t>(aLo + j * advA);
+                        const uint64_t db = descHiB | static_cast<uint64_t>(bLo + j * advB);
+                        umma<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
                     ummaCommit(&s.empty[stage]);           // the stage is free once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -499,6 +507,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint32_t stageBytes = p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes;
+            const uint32_t leaderFull0 = mapToCta(smemAddr(&s.full[0]), 0);
             for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
             {
                 uint32_t tm, tn;
@@ -507,13 +517,13 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
                     const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
-                    for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                    for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
+                    for (uint32_t kb = kbBegin; kb < kbBegin + kbCount; ++kb)
                     {
                         if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
-                        const uint32_t leaderFull = mapToCta(smemAddr(&s.full[stage]), 0);
-                        mbarExpectTxCluster(leaderFull, p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes);
-                        const uint32_t passIndex = it / kbCount, kb = kbBegin + (it - passIndex * kbCount);
-                        const uint32_t pass = p.kPhases == 3 ? (passIndex + 1) % 3 : 0;
+                        const uint32_t leaderFull = leaderFull0 + stage * 8;
+                        mbarExpectTxCluster(leaderFull, stageBytes);
+                        const uint32_t pass = p.kPhases == 3 ? (passIndex == 2 ? 0u : passIndex + 1u) : 0u;
                         const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
                         const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
                         for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
@@ -536,6 +546,12 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     {
         if (lane == 0 && leader)
         {
+            // Descriptor halves that never change: the high word (stride offsets, version, swizzle) and the low word of
+            // stage 0; per stage and per MMA only a 32-bit add remains.
+            const uint64_t descHiA = smemDescriptor(0, p.aLbo, 1024), descHiB = smemDescriptor(0, p.bLbo, 1024);
+            const uint32_t descLoA = (smemAddr(&s.a[0][0]) & 0x3FFFFu) >> 4, descLoB = (smemAddr(&s.b[0][0]) & 0x3FFFFu) >> 4;
+            const uint32_t aStageBytes = sizeof(s.a[0]), bStageBytes = sizeof(s.b[0]);
+            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc;
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
@@ -549,12 +565,13 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
-                    const uint32_t aAddr = smemAddr(&s.a[stage][0]), bAddr = smemAddr(&s.b[stage][0]);
-                    for (uint32_t j = 0; j < p.mmasPerStage; ++j)
+                    const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j)
                     {
-                        const uint64_t da = smemDescriptor(aAddr + j * p.kAdvanceA, p.aLbo, 1024);
-                        const uint64_t db = smemDescriptor(bAddr + j * p.kAdvanceB, p.bLbo, 1024);
-                        ummaPair<Tf32>(tmemD, da, db, p.idesc, (it | j) != 0 ? 1u : 0u);
+                        const uint64_t da = descHiA | static_cast<uint64_t>(aLo + j * advA);
+                        const uint64_t db = descHiB | static_cast<uint64_t>(bLo + j * advB);
+                        ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
                     ummaCommitPair(&s.empty[stage]);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
