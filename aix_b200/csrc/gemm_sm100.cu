@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 
@@ -46,6 +47,7 @@ struct KernelParams
     uint32_t m, n, k;
     uint32_t tilesM, tilesN, kBlocks;
     uint32_t blockK;            // elements of K per stage (64 for 16-bit, 32 for tf32)
+    uint32_t blockN;            // output tile width: 256, or 128 when that fills the last wave of tiles better
     uint32_t aMnMajor, bMnMajor;
     uint32_t aBoxes, bBoxes;    // TMA boxes per stage and operand
     uint32_t aBoxBytes, bBoxBytes;
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             {
                 uint32_t tm, tn;
                 tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
-                const int32_t m0 = static_cast<int32_t>(tm * kBlockM), n0 = static_cast<int32_t>(tn * kBlockN);
+                const int32_t m0 = static_cast<int32_t>(tm * kBlockM), n0 = static_cast<int32_t>(tn * p.blockN);
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
                 const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
@@ -369,10 +371,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             const uint32_t row = tm * kBlockM + quarter * 32 + lane;
             const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
             #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32)
+            for (uint32_t c0 = 0; c0 < p.blockN; c0 += 32)
             {
                 uint32_t r[32];
-                const uint32_t col = tn * kBlockN + c0;
+                const uint32_t col = tn * p.blockN + c0;
                 // Later partial results are added to what C already holds: fetch that first so the global loads and the
                 // TMEM load are in flight together.
                 float4 old[8];
@@ -513,7 +515,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             {
                 uint32_t tm, tn;
                 tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
-                const int32_t m0 = static_cast<int32_t>(tm * 256 + rank * 128), n0 = static_cast<int32_t>(tn * 256 + rank * 128);
+                const int32_t m0 = static_cast<int32_t>(tm * 256 + rank * 128), n0 = static_cast<int32_t>(tn * p.blockN + rank * (p.blockN >> 1));
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
                     const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
@@ -598,10 +600,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t row = tm * 256 + rank * 128 + quarter * 32 + lane;
                 const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
                 #pragma unroll 1
-                for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32)
+                for (uint32_t c0 = 0; c0 < p.blockN; c0 += 32)
                 {
                     uint32_t r[32];
-                    const uint32_t col = tn * kBlockN + c0;
+                    const uint32_t col = tn * p.blockN + c0;
                     float4 old[8];
                     const bool fastF32 = p.outDtype == F32 && p.vectorStores && row < p.m && col + 32 <= p.n;
                     if (fastF32 && c > 0)
@@ -738,11 +740,24 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     // CTA pairs (256 x 256 tiles) unless switched off or the problem has a single row of 128-row tiles.
     static const bool pairEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_PAIR"); return !(v && v[0] == '0'); }();
     const bool pair = pairEnabled && q.m > 128;
-    const uint32_t bRows = pair ? 128u : static_cast<uint32_t>(kBlockN);      // B rows (N) each CTA loads per stage
     KernelParams p{};
     p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
     p.tilesM = pair ? (p.m + 255) / 256 : (p.m + kBlockM - 1) / kBlockM;
-    p.tilesN = (p.n + kBlockN - 1) / kBlockN;
+    // Tile width: 256 columns keep the tensor pipe busiest, but a persistent grid loses the idle part of its last wave
+    // of tiles; 128-column tiles halve that loss at a small cost per tile. Pick by the modelled efficiency.
+    {
+        const double workers = pair ? ctx.smCount / 2 : ctx.smCount;
+        auto efficiency = [&](uint32_t blockN, double perTile)
+        {
+            const double tiles = static_cast<double>(p.tilesM) * ((p.n + blockN - 1) / blockN);
+            const double waves = std::ceil(tiles / workers);
+            return perTile * tiles / (waves * workers) * (static_cast<double>(p.n) / (((p.n + blockN - 1) / blockN) * blockN));
+        };
+        static const int forced = []{ const char* v = std::getenv("AIXB200_GEMM_BLOCKN"); return v ? std::atoi(v) : 0; }();
+        p.blockN = (forced == 128 || forced == 256) ? static_cast<uint32_t>(forced) : (efficiency(128, 0.93) > efficiency(256, 1.0) ? 128u : 256u);
+    }
+    p.tilesN = (p.n + p.blockN - 1) / p.blockN;
+    const uint32_t bRows = pair ? p.blockN / 2 : p.blockN;                   // B rows (N) each CTA loads per stage
     p.c = q.c;
     p.outDtype = q.dtype;
     p.vectorStores = (reinterpret_cast<uintptr_t>(q.c) % 16 == 0) && ((q.n * dtypeSize(q.dtype)) % 16 == 0);
@@ -785,7 +800,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         }
         // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
         p.idesc = (1u << 4) | ((q.dtype == BF16 ? 1u : 0u) << 7) | ((q.dtype == BF16 ? 1u : 0u) << 10) |
-                  ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((kBlockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
+                  ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
     }
     else
     {
@@ -810,7 +825,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.kAdvanceB = 32;
         if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitA, 2ull * kPad, q.m, 2ull * kPad * 4, 32, kBlockM)) return false;
         if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitB, 2ull * kPad, q.n, 2ull * kPad * 4, 32, bRows)) return false;
-        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kBlockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
+        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
     }
 
     const size_t smemBytes = sizeof(SharedStorage) + 1024;

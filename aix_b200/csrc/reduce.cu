@@ -241,14 +241,13 @@ __global__ void __launch_bounds__(kBlock) reduceColsKernel(const typename Elem<D
     if (col < cols)
     {
         uint64_t r = rowBegin + warp;
-        for (; r + 3 * kWarps < rowEnd; r += 4 * kWarps)      // four rows in flight per thread
+        for (; r + kWarps < rowEnd; r += 2 * kWarps)
         {
             const S a = src[r * rowStride + col], b = src[(r + kWarps) * rowStride + col];
-            const S c = src[(r + 2 * kWarps) * rowStride + col], d = src[(r + 3 * kWarps) * rowStride + col];
-            acc0 = R::step(R::step(acc0, a), c);
-            acc1 = R::step(R::step(acc1, b), d);
+            acc0 = R::step(acc0, a);
+            acc1 = R::step(acc1, b);
         }
-        for (; r < rowEnd; r += kWarps) acc0 = R::step(acc0, src[r * rowStride + col]);
+        if (r < rowEnd) acc0 = R::step(acc0, src[r * rowStride + col]);
     }
     tile[warp][lane] = R::merge(R::widen(acc0), R::widen(acc1));
     __syncthreads();
@@ -257,6 +256,60 @@ __global__ void __launch_bounds__(kBlock) reduceColsKernel(const typename Elem<D
         W w = tile[0][lane];
         #pragma unroll
         for (int k = 1; k < kWarps; ++k) w = R::merge(w, tile[k][lane]);
+        if (gridDim.y == 1) dst[col] = R::finish(R::merge(R::liftStored(dst[col]), w));
+        else partials[static_cast<uint64_t>(blockIdx.y) * cols + col] = *reinterpret_cast<unsigned long long*>(&w);
+    }
+}
+
+// Same reduction when rows are 16-byte aligned and the column count is a multiple of the pack width: every lane owns
+// one pack of adjacent columns, so a warp reads 512 contiguous bytes of a row per instruction.
+template <int DT, bool IsMax>
+__global__ void __launch_bounds__(kBlock) reduceColsVecKernel(const typename Elem<DT>::S* __restrict__ src, uint64_t rows, uint64_t cols,
+                                                              uint64_t rowStride, uint64_t rowsPerSlab, unsigned long long* partials,
+                                                              typename Elem<DT>::S* dst)
+{
+    typedef Reduce<DT, IsMax> R;
+    typedef typename R::S S;
+    typedef typename R::A A;
+    typedef typename R::W W;
+    constexpr int VEC = 16 / sizeof(S);
+    constexpr int kWarps = kBlock / 32;
+    __shared__ W tile[kWarps][32 * VEC + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t col0 = (static_cast<uint64_t>(blockIdx.x) * 32 + lane) * VEC;
+    const uint64_t rowBegin = static_cast<uint64_t>(blockIdx.y) * rowsPerSlab;
+    const uint64_t rowEnd = min(rows, rowBegin + rowsPerSlab);
+    A acc0[VEC], acc1[VEC];
+    #pragma unroll
+    for (int e = 0; e < VEC; ++e) { acc0[e] = R::init(); acc1[e] = R::init(); }
+    if (col0 < cols)
+    {
+        uint64_t r = rowBegin + warp;
+        for (; r + kWarps < rowEnd; r += 2 * kWarps)
+        {
+            const Pack<S, VEC> a = *reinterpret_cast<const Pack<S, VEC>*>(src + r * rowStride + col0);
+            const Pack<S, VEC> b = *reinterpret_cast<const Pack<S, VEC>*>(src + (r + kWarps) * rowStride + col0);
+            #pragma unroll
+            for (int e = 0; e < VEC; ++e) { acc0[e] = R::step(acc0[e], a.v[e]); acc1[e] = R::step(acc1[e], b.v[e]); }
+        }
+        if (r < rowEnd)
+        {
+            const Pack<S, VEC> a = *reinterpret_cast<const Pack<S, VEC>*>(src + r * rowStride + col0);
+            #pragma unroll
+            for (int e = 0; e < VEC; ++e) acc0[e] = R::step(acc0[e], a.v[e]);
+        }
+    }
+    #pragma unroll
+    for (int e = 0; e < VEC; ++e) tile[warp][lane * VEC + e] = R::merge(R::widen(acc0[e]), R::widen(acc1[e]));
+    __syncthreads();
+    // 32 * VEC columns per CTA, folded over the warps by the first threads
+    for (int c = threadIdx.x; c < 32 * VEC; c += kBlock)
+    {
+        const uint64_t col = static_cast<uint64_t>(blockIdx.x) * 32 * VEC + c;
+        if (col >= cols) continue;
+        W w = tile[0][c];
+        #pragma unroll
+        for (int k = 1; k < kWarps; ++k) w = R::merge(w, tile[k][c]);
         if (gridDim.y == 1) dst[col] = R::finish(R::merge(R::liftStored(dst[col]), w));
         else partials[static_cast<uint64_t>(blockIdx.y) * cols + col] = *reinterpret_cast<unsigned long long*>(&w);
     }
@@ -333,7 +386,9 @@ void launchReduceInto(const LaunchContext& ctx, bool isMax, const void* srcRaw, 
     if (rank == 2 && dims[0].kept && !dims[1].kept && dims[1].stride == 1)
     {
         const uint64_t rows = dims[0].extent, cols = dims[1].extent;
-        const bool warpPerRow = cols < 1024;
+        // A warp per row needs no block-wide synchronisation; it wins whenever there are enough rows to fill the GPU
+        // with warps and a row is short enough (<= 64 KiB) for one warp to stream.
+        const bool warpPerRow = cols < 1024 || (cols * sizeof(S) <= 65536 && rows >= static_cast<uint64_t>(ctx.smCount) * 16);
         const uint64_t blocksWanted = warpPerRow ? (rows + 7) / 8 : rows;
         const unsigned int grid = static_cast<unsigned int>(std::max<uint64_t>(1, std::min<uint64_t>(blocksWanted, static_cast<uint64_t>(ctx.smCount) * 16)));
         if (isMax)
@@ -353,7 +408,9 @@ void launchReduceInto(const LaunchContext& ctx, bool isMax, const void* srcRaw, 
     if (rank == 2 && !dims[0].kept && dims[1].kept && dims[1].stride == 1)
     {
         const uint64_t rows = dims[0].extent, cols = dims[1].extent;
-        const uint64_t colTiles = (cols + 31) / 32;
+        constexpr uint64_t kVec = 16 / sizeof(S);
+        const bool vectorised = cols % kVec == 0 && (dims[0].stride * sizeof(S)) % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0;
+        const uint64_t colTiles = vectorised ? (cols + 32 * kVec - 1) / (32 * kVec) : (cols + 31) / 32;
         auto partials = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx.scratch) + kScratchCounterBytes);
         const uint64_t partialCapacity = (ctx.scratchBytes - kScratchCounterBytes) / 8;
         uint64_t slabs = std::max<uint64_t>(1, (static_cast<uint64_t>(ctx.smCount) * 4 + colTiles - 1) / colTiles);
@@ -363,8 +420,13 @@ void launchReduceInto(const LaunchContext& ctx, bool isMax, const void* srcRaw, 
         const uint64_t rowsPerSlab = (rows + slabs - 1) / slabs;
         slabs = (rows + rowsPerSlab - 1) / rowsPerSlab;
         dim3 grid(static_cast<unsigned int>(colTiles), static_cast<unsigned int>(slabs));
-        if (isMax) reduceColsKernel<DT, true><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
-        else       reduceColsKernel<DT, false><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
+        if (vectorised)
+        {
+            if (isMax) reduceColsVecKernel<DT, true><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
+            else       reduceColsVecKernel<DT, false><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
+        }
+        else if (isMax) reduceColsKernel<DT, true><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
+        else            reduceColsKernel<DT, false><<<grid, kBlock, 0, ctx.stream>>>(src, rows, cols, dims[0].stride, rowsPerSlab, partials, dst);
         if (slabs > 1)
         {
             const unsigned int cgrid = static_cast<unsigned int>((cols + kBlock - 1) / kBlock);
