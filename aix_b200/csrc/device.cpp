@@ -192,8 +192,18 @@ void* Device::allocate(size_t bytes)
 {
     // Headroom of one 16-byte pack so that vector tails stay inside the block (the reference pads to 4 elements,
     // aixDeviceMetal.cpp:245-248).
-    void* p = m_allocator->allocate(bytes + 16);
-    return p;
+    try
+    {
+        return m_allocator->allocate(bytes + 16);
+    }
+    catch (const Error&)
+    {
+        // Out of memory with dead buffers still parked behind recorded ops: emit those ops (which returns the buffers
+        // to the cache), then try once more.
+        if (m_deferredFrees.empty() || m_inFlush) throw;
+        flush();
+        return m_allocator->allocate(bytes + 16);
+    }
 }
 
 void* Device::temporary(size_t bytes)
@@ -220,7 +230,7 @@ void Device::deallocate(void* p)
     m_deferredBytes += m_allocator->blockSize(p);
     // Memory pressure: do not let dead buffers pile up behind a long recorded chain
     // (the reference commits when half its working-set budget is queued, aixDeviceMetal.cpp:1438-1444).
-    const uint64_t budget = dryRun() ? (uint64_t(1) << 30) : m_totalMemory / 4;
+    const uint64_t budget = dryRun() ? (uint64_t(1) << 30) : m_totalMemory / 2;
     if (m_deferredBytes > budget) flush();
 }
 

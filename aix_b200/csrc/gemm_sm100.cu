@@ -743,8 +743,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     KernelParams p{};
     p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
     p.tilesM = pair ? (p.m + 255) / 256 : (p.m + kBlockM - 1) / kBlockM;
-    // Tile width: 256 columns keep the tensor pipe busiest, but a persistent grid loses the idle part of its last wave
-    // of tiles; 128-column tiles halve that loss at a small cost per tile. Pick by the modelled efficiency.
+    // Tile width: 256 columns keep the tensor pipe busiest (measured: a 128-column tile reaches about 0.62 of its
+    // throughput), but a persistent grid loses the idle part of its last wave of tiles; narrow tiles only pay off
+    // when that loss is larger still (few tiles). Pick by the modelled efficiency.
     {
         const double workers = pair ? ctx.smCount / 2 : ctx.smCount;
         auto efficiency = [&](uint32_t blockN, double perTile)
@@ -754,7 +755,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             return perTile * tiles / (waves * workers) * (static_cast<double>(p.n) / (((p.n + blockN - 1) / blockN) * blockN));
         };
         static const int forced = []{ const char* v = std::getenv("AIXB200_GEMM_BLOCKN"); return v ? std::atoi(v) : 0; }();
-        p.blockN = (forced == 128 || forced == 256) ? static_cast<uint32_t>(forced) : (efficiency(128, 0.93) > efficiency(256, 1.0) ? 128u : 256u);
+        p.blockN = (forced == 128 || forced == 256) ? static_cast<uint32_t>(forced) : (efficiency(128, 0.62) > efficiency(256, 1.0) ? 128u : 256u);
     }
     p.tilesN = (p.n + p.blockN - 1) / p.blockN;
     const uint32_t bRows = pair ? p.blockN / 2 : p.blockN;                   // B rows (N) each CTA loads per stage

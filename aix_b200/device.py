@@ -55,6 +55,9 @@ class DeviceTensorParams:
     strides: Sequence[int] = field(default_factory=tuple)
 
     def to_c(self) -> C.Tensor:
+        cached = self.__dict__.get("_c")
+        if cached is not None:
+            return cached
         t = C.Tensor()
         t.data = self.data
         t.offset = self.offset
@@ -66,6 +69,7 @@ class DeviceTensorParams:
         for i, (s, st) in enumerate(zip(self.shape, self.strides)):
             t.shape[i] = s
             t.strides[i] = st
+        self.__dict__["_c"] = t        # descriptors are immutable once built: convert once
         return t
 
     @property

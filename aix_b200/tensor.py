@@ -98,7 +98,11 @@ class TensorValue:
         return numel(self.shape)
 
     def deviceParams(self) -> DeviceTensorParams:
-        return DeviceTensorParams(self.storage.data, self.dtype, self.offset, self.shape, self.size, self.strides)
+        p = self.__dict__.get("_params")
+        if p is None or p.data != self.storage.data:
+            p = DeviceTensorParams(self.storage.data, self.dtype, self.offset, self.shape, self.size, self.strides)
+            self.__dict__["_params"] = p
+        return p
 
     def isContiguous(self) -> bool:
         return self.strides == contiguous_strides(self.shape)
@@ -212,6 +216,7 @@ class TensorValue:
             lhs, rhs, result = TensorValue._prepare(self, rhs)
             getattr(self.device, name)(lhs.deviceParams(), rhs.deviceParams(), result.deviceParams())
             self.__dict__.update(result.__dict__)
+            self.__dict__.pop("_params", None)
             return self
         getattr(self.device, name)(self.deviceParams(), rhs.deviceParams(), self.deviceParams())
         return self
