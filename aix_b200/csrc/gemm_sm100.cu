@@ -11,8 +11,10 @@
 //   * warps 2-5 read the accumulator with tcgen05.ld, convert and store C.
 // Operands may be K-major or MN-major (row- or column-major views): the shared-memory matrix descriptors and the
 // TMA boxes are chosen per operand, so forward (A.B), dX (G.B^T) and dW (A^T.G) run without materialised transposes.
-// f32 problems are computed as three TF32 products of a hi/lo split (a = hi + lo): C = Ahi.Bhi + Alo.Bhi + Ahi.Blo,
-// accumulated in f32, which keeps f32-level accuracy; the split pass also makes both operands K-major.
+// f32 problems are split as a = hi + lo with hi = a rounded to TF32: C = hi(A).hi(B) in TF32 plus the two cross terms
+// lo(A).hi(B) and hi(A).lo(B), which are 2^-11 of the result and therefore run as bf16 MMAs (twice the TF32 rate) at no
+// visible loss; lo.lo is dropped. The split pass also makes both operands K-major. Because the tensor core's f32
+// accumulation truncates, K is cut into chunks of 512 whose partial sums the epilogue adds into C with IEEE additions.
 // Every wait on an mbarrier is bounded in time; on expiry the kernel raises an error word and drains.
 #include "gemm.hpp"
 
@@ -53,12 +55,13 @@ struct KernelParams
     uint32_t aBoxBytes, bBoxBytes;
     uint32_t aBoxStepMn, bBoxStepMn;   // MN elements covered by one box (MN-major) / unused (K-major)
     uint32_t idesc;             // tcgen05 instruction descriptor
+    uint32_t idesc16;           // f32 problems: descriptor of the bf16 cross-term passes
     uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
     uint32_t kAdvanceA, kAdvanceB;     // bytes to advance the descriptor start per MMA along K
     uint32_t mmasPerStage;
     uint32_t outDtype;          // F32, F16, BF16
-    uint32_t kPhases;           // 1, or 3 for the split-f32 scheme
-    uint32_t kPerPhase;         // K of the original problem (elements) when kPhases == 3
+    uint32_t kPhases;           // 1, or 3 for f32 problems: two bf16 cross-term passes, then the TF32 main pass
+    uint32_t kPerPhase;         // f32 problems: padded K = offset of the `lo` half inside the bf16 split buffers
     uint32_t chunkBlocks;       // k-blocks folded inside TMEM before the partial result is added to C in f32
     uint32_t chunks;            // number of such partial results per tile (1: plain store)
     uint32_t vectorStores;      // C rows are 16-byte aligned
@@ -247,6 +250,7 @@ __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const
 
 template <bool Tf32>
 __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                                           const __grid_constant__ CUtensorMap mapA16, const __grid_constant__ CUtensorMap mapB16,
                                                            const __grid_constant__ KernelParams p)
 {
     extern __shared__ uint8_t rawSmem[];
@@ -289,26 +293,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 {
                 const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
                 for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
-                for (uint32_t kb = kbBegin; kb < kbBegin + kbCount; ++kb)
+                {
+                // f32 problems: passes 0 and 1 are the cross terms lo(A).hi(B) and hi(A).lo(B) from the bf16 split
+                // buffers (64 elements of K per stage); they go first, while the accumulator is still tiny. Pass 2 is
+                // hi(A).hi(B) in TF32 (32 elements per stage).
+                const bool cross = Tf32 && passIndex < 2;
+                const uint32_t first = cross ? kbBegin >> 1 : kbBegin, count = cross ? kbCount >> 1 : kbCount;
+                const uint32_t blockK = cross ? 64u : p.blockK;
+                const CUtensorMap* ma = cross ? &mapA16 : &mapA;
+                const CUtensorMap* mb = cross ? &mapB16 : &mapB;
+                const uint32_t offA = (cross && passIndex == 0) ? p.kPerPhase : 0u, offB = (cross && passIndex == 1) ? p.kPerPhase : 0u;
+                for (uint32_t kb = first; kb < first + count; ++kb)
                 {
                     if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
                     mbarExpectTx(&s.full[stage], stageBytes);
-                    // Split-f32: K is laid out as [hi | lo] per operand. Per chunk the two small products (lo.hi, hi.lo)
-                    // go first, while the accumulator is still tiny, then hi.hi.
-                    const uint32_t pass = p.kPhases == 3 ? (passIndex == 2 ? 0u : passIndex + 1u) : 0u;
-                    const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
-                    const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
+                    const int32_t kA = static_cast<int32_t>(kb * blockK + offA), kB = static_cast<int32_t>(kb * blockK + offB);
                     for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
                     {
-                        if (p.aMnMajor) tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], &mapA, &s.full[stage], m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
-                        else            tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], &mapA, &s.full[stage], kA, m0);
+                        if (p.aMnMajor) tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], ma, &s.full[stage], m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
+                        else            tmaLoad2d(&s.a[stage][bx * p.aBoxBytes], ma, &s.full[stage], kA, m0);
                     }
                     for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
                     {
-                        if (p.bMnMajor) tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], &mapB, &s.full[stage], n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
-                        else            tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], &mapB, &s.full[stage], kB, n0);
+                        if (p.bMnMajor) tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], mb, &s.full[stage], n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
+                        else            tmaLoad2d(&s.b[stage][bx * p.bBoxBytes], mb, &s.full[stage], kB, n0);
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
                 }
                 }
             }
@@ -323,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             const uint64_t descHiA = smemDescriptor(0, p.aLbo, 1024), descHiB = smemDescriptor(0, p.bLbo, 1024);
             const uint32_t descLoA = (smemAddr(&s.a[0][0]) & 0x3FFFFu) >> 4, descLoB = (smemAddr(&s.b[0][0]) & 0x3FFFFu) >> 4;
             const uint32_t aStageBytes = sizeof(s.a[0]), bStageBytes = sizeof(s.b[0]);
-            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc;
+            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc, idesc16 = p.idesc16;
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
@@ -333,17 +344,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
                 fenceAfterSync();
                 const uint32_t tmemD = tmemBase + acc * kBlockN;
                 const uint32_t kbCount = min(p.kBlocks - c * p.chunkBlocks, p.chunkBlocks);
-                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2), then kbCount TF32 stages
+                const uint32_t stagesInChunk = Tf32 ? 2 * kbCount : kbCount;
+                for (uint32_t it = 0; it < stagesInChunk; ++it)
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
                     const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
+                    const bool cross = Tf32 && it < kbCount;
                     #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j)
                     {
                         const uint64_t da = descHiA | static_cast<uint64_t>(aLo + j * advA);
                         const uint64_t db = descHiB | static_cast<uint64_t>(bLo + j * advB);
-                        umma<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
+                        if (cross) umma<false>(tmemD, da, db, idesc16, (it | j) != 0 ? 1u : 0u);
+                        else       umma<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
                     ummaCommit(&s.empty[stage]);           // the stage is free once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -473,7 +488,8 @@ __device__ __forceinline__ void ummaCommitPair(uint64_t* bar)
 
 template <bool Tf32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ KernelParams p)
+gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
+               const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ KernelParams p)
 {
     extern __shared__ uint8_t rawSmem[];
     PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
@@ -520,25 +536,31 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 {
                     const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
                     for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
-                    for (uint32_t kb = kbBegin; kb < kbBegin + kbCount; ++kb)
+                    {
+                    const bool cross = Tf32 && passIndex < 2;          // see gemmKernel: bf16 cross terms first
+                    const uint32_t first = cross ? kbBegin >> 1 : kbBegin, count = cross ? kbCount >> 1 : kbCount;
+                    const uint32_t blockK = cross ? 64u : p.blockK;
+                    const CUtensorMap* ma = cross ? &mapA16 : &mapA;
+                    const CUtensorMap* mb = cross ? &mapB16 : &mapB;
+                    const uint32_t offA = (cross && passIndex == 0) ? p.kPerPhase : 0u, offB = (cross && passIndex == 1) ? p.kPerPhase : 0u;
+                    for (uint32_t kb = first; kb < first + count; ++kb)
                     {
                         if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
                         const uint32_t leaderFull = leaderFull0 + stage * 8;
                         mbarExpectTxCluster(leaderFull, stageBytes);
-                        const uint32_t pass = p.kPhases == 3 ? (passIndex == 2 ? 0u : passIndex + 1u) : 0u;
-                        const int32_t kA = static_cast<int32_t>(kb * p.blockK + (pass == 1 ? p.kPerPhase : 0));
-                        const int32_t kB = static_cast<int32_t>(kb * p.blockK + (pass == 2 ? p.kPerPhase : 0));
+                        const int32_t kA = static_cast<int32_t>(kb * blockK + offA), kB = static_cast<int32_t>(kb * blockK + offB);
                         for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
                         {
-                            if (p.aMnMajor) tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], &mapA, leaderFull, m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
-                            else            tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], &mapA, leaderFull, kA, m0);
+                            if (p.aMnMajor) tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
+                            else            tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, kA, m0);
                         }
                         for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
                         {
-                            if (p.bMnMajor) tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], &mapB, leaderFull, n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
-                            else            tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], &mapB, leaderFull, kB, n0);
+                            if (p.bMnMajor) tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
+                            else            tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, kB, n0);
                         }
                         if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    }
                     }
                 }
             }
@@ -553,7 +575,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint64_t descHiA = smemDescriptor(0, p.aLbo, 1024), descHiB = smemDescriptor(0, p.bLbo, 1024);
             const uint32_t descLoA = (smemAddr(&s.a[0][0]) & 0x3FFFFu) >> 4, descLoB = (smemAddr(&s.b[0][0]) & 0x3FFFFu) >> 4;
             const uint32_t aStageBytes = sizeof(s.a[0]), bStageBytes = sizeof(s.b[0]);
-            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc;
+            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc, idesc16 = p.idesc16;
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
@@ -563,17 +585,21 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 fenceAfterSync();
                 const uint32_t tmemD = tmemBase + acc * kBlockN;
                 const uint32_t kbCount = min(p.kBlocks - c * p.chunkBlocks, p.chunkBlocks);
-                for (uint32_t it = 0; it < kbCount * p.kPhases; ++it)
+                // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2), then kbCount TF32 stages
+                const uint32_t stagesInChunk = Tf32 ? 2 * kbCount : kbCount;
+                for (uint32_t it = 0; it < stagesInChunk; ++it)
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
                     const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
+                    const bool cross = Tf32 && it < kbCount;
                     #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j)
                     {
                         const uint64_t da = descHiA | static_cast<uint64_t>(aLo + j * advA);
                         const uint64_t db = descHiB | static_cast<uint64_t>(bLo + j * advB);
-                        ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
+                        if (cross) ummaPair<false>(tmemD, da, db, idesc16, (it | j) != 0 ? 1u : 0u);
+                        else       ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
                     ummaCommitPair(&s.empty[stage]);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
@@ -635,9 +661,12 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     if (threadIdx.x == 0 && s.abortFlag) atomicExch(p.errorWord, 1u);
 }
 
-// ---- f32 split pass: src (any 2-D strides) -> dst[rows][2*k] = [hi(k) | lo(k)], K-major, zero padded to kPad ------
+// ---- f32 split pass: src (any 2-D strides) -> K-major scratch, zero padded to kPad (a multiple of 64) ---------------
+//   hi32[rows][kPad]      a rounded to TF32 (low 13 mantissa bits zero): operand of the main pass
+//   pair16[rows][2*kPad]  [ bf16(a) | bf16(a - hi) ]: operands of the two cross-term passes
 __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ src, uint64_t rowStride, uint64_t colStride,
-                                                      uint32_t rows, uint32_t k, uint32_t kPad, float* __restrict__ dst)
+                                                      uint32_t rows, uint32_t k, uint32_t kPad, float* __restrict__ hi32,
+                                                      uint16_t* __restrict__ pair16)
 {
     // One CTA handles a 32 x 32 tile through shared memory so that both the strided read and the dense write coalesce
     // whichever way the source is laid out.
@@ -647,7 +676,6 @@ __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ 
     const bool colContiguous = colStride == 1;
     for (uint32_t i = ty; i < 32; i += 8)
     {
-        // read so that the contiguous source direction maps to tx
         const uint32_t r = colContiguous ? r0 + i : r0 + tx;
         const uint32_t c = colContiguous ? c0 + tx : c0 + i;
         float v = 0.f;
@@ -661,10 +689,15 @@ __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ 
         if (r < rows && c < kPad)
         {
             const float v = tile[i][tx];
-            const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);     // exactly representable in TF32
-            float* out = dst + static_cast<uint64_t>(r) * (2ull * kPad);
-            out[c] = hi;
-            out[kPad + c] = v - hi;
+            const uint32_t bits = __float_as_uint(v);
+            // round to nearest even at 10 mantissa bits; values that would overflow keep their truncated form
+            uint32_t rounded = (bits + 0xFFFu + ((bits >> 13) & 1u)) & 0xFFFFE000u;
+            if ((rounded & 0x7F800000u) == 0x7F800000u) rounded = bits & 0xFFFFE000u;
+            const float hi = __uint_as_float(rounded);
+            hi32[static_cast<uint64_t>(r) * kPad + c] = hi;
+            uint16_t* out = pair16 + static_cast<uint64_t>(r) * (2ull * kPad);
+            out[c] = dev::f32ToBf16(v);
+            out[kPad + c] = dev::f32ToBf16(v - hi);
         }
     }
 }
@@ -763,7 +796,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     p.outDtype = q.dtype;
     p.vectorStores = (reinterpret_cast<uintptr_t>(q.c) % 16 == 0) && ((q.n * dtypeSize(q.dtype)) % 16 == 0);
     p.errorWord = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + 128);
-    CUtensorMap mapA, mapB;
+    CUtensorMap mapA, mapB, mapA16, mapB16;
     const bool tf32 = q.dtype == F32;
 
     if (!tf32)
@@ -799,21 +832,24 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.bLbo = 0; p.kAdvanceB = 32;
             if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, bRows)) return false;
         }
+        mapA16 = mapA; mapB16 = mapB;                      // unused by 16-bit problems
         // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
         p.idesc = (1u << 4) | ((q.dtype == BF16 ? 1u : 0u) << 7) | ((q.dtype == BF16 ? 1u : 0u) << 10) |
                   ((a.mnMajor ? 1u : 0u) << 15) | ((b.mnMajor ? 1u : 0u) << 16) | ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
     }
     else
     {
-        // hi/lo split into K-major scratch: A' [m][2*kPad], B' [n][2*kPad]
-        const uint32_t kPad = (p.k + 31) & ~31u;
-        const size_t bytesA = static_cast<size_t>(p.m) * 2 * kPad * 4, bytesB = static_cast<size_t>(p.n) * 2 * kPad * 4;
-        float* splitA = static_cast<float*>(device.temporary(bytesA));
-        float* splitB = static_cast<float*>(device.temporary(bytesB));
+        // Split into K-major scratch (see splitF32Kernel). kPad is a multiple of 64 so that bf16 stages (64 elements)
+        // and TF32 stages (32 elements) cover the same K ranges.
+        const uint32_t kPad = (p.k + 63) & ~63u;
+        float* hiA = static_cast<float*>(device.temporary(static_cast<size_t>(p.m) * kPad * 4));
+        float* hiB = static_cast<float*>(device.temporary(static_cast<size_t>(p.n) * kPad * 4));
+        uint16_t* pairA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
+        uint16_t* pairB = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.n) * 2 * kPad * 2));
         dim3 gridA((kPad + 31) / 32, (p.m + 31) / 32), gridB((kPad + 31) / 32, (p.n + 31) / 32);
-        splitF32Kernel<<<gridA, 256, 0, ctx.stream>>>(static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, splitA);
+        splitF32Kernel<<<gridA, 256, 0, ctx.stream>>>(static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, hiA, pairA);
         // B is k x n: its "rows" for the split are the n columns
-        splitF32Kernel<<<gridB, 256, 0, ctx.stream>>>(static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, splitB);
+        splitF32Kernel<<<gridB, 256, 0, ctx.stream>>>(static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, hiB, pairB);
         if (ctx.launches) *ctx.launches += 2;
         p.blockK = 32;
         p.kBlocks = kPad / 32;
@@ -824,9 +860,13 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.mmasPerStage = 4;
         p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
         p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.kAdvanceB = 32;
-        if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitA, 2ull * kPad, q.m, 2ull * kPad * 4, 32, kBlockM)) return false;
-        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, splitB, 2ull * kPad, q.n, 2ull * kPad * 4, 32, bRows)) return false;
-        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
+        if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiA, kPad, q.m, static_cast<uint64_t>(kPad) * 4, 32, kBlockM)) return false;
+        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiB, kPad, q.n, static_cast<uint64_t>(kPad) * 4, 32, bRows)) return false;
+        if (!makeMap(&mapA16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairA, 2ull * kPad, q.m, 2ull * kPad * 2, 64, kBlockM)) return false;
+        if (!makeMap(&mapB16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairB, 2ull * kPad, q.n, 2ull * kPad * 2, 64, bRows)) return false;
+        const uint32_t shape = ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
+        p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | shape;            // D f32, A/B tf32
+        p.idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | shape;          // D f32, A/B bf16
     }
 
     const size_t smemBytes = sizeof(SharedStorage) + 1024;
@@ -862,14 +902,14 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             }
         });
         const uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
-        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, p);
-        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, p);
+        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
+        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
         if (ctx.launches) ++*ctx.launches;
         return true;
     }
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(ctx.smCount));
-    if (tf32) gemmKernel<true><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
-    else      gemmKernel<false><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, p);
+    if (tf32) gemmKernel<true><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
+    else      gemmKernel<false><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
     if (ctx.launches) ++*ctx.launches;
     return true;
 }
