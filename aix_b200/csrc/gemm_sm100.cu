@@ -248,6 +248,40 @@ __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const
     }
 }
 
+// Epilogue of one accumulator (blockN columns of one tile row per thread). Two 32-column strips are in flight at a
+// time: both TMEM loads are issued before the single wait, and for partial results after the first (split-f32 scheme)
+// the values C already holds are fetched one strip pair ahead, so that neither the TMEM latency nor the global-load
+// latency is paid once per strip.
+__device__ __forceinline__ void loadOld(const KernelParams& p, float4 (&old)[8], uint32_t row, uint32_t col, bool wanted)
+{
+    if (wanted && row < p.m && col + 32 <= p.n)
+    {
+        const float4* in = reinterpret_cast<const float4*>(static_cast<const float*>(p.c) + static_cast<size_t>(row) * p.n + col);
+        #pragma unroll
+        for (int v = 0; v < 8; ++v) old[v] = in[v];
+    }
+}
+
+__device__ __forceinline__ void drainAccumulator(const KernelParams& p, uint32_t taddr, uint32_t row, uint32_t colBase, uint32_t c)
+{
+    const bool addToC = c > 0 && p.outDtype == F32 && p.vectorStores != 0;
+    float4 old0[8], old1[8];
+    loadOld(p, old0, row, colBase, addToC);
+    loadOld(p, old1, row, colBase + 32, addToC);
+    #pragma unroll 1
+    for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)
+    {
+        uint32_t r0[32], r1[32];
+        tmemLoad32(taddr + c0, r0);
+        tmemLoad32(taddr + c0 + 32, r1);
+        tmemLoadWait();
+        storeAccumulatorRow(p, r0, old0, row, colBase + c0, c);
+        if (c0 + 64 < p.blockN) loadOld(p, old0, row, colBase + c0 + 64, addToC);
+        storeAccumulatorRow(p, r1, old1, row, colBase + c0 + 32, c);
+        if (c0 + 64 < p.blockN) loadOld(p, old1, row, colBase + c0 + 96, addToC);
+    }
+}
+
 template <bool Tf32>
 __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                            const __grid_constant__ CUtensorMap mapA16, const __grid_constant__ CUtensorMap mapB16,
@@ -385,25 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             fenceAfterSync();
             const uint32_t row = tm * kBlockM + quarter * 32 + lane;
             const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
-            #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < p.blockN; c0 += 32)
-            {
-                uint32_t r[32];
-                const uint32_t col = tn * p.blockN + c0;
-                // Later partial results are added to what C already holds: fetch that first so the global loads and the
-                // TMEM load are in flight together.
-                float4 old[8];
-                const bool fastF32 = p.outDtype == F32 && p.vectorStores && row < p.m && col + 32 <= p.n;
-                if (fastF32 && c > 0)
-                {
-                    const float4* in = reinterpret_cast<const float4*>(static_cast<const float*>(p.c) + static_cast<size_t>(row) * p.n + col);
-                    #pragma unroll
-                    for (int v = 0; v < 8; ++v) old[v] = in[v];
-                }
-                tmemLoad32(taddr + c0, r);
-                tmemLoadWait();
-                storeAccumulatorRow(p, r, old, row, col, c);
-            }
+            drainAccumulator(p, taddr, row, tn * p.blockN, c);
             fenceBeforeSync();
             mbarArrive(&s.tmemEmpty[acc]);
             acc ^= 1u;
@@ -625,23 +641,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 fenceAfterSync();
                 const uint32_t row = tm * 256 + rank * 128 + quarter * 32 + lane;
                 const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
-                #pragma unroll 1
-                for (uint32_t c0 = 0; c0 < p.blockN; c0 += 32)
-                {
-                    uint32_t r[32];
-                    const uint32_t col = tn * p.blockN + c0;
-                    float4 old[8];
-                    const bool fastF32 = p.outDtype == F32 && p.vectorStores && row < p.m && col + 32 <= p.n;
-                    if (fastF32 && c > 0)
-                    {
-                        const float4* in = reinterpret_cast<const float4*>(static_cast<const float*>(p.c) + static_cast<size_t>(row) * p.n + col);
-                        #pragma unroll
-                        for (int v = 0; v < 8; ++v) old[v] = in[v];
-                    }
-                    tmemLoad32(taddr + c0, r);
-                    tmemLoadWait();
-                    storeAccumulatorRow(p, r, old, row, col, c);
-                }
+                drainAccumulator(p, taddr, row, tn * p.blockN, c);
                 fenceBeforeSync();
                 mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
                 acc ^= 1u;

@@ -27,6 +27,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 DT = {"f32": 1, "bf16": 3}
+# DRAM traffic of the generated chain kernel per element, from the ncu capture at n = 2^26 (1054.9 MB for 2^26 f32
+# elements; the algorithmic figure is 16 bytes). Not captured for bf16.
+TRAFFIC_BYTES_PER_ELEMENT = {"f32": 1054.9e6 / (1 << 26)}
 
 
 def chain(a, b, c, scalar_like):
@@ -264,7 +267,10 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "kernel": "generated fused chain kernel", "bytes_per_launch": chain_bytes,
+                     "traffic": TRAFFIC_BYTES_PER_ELEMENT.get(args.dtype, 0) * n or None,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel at n=2^26 "
+                                       "(profiles/fused_chain_f32_2p26.md), scaled by n: traffic is proportional to n",
+                     "kernel": "generated fused chain kernel", "bytes_per_launch": chain_bytes,
                      "ms_per_launch": chain_ms, "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": achieved / 8000.0},
         "checksum": result_sum,
         "fusion": {k: stats1[k] - stats0[k] for k in ("ops_recorded", "fused_kernels", "fused_ops", "fills_absorbed", "stores_elided",

@@ -88,7 +88,7 @@ typedef struct aixb200_config
     int32_t  disk_cache;         /* 1: keep compiled cubins in $AIXB200_CACHE_DIR (default ~/.cache/aixb200) */
     uint64_t cache_limit_bytes;  /* idle blocks kept by the allocator before it trims (0 = 3/4 of device memory) */
     void*    stream;             /* cudaStream_t to run on; NULL = the device creates its own non-blocking stream */
-    int32_t  tf32x3_matmul;      /* f32 matmul: 1 = 3xBF16/TF32-class split on tensor cores, 0 = CUDA-core f32 */
+    int32_t  tf32x3_matmul;      /* f32 matmul: 1 = split-precision TF32 + bf16 cross terms on tensor cores, 0 = CUDA-core f32 */
     int32_t  dry_run;            /* 1: no GPU is touched - ops are recorded, planned and compiled with NVRTC but not
                                     launched, and memory comes from malloc (host-logic tests on machines without a GPU) */
     int32_t  reserved[6];
