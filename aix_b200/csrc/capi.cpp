@@ -229,6 +229,9 @@ int aixb200_comm_init(aixb200_device* dev, int rank, int nranks, const void* id)
 { return guarded(dev, [&](Device& d) { if (!id) failInvalid("null id"); d.commInit(rank, nranks, id); }); }
 int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale)
 { return guarded(dev, [&](Device& d) { d.allReduce(data, count, dtype, scale); }); }
+int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale)
+{ return guarded(dev, [&](Device& d) { d.allReduceAsync(data, count, dtype, scale); }); }
+int aixb200_comm_wait(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commWait(); }); }
 int aixb200_comm_destroy(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commDestroy(); }); }
 
 }   // extern "C"

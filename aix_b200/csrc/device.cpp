@@ -165,8 +165,8 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_allocator = std::make_unique<CachingAllocator>(raw, limit);
 
     m_scratchBytes = size_t(4) << 20;
-    check(cudaMalloc(&m_scratch, m_scratchBytes), "cudaMalloc(scratch)");
-    check(cudaMemsetAsync(m_scratch, 0, m_scratchBytes, m_stream), "cudaMemset(scratch)");
+    check(cudaMalloc(&m_scratch, m_scratchBytes + kernels::kGemmCounterBytes), "cudaMalloc(scratch)");
+    check(cudaMemsetAsync(m_scratch, 0, m_scratchBytes + kernels::kGemmCounterBytes, m_stream), "cudaMemset(scratch)");
 }
 
 Device::~Device()
@@ -174,7 +174,9 @@ Device::~Device()
     if (!dryRun())
     {
         cudaSetDevice(m_cfg.ordinal);
+        if (m_commStream) cudaStreamSynchronize(m_commStream);
         m_comm.reset();
+        if (m_commStream) { cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork); cudaEventDestroy(m_commJoin); }
         if (m_stream) cudaStreamSynchronize(m_stream);
         for (auto& [key, k] : m_kernels)
             if (k.module) driver().moduleUnload(k.module);
@@ -253,6 +255,7 @@ void Device::synchronize()
 {
     flush();
     if (dryRun()) return;
+    commWait();
     check(cudaStreamSynchronize(m_stream), "cudaStreamSynchronize");
     check(cudaGetLastError(), "asynchronous kernel failure");
     if (m_checkErrorWord)
@@ -264,6 +267,7 @@ void Device::synchronize()
         if (word)
         {
             cudaMemset(static_cast<char*>(m_scratch) + 128, 0, 4);
+            cudaMemset(static_cast<char*>(m_scratch) + m_scratchBytes, 0, kernels::kGemmCounterBytes);   // split-tile counters
             throw Error(AIXB200_ERR_TIMEOUT, "a bounded device-side wait ran out inside the tensor-core matmul; its result is invalid");
         }
     }
@@ -894,6 +898,7 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
     flush();
+    commWait();                 // collectives of one communicator are issued in one order on every rank
     // A scale of exactly 1/ranks on a floating type is the collective's own averaging: no extra pass over the data.
     const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
     m_comm->allReduceSum(data, count, dtype, m_stream, average);
@@ -905,9 +910,48 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
     }
 }
 
+// Overlapped form: the collective runs on a side stream, ordered after everything issued so far on the device's
+// stream; later work on the device's stream does NOT wait for it until commWait(). Between the two calls the caller
+// must leave `data` alone (the gradient of a parameter is final once its last contribution has been accumulated).
+void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double scale)
+{
+    if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");
+    const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
+    if (scale != 1.0 && !average) failInvalid("all_reduce_async: scale must be 1 or 1/ranks on a floating type");
+    flush();
+    if (!m_commStream)
+    {
+        check(cudaStreamCreateWithFlags(&m_commStream, cudaStreamNonBlocking), "cudaStreamCreate(comm)");
+        check(cudaEventCreateWithFlags(&m_commFork, cudaEventDisableTiming), "cudaEventCreate(comm)");
+        check(cudaEventCreateWithFlags(&m_commJoin, cudaEventDisableTiming), "cudaEventCreate(comm)");
+    }
+    check(cudaEventRecord(m_commFork, m_stream), "cudaEventRecord(comm fork)");
+    check(cudaStreamWaitEvent(m_commStream, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
+    m_comm->allReduceSum(data, count, dtype, m_commStream, average);
+    m_commPending = true;
+}
+
+void Device::commWait()
+{
+    if (!m_commPending) return;
+    m_commPending = false;
+    check(cudaEventRecord(m_commJoin, m_commStream), "cudaEventRecord(comm join)");
+    check(cudaStreamWaitEvent(m_stream, m_commJoin, 0), "cudaStreamWaitEvent(comm join)");
+}
+
 void Device::commDestroy()
 {
-    if (m_comm) { cudaStreamSynchronize(m_stream); m_comm.reset(); }
+    if (m_comm)
+    {
+        commWait();
+        cudaStreamSynchronize(m_stream);
+        m_comm.reset();
+    }
+    if (m_commStream)
+    {
+        cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork); cudaEventDestroy(m_commJoin);
+        m_commStream = nullptr; m_commFork = m_commJoin = nullptr;
+    }
 }
 
 }   // namespace aixb200

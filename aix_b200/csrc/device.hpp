@@ -16,6 +16,7 @@
 #include <vector>
 
 typedef struct CUstream_st* cudaStream_t;
+typedef struct CUevent_st* cudaEvent_t;
 typedef struct CUfunc_st* CUfunction;
 typedef struct CUmod_st* CUmodule;
 
@@ -83,6 +84,8 @@ public:
     // data-parallel exchange
     void commInit(int rank, int nranks, const void* id);
     void allReduce(void* data, size_t count, uint32_t dtype, double scale);
+    void allReduceAsync(void* data, size_t count, uint32_t dtype, double scale);
+    void commWait();
     void commDestroy();
 
     // Scratch for fixed kernels (reduction partials, counters); lives as long as the device.
@@ -133,6 +136,9 @@ private:
     std::string m_lastSource;
     aixb200_stats m_stats{};
     std::unique_ptr<Comm> m_comm;
+    cudaStream_t   m_commStream = nullptr;      // side stream of overlapped all-reduces
+    cudaEvent_t    m_commFork = nullptr, m_commJoin = nullptr;
+    bool           m_commPending = false;
     bool m_inFlush = false;
     bool m_checkErrorWord = false;
 };

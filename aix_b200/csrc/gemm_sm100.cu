@@ -65,8 +65,12 @@ struct KernelParams
     uint32_t chunkBlocks;       // k-blocks folded inside TMEM before the partial result is added to C in f32
     uint32_t chunks;            // number of such partial results per tile (1: plain store)
     uint32_t vectorStores;      // C rows are 16-byte aligned
+    uint32_t splitTiles;        // pair kernel: tiles [0, splitTiles) are cut along K and shared by all clusters
+    uint32_t splitUnits;        // splitTiles * kBlocks
     void*    c;
     uint32_t* errorWord;
+    float*   splitWorkspace;    // one 256 x 256 f32 partial accumulator per cluster
+    uint32_t* splitCounters;    // per (split tile, CTA rank): partial accumulators published so far; left at zero
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -445,6 +449,110 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
 // kernel stalls on TMA latency with its 4 stages (tensor pipe 56 % busy at 4096^3). No TMA multicast is used: every
 // CTA loads its own operand slices and signals the leader's `full` barrier (cp.async.bulk.tensor ... .cta_group::2).
 // ==================================================================================================================
+// Work distribution of the pair kernel. A persistent grid loses the idle part of its last wave of tiles (256 tiles on
+// 74 clusters: 3.46 waves cost 4). The remainder tiles [0, splitTiles) are therefore cut along K into `splitUnits`
+// k-blocks that are dealt out evenly: cluster i takes units [i*U/C, (i+1)*U/C), a range shorter than one tile, i.e.
+// the tail of one tile followed by the head of the next. These pieces come FIRST in every cluster's sequence, the whole
+// tiles [splitTiles, tiles) follow round-robin. The cluster that owns the head of a tile (k-block 0) finishes it: the
+// others publish their f32 partial accumulators in a workspace slot of their own and bump a counter; the finisher -
+// which reaches that piece last in its own range, when the others are normally long done - waits for the counter,
+// adds the partials in cluster order (deterministic) and stores C. Nobody ever waits for the finisher, so the wait
+// cannot cycle; it is bounded in time like every other wait of the kernel.
+enum : uint32_t { kWorkWhole = 0, kWorkPartial = 1, kWorkFinish = 2 };
+struct WorkItem
+{
+    uint32_t tile, kbBegin, kbCount, kind;
+    uint32_t partials;          // kWorkFinish: accumulators of the following `partials` clusters belong to this tile
+};
+struct WorkIterator
+{
+    uint32_t cluster, clusters, kBlocks, tiles, unit, unitEnd, units, next;
+    __device__ WorkIterator(const KernelParams& p, uint32_t clusterId, uint32_t clusterCount)
+        : cluster(clusterId), clusters(clusterCount), kBlocks(p.kBlocks), tiles(p.tilesM * p.tilesN),
+          unit(static_cast<uint32_t>(static_cast<uint64_t>(clusterId) * p.splitUnits / clusterCount)),
+          unitEnd(static_cast<uint32_t>(static_cast<uint64_t>(clusterId + 1) * p.splitUnits / clusterCount)),
+          units(p.splitUnits), next(p.splitTiles + clusterId) {}
+    __device__ bool get(WorkItem& w)
+    {
+        if (unit < unitEnd)
+        {
+            w.tile = unit / kBlocks;
+            w.kbBegin = unit - w.tile * kBlocks;
+            w.kbCount = min(kBlocks - w.kbBegin, unitEnd - unit);
+            w.partials = 0;
+            if (w.kbCount == kBlocks) w.kind = kWorkWhole;
+            else if (w.kbBegin != 0) w.kind = kWorkPartial;
+            else
+            {
+                // the cluster whose range holds the tile's last unit u: the largest j with floor(j*U/C) <= u
+                const uint64_t u = static_cast<uint64_t>(w.tile + 1) * kBlocks - 1;
+                const uint32_t last = static_cast<uint32_t>(((u + 1) * clusters - 1) / units);
+                w.kind = kWorkFinish;
+                w.partials = last - cluster;
+            }
+            unit += w.kbCount;
+            return true;
+        }
+        if (next < tiles)
+        {
+            w.tile = next; w.kbBegin = 0; w.kbCount = kBlocks; w.kind = kWorkWhole; w.partials = 0;
+            next += clusters;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ void epilogueBarrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // warps 2..5 only
+
+// kWorkPartial: the accumulator row of this thread goes to the cluster's workspace slot as f32.
+__device__ __forceinline__ void publishPartial(const KernelParams& p, uint32_t taddr, float* slotRow)
+{
+    #pragma unroll 1
+    for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)
+    {
+        uint32_t r0[32], r1[32];
+        tmemLoad32(taddr + c0, r0);
+        tmemLoad32(taddr + c0 + 32, r1);
+        tmemLoadWait();
+        float4* out = reinterpret_cast<float4*>(slotRow + c0);
+        #pragma unroll
+        for (int v = 0; v < 8; ++v)
+            out[v] = make_float4(__uint_as_float(r0[4 * v]), __uint_as_float(r0[4 * v + 1]), __uint_as_float(r0[4 * v + 2]), __uint_as_float(r0[4 * v + 3]));
+        #pragma unroll
+        for (int v = 0; v < 8; ++v)
+            out[8 + v] = make_float4(__uint_as_float(r1[4 * v]), __uint_as_float(r1[4 * v + 1]), __uint_as_float(r1[4 * v + 2]), __uint_as_float(r1[4 * v + 3]));
+    }
+}
+
+// kWorkFinish: own accumulator plus the partials of the following clusters (read through L2), then the usual store.
+__device__ __forceinline__ void finishTile(const KernelParams& p, uint32_t taddr, uint32_t row, uint32_t colBase, const float* firstSlotRow,
+                                           size_t slotStride, uint32_t partials)
+{
+    const float4 unusedOld[8] = {};
+    #pragma unroll 1
+    for (uint32_t c0 = 0; c0 < p.blockN; c0 += 32)
+    {
+        uint32_t r[32];
+        tmemLoad32(taddr + c0, r);
+        tmemLoadWait();
+        for (uint32_t j = 0; j < partials; ++j)
+        {
+            const float4* in = reinterpret_cast<const float4*>(firstSlotRow + j * slotStride + c0);
+            #pragma unroll
+            for (int v = 0; v < 8; ++v)
+            {
+                const float4 x = __ldcg(in + v);
+                r[4 * v]     = __float_as_uint(__uint_as_float(r[4 * v]) + x.x);
+                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + x.y);
+                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + x.z);
+                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + x.w);
+            }
+        }
+        storeAccumulatorRow(p, r, unusedOld, row, colBase + c0, 0);
+    }
+}
+
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytesB = 128 * 128;
 
@@ -532,7 +640,6 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     clusterSync();                      // barriers of both CTAs are initialised before anyone signals across
     fenceAfterSync();
     const uint32_t tmemBase = s.tmemBase;
-    const uint32_t totalTiles = p.tilesM * p.tilesN;                 // tiles of 256 x 256
     const uint32_t clusterId = blockIdx.x >> 1, clusters = gridDim.x >> 1;
 
     if (warp == 0)
@@ -543,14 +650,16 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             bool ok = true;
             const uint32_t stageBytes = p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes;
             const uint32_t leaderFull0 = mapToCta(smemAddr(&s.full[0]), 0);
-            for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+            WorkIterator work(p, clusterId, clusters);
+            WorkItem w;
+            while (ok && work.get(w))
             {
                 uint32_t tm, tn;
-                tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+                tileCoordinates(w.tile, p.tilesM, p.tilesN, tm, tn);
                 const int32_t m0 = static_cast<int32_t>(tm * 256 + rank * 128), n0 = static_cast<int32_t>(tn * p.blockN + rank * (p.blockN >> 1));
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
-                    const uint32_t kbBegin = c * p.chunkBlocks, kbCount = min(p.kBlocks - kbBegin, p.chunkBlocks);
+                    const uint32_t kbBegin = w.kbBegin + c * p.chunkBlocks, kbCount = min(w.kbBegin + w.kbCount - kbBegin, p.chunkBlocks);
                     for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
                     {
                     const bool cross = Tf32 && passIndex < 2;          // see gemmKernel: bf16 cross terms first
@@ -594,13 +703,15 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc, idesc16 = p.idesc16;
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
-            for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+            WorkIterator work(p, clusterId, clusters);
+            WorkItem w;
+            while (ok && work.get(w))
             for (uint32_t c = 0; c < p.chunks && ok; ++c)
             {
                 if (!mbarWait(&s.tmemEmpty[acc], accPhase ^ 1u, abortFlag)) { ok = false; break; }
                 fenceAfterSync();
                 const uint32_t tmemD = tmemBase + acc * kBlockN;
-                const uint32_t kbCount = min(p.kBlocks - c * p.chunkBlocks, p.chunkBlocks);
+                const uint32_t kbCount = min(w.kbCount - c * p.chunkBlocks, p.chunkBlocks);
                 // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2), then kbCount TF32 stages
                 const uint32_t stagesInChunk = Tf32 ? 2 * kbCount : kbCount;
                 for (uint32_t it = 0; it < stagesInChunk; ++it)
@@ -629,24 +740,75 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     else
     {
         const uint32_t quarter = warp & 3u;
+        const bool captain = threadIdx.x == 64;                          // first thread of the epilogue warps
+        const uint32_t rowInCta = quarter * 32 + lane;
+        const size_t slotStride = size_t(2) * 128 * 256;                 // floats per cluster slot of the workspace
         uint32_t acc = 0, accPhase = 0;
         bool ok = true;
-        for (uint32_t t = clusterId; t < totalTiles && ok; t += clusters)
+        WorkIterator work(p, clusterId, clusters);
+        WorkItem w;
+        while (ok && work.get(w))
         {
             uint32_t tm, tn;
-            tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
-            for (uint32_t c = 0; c < p.chunks && ok; ++c)
+            tileCoordinates(w.tile, p.tilesM, p.tilesN, tm, tn);
+            const uint32_t row = tm * 256 + rank * 128 + rowInCta;
+            const uint32_t leaderEmpty = mapToCta(smemAddr(&s.tmemEmpty[0]), 0);
+            if (w.kind == kWorkWhole)
             {
-                if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
-                fenceAfterSync();
-                const uint32_t row = tm * 256 + rank * 128 + quarter * 32 + lane;
-                const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
-                drainAccumulator(p, taddr, row, tn * p.blockN, c);
-                fenceBeforeSync();
-                mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
-                acc ^= 1u;
-                if (acc == 0) accPhase ^= 1u;
+                for (uint32_t c = 0; c < p.chunks && ok; ++c)
+                {
+                    if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
+                    fenceAfterSync();
+                    const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
+                    drainAccumulator(p, taddr, row, tn * p.blockN, c);
+                    fenceBeforeSync();
+                    mbarArriveCluster(leaderEmpty + acc * 8);
+                    acc ^= 1u;
+                    if (acc == 0) accPhase ^= 1u;
+                }
+                continue;
             }
+            if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
+            fenceAfterSync();
+            const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
+            uint32_t* counter = p.splitCounters + (w.tile * 2 + rank);
+            if (w.kind == kWorkPartial)
+            {
+                publishPartial(p, taddr, p.splitWorkspace + clusterId * slotStride + (rank * 128 + rowInCta) * size_t(256));
+                fenceBeforeSync();
+                mbarArriveCluster(leaderEmpty + acc * 8);
+                __threadfence();
+                epilogueBarrier();
+                if (captain) atomicAdd(counter, 1u);
+            }
+            else
+            {
+                if (captain)
+                {
+                    const uint64_t start = globalTimerNs();
+                    uint32_t seen = 0, spins = 0;
+                    for (;;)
+                    {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                        if (seen >= w.partials) break;
+                        if ((++spins & 63u) == 0)
+                        {
+                            if (*abortFlag) break;
+                            if (globalTimerNs() - start > kWaitLimitNs) { *abortFlag = 1; break; }
+                        }
+                    }
+                    __threadfence();
+                }
+                epilogueBarrier();
+                if (*abortFlag) { ok = false; break; }
+                finishTile(p, taddr, row, tn * p.blockN,
+                           p.splitWorkspace + (clusterId + 1) * slotStride + (rank * 128 + rowInCta) * size_t(256), slotStride, w.partials);
+                fenceBeforeSync();
+                mbarArriveCluster(leaderEmpty + acc * 8);
+                if (captain) *counter = 0;            // every partial of this tile has arrived: ready for the next launch
+            }
+            acc ^= 1u;
+            if (acc == 0) accPhase ^= 1u;
         }
     }
 
@@ -784,7 +946,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         auto efficiency = [&](uint32_t blockN, double perTile)
         {
             const double tiles = static_cast<double>(p.tilesM) * ((p.n + blockN - 1) / blockN);
-            const double waves = std::ceil(tiles / workers);
+            // 16-bit problems on CTA pairs share the remainder wave along K (see WorkIterator): no idle tail to model
+            const bool sharedTail = pair && q.dtype != F32 && (q.k + 63) / 64 >= 8 && tiles * ((q.k + 63) / 64) >= workers;
+            const double waves = sharedTail ? std::max(1.0, tiles / workers) : std::ceil(tiles / workers);
             return perTile * tiles / (waves * workers) * (static_cast<double>(p.n) / (((p.n + blockN - 1) / blockN) * blockN));
         };
         static const int forced = []{ const char* v = std::getenv("AIXB200_GEMM_BLOCKN"); return v ? std::atoi(v) : 0; }();
@@ -901,7 +1065,25 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                 maxClusters = ctx.smCount / 2;
             }
         });
-        const uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
+        uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
+        // Remainder tiles are cut along K and shared by all clusters (see WorkIterator) when that saves at least a few
+        // stages of idle time per cluster; split-f32 problems keep whole tiles (their partial sums already go through C).
+        static const bool splitEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_SPLITK"); return !(v && v[0] == '0'); }();
+        const uint32_t remainder = tiles % static_cast<uint32_t>(maxClusters);
+        if (splitEnabled && !tf32 && remainder != 0 && p.kBlocks >= 8)
+        {
+            const uint64_t units = static_cast<uint64_t>(remainder) * p.kBlocks;
+            const uint64_t idleStages = (static_cast<uint64_t>(maxClusters) - remainder) * p.kBlocks / maxClusters;
+            if (idleStages >= 6 && units >= static_cast<uint64_t>(maxClusters) && units < 0x7FFFFFFFull)
+            {
+                clusters = static_cast<uint32_t>(maxClusters);
+                p.splitTiles = remainder;
+                p.splitUnits = static_cast<uint32_t>(units);
+                p.splitWorkspace = static_cast<float*>(device.temporary(static_cast<size_t>(clusters) * 2 * 128 * 256 * sizeof(float)));
+                p.splitCounters = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + ctx.scratchBytes);
+                if (2ull * remainder * sizeof(uint32_t) > kernels::kGemmCounterBytes) return false;
+            }
+        }
         if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
         else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
         if (ctx.launches) ++*ctx.launches;

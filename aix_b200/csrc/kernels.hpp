@@ -20,6 +20,8 @@ struct LaunchContext
 // Layout of the scratch block shared by the reduction kernels.
 constexpr size_t kScratchCounterBytes = 256;        // ticket counters at the start
 constexpr size_t kMaxReduceBlocks     = 4096;       // upper bound of partials a full reduction may write
+// The device allocates this much beyond LaunchContext::scratchBytes: counters of the tensor-core matmul's split tiles.
+constexpr size_t kGemmCounterBytes    = 4096;
 
 // ---- full reductions (Device::sum / Device::max, aixDevice.hpp:52,60) -----------------------------------------
 // dst[0] = sum or max of all elements of src, in src's element type.

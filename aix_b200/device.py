@@ -246,6 +246,11 @@ class DeviceB200:
     def allReduce(self, data: int, count: int, dtype: int, scale: float = 1.0):
         self._check(self._lib.aixb200_all_reduce(self._h, data, count, dtype, scale))
 
+    def allReduceAsync(self, data: int, count: int, dtype: int, scale: float = 1.0):
+        self._check(self._lib.aixb200_all_reduce_async(self._h, data, count, dtype, scale))
+
+    def commWait(self): self._check(self._lib.aixb200_comm_wait(self._h))
+
     def commDestroy(self): self._check(self._lib.aixb200_comm_destroy(self._h))
 
     # Host <-> device helpers built on copy / copyImmediate (what TensorValue's host-pointer constructor and

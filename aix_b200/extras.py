@@ -76,11 +76,11 @@ def measure_matmul(dev, tensor_peak, size=4096):
     return out
 
 
-def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batch=4096, barrier=None, reduce_max=None):
+def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batch=4096, barrier=None, reduce_max=None, overlap=True):
     """MLP training configuration: device time of `steps` steps (forward, backward, gradient all-reduce when
     world_size > 1, Adam), loss not read inside the timed region."""
     from .mlp import MlpTrainer
-    trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size)
+    trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size, overlap=overlap)
     for _ in range(warmup):
         loss = trainer.step()
     first = float(loss.value.item())
@@ -105,6 +105,8 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
             "kernel_launches_per_step": (s1["total_kernel_launches"] - s0["total_kernel_launches"]) / steps,
             "fused_kernels_per_step": (s1["fused_kernels"] - s0["fused_kernels"]) / steps,
             "device_calls_per_step": (s1["ops_recorded"] - s0["ops_recorded"]) / steps,
+            "gradient_exchange": "none" if world_size == 1 else ("all-reduce per parameter, started inside backward" if overlap
+                                                                  else "all-reduce per parameter after backward"),
             "loss_after_warmup": first, "loss_at_end": last}
 
 

@@ -28,6 +28,7 @@ class TensorNode:
         self.inputs: List["TensorNode"] = []
         self.backwardFunc: Callable = defaultBackward
         self._grad: Optional[TensorValue] = None
+        self.gradReadyHook: Optional[Callable] = None   # no counterpart in the reference; see GradientExchange
 
     def grad(self) -> TensorValue:
         if self._grad is None:
@@ -57,6 +58,8 @@ def defaultBackward(node: TensorNode, seed: TensorValue):
     if node.requireGrad and not node.retainGrad:
         g = node.grad()
         g += seed                                  # in-place Device::add into the gradient buffer
+        if node.gradReadyHook is not None:
+            node.gradReadyHook(node)
 
 
 def broadcastBackwardFunc(node, seed):
@@ -293,3 +296,38 @@ def all_reduce_gradients(device, parameters: Sequence[Tensor], world_size: int):
     for p in parameters:
         g = p.grad()
         device.allReduce(g.storage.data, g.size, g.dtype, 1.0 / world_size)
+
+
+class GradientExchange:
+    """The same exchange, overlapped with the rest of backward(): as soon as a parameter's gradient has been accumulated
+    (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side stream, so that the collectives
+    of the late layers run under the matmuls of the early ones; `finish()` orders the device's stream after all of
+    them and goes between backward() and step(). The reference would need one hook call at the end of defaultBackward.
+
+    Valid when every parameter receives exactly one gradient contribution per backward pass (true for a feed-forward
+    stack); a second contribution to a gradient already in flight raises instead of racing with the collective."""
+
+    def __init__(self, device, parameters: Sequence[Tensor], world_size: int):
+        self.device, self.world_size = device, world_size
+        self.parameters = list(parameters)
+        self._inFlight = set()
+        if world_size > 1:
+            for p in self.parameters:
+                p.node.gradReadyHook = self._ready
+
+    def _ready(self, node: TensorNode):
+        if id(node) in self._inFlight:
+            raise RuntimeError("GradientExchange: a parameter received a second gradient contribution while its "
+                               "all-reduce was in flight; use all_reduce_gradients for this model")
+        self._inFlight.add(id(node))
+        g = node.grad()
+        self.device.allReduceAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
+
+    def finish(self):
+        if self.world_size > 1:
+            self.device.commWait()
+            self._inFlight.clear()
+
+    def detach(self):
+        for p in self.parameters:
+            p.node.gradReadyHook = None

@@ -4,7 +4,7 @@ all-reduce over the ranks) + optimizer step, issued through the mirrored front e
 import numpy as np
 
 from . import _capi as C
-from .frontend import Adam, Linear, MSELoss, Sequential, Tanh, Tensor, all_reduce_gradients
+from .frontend import Adam, GradientExchange, Linear, MSELoss, Sequential, Tanh, Tensor, all_reduce_gradients
 from .tensor import TensorValue
 
 DEFAULT_DIMS = (1024, 4096, 4096, 4096, 1024)
@@ -30,7 +30,8 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 
 class MlpTrainer:
-    def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None):
+    def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
+                 overlap=True):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -45,6 +46,8 @@ class MlpTrainer:
         self.y = Tensor(TensorValue.from_numpy(y, device))
         self.optimizer = Adam(self.model.parameters(), lr=lr)      # created after the parameters live on the device
         self.loss_fn = MSELoss()
+        # overlap=True: each gradient's all-reduce starts inside backward(); False: all of them after it
+        self.exchange = GradientExchange(device, self.model.parameters(), world_size) if overlap and world_size > 1 else None
         self.flops_per_step = 2.0 * batch * sum(a * b for a, b in zip(dims[:-1], dims[1:])) * 3 \
             - 2.0 * batch * dims[0] * dims[1]                        # forward + dW + dX (no dX for the first layer)
 
@@ -58,7 +61,10 @@ class MlpTrainer:
         loss = self.loss_fn(pred, self.y)
         self.optimizer.zeroGrad()
         loss.backward()
-        all_reduce_gradients(self.device, self.model.parameters(), self.world_size)
+        if self.exchange is not None:
+            self.exchange.finish()
+        else:
+            all_reduce_gradients(self.device, self.model.parameters(), self.world_size)
         self.optimizer.step()
         return loss
 

@@ -291,6 +291,10 @@ def main():
             line["mlp_train"] = measure_mlp(dev, tensor_peak, steps=max(3, min(args.steps, 10)), warmup=3, rank=rank, world_size=world,
                                             barrier=barrier, reduce_max=max_over_ranks)
             if world > 1:
+                # the same steps with every all-reduce issued after backward(), to show what the overlap buys
+                plain = measure_mlp(dev, tensor_peak, steps=max(3, min(args.steps, 10)), warmup=3, rank=rank, world_size=world,
+                                    barrier=barrier, reduce_max=max_over_ranks, overlap=False)
+                line["mlp_train"]["ms_per_step_exchange_after_backward"] = plain["ms_per_step"]
                 dev.commDestroy()
         except Exception as exc:
             line["mlp_train"] = {"error": str(exc)}

@@ -1,0 +1,51 @@
+"""Child process of tests/test_gpu_comm.py: one data-parallel rank on its own GPU.
+
+    python tests/_dp_worker.py <rank> <world> <dir> <overlap 0|1> <steps>
+
+Rank 0 publishes the communicator id through a file in <dir>; every rank trains the small MLP and writes its parameters
+and losses to <dir>/rank<r>_<overlap>.npz."""
+import os
+import sys
+import time
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from aix_b200 import DeviceB200                      # noqa: E402
+from aix_b200.mlp import MlpTrainer                  # noqa: E402
+
+DIMS = (256, 512, 512, 128)
+BATCH = 384
+
+
+def main():
+    rank, world, out_dir, overlap, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4] == "1", int(sys.argv[5])
+    id_path = os.path.join(out_dir, f"comm_id_{int(overlap)}")
+    if rank == 0:
+        unique = DeviceB200.commUniqueId()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(unique)
+        os.replace(id_path + ".tmp", id_path)
+    else:
+        deadline = time.time() + 120
+        while not os.path.exists(id_path):
+            if time.time() > deadline:
+                raise SystemExit("rank 0 never published the communicator id")
+            time.sleep(0.05)
+        with open(id_path, "rb") as f:
+            unique = f.read()
+    dev = DeviceB200(rank)
+    dev.commInit(rank, world, unique)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, overlap=overlap)
+    losses = []
+    for _ in range(steps):
+        losses.append(float(trainer.step().value.numpy()))
+    dev.synchronize()
+    np.savez(os.path.join(out_dir, f"rank{rank}_{int(overlap)}.npz"), *trainer.parameters_numpy(), losses=np.array(losses))
+    dev.commDestroy()
+    dev.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -32,31 +32,45 @@ class GlooDevice(DeviceNumpyOracle):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         view[:] = (t.numpy() * np.float32(scale)).astype(np.float32)
 
+    # A CPU device has one "stream": the overlapped form degenerates to the blocking one, which still exercises the
+    # hook order (one collective per parameter, issued in the same order on every rank).
+    def allReduceAsync(self, data, count, dtype, scale=1.0):
+        self.async_calls = getattr(self, "async_calls", 0) + 1
+        self.allReduce(data, count, dtype, scale)
+
+    def commWait(self):
+        self.waits = getattr(self, "waits", 0) + 1
+
 
 def set_batch(trainer, dev, x, y):
     trainer.x = Tensor(TensorValue.from_numpy(x, dev))
     trainer.y = Tensor(TensorValue.from_numpy(y, dev))
 
 
-def worker(rank, world, port, out_dir):
+def worker(rank, world, port, out_dir, overlap=True):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     dev = GlooDevice()
     weights, biases = xavier_parameters(DIMS, seed=0)
-    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases, overlap=overlap)
     x, y = synthetic_batch(DIMS, BATCH, rank)
     set_batch(trainer, dev, x, y)
     for _ in range(STEPS):
         trainer.step()
+    if overlap:
+        assert dev.async_calls == STEPS * len(trainer.model.parameters()) and dev.waits == STEPS
+    else:
+        assert not hasattr(dev, "async_calls")
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *trainer.parameters_numpy())
     dist.destroy_process_group()
 
 
-def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path):
+@pytest.mark.parametrize("overlap", [True, False], ids=["overlapped", "after_backward"])
+def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path, overlap):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, port, str(tmp_path), overlap), nprocs=2, join=True)
     r0 = np.load(tmp_path / "rank0.npz")
     r1 = np.load(tmp_path / "rank1.npz")
     for k in r0.files:
@@ -81,3 +95,21 @@ def test_shards_are_disjoint_and_deterministic():
     w0, _ = xavier_parameters(DIMS, seed=0)
     w1, _ = xavier_parameters(DIMS, seed=0)
     assert all(np.array_equal(x, y) for x, y in zip(w0, w1))          # identical replicas on every rank
+
+
+def test_exchange_refuses_a_second_contribution_in_flight():
+    from aix_b200.frontend import GradientExchange
+
+    class Recorder(DeviceNumpyOracle):
+        def allReduceAsync(self, data, count, dtype, scale=1.0): pass
+        def commWait(self): pass
+
+    dev = Recorder()
+    w = Tensor(TensorValue.from_numpy(np.ones((2, 2), np.float32), dev), requireGrad=True)
+    exchange = GradientExchange(dev, [w], world_size=2)
+    y = (w + w.tanh()).sum()                              # two separate contributions to w
+    with pytest.raises(RuntimeError, match="second gradient contribution"):
+        y.backward()
+    exchange.finish()
+    exchange.detach()
+    assert w.node.gradReadyHook is None

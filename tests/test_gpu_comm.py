@@ -1,0 +1,91 @@
+"""Data-parallel exchange on the GPU through the C ABI: the blocking and the overlapped all-reduce on a communicator of
+one rank (stream fork/join, scaling, error behaviour), and - where two GPUs are visible - two ranks as child processes
+training the small MLP with both forms of the exchange. Rank failures are not provoked here."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from aix_b200 import _capi as C
+from aix_b200.tensor import TensorValue
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_count():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.fixture()
+def comm1(b200):
+    from aix_b200 import DeviceB200
+    b200.commInit(0, 1, DeviceB200.commUniqueId())
+    yield b200
+    b200.commDestroy()
+
+
+def test_exchange_needs_a_communicator(b200):
+    x = TensorValue.from_numpy(np.ones(16, np.float32), b200)
+    with pytest.raises(Exception, match="comm_init"):
+        b200.allReduce(x.storage.data, x.size, C.F32, 1.0)
+    with pytest.raises(Exception, match="comm_init"):
+        b200.allReduceAsync(x.storage.data, x.size, C.F32, 1.0)
+    b200.commWait()                                     # nothing in flight: a no-op
+
+
+def test_single_rank_blocking_sum_and_scale(comm1):
+    rng = np.random.default_rng(0)
+    host = rng.normal(size=100003).astype(np.float32)
+    x = TensorValue.from_numpy(host, comm1)
+    comm1.allReduce(x.storage.data, x.size, C.F32, 1.0)
+    assert np.array_equal(x.numpy(), host)
+    comm1.allReduce(x.storage.data, x.size, C.F32, 0.5)
+    assert np.array_equal(x.numpy(), host * np.float32(0.5))
+    ints = TensorValue.from_numpy(np.arange(1000, dtype=np.int32), comm1, C.I32)
+    comm1.allReduce(ints.storage.data, ints.size, C.I32, 1.0)
+    assert np.array_equal(ints.numpy(), np.arange(1000, dtype=np.int32))
+
+
+def test_single_rank_overlapped_exchange_orders_both_streams(comm1):
+    rng = np.random.default_rng(1)
+    a = rng.normal(size=(1 << 20)).astype(np.float32)
+    b = rng.normal(size=(1 << 20)).astype(np.float32)
+    ta, tb = TensorValue.from_numpy(a, comm1), TensorValue.from_numpy(b, comm1)
+    g = ta * tb                                          # recorded, not yet launched: the exchange must come after it
+    comm1.allReduceAsync(g.storage.data, g.size, C.F32, 1.0)
+    other = ta + tb                                      # runs on the device's stream next to the collective
+    comm1.commWait()
+    out = g + other                                      # must see the exchanged gradient
+    assert np.array_equal(out.numpy(), a * b + (a + b))
+    with pytest.raises(Exception, match="scale"):
+        comm1.allReduceAsync(g.storage.data, g.size, C.F32, 0.25)
+    # synchronize() joins the side stream on its own
+    comm1.allReduceAsync(g.storage.data, g.size, C.F32, 1.0)
+    comm1.synchronize()
+    assert np.array_equal(g.numpy(), a * b)
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_ranks_overlapped_equals_blocking(tmp_path):
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_dp_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    results = {}
+    for overlap in (0, 1):
+        procs = [subprocess.Popen([sys.executable, worker, str(r), "2", str(tmp_path), str(overlap), "4"], env=env) for r in range(2)]
+        codes = [p.wait(timeout=600) for p in procs]
+        assert codes == [0, 0]
+        results[overlap] = [np.load(tmp_path / f"rank{r}_{overlap}.npz") for r in range(2)]
+    for overlap in (0, 1):
+        r0, r1 = results[overlap]
+        for k in r0.files:
+            if k != "losses":
+                assert np.array_equal(r0[k], r1[k]), "ranks diverged"
+    # the two forms issue the same collectives on the same data: identical parameters
+    for k in results[0][0].files:
+        if k != "losses":
+            assert np.array_equal(results[0][0][k], results[1][0][k])
+    losses = results[1][0]["losses"]
+    assert losses[-1] < losses[0]
