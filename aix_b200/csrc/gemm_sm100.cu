@@ -947,7 +947,8 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         {
             const double tiles = static_cast<double>(p.tilesM) * ((p.n + blockN - 1) / blockN);
             // 16-bit problems on CTA pairs share the remainder wave along K (see WorkIterator): no idle tail to model
-            const bool sharedTail = pair && q.dtype != F32 && (q.k + 63) / 64 >= 8 && tiles * ((q.k + 63) / 64) >= workers;
+            static const bool splitOn = []{ const char* v = std::getenv("AIXB200_GEMM_SPLITK"); return v && v[0] == '1'; }();
+            const bool sharedTail = splitOn && pair && q.dtype != F32 && (q.k + 63) / 64 >= 8 && tiles * ((q.k + 63) / 64) >= workers;
             const double waves = sharedTail ? std::max(1.0, tiles / workers) : std::ceil(tiles / workers);
             return perTile * tiles / (waves * workers) * (static_cast<double>(p.n) / (((p.n + blockN - 1) / blockN) * blockN));
         };
@@ -1068,7 +1069,10 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
         // Remainder tiles are cut along K and shared by all clusters (see WorkIterator) when that saves at least a few
         // stages of idle time per cluster; split-f32 problems keep whole tiles (their partial sums already go through C).
-        static const bool splitEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_SPLITK"); return !(v && v[0] == '0'); }();
+        // Off unless AIXB200_GEMM_SPLITK=1: measured on B200 it helps A^T.B at 4096^3 (+8 %) but costs A.B^T 6 % there
+        // and is neutral at 8192^3 - the finisher's epilogue (partials fetched strip by strip) holds its accumulator
+        // too long when K is short.
+        static const bool splitEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_SPLITK"); return v && v[0] == '1'; }();
         const uint32_t remainder = tiles % static_cast<uint32_t>(maxClusters);
         if (splitEnabled && !tf32 && remainder != 0 && p.kBlocks >= 8)
         {

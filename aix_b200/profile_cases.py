@@ -3,7 +3,8 @@ than the 126 MB L2 but hold well under a few GB on the device.
 
     python -m aix_b200.profile_cases <case> [repeats]
 
-cases: chain_f32 chain_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32 adam_f32
+cases: chain_f32 chain_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
+       gemm_bf16_k1024 gemm_f32_4096 gemm_f32_k1024 adam_f32 mlp_f32
 Prints the device time per repeat measured with events on the device's stream.
 """
 import sys
@@ -39,6 +40,16 @@ def build(dev, case):
     if case == "colsum_f32":
         x = _rand(dev, (16384, 4096), C.F32, 0)
         return lambda: x.sum(0)
+    if case in ("gemm_bf16_k1024", "gemm_f32_k1024", "gemm_f32_4096"):
+        # the MLP's shapes: batch 4096, a 1024-wide or 4096-wide contraction
+        dt = C.BF16 if "bf16" in case else C.F32
+        k = 1024 if case.endswith("k1024") else 4096
+        a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (k, 4096), dt, 1, 0.05)
+        return lambda: a.matmul(b)
+    if case == "mlp_f32":
+        from .mlp import MlpTrainer
+        trainer = MlpTrainer(dev)
+        return trainer.step
     if case.startswith("gemm_"):
         dt = C.F32 if case == "gemm_f32" else C.BF16
         n = 2048 if dt == C.F32 else 4096
@@ -72,7 +83,9 @@ def main():
         out = fn()
         dev.recordEvent(e1)
     ms = dev.elapsedMs(e0, e1) / repeats
-    print(f"{case}: {ms:.4f} ms per repeat over {repeats} repeats; launches so far {dev.stats()['total_kernel_launches']}")
+    stats = dev.stats()
+    print(f"{case}: {ms:.4f} ms per repeat over {repeats} repeats (one event pair around all repeats: the device queue stays "
+          f"full); launches so far {stats['total_kernel_launches']}")
     del out
     dev.close()
 
