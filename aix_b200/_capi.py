@@ -48,7 +48,7 @@ class Stats(ctypes.Structure):
         "kernel_cache_hits", "kernel_cache_misses", "nvrtc_compiles")] + [("nvrtc_ms", ctypes.c_double)] + [
         (n, ctypes.c_uint64) for n in (
         "static_kernel_launches", "total_kernel_launches", "bytes_in_use", "bytes_cached", "bytes_reserved",
-        "cuda_mallocs", "h2d_bytes", "d2h_bytes")] + [("reserved", ctypes.c_uint64 * 6)]
+        "cuda_mallocs", "h2d_bytes", "d2h_bytes", "reductions_fused")] + [("reserved", ctypes.c_uint64 * 5)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}

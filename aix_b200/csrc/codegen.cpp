@@ -195,6 +195,97 @@ template <class D> __device__ __forceinline__ unsigned pp_tanh(unsigned a)
 #else
 AIX_PP_UNARY(tanh)
 #endif
+
+// ---- full reductions folded into a fused kernel ---------------------------------------------------------------------
+// Per thread: float (double for f64) or wrapping unsigned partial sums, the element's own register type for maxima.
+// Across threads and blocks: 64-bit values, one partial per block in device scratch; the block that draws the last
+// ticket folds the partials (fixed order for a fixed grid: reproducible), converts once and resets the ticket.
+template <class D> __device__ __forceinline__ AIX_C red_lowest()
+{
+    if constexpr (D::kind == 0) return (AIX_C)(-__int_as_float(0x7f800000));
+    else if constexpr (D::id == 4) return (i64_t)0x8000000000000000ull;
+    else if constexpr (D::id == 5) return (int)0x80000000u;
+    else if constexpr (D::id == 6) return -32768;
+    else if constexpr (D::id == 7) return -128;
+    else return 0;
+}
+template <bool B, class X, class Y> struct red_sel { typedef X T; };
+template <class X, class Y> struct red_sel<false, X, Y> { typedef Y T; };
+template <class D, bool IsMax> struct Red;
+template <class D> struct Red<D, false>
+{
+    typedef typename D::S S;
+    typedef typename red_sel<D::kind == 0, typename red_sel<D::id == 0, double, float>::T, typename red_sel<D::id == 4, u64_t, unsigned>::T>::T A;
+    typedef typename red_sel<D::kind == 0, double, u64_t>::T W;
+    static __device__ __forceinline__ A init() { return (A)0; }
+    static __device__ __forceinline__ A step(A acc, AIX_C v) { return acc + (A)v; }
+    static __device__ __forceinline__ W widen(A a) { return (W)a; }
+    static __device__ __forceinline__ W identity() { return (W)0; }
+    static __device__ __forceinline__ W merge(W a, W b) { return a + b; }
+    static __device__ __forceinline__ S finish(W w)
+    {
+        if constexpr (D::kind == 0 && D::id == 0) return w;
+        else if constexpr (D::kind == 0) return D::st((float)w);
+        else if constexpr (D::id == 4) return (i64_t)w;
+        else return D::st((AIX_C)(unsigned)w);
+    }
+};
+template <class D> struct Red<D, true>
+{
+    typedef typename D::S S;
+    typedef AIX_C A;
+    typedef typename red_sel<D::kind == 0, double, i64_t>::T W;
+    static __device__ __forceinline__ A init() { return red_lowest<D>(); }
+    static __device__ __forceinline__ A step(A acc, A v) { return v > acc ? v : acc; }
+    static __device__ __forceinline__ W widen(A a) { return (W)a; }
+    static __device__ __forceinline__ W identity() { return (W)red_lowest<D>(); }
+    static __device__ __forceinline__ W merge(W a, W b) { return b > a ? b : a; }
+    static __device__ __forceinline__ S finish(W w) { return D::st((A)w); }
+};
+template <class W> __device__ __forceinline__ W red_shfl(W v, int d)
+{
+    i64_t bits = __shfl_down_sync(0xffffffffu, *(i64_t*)&v, d);
+    return *(W*)&bits;
+}
+template <class R> __device__ __forceinline__ typename R::W red_block(typename R::W v, typename R::W* smem)
+{
+    #pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = R::merge(v, red_shfl<typename R::W>(v, d));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    if (warp == 0)
+    {
+        v = lane < warps ? smem[lane] : R::identity();
+        #pragma unroll
+        for (int d = 16; d > 0; d >>= 1) v = R::merge(v, red_shfl<typename R::W>(v, d));
+    }
+    return v;
+}
+template <class R> __device__ __forceinline__ void red_finish(typename R::A acc, u64_t* partials, unsigned* ticket, typename R::S* out)
+{
+    __shared__ typename R::W smem[32];
+    __shared__ bool last;
+    typename R::W w = red_block<R>(R::widen(acc), smem);
+    if (threadIdx.x == 0)
+    {
+        partials[blockIdx.x] = *(u64_t*)&w;
+        __threadfence();
+        last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    typename R::W total = R::identity();
+    for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x)
+    {
+        u64_t bits = __ldcg(partials + b);
+        total = R::merge(total, *(typename R::W*)&bits);
+    }
+    total = red_block<R>(total, smem);
+    if (threadIdx.x == 0) { out[0] = R::finish(total); *ticket = 0; }
+}
 )PRELUDE";
 
 const char* kTraits[DTYPE_COUNT] = {"Df64", "Df32", "Df16", "Dbf16", "Di64", "Di32", "Di16", "Di8", "Du8"};
@@ -250,7 +341,7 @@ KernelVariant chooseVariant(const KernelSpec& spec)
         for (auto& l : spec.loads) see(l.view.dtype);
         for (auto& st : spec.stores) see(st.view.dtype);
         for (auto& nd : spec.nodes) { see(nd.dtype); if (nd.op == Op::Cast) see(nd.srcDtype); }
-        v.packed16 = uniform && (common == F16 || common == BF16) && v.vec >= 2 && v.vec % 2 == 0;
+        v.packed16 = uniform && (common == F16 || common == BF16) && v.vec >= 2 && v.vec % 2 == 0 && spec.reductions.empty();
     }
     v.index64 = maxSpan >= (uint64_t(1) << 31);
     for (size_t i = 0; i < spec.loads.size(); ++i)
@@ -303,10 +394,15 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
         put(s.view.dtype); put(static_cast<unsigned>(p)); put(s.node);
         if (p == Path::General) put(s.view.rank);
     }
+    if (!spec.reductions.empty())
+    {
+        key += "R";
+        for (const auto& r : spec.reductions) { put(r.node); put(r.isMax); put(r.dtype); }
+    }
     return key;
 }
 
-std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVariant& variant)
+std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVariant& variant, void* scratch)
 {
     std::vector<uint64_t> a;
     a.reserve(spec.loads.size() * 3 + spec.stores.size() * 3 + spec.scalars.size() + 1);
@@ -332,6 +428,11 @@ std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVa
     }
     for (size_t i = 0; i < spec.stores.size(); ++i)
         if (storePath(spec.stores[i], (variant.fastStores >> i) & 1u) == Path::General) pushLayout(spec.stores[i].view);
+    if (!spec.reductions.empty())
+    {
+        for (const auto& r : spec.reductions) a.push_back(reinterpret_cast<uint64_t>(r.out.firstByte()));
+        a.push_back(reinterpret_cast<uint64_t>(scratch));
+    }
     return a;
 }
 
@@ -365,6 +466,11 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         storeAux[i] = slot;
         if (sp[i] == Path::General) slot += 2 * spec.stores[i].view.rank;
     }
+    const size_t nR = spec.reductions.size();
+    const size_t slotReductions = slot;
+    slot += nR;
+    const size_t slotScratch = slot;
+    if (nR) ++slot;
     o << "struct Params { u64_t a[" << std::max<size_t>(slot, 1) << "]; };\n\n";
 
     auto T = [&](uint8_t dt) { return std::string(kTraits[dt]); };
@@ -475,6 +581,15 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
     for (size_t i = 0; i < nL; ++i)
         if (lp[i] == Path::Scalar) o << "    const " << T(spec.loads[i].view.dtype) << "::S x" << i << "s = l" << i << "[0];\n";
 
+    auto redType = [&](size_t r) { return "Red<" + T(spec.reductions[r].dtype) + ", " + (spec.reductions[r].isMax ? "true" : "false") + ">"; };
+    for (size_t r = 0; r < nR; ++r)
+        o << "    " << redType(r) << "::A racc" << r << " = " << redType(r) << "::init();\n";
+    auto emitReduceSteps = [&](std::ostream& os, const std::string& indent)
+    {
+        for (size_t r = 0; r < nR; ++r)
+            os << indent << "racc" << r << " = " << redType(r) << "::step(racc" << r << ", v" << spec.reductions[r].node << ");\n";
+    };
+
     // ---- main loop: U packs of E elements per thread and iteration ----------------------------------------------
     if (E > 1)
     {
@@ -584,6 +699,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         });
         for (size_t i = 0; i < nS; ++i)
             o << "                    y" << i << ".v[e] = " << T(spec.stores[i].view.dtype) << "::st(" << "v" << spec.stores[i].node << ");\n";
+        emitReduceSteps(o, "                    ");
         o << "                }\n";
         }
         for (size_t i = 0; i < nS; ++i)
@@ -644,7 +760,14 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         else
             o << "        s" << i << "[i] = " << D << "::st(v" << spec.stores[i].node << ");\n";
     }
-    o << "    }\n}\n";
+    emitReduceSteps(o, "        ");
+    o << "    }\n";
+    // ---- reduction epilogue: every thread of every block arrives here ------------------------------------------------
+    for (size_t r = 0; r < nR; ++r)
+        o << "    red_finish<" << redType(r) << " >(racc" << r << ", (u64_t*)(" << arg(slotScratch) << " + " << kReductionPartialsOffset
+          << "ull + " << (r * kReductionMaxBlocks * 8) << "ull), (unsigned*)(" << arg(slotScratch) << " + " << (4 * (r + 1)) << "ull), ("
+          << T(spec.reductions[r].dtype) << "::S*)" << arg(slotReductions + r) << ");\n";
+    o << "}\n";
     return o.str();
 }
 

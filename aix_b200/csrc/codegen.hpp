@@ -41,7 +41,11 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
 std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& variant, const CodegenOptions& options,
                                  const std::string& entryName);
 
-// Kernel argument block (an array of 64-bit slots) in the order the generated kernel expects.
-std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVariant& variant);
+// Kernel argument block (an array of 64-bit slots) in the order the generated kernel expects. `scratch` is the
+// device scratch block (tickets in its first bytes, 64-bit partials from kReductionPartialsOffset on); only kernels
+// with reductions use it.
+constexpr size_t kReductionPartialsOffset = 256;
+constexpr size_t kReductionMaxBlocks = 4096;       // partials per reduction: the launch grid is capped to this
+std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVariant& variant, void* scratch);
 
 }   // namespace aixb200

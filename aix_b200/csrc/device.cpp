@@ -93,6 +93,7 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_codegen.block = envInt("AIXB200_EW_BLOCK", 256);
     m_codegen.unroll = std::max(1, std::min(8, envInt("AIXB200_EW_UNROLL", 2)));
     m_wavesPerSm = std::max(1, envInt("AIXB200_EW_WAVES", 8));
+    m_fuseReductions = envInt("AIXB200_FUSE_REDUCTIONS", 1) != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -489,9 +490,10 @@ void Device::launchSpec(const KernelSpec& spec)
     const std::string key = kernelKey(spec, variant, m_codegen);
     CompiledKernel& k = getKernel(spec, variant, key);
     m_lastSource = k.source;
+    m_stats.reductions_fused += spec.reductions.size();
     if (dryRun()) { countLaunch(true); return; }
 
-    std::vector<uint64_t> args = packKernelArguments(spec, variant);
+    std::vector<uint64_t> args = packKernelArguments(spec, variant, m_scratch);
     if (args.empty()) args.push_back(0);
     const uint64_t block = static_cast<uint64_t>(m_codegen.block);
     const uint64_t nvec = variant.vec > 1 ? spec.count / variant.vec : 0;
@@ -500,6 +502,7 @@ void Device::launchSpec(const KernelSpec& spec)
     const uint64_t tailBlocks = (tailElems + block - 1) / block;
     uint64_t grid = std::max<uint64_t>(1, std::max(mainBlocks, tailBlocks));
     grid = std::min<uint64_t>(grid, static_cast<uint64_t>(m_smCount) * m_wavesPerSm);
+    if (!spec.reductions.empty()) grid = std::min<uint64_t>(grid, kReductionMaxBlocks);    // one scratch partial per block
     void* params[] = {args.data()};
     checkDriver(driver().launchKernel(k.function, static_cast<unsigned>(grid), 1, 1, static_cast<unsigned>(block), 1, 1, 0, m_stream, params, nullptr),
                 "cuLaunchKernel(fused)");
@@ -536,11 +539,30 @@ void Device::sum(const aixb200_tensor* a, const aixb200_tensor* r)
     View dst = outputView(r, "sum");
     if (src.dtype != dst.dtype) failInvalid("sum: result must have the element type of the input");
     if (dst.size != 1) failInvalid("sum: result must have one element");
+    if (recordReduction(Op::SumAll, src, dst)) return;
     flush();
     if (dryRun()) return;
     AIXB200_CTX();
     kernels::reduceAll(ctx, false, src, dst.firstByte());
     AIXB200_DONE("sum");
+}
+
+// A full reduction whose operand is the result of a recorded, not yet launched op is recorded too: the planner folds
+// it into the producer's kernel, where the operand is still in registers.
+bool Device::recordReduction(Op op, const View& src, const View& dst)
+{
+    if (!m_limits.fusion || !m_fuseReductions || src.size < 2) return false;
+    bool producerPending = false;
+    for (size_t i = m_pending.size(); i-- > 0 && !producerPending;)
+        producerPending = m_pending[i].out.base == src.base && !isReduction(m_pending[i].op) && m_pending[i].out.sameElements(src);
+    if (!producerPending) return false;
+    OpRecord rec;
+    rec.op = op;
+    rec.numInputs = 1;
+    rec.in[0] = src;
+    rec.out = dst;
+    record(std::move(rec));
+    return true;
 }
 
 // Sum for callers that must not allocate: no staging of host inputs, no flush of recorded work (a flush may
@@ -573,6 +595,7 @@ void Device::max(const aixb200_tensor* a, const aixb200_tensor* r)
     View dst = outputView(r, "max");
     if (src.dtype != dst.dtype) failInvalid("max: result must have the element type of the input");
     if (dst.size != 1 || src.size == 0) failInvalid("max: result must have one element and the input at least one");
+    if (recordReduction(Op::MaxAll, src, dst)) return;
     flush();
     if (dryRun()) return;
     AIXB200_CTX();

@@ -57,6 +57,7 @@ public:
     void recordUnary(Op op, const aixb200_tensor* a, const aixb200_tensor* r, const char* what);
     void recordFill(const void* scalar, uint32_t scalarDtype, const aixb200_tensor* r);
     void recordFillMin(const aixb200_tensor* r);
+    bool recordReduction(Op op, const View& src, const View& dst);
     void flush();
 
     // immediate ops (flush first, then launch fixed kernels)
@@ -130,6 +131,7 @@ private:
     PlannerLimits  m_limits;
     CodegenOptions m_codegen;
     int            m_wavesPerSm = 8;
+    bool           m_fuseReductions = true;     // AIXB200_FUSE_REDUCTIONS=0 keeps full reductions as kernels of their own
 
     std::unordered_map<std::string, CompiledKernel> m_kernels;
     std::string m_cacheDir;

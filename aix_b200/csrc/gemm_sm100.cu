@@ -54,6 +54,7 @@ struct KernelParams
     uint32_t aBoxes, bBoxes;    // TMA boxes per stage and operand
     uint32_t aBoxBytes, bBoxBytes;
     uint32_t aBoxStepMn, bBoxStepMn;   // MN elements covered by one box (MN-major) / unused (K-major)
+    uint32_t aMap3d, bMap3d;    // MN-major operand fetched as ONE box of a 3-D map (64 mn, k, atoms of 64 mn)
     uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t idesc16;           // f32 problems: descriptor of the bf16 cross-term passes
     uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
@@ -593,6 +594,11 @@ __device__ __forceinline__ void tmaLoad2dPair(void* dst, const CUtensorMap* map,
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smemAddr(dst)), "l"(map), "r"(leaderBar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tmaLoad3dPair(void* dst, const CUtensorMap* map, uint32_t leaderBar, int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smemAddr(dst)), "l"(map), "r"(leaderBar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 template <bool Tf32>
 __device__ __forceinline__ void ummaPair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
 {
@@ -674,12 +680,14 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         const uint32_t leaderFull = leaderFull0 + stage * 8;
                         mbarExpectTxCluster(leaderFull, stageBytes);
                         const int32_t kA = static_cast<int32_t>(kb * blockK + offA), kB = static_cast<int32_t>(kb * blockK + offB);
-                        for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
+                        if (p.aMap3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, kA, m0 >> 6);
+                        else for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
                         {
                             if (p.aMnMajor) tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
                             else            tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, kA, m0);
                         }
-                        for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
+                        if (p.bMap3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, kB, n0 >> 6);
+                        else for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
                         {
                             if (p.bMnMajor) tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
                             else            tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, kB, n0);
@@ -826,41 +834,121 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 // ---- f32 split pass: src (any 2-D strides) -> K-major scratch, zero padded to kPad (a multiple of 64) ---------------
 //   hi32[rows][kPad]      a rounded to TF32 (low 13 mantissa bits zero): operand of the main pass
 //   pair16[rows][2*kPad]  [ bf16(a) | bf16(a - hi) ]: operands of the two cross-term passes
+// One CTA converts a 64 x 64 tile; every thread owns runs of 8 consecutive k, so that all three outputs leave as
+// 16-byte stores (12 bytes written per 4 bytes read: the pass is bound by HBM writes). A source whose unit stride runs
+// along k is read in place with 16-byte loads; one whose unit stride runs along the rows is read with 16-byte loads
+// along the rows and turned through shared memory.
+__device__ __forceinline__ void splitEmit(const float (&v)[8], uint32_t r, uint32_t c, uint32_t kPad, float* __restrict__ hi32, uint16_t* __restrict__ pair16)
+{
+    float hi[8];
+    uint32_t full[4], low[4];
+    #pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const uint32_t bits = __float_as_uint(v[j]);
+        // round to nearest even at 10 mantissa bits; values that would overflow keep their truncated form
+        uint32_t rounded = (bits + 0xFFFu + ((bits >> 13) & 1u)) & 0xFFFFE000u;
+        if ((rounded & 0x7F800000u) == 0x7F800000u) rounded = bits & 0xFFFFE000u;
+        hi[j] = __uint_as_float(rounded);
+    }
+    #pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        full[j] = static_cast<uint32_t>(dev::f32ToBf16(v[2 * j])) | (static_cast<uint32_t>(dev::f32ToBf16(v[2 * j + 1])) << 16);
+        low[j] = static_cast<uint32_t>(dev::f32ToBf16(v[2 * j] - hi[2 * j])) | (static_cast<uint32_t>(dev::f32ToBf16(v[2 * j + 1] - hi[2 * j + 1])) << 16);
+    }
+    float4* h = reinterpret_cast<float4*>(hi32 + static_cast<uint64_t>(r) * kPad + c);
+    h[0] = make_float4(hi[0], hi[1], hi[2], hi[3]);
+    h[1] = make_float4(hi[4], hi[5], hi[6], hi[7]);
+    uint16_t* out = pair16 + static_cast<uint64_t>(r) * (2ull * kPad) + c;
+    *reinterpret_cast<uint4*>(out) = make_uint4(full[0], full[1], full[2], full[3]);
+    *reinterpret_cast<uint4*>(out + kPad) = make_uint4(low[0], low[1], low[2], low[3]);
+}
+
+template <bool Transposed>
 __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ src, uint64_t rowStride, uint64_t colStride,
                                                       uint32_t rows, uint32_t k, uint32_t kPad, float* __restrict__ hi32,
-                                                      uint16_t* __restrict__ pair16)
+                                                      uint16_t* __restrict__ pair16, uint32_t vectorLoads)
 {
-    // One CTA handles a 32 x 32 tile through shared memory so that both the strided read and the dense write coalesce
-    // whichever way the source is laid out.
-    __shared__ float tile[32][33];
-    const uint32_t r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
-    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
-    const bool colContiguous = colStride == 1;
-    for (uint32_t i = ty; i < 32; i += 8)
+    const uint32_t r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    if (!Transposed)
     {
-        const uint32_t r = colContiguous ? r0 + i : r0 + tx;
-        const uint32_t c = colContiguous ? c0 + tx : c0 + i;
-        float v = 0.f;
-        if (r < rows && c < k) v = src[static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride];
-        if (colContiguous) tile[i][tx] = v; else tile[tx][i] = v;
-    }
-    __syncthreads();
-    for (uint32_t i = ty; i < 32; i += 8)
-    {
-        const uint32_t r = r0 + i, c = c0 + tx;
-        if (r < rows && c < kPad)
+        #pragma unroll
+        for (uint32_t it = 0; it < 2; ++it)
         {
-            const float v = tile[i][tx];
-            const uint32_t bits = __float_as_uint(v);
-            // round to nearest even at 10 mantissa bits; values that would overflow keep their truncated form
-            uint32_t rounded = (bits + 0xFFFu + ((bits >> 13) & 1u)) & 0xFFFFE000u;
-            if ((rounded & 0x7F800000u) == 0x7F800000u) rounded = bits & 0xFFFFE000u;
-            const float hi = __uint_as_float(rounded);
-            hi32[static_cast<uint64_t>(r) * kPad + c] = hi;
-            uint16_t* out = pair16 + static_cast<uint64_t>(r) * (2ull * kPad);
-            out[c] = dev::f32ToBf16(v);
-            out[kPad + c] = dev::f32ToBf16(v - hi);
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t r = r0 + (idx >> 3), c = c0 + (idx & 7u) * 8;
+            if (r >= rows) continue;
+            float v[8];
+            const float* in = src + static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride;
+            if (vectorLoads && c + 8 <= k)
+            {
+                const float4 x = reinterpret_cast<const float4*>(in)[0], y = reinterpret_cast<const float4*>(in)[1];
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+            }
+            else
+            {
+                #pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) v[j] = (c + j < k) ? in[j * colStride] : 0.f;
+            }
+            splitEmit(v, r, c, kPad, hi32, pair16);
         }
+    }
+    else
+    {
+        __shared__ __align__(16) float tile[64][68];          // [k][row]
+        #pragma unroll
+        for (uint32_t it = 0; it < 4; ++it)
+        {
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t kk = idx >> 4, rg = (idx & 15u) * 4;
+            const uint32_t c = c0 + kk, r = r0 + rg;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < k)
+            {
+                const float* in = src + static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride;
+                if (vectorLoads && r + 4 <= rows) x = *reinterpret_cast<const float4*>(in);
+                else
+                {
+                    if (r < rows) x.x = in[0];
+                    if (r + 1 < rows) x.y = in[rowStride];
+                    if (r + 2 < rows) x.z = in[2 * rowStride];
+                    if (r + 3 < rows) x.w = in[3 * rowStride];
+                }
+            }
+            *reinterpret_cast<float4*>(&tile[kk][rg]) = x;
+        }
+        __syncthreads();
+        #pragma unroll
+        for (uint32_t it = 0; it < 2; ++it)
+        {
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t r = idx & 63u, kg = (idx >> 6) * 8;
+            if (r0 + r >= rows) continue;
+            float v[8];
+            #pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) v[j] = tile[kg + j][r];
+            splitEmit(v, r0 + r, c0 + kg, kPad, hi32, pair16);
+        }
+    }
+}
+
+// Launches the split of a rows x k operand whose element (r, c) sits at src[r * rowStride + c * colStride].
+void launchSplit(cudaStream_t stream, const float* src, uint64_t rowStride, uint64_t colStride, uint32_t rows, uint32_t k, uint32_t kPad,
+                 float* hi32, uint16_t* pair16)
+{
+    const dim3 grid(kPad / 64, (rows + 63) / 64);
+    const bool aligned = reinterpret_cast<uintptr_t>(src) % 16 == 0;
+    if (colStride == 1 || rowStride != 1)
+    {
+        // unit stride along k (or no unit stride at all: element loads)
+        const uint32_t vec = colStride == 1 && aligned && rowStride % 4 == 0;
+        splitF32Kernel<false><<<grid, 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, hi32, pair16, vec);
+    }
+    else
+    {
+        const uint32_t vec = aligned && colStride % 4 == 0;
+        splitF32Kernel<true><<<grid, 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, hi32, pair16, vec);
     }
 }
 
@@ -892,6 +980,21 @@ bool makeMap(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint6
     EncodeTiledFn fn = encodeTiled();
     if (!fn) return false;
     return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 3-D view of an MN-major matrix (mn fastest): (64 mn, k, mn / 64). One box {64, boxK, atoms} lands in shared memory
+// as `atoms` consecutive 64-mn x boxK blocks - the layout the MN-major descriptors expect - with one TMA instruction.
+bool makeMap3d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t mn, uint64_t k, uint64_t pitchBytes, uint32_t boxK,
+               uint32_t atoms)
+{
+    cuuint64_t dims[3] = {64, k, mn / 64};
+    cuuint64_t strides[2] = {pitchBytes, 128};
+    cuuint32_t box[3] = {64, boxK, atoms};
+    cuuint32_t elemStrides[3] = {1, 1, 1};
+    EncodeTiledFn fn = encodeTiled();
+    if (!fn) return false;
+    return fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -967,6 +1070,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     if (!tf32)
     {
         Operand a, b;
+        static const bool mn3d = []{ const char* v = std::getenv("AIXB200_GEMM_MN3D"); return !(v && v[0] == '0'); }();
         if (!classify(q.a, q.aRowStride, q.aColStride, q.m, q.k, true, 2, &a)) return false;
         if (!classify(q.b, q.bRowStride, q.bColStride, q.k, q.n, false, 2, &b)) return false;
         p.blockK = 64;
@@ -980,7 +1084,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         if (a.mnMajor)
         {
             p.aBoxes = kBlockM / 64; p.aBoxBytes = 64 * 128; p.aBoxStepMn = 64; p.aLbo = 64 * 128; p.kAdvanceA = 16 * 128;
-            if (!makeMap(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, 64)) return false;
+            p.aMap3d = mn3d && pair && q.m % 64 == 0;
+            if (p.aMap3d ? !makeMap3d(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, kBlockM / 64)
+                         : !makeMap(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, 64)) return false;
         }
         else
         {
@@ -990,7 +1096,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         if (b.mnMajor)
         {
             p.bBoxes = bRows / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
-            if (!makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
+            p.bMap3d = mn3d && pair && q.n % 64 == 0;
+            if (p.bMap3d ? !makeMap3d(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, bRows / 64)
+                         : !makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
         }
         else
         {
@@ -1011,10 +1119,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         float* hiB = static_cast<float*>(device.temporary(static_cast<size_t>(p.n) * kPad * 4));
         uint16_t* pairA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
         uint16_t* pairB = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.n) * 2 * kPad * 2));
-        dim3 gridA((kPad + 31) / 32, (p.m + 31) / 32), gridB((kPad + 31) / 32, (p.n + 31) / 32);
-        splitF32Kernel<<<gridA, 256, 0, ctx.stream>>>(static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, hiA, pairA);
+        launchSplit(ctx.stream, static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, hiA, pairA);
         // B is k x n: its "rows" for the split are the n columns
-        splitF32Kernel<<<gridB, 256, 0, ctx.stream>>>(static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, hiB, pairB);
+        launchSplit(ctx.stream, static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, hiB, pairB);
         if (ctx.launches) *ctx.launches += 2;
         p.blockK = 32;
         p.kBlocks = kPad / 32;

@@ -9,7 +9,7 @@ namespace aixb200
 const char* opName(Op op)
 {
     static const char* names[] = {"add", "sub", "mul", "div", "neg", "sqrt", "sin", "cos", "tanh", "log", "exp", "pow",
-                                  "fill", "cast"};
+                                  "fill", "cast", "sumall", "maxall"};
     return names[static_cast<size_t>(op)];
 }
 
@@ -31,6 +31,7 @@ struct Group
     std::vector<size_t> ops;        // indices into the recorded list, program order
     std::vector<View> loads;        // distinct views this group reads from memory
     size_t liveOutputs = 0;         // results whose storage is still alive (they will be stored)
+    size_t reductions = 0;
 };
 
 // Where an input of a recorded op comes from.
@@ -67,6 +68,13 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 const View& w = ops[i].out;
                 if (w.base != in.base || !w.overlaps(in)) continue;
+                if (isReduction(ops[i].op))
+                {
+                    // written when the producing grid has finished: readable from the next kernel on
+                    shadowed = true;
+                    minGroup = std::max(minGroup, groupOf[i] + 1);
+                    continue;
+                }
                 if (!shadowed && isOneElementFill(ops[i]) && in.isBroadcastScalar() && w.dtype == in.dtype &&
                     w.offset == in.offset)
                 {
@@ -87,6 +95,8 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
         }
 
         // write-after-read and write-after-write
+        // (a reduction's result is not written element by element: no same-kernel ordering with anything that touches it)
+        const bool jReduces = isReduction(rj.op);
         for (size_t i = 0; i < j; ++i)
         {
             const OpRecord& ri = ops[i];
@@ -94,14 +104,14 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 const View& r = ri.in[k];
                 if (r.base != rj.out.base || !r.overlaps(rj.out)) continue;
-                minGroup = std::max(minGroup, r.sameElements(rj.out) ? groupOf[i] : groupOf[i] + 1);
+                minGroup = std::max(minGroup, (r.sameElements(rj.out) && !jReduces) ? groupOf[i] : groupOf[i] + 1);
             }
             if (ri.out.base == rj.out.base && ri.out.overlaps(rj.out))
-                minGroup = std::max(minGroup, ri.out.sameElements(rj.out) ? groupOf[i] : groupOf[i] + 1);
+                minGroup = std::max(minGroup, (ri.out.sameElements(rj.out) && !jReduces && !isReduction(ri.op)) ? groupOf[i] : groupOf[i] + 1);
         }
 
-        const uint64_t count = rj.out.size;
-        const bool liveOutput = released.count(rj.out.base) == 0;
+        const uint64_t count = jReduces ? rj.in[0].size : rj.out.size;
+        const bool liveOutput = !jReduces && released.count(rj.out.base) == 0;
         // Views op j would have to load if it joined group g: inputs not produced inside g and not loaded by g yet.
         auto newLoads = [&](size_t g, std::vector<const View*>* out) -> size_t
         {
@@ -124,6 +134,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             for (size_t g = groups.size(); g-- > minGroup;)
             {
                 if (groups[g].count != count || groups[g].ops.size() + 2 > limits.maxNodesPerKernel) continue;
+                if (jReduces && groups[g].reductions + 1 > limits.maxReductionsPerKernel) continue;
                 if (groups[g].loads.size() + groups[g].liveOutputs + newLoads(g, nullptr) + (liveOutput ? 1 : 0) > limits.maxTensorsPerKernel) continue;
                 chosen = g;
                 break;
@@ -138,6 +149,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
         newLoads(chosen, &added);
         for (const View* v : added) groups[chosen].loads.push_back(*v);
         groups[chosen].liveOutputs += liveOutput ? 1 : 0;
+        groups[chosen].reductions += jReduces ? 1 : 0;
         groups[chosen].ops.push_back(j);
         groupOf[j] = chosen;
     }
@@ -216,6 +228,22 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                 }
             }
 
+            if (isReduction(r.op))
+            {
+                // the operand as a node: a register of this kernel, or an identity conversion of a loaded value
+                uint16_t node = refs[0].index;
+                if (refs[0].kind == OperandRef::Load)
+                {
+                    KernelNode copy{};
+                    copy.op = Op::Cast;
+                    copy.dtype = copy.srcDtype = r.in[0].dtype;
+                    copy.a = refs[0];
+                    spec.nodes.push_back(copy);
+                    node = static_cast<uint16_t>(spec.nodes.size() - 1);
+                }
+                spec.reductions.push_back({node, r.op == Op::MaxAll, r.in[0].dtype, r.out});
+                continue;
+            }
             if (r.op == Op::Fill)
             {
                 nodeOf[j] = addFillNode(r);
@@ -257,7 +285,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                 if (r.op == Op::Fill) ++spec.fillsAbsorbed;
             }
         }
-        if (!spec.stores.empty()) kernels.push_back(std::move(spec));
+        if (!spec.stores.empty() || !spec.reductions.empty()) kernels.push_back(std::move(spec));
     }
     return kernels;
 }

@@ -11,6 +11,10 @@
 //     earlier through a different view) forces a later kernel, because it needs a grid-wide barrier;
 //   * a fill of a one-element tensor that is later read through an all-zero-stride broadcast view becomes a kernel
 //     scalar of the reader (what the reference achieves with absorbed fills, aixFuse.cpp:552-576, 693-710).
+// A full sum or max whose operand is produced by a pending op joins that op's kernel as a reduction epilogue (the
+// reference ends the fused region at every reduction, aixDeviceMetal.cpp:296-359): the operand is folded while it is
+// still in registers, and if its storage is already dead it never reaches memory. The one-element result is written
+// when the whole grid has finished, so every other access to it is ordered into a later (or earlier) kernel.
 // A result whose storage has already been deallocated and whose readers all sit in the same group is never
 // written to memory (the reference's dead-intermediate elision, aixFuse.cpp:538-550).
 #pragma once
@@ -24,7 +28,10 @@
 namespace aixb200
 {
 
-enum class Op : uint8_t { Add, Sub, Mul, Div, Neg, Sqrt, Sin, Cos, Tanh, Log, Exp, Pow, Fill, Cast, COUNT };
+enum class Op : uint8_t { Add, Sub, Mul, Div, Neg, Sqrt, Sin, Cos, Tanh, Log, Exp, Pow, Fill, Cast,
+                          SumAll, MaxAll,   // full reductions recorded behind a pending producer: in[0] -> one element
+                          COUNT };
+inline bool isReduction(Op op) { return op == Op::SumAll || op == Op::MaxAll; }
 const char* opName(Op op);
 
 struct OpRecord
@@ -62,6 +69,7 @@ struct KernelNode
 };
 
 struct KernelLoad  { View view; Access access; };
+struct KernelReduce { uint16_t node; bool isMax; uint8_t dtype; View out; };   // out: the one-element result
 struct KernelStore { View view; Access access; uint16_t node; };
 
 // One fused kernel: loads, straight-line nodes, stores, all over `count` elements.
@@ -71,6 +79,7 @@ struct KernelSpec
     std::vector<KernelLoad>  loads;
     std::vector<KernelNode>  nodes;
     std::vector<KernelStore> stores;
+    std::vector<KernelReduce> reductions;  // folded over all `count` elements of a node
     std::vector<ScalarBits>  scalars;      // runtime values; not part of the kernel's identity
     std::vector<uint8_t>     scalarDtypes;
     uint32_t                 opsFolded = 0;    // recorded ops this kernel stands for
@@ -82,6 +91,7 @@ struct PlannerLimits
 {
     size_t maxTensorsPerKernel = 24;   // loads + stores
     size_t maxNodesPerKernel   = 160;
+    size_t maxReductionsPerKernel = 4;
     bool   fusion              = true;
 };
 

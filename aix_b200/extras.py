@@ -9,16 +9,24 @@ from .tensor import TensorValue
 
 
 def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
-    """Device time of one call of fn: `iters` calls are queued back to back behind a few L2-flush kernels, so that the
-    host is ahead of the GPU and the interval between the two events holds kernel time only. The working sets used
-    here (>= 128 MiB per call) do not fit the L2 together with the next call's."""
+    """Device time of one call of fn. The calls are issued from Python, whose per-call cost (tens of microseconds) can
+    exceed a kernel's duration; to keep the interval between the two events free of host time, enough L2-flush kernels
+    (about 45 us each) are queued first that the host finishes issuing all `iters` calls while the GPU is still busy
+    with them. The host cost per call is measured during the warm-up. The working sets used here (>= 128 MiB per
+    call) do not fit the L2 together with the next call's."""
+    import time
+    marker = dev.createEvent()
+    host_s = 0.0
     for _ in range(warmup):
+        t0 = time.perf_counter()
         fn()
+        dev.recordEvent(marker)
+        host_s = max(host_s, time.perf_counter() - t0)
     dev.synchronize()
     e0, e1 = dev.createEvent(), dev.createEvent()
-    for _ in range(3 if flush_l2 else 1):
+    head = min(400, 3 + int(1.5 * iters * host_s / 45e-6))
+    for _ in range(head if flush_l2 or head > 3 else 1):
         dev.flushL2()
-    marker = dev.createEvent()
     dev.recordEvent(e0)
     for _ in range(iters):
         fn()
@@ -28,7 +36,7 @@ def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
     dev.destroyEvent(marker)
     dev.destroyEvent(e0)
     dev.destroyEvent(e1)
-    return float(ms), float(ms)
+    return float(ms), float(host_s * 1e3)
 
 
 def relu(v):
@@ -54,9 +62,9 @@ def measure_reductions(dev, hbm_peak, rows=8192, cols=8192):
         "global sum bf16": (lambda: holder.__setitem__("t", y.sum()), n * 2),
     }
     for name, (fn, nbytes) in cases.items():
-        med, best = _time(dev, fn)
+        med, host_ms = _time(dev, fn)
         out[name] = {"ms": med, "GB/s": nbytes / (med * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (med * 1e-3) / 1e9 / hbm_peak,
-                     "bytes": nbytes}
+                     "bytes": nbytes, "host_ms_per_call": host_ms}
     return out
 
 
@@ -70,7 +78,7 @@ def measure_matmul(dev, tensor_peak, size=4096):
         holder = {}
         forms = {"A.B": lambda: a.matmul(b), "G.B^T": lambda: a.matmul(b.transpose(0, 1)), "A^T.G": lambda: a.transpose(0, 1).matmul(b)}
         for form, fn in forms.items():
-            med, best = _time(dev, lambda: holder.__setitem__("c", fn()), iters=5, warmup=2, flush_l2=False)
+            med, _host = _time(dev, lambda: holder.__setitem__("c", fn()), iters=5, warmup=2, flush_l2=False)
             tf = 2.0 * size ** 3 / (med * 1e-3) / 1e12
             out[f"{name} {form} {size}^3"] = {"ms": med, "TFLOP/s": tf, "frac_of_measured_bf16_peak": tf / tensor_peak}
     return out

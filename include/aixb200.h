@@ -201,7 +201,8 @@ typedef struct aixb200_stats
     uint64_t cuda_mallocs;          /* calls that reached the CUDA allocator */
     uint64_t h2d_bytes;             /* staged host->device */
     uint64_t d2h_bytes;
-    uint64_t reserved[6];
+    uint64_t reductions_fused;      /* full sums / maxima folded into the kernel that produces their operand */
+    uint64_t reserved[5];
 } aixb200_stats;
 int aixb200_get_stats(aixb200_device* dev, aixb200_stats* out);
 /* CUDA C source of the most recently generated kernel (for inspection and tests); NULL if none yet. */

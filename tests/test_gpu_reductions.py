@@ -143,3 +143,73 @@ def test_config1_broadcast_and_reductions_bf16(b200, ref, rows, cols):
     assert_close(gsum.numpy(), round_to(wide_y.sum(1).numpy(), BF16), BF16, "row sum", scale=np.maximum(1.0, y_ref.sum(axis=1)))
     want_mean = round_to(np.array(round_to(np.array(y_ref.astype(np.float64).sum()), BF16) / round_to(np.array(float(y_ref.size)), BF16)), BF16)
     assert_close(gmean.numpy(), want_mean, BF16, "mean")
+
+
+# ---- full reductions folded into the producing kernel ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ALL_DTYPES, ids=lambda d: DTYPE_NAMES[d])
+def test_sum_and_max_fused_behind_their_producer(b200, ref, dtype):
+    """`(a op b).sum()` / `.max()` with the elementwise op still pending: the reduction runs as an epilogue of the generated
+    kernel. Oracle as above: the CPU device on the same op sequence (16-bit floats: elementwise in the 16-bit type,
+    reduction on the values widened to f32)."""
+    rng = np.random.default_rng(300 + dtype)
+    for n in [2, 3, 5, 17, 127, 1025, 2049, 65537, (1 << 20) + 3]:
+        x, y = values(rng, n, dtype), values(rng, n, dtype)
+        before = b200.stats()["reductions_fused"]
+        ga, gb = TensorValue.from_numpy(x, b200, dtype), TensorValue.from_numpy(y, b200, dtype)
+        b200.synchronize()
+        kept = ga + gb                                  # stays alive: stored AND reduced
+        got_sum, got_max = kept.sum(), kept.max()
+        got_dead = (ga * gb).sum()                      # the product never reaches memory
+        got_sum, got_max, got_dead, got_kept = got_sum.numpy(), got_max.numpy(), got_dead.numpy(), kept.numpy()
+        assert b200.stats()["reductions_fused"] - before == 3, "the reductions were not folded into the producer's kernel"
+
+        ra, rb = TensorValue.from_numpy(x, ref, dtype), TensorValue.from_numpy(y, ref, dtype)
+        rkept, rprod = ra + rb, ra * rb
+        assert_close(got_kept, rkept.numpy(), dtype, f"kept n={n}")
+        want_max = rkept.max().numpy()
+        assert_close(got_max, want_max, dtype, f"max n={n}")
+        if dtype in FLOATS:
+            for got, r in ((got_sum, rkept), (got_dead, rprod)):
+                vals = np.asarray(r.numpy(), dtype=np.float64)
+                exact = vals.sum()
+                bound = {F64: 1e-12, F32: 1e-5, F16: 1e-2, BF16: 1e-2}[dtype]
+                assert abs(float(got) - exact) <= bound * max(1.0, float(np.abs(vals).sum())), f"sum n={n}"
+                if dtype in (F16, BF16) and np.isfinite(round_to(np.array([exact]), dtype)[0]):
+                    assert_close(got, round_to(r.to(F32).sum().numpy(), dtype), dtype, f"sum n={n}", scale=max(1.0, abs(exact)))
+        else:
+            assert_close(got_sum, rkept.sum().numpy(), dtype, f"sum n={n}")
+            assert_close(got_dead, rprod.sum().numpy(), dtype, f"dead sum n={n}")
+
+
+def test_fused_reduction_result_feeds_later_ops_and_repeats_exactly(b200, ref):
+    rng = np.random.default_rng(9)
+    x = rng.normal(0, 1, (1 << 18,)).astype(np.float32)
+    t = rng.normal(0, 1, (1 << 18,)).astype(np.float32)
+    outs = []
+    for dev in (b200, ref):
+        p, q = TensorValue.from_numpy(x, dev), TensorValue.from_numpy(t, dev)
+        dev.synchronize()
+        diff = p - q
+        loss = (diff * diff).sum() / float(x.size)      # mean squared error: sum folded, division in the next kernel
+        again = ((p - q) * (p - q)).sum() / float(x.size)
+        outs.append((loss.numpy(), again.numpy()))
+    assert np.array_equal(outs[0][0], outs[0][1]), "same grid, same fold order: bit-identical repeats"
+    assert_close(outs[0][0], outs[1][0], F32, "mse", scale=1.0)
+
+
+def test_fused_reduction_over_a_broadcast_chain_bf16(b200, ref):
+    rng = np.random.default_rng(10)
+    x = rng.normal(0, 1, (512, 1024)).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, (1024,)).astype(np.float32)
+    res = []
+    for dev in (b200, ref):
+        tx, tg = TensorValue.from_numpy(x, dev, BF16), TensorValue.from_numpy(g, dev, BF16)
+        dev.synchronize()
+        v = tx * tg
+        y = (v + (v * v).sqrt()) * 0.5
+        if dev is b200:
+            res.append((y.sum().numpy(), y.max().numpy()))
+        else:
+            res.append((round_to(y.to(F32).sum().numpy(), BF16), y.max().numpy()))
+    assert_close(res[0][1], res[1][1], BF16, "max")
+    assert_close(res[0][0], res[1][0], BF16, "sum", scale=float(abs(res[1][0])))

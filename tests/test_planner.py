@@ -163,3 +163,54 @@ def test_fusion_can_be_switched_off():
     d = delta(dev, s0)
     assert d["fused_kernels"] == 3          # fill, add, mul: one kernel each
     dev.close()
+
+
+def test_full_reductions_join_the_kernel_that_produces_their_operand(dry):
+    a, b = TensorValue.full(1.0, (64, 1024), dry), TensorValue.full(2.0, (64, 1024), dry)
+    dry.synchronize()
+    s0 = dry.stats()
+    d = a - b
+    loss = (d * d).sum()                  # the product is dead: neither d*d nor (once d dies) d needs memory
+    peak = (a * b).max()
+    del d
+    mean = loss / 65536.0                 # reads the reduction's result: next kernel
+    dry.synchronize()
+    st = delta(dry, s0)
+    assert st["reductions_fused"] == 2 and st["fused_kernels"] == 2 and st["static_kernel_launches"] == 0
+    assert st["stores_elided"] >= 3
+    first, second = None, dry.lastKernelSource()
+    assert "red_finish" not in second.split("extern")[1]             # the division kernel has no reduction
+
+
+def test_reduction_kernel_source_has_one_epilogue_per_reduction(dry):
+    a = TensorValue.full(1.0, (1000,), dry)
+    dry.synchronize()
+    t = a * 3.0
+    s, m = t.sum(), t.max()
+    dry.synchronize()
+    body = dry.lastKernelSource().split("extern")[1]
+    assert body.count("red_finish<Red<Df32, false> >") == 1 and body.count("red_finish<Red<Df32, true> >") == 1
+    assert "racc0 = Red<Df32, false>::step" in body and "racc1 = Red<Df32, true>::step" in body
+
+
+def test_reduction_of_a_tensor_already_in_memory_is_not_recorded(dry):
+    a = TensorValue.full(1.0, (1000,), dry)
+    dry.synchronize()
+    s0 = dry.stats()
+    s = a.sum()
+    dry.synchronize()
+    st = delta(dry, s0)
+    assert st["reductions_fused"] == 0 and st["fused_kernels"] == 0
+
+
+def test_result_of_a_reduction_orders_later_writers_and_readers(dry):
+    a = TensorValue.full(2.0, (4096,), dry)
+    dry.synchronize()
+    s0 = dry.stats()
+    t = a * a
+    s = t.sum()
+    u = t + s.broadcastTo((4096,)) if hasattr(s, "broadcastTo") else t + t     # reads the scalar: a later kernel
+    s.fill(0.0)                                                                # overwrites it: not before the reduction ran
+    dry.synchronize()
+    st = delta(dry, s0)
+    assert st["reductions_fused"] == 1 and st["fused_kernels"] >= 2
