@@ -66,6 +66,7 @@ struct KernelParams
     uint32_t chunkBlocks;       // k-blocks folded inside TMEM before the partial result is added to C in f32
     uint32_t chunks;            // number of such partial results per tile (1: plain store)
     uint32_t vectorStores;      // C rows are 16-byte aligned
+    uint32_t tmaEpilogue;       // pair kernel: C leaves through shared memory and TMA stores / f32 reduce-adds
     uint32_t splitTiles;        // pair kernel: tiles [0, splitTiles) are cut along K and shared by all clusters
     uint32_t splitUnits;        // splitTiles * kBlocks
     void*    c;
@@ -556,6 +557,7 @@ __device__ __forceinline__ void finishTile(const KernelParams& p, uint32_t taddr
 
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytesB = 128 * 128;
+constexpr int kStagingBytes = 128 * 128;
 
 struct PairStorage
 {
@@ -567,6 +569,7 @@ struct PairStorage
     uint64_t tmemEmpty[2];             // used in the leader CTA: 256 epilogue threads of the pair arrive
     uint32_t tmemBase;
     uint32_t abortFlag;
+    alignas(1024) uint8_t staging[2][kStagingBytes];   // epilogue: 128 rows x 128 bytes, swizzled, for TMA stores
 };
 
 __device__ __forceinline__ uint32_t clusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -616,10 +619,92 @@ __device__ __forceinline__ void ummaCommitPair(uint64_t* bar)
                  ::"r"(smemAddr(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
 }
 
+// ---- epilogue through shared memory and TMA ---------------------------------------------------------------------------
+// The direct epilogue has every thread store its own accumulator row: each warp-wide 16-byte store touches 32
+// different 128-byte lines, and for split-f32 problems every partial sum also READS C that way. Those accesses share
+// the L1 / shared-memory pipe with the TMA loads and the tensor core's operand reads (measured: l1tex throughput 77 % in
+// the f32 kernel). Here a slice of 128 rows x 128 bytes is written to shared memory in the 128-byte swizzle (conflict
+// free: 4 wavefronts per warp store), and one thread hands it to the TMA unit: a tile store for the first partial
+// sum, an f32 reduce-add (performed in L2, IEEE round-to-nearest) for the later ones, so C is never loaded by the SM.
+// The TMA unit also clips rows >= M and columns >= N. Partial sums of one tile are ordered by waiting for the earlier
+// bulk groups to complete before the next partial sum's first reduce-add is issued.
+__device__ __forceinline__ void tmaStoreTile(const CUtensorMap* map, const void* src, int32_t x, int32_t y, bool reduceAdd)
+{
+    if (reduceAdd)
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                     ::"l"(map), "r"(smemAddr(src)), "r"(x), "r"(y) : "memory");
+    else
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                     ::"l"(map), "r"(smemAddr(src)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const CUtensorMap* mapC, uint8_t (*staging)[kStagingBytes],
+                                                    uint32_t& sliceCounter, uint32_t taddr, uint32_t rowInCta, int32_t tileRow0, int32_t colBase,
+                                                    uint32_t c, bool captain)
+{
+    const bool f32Out = p.outDtype == F32;
+    const uint32_t colsPerSlice = f32Out ? 32u : 64u;              // 128 bytes of C per row and slice
+    const uint32_t swizzle = rowInCta & 7u;
+    if (captain && c > 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // earlier partial sums of this tile have landed
+    #pragma unroll 1
+    for (uint32_t c0 = 0; c0 < p.blockN; c0 += colsPerSlice)
+    {
+        uint8_t* buffer = staging[sliceCounter & 1u];
+        // the TMA operation that used this buffer two slices ago must have read it
+        if (captain) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        epilogueBarrier();
+        uint8_t* rowPtr = buffer + rowInCta * 128u;
+        if (f32Out)
+        {
+            uint32_t r[32];
+            tmemLoad32(taddr + c0, r);
+            tmemLoadWait();
+            #pragma unroll
+            for (uint32_t v = 0; v < 8; ++v)
+                *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+        else
+        {
+            uint32_t r0[32], r1[32];
+            tmemLoad32(taddr + c0, r0);
+            tmemLoad32(taddr + c0 + 32, r1);
+            tmemLoadWait();
+            uint32_t packed[32];
+            #pragma unroll
+            for (int v = 0; v < 16; ++v)
+            {
+                const float a0 = __uint_as_float(r0[2 * v]), a1 = __uint_as_float(r0[2 * v + 1]);
+                const float b0 = __uint_as_float(r1[2 * v]), b1 = __uint_as_float(r1[2 * v + 1]);
+                if (p.outDtype == BF16)
+                {
+                    packed[v] = static_cast<uint32_t>(dev::f32ToBf16(a0)) | (static_cast<uint32_t>(dev::f32ToBf16(a1)) << 16);
+                    packed[16 + v] = static_cast<uint32_t>(dev::f32ToBf16(b0)) | (static_cast<uint32_t>(dev::f32ToBf16(b1)) << 16);
+                }
+                else
+                {
+                    packed[v] = static_cast<uint32_t>(dev::f32ToF16(a0)) | (static_cast<uint32_t>(dev::f32ToF16(a1)) << 16);
+                    packed[16 + v] = static_cast<uint32_t>(dev::f32ToF16(b0)) | (static_cast<uint32_t>(dev::f32ToF16(b1)) << 16);
+                }
+            }
+            #pragma unroll
+            for (uint32_t v = 0; v < 8; ++v)
+                *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy writes -> visible to the TMA unit
+        epilogueBarrier();
+        if (captain)
+        {
+            tmaStoreTile(mapC, buffer, colBase + static_cast<int32_t>(c0), tileRow0, c > 0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++sliceCounter;
+    }
+}
+
 template <bool Tf32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
-               const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ KernelParams p)
+               const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ KernelParams p)
 {
     extern __shared__ uint8_t rawSmem[];
     PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
@@ -751,7 +836,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const bool captain = threadIdx.x == 64;                          // first thread of the epilogue warps
         const uint32_t rowInCta = quarter * 32 + lane;
         const size_t slotStride = size_t(2) * 128 * 256;                 // floats per cluster slot of the workspace
-        uint32_t acc = 0, accPhase = 0;
+        uint32_t acc = 0, accPhase = 0, sliceCounter = 0;
         bool ok = true;
         WorkIterator work(p, clusterId, clusters);
         WorkItem w;
@@ -768,7 +853,11 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
                     const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
-                    drainAccumulator(p, taddr, row, tn * p.blockN, c);
+                    if (p.tmaEpilogue)
+                        drainAccumulatorTma(p, &mapC, s.staging, sliceCounter, taddr, rowInCta, static_cast<int32_t>(tm * 256 + rank * 128),
+                                            static_cast<int32_t>(tn * p.blockN), c, captain);
+                    else
+                        drainAccumulator(p, taddr, row, tn * p.blockN, c);
                     fenceBeforeSync();
                     mbarArriveCluster(leaderEmpty + acc * 8);
                     acc ^= 1u;
@@ -818,6 +907,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             acc ^= 1u;
             if (acc == 0) accPhase ^= 1u;
         }
+        if (captain) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // staging buffers are read, C is written
     }
 
     fenceBeforeSync();
@@ -1195,8 +1285,18 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                 if (2ull * remainder * sizeof(uint32_t) > kernels::kGemmCounterBytes) return false;
             }
         }
-        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
-        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
+        // C through shared memory and TMA whenever its rows are 16-byte aligned (AIXB200_GEMM_TMA_STORE=0: direct stores)
+        static const bool tmaStoreEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_TMA_STORE"); return !(v && v[0] == '0'); }();
+        CUtensorMap mapC = mapA;
+        if (tmaStoreEnabled && p.vectorStores)
+        {
+            const CUtensorMapDataType ctype = q.dtype == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                            : (q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+            const size_t es = dtypeSize(q.dtype);
+            p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 128) ? 1u : 0u;
+        }
+        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
         if (ctx.launches) ++*ctx.launches;
         return true;
     }

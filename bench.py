@@ -30,6 +30,9 @@ DT = {"f32": 1, "bf16": 3}
 # DRAM traffic of the generated chain kernel per element, from the ncu capture at n = 2^26 (1054.9 MB for 2^26 f32
 # elements; the algorithmic figure is 16 bytes). Not captured for bf16.
 TRAFFIC_BYTES_PER_ELEMENT = {"f32": 1054.9e6 / (1 << 26)}
+# Algorithmic bytes of one step (chain + sum) per element, both arms: a, b, c are read and z is written once; the sum needs
+# no traffic of its own (the device folds it into the chain's kernel; an implementation that re-reads z is simply slower).
+STEP_BYTES_PER_ELEMENT_F32 = 16.0
 
 
 def chain(a, b, c, scalar_like):
@@ -100,7 +103,7 @@ def cpu_reference_chain(n_sample, repeats=1):
     for _ in range(repeats):
         _, _, secs = ref.chain_f32(a, b, c)
         best = secs if best is None else min(best, secs)
-    return 20.0 * rows * 1024 / best / 1e9, best
+    return STEP_BYTES_PER_ELEMENT_F32 * rows * 1024 / best / 1e9, best
 
 
 def run_reference(args, rank, world):
@@ -118,7 +121,7 @@ def run_reference(args, rank, world):
     total = 0.0
     for _ in range(args.steps):
         total += ref.chain_f32(a, b, c)[2]
-    gbs = 20.0 * n_sample * args.steps / total / 1e9
+    gbs = STEP_BYTES_PER_ELEMENT_F32 * n_sample * args.steps / total / 1e9
     line = {
         "impl": "reference", "metric": "fused-elementwise HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
@@ -203,9 +206,13 @@ def main():
         z = chain(a, b, c, scalar_like)
         return z, z.sum()
 
+    warm0 = dev.stats()
     for _ in range(args.warmup):
         z, s = step()
     dev.synchronize()
+    # The device folds z.sum() into the chain's kernel when it is recorded behind it (one launch per step, z is still
+    # written: 16 bytes per element); with that switched off the sum is a second kernel that reads z again (20 bytes).
+    sum_fused = dev.stats()["reductions_fused"] - warm0["reductions_fused"] >= args.warmup > 0
     del z, s
 
     # ---- timed region: K steps, device time, max over ranks ------------------------------------------------------
@@ -219,8 +226,11 @@ def main():
         for k in range(args.steps):
             dev.recordEvent(kev[k][0])
             z = chain(a, b, c, scalar_like)
+            if sum_fused:
+                s = z.sum()                      # recorded behind the chain: same kernel
             dev.recordEvent(kev[k][1])           # flushes: the fused chain kernel runs between the two events
-            s = z.sum()
+            if not sum_fused:
+                s = z.sum()
         dev.recordEvent(ev1)
         dev.synchronize()
         barrier()
@@ -228,7 +238,7 @@ def main():
     ms_total = max_over_ranks(dev.elapsedMs(ev0, ev1))
     chain_ms = float(np.mean([dev.elapsedMs(x, y) for x, y in kev]))
     result_sum = float(s.item())
-    step_bytes = (4 * n + n) * esize
+    step_bytes = 4 * n * esize        # algorithmic bytes of one step, whether or not the sum runs as a kernel of its own
     value = world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9
     launches = stats1["total_kernel_launches"] - stats0["total_kernel_launches"]
 
@@ -261,7 +271,9 @@ def main():
         "config": {"workload": f"fused chain z=(a*b+c)*sigmoid(a)-tanh(b)/(1+exp(-c)) + z.sum(), {args.dtype}, n=2^{args.log2n} "
                                f"elements per GPU as [{rows},1024] (config 4 of the sweep; config 0 expression)",
                    "l2": f"inputs are {3 * n * esize >> 20} MiB per step, larger than the 126 MB L2; no explicit flush",
-                   "sharding": "rows split across ranks, no data-path collective", "bytes_per_step_per_gpu": step_bytes},
+                   "sharding": "rows split across ranks, no data-path collective", "bytes_per_step_per_gpu": step_bytes,
+                   "bytes_counted": "a, b, c read + z written once per step; z.sum() " +
+                                    ("is folded into the chain kernel" if sum_fused else "runs as a second kernel that re-reads z (not counted)")},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 3 * n * esize, "d2h_bytes_per_step": esize,
                 "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": int(launches),
@@ -270,11 +282,12 @@ def main():
                      "traffic": TRAFFIC_BYTES_PER_ELEMENT.get(args.dtype, 0) * n or None,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel at n=2^26 "
                                        "(profiles/fused_chain_f32_2p26.md), scaled by n: traffic is proportional to n",
-                     "kernel": "generated fused chain kernel", "bytes_per_launch": chain_bytes,
+                     "kernel": "generated fused chain kernel" + (" with the sum folded in as a reduction epilogue" if sum_fused else ""),
+                     "bytes_per_launch": chain_bytes,
                      "ms_per_launch": chain_ms, "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": achieved / 8000.0},
         "checksum": result_sum,
         "fusion": {k: stats1[k] - stats0[k] for k in ("ops_recorded", "fused_kernels", "fused_ops", "fills_absorbed", "stores_elided",
-                                                      "kernel_cache_hits", "kernel_cache_misses")},
+                                                      "reductions_fused", "kernel_cache_hits", "kernel_cache_misses")},
     }
 
     # ---- the data-parallel MLP training configuration, at every N (gradient all-reduce over NCCL for N > 1) --------------
