@@ -194,7 +194,10 @@ def test_fused_reduction_result_feeds_later_ops_and_repeats_exactly(b200, ref):
         again = ((p - q) * (p - q)).sum() / float(x.size)
         outs.append((loss.numpy(), again.numpy()))
     assert np.array_equal(outs[0][0], outs[0][1]), "same grid, same fold order: bit-identical repeats"
-    assert_close(outs[0][0], outs[1][0], F32, "mse", scale=1.0)
+    # the CPU device sums 2^18 values sequentially in f32 (itself ~1e-4 off): both are held against the float64 value
+    exact = float(np.mean(np.square((x - t).astype(np.float32).astype(np.float64))))
+    assert abs(float(outs[0][0]) - exact) <= 1e-5 * exact, (outs[0][0], exact)
+    assert abs(float(outs[1][0]) - exact) <= 5e-4 * exact, (outs[1][0], exact)
 
 
 def test_fused_reduction_over_a_broadcast_chain_bf16(b200, ref):
