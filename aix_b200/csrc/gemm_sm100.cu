@@ -54,7 +54,12 @@ struct KernelParams
     uint32_t aBoxes, bBoxes;    // TMA boxes per stage and operand
     uint32_t aBoxBytes, bBoxBytes;
     uint32_t aBoxStepMn, bBoxStepMn;   // MN elements covered by one box (MN-major) / unused (K-major)
-    uint32_t aMap3d, bMap3d;    // MN-major operand fetched as ONE box of a 3-D map (64 mn, k, atoms of 64 mn)
+    // pair kernel (stages of two swizzle atoms along K):
+    uint32_t aLoad3d, bLoad3d;  // the operand's stage is ONE box of a 3-D map, else 2-D boxes of one atom each
+    uint32_t pairABytes, pairBBytes;   // bytes per stage and CTA
+    uint32_t pairAOff[8], pairBOff[8]; // shared-memory descriptor start of the stage's 8 MMAs, in 16-byte units
+    uint32_t pairALbo, pairBLbo;
+    uint32_t atomK;             // K elements per swizzle atom in the main pass: 64 (16-bit) or 32 (TF32); cross passes: 64
     uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t idesc16;           // f32 problems: descriptor of the bf16 cross-term passes
     uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
@@ -555,13 +560,18 @@ __device__ __forceinline__ void finishTile(const KernelParams& p, uint32_t taddr
     }
 }
 
-constexpr int kPairStages = 6;
-constexpr int kPairStageBytesB = 128 * 128;
+// One stage of the pair kernel holds TWO 128-byte swizzle atoms along K per operand (128 16-bit or 64 TF32 elements of
+// K): fetched as ONE 3-D TMA box, every operand row (or K line of an MN-major operand) is then a 256-byte contiguous run
+// in global memory. Measured: MN-major operands loaded as two 64 x 64 boxes ran A.B at 1006 and A^T.B at 887 TFLOP/s
+// (4096^3 bf16); as one 3-D box each, at 1325 and 1411 - above the all-K-major form with its 128-byte runs (1182).
+constexpr int kPairStages = 3;
+constexpr int kPairStageBytesA = 128 * 256;
+constexpr int kPairStageBytesB = 128 * 256;
 constexpr int kStagingBytes = 128 * 128;
 
 struct PairStorage
 {
-    alignas(1024) uint8_t a[kPairStages][kStageBytesA];
+    alignas(1024) uint8_t a[kPairStages][kPairStageBytesA];
     alignas(1024) uint8_t b[kPairStages][kPairStageBytesB];
     uint64_t full[kPairStages];        // used in the leader CTA: both CTAs' loads land here
     uint64_t empty[kPairStages];       // one per CTA, released by the leader's multicast commit
@@ -739,7 +749,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const uint32_t stageBytes = p.aBoxes * p.aBoxBytes + p.bBoxes * p.bBoxBytes;
+            const uint32_t stageBytes = p.pairABytes + p.pairBBytes;
             const uint32_t leaderFull0 = mapToCta(smemAddr(&s.full[0]), 0);
             WorkIterator work(p, clusterId, clusters);
             WorkItem w;
@@ -755,7 +765,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     {
                     const bool cross = Tf32 && passIndex < 2;          // see gemmKernel: bf16 cross terms first
                     const uint32_t first = cross ? kbBegin >> 1 : kbBegin, count = cross ? kbCount >> 1 : kbCount;
-                    const uint32_t blockK = cross ? 64u : p.blockK;
+                    const uint32_t atomK = cross ? 64u : p.atomK;
                     const CUtensorMap* ma = cross ? &mapA16 : &mapA;
                     const CUtensorMap* mb = cross ? &mapB16 : &mapB;
                     const uint32_t offA = (cross && passIndex == 0) ? p.kPerPhase : 0u, offB = (cross && passIndex == 1) ? p.kPerPhase : 0u;
@@ -764,18 +774,31 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
                         const uint32_t leaderFull = leaderFull0 + stage * 8;
                         mbarExpectTxCluster(leaderFull, stageBytes);
-                        const int32_t kA = static_cast<int32_t>(kb * blockK + offA), kB = static_cast<int32_t>(kb * blockK + offB);
-                        if (p.aMap3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, kA, m0 >> 6);
-                        else for (uint32_t bx = 0; bx < p.aBoxes; ++bx)
+                        // K coordinate of the stage in elements; split-f32 operands keep their `lo` halves kPerPhase further
+                        const uint32_t kA = kb * 2 * atomK + offA, kB = kb * 2 * atomK + offB;
+                        if (p.aMnMajor)
                         {
-                            if (p.aMnMajor) tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, m0 + static_cast<int32_t>(bx * p.aBoxStepMn), kA);
-                            else            tmaLoad2dPair(&s.a[stage][bx * p.aBoxBytes], ma, leaderFull, kA, m0);
+                            if (p.aLoad3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, static_cast<int32_t>(kA), m0 >> 6);
+                            else for (uint32_t at = 0; at < 2; ++at) for (uint32_t h = 0; h < 2; ++h)
+                                tmaLoad2dPair(&s.a[stage][at * 16384 + h * 8192], ma, leaderFull, m0 + static_cast<int32_t>(at * 64), static_cast<int32_t>(kA + h * 64));
                         }
-                        if (p.bMap3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, kB, n0 >> 6);
-                        else for (uint32_t bx = 0; bx < p.bBoxes; ++bx)
+                        else
                         {
-                            if (p.bMnMajor) tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, n0 + static_cast<int32_t>(bx * p.bBoxStepMn), kB);
-                            else            tmaLoad2dPair(&s.b[stage][bx * p.bBoxBytes], mb, leaderFull, kB, n0);
+                            if (p.aLoad3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, m0, static_cast<int32_t>(kA / atomK));
+                            else for (uint32_t h = 0; h < 2; ++h)
+                                tmaLoad2dPair(&s.a[stage][h * (p.pairABytes >> 1)], ma, leaderFull, static_cast<int32_t>(kA + h * atomK), m0);
+                        }
+                        if (p.bMnMajor)
+                        {
+                            if (p.bLoad3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, static_cast<int32_t>(kB), n0 >> 6);
+                            else for (uint32_t at = 0; at < (p.blockN >> 7); ++at) for (uint32_t h = 0; h < 2; ++h)
+                                tmaLoad2dPair(&s.b[stage][at * 16384 + h * 8192], mb, leaderFull, n0 + static_cast<int32_t>(at * 64), static_cast<int32_t>(kB + h * 64));
+                        }
+                        else
+                        {
+                            if (p.bLoad3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, n0, static_cast<int32_t>(kB / atomK));
+                            else for (uint32_t h = 0; h < 2; ++h)
+                                tmaLoad2dPair(&s.b[stage][h * (p.pairBBytes >> 1)], mb, leaderFull, static_cast<int32_t>(kB + h * atomK), n0);
                         }
                         if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                     }
@@ -790,10 +813,13 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         {
             // Descriptor halves that never change: the high word (stride offsets, version, swizzle) and the low word of
             // stage 0; per stage and per MMA only a 32-bit add remains.
-            const uint64_t descHiA = smemDescriptor(0, p.aLbo, 1024), descHiB = smemDescriptor(0, p.bLbo, 1024);
+            const uint64_t descHiA = smemDescriptor(0, p.pairALbo, 1024), descHiB = smemDescriptor(0, p.pairBLbo, 1024);
             const uint32_t descLoA = (smemAddr(&s.a[0][0]) & 0x3FFFFu) >> 4, descLoB = (smemAddr(&s.b[0][0]) & 0x3FFFFu) >> 4;
             const uint32_t aStageBytes = sizeof(s.a[0]), bStageBytes = sizeof(s.b[0]);
-            const uint32_t advA = p.kAdvanceA >> 4, advB = p.kAdvanceB >> 4, idesc = p.idesc, idesc16 = p.idesc16;
+            const uint32_t idesc = p.idesc, idesc16 = p.idesc16;
+            uint32_t aOff[8], bOff[8];
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) { aOff[j] = p.pairAOff[j]; bOff[j] = p.pairBOff[j]; }
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             WorkIterator work(p, clusterId, clusters);
@@ -805,7 +831,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 fenceAfterSync();
                 const uint32_t tmemD = tmemBase + acc * kBlockN;
                 const uint32_t kbCount = min(w.kbCount - c * p.chunkBlocks, p.chunkBlocks);
-                // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2), then kbCount TF32 stages
+                // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2 stages of 128), then kbCount
+                // TF32 stages of 64
                 const uint32_t stagesInChunk = Tf32 ? 2 * kbCount : kbCount;
                 for (uint32_t it = 0; it < stagesInChunk; ++it)
                 {
@@ -814,10 +841,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
                     const bool cross = Tf32 && it < kbCount;
                     #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j)
+                    for (uint32_t j = 0; j < 8; ++j)
                     {
-                        const uint64_t da = descHiA | static_cast<uint64_t>(aLo + j * advA);
-                        const uint64_t db = descHiB | static_cast<uint64_t>(bLo + j * advB);
+                        const uint64_t da = descHiA | static_cast<uint64_t>(aLo + aOff[j]);
+                        const uint64_t db = descHiB | static_cast<uint64_t>(bLo + bOff[j]);
                         if (cross) ummaPair<false>(tmemD, da, db, idesc16, (it | j) != 0 ? 1u : 0u);
                         else       ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
@@ -1088,6 +1115,21 @@ bool makeMap3d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uin
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D view of a K-major matrix (k fastest): (atomElems k, rows, k / atomElems), atomElems = 128 bytes of K. One box
+// {atomElems, boxRows, 2} lands as two consecutive K-major swizzle atoms of boxRows rows: 256 contiguous bytes per row.
+bool makeMapK3d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t rows, uint64_t kElems, uint64_t pitchBytes,
+                uint32_t atomElems, uint32_t boxRows)
+{
+    cuuint64_t dims[3] = {atomElems, rows, kElems / atomElems};
+    cuuint64_t strides[2] = {pitchBytes, 128};
+    cuuint32_t box[3] = {atomElems, boxRows, 2};
+    cuuint32_t elemStrides[3] = {1, 1, 1};
+    EncodeTiledFn fn = encodeTiled();
+    if (!fn) return false;
+    return fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct Operand
 {
     const void* base;
@@ -1160,7 +1202,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     if (!tf32)
     {
         Operand a, b;
-        static const bool mn3d = []{ const char* v = std::getenv("AIXB200_GEMM_MN3D"); return !(v && v[0] == '0'); }();
+        static const bool box3d = []{ const char* v = std::getenv("AIXB200_GEMM_BOX3D"); return !(v && v[0] == '0'); }();
         if (!classify(q.a, q.aRowStride, q.aColStride, q.m, q.k, true, 2, &a)) return false;
         if (!classify(q.b, q.bRowStride, q.bColStride, q.k, q.n, false, 2, &b)) return false;
         p.blockK = 64;
@@ -1171,29 +1213,52 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.mmasPerStage = 4;
         const CUtensorMapDataType type = q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         p.aMnMajor = a.mnMajor; p.bMnMajor = b.mnMajor;
-        if (a.mnMajor)
+        if (!pair)
         {
-            p.aBoxes = kBlockM / 64; p.aBoxBytes = 64 * 128; p.aBoxStepMn = 64; p.aLbo = 64 * 128; p.kAdvanceA = 16 * 128;
-            p.aMap3d = mn3d && pair && q.m % 64 == 0;
-            if (p.aMap3d ? !makeMap3d(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, kBlockM / 64)
-                         : !makeMap(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, 64)) return false;
+            if (a.mnMajor)
+            {
+                p.aBoxes = kBlockM / 64; p.aBoxBytes = 64 * 128; p.aBoxStepMn = 64; p.aLbo = 64 * 128; p.kAdvanceA = 16 * 128;
+                if (!makeMap(&mapA, type, a.base, q.m, q.k, a.pitch * 2, 64, 64)) return false;
+            }
+            else
+            {
+                p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.aLbo = 0; p.kAdvanceA = 32;
+                if (!makeMap(&mapA, type, a.base, q.k, q.m, a.pitch * 2, 64, kBlockM)) return false;
+            }
+            if (b.mnMajor)
+            {
+                p.bBoxes = bRows / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
+                if (!makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
+            }
+            else
+            {
+                p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.bLbo = 0; p.kAdvanceB = 32;
+                if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, bRows)) return false;
+            }
         }
         else
         {
-            p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.aLbo = 0; p.kAdvanceA = 32;
-            if (!makeMap(&mapA, type, a.base, q.k, q.m, a.pitch * 2, 64, kBlockM)) return false;
-        }
-        if (b.mnMajor)
-        {
-            p.bBoxes = bRows / 64; p.bBoxBytes = 64 * 128; p.bBoxStepMn = 64; p.bLbo = 64 * 128; p.kAdvanceB = 16 * 128;
-            p.bMap3d = mn3d && pair && q.n % 64 == 0;
-            if (p.bMap3d ? !makeMap3d(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, bRows / 64)
-                         : !makeMap(&mapB, type, b.base, q.n, q.k, b.pitch * 2, 64, 64)) return false;
-        }
-        else
-        {
-            p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.bLbo = 0; p.kAdvanceB = 32;
-            if (!makeMap(&mapB, type, b.base, q.k, q.n, b.pitch * 2, 64, bRows)) return false;
+            // stages of 128 elements of K: two swizzle atoms per operand
+            p.atomK = 64;
+            p.kBlocks = (p.k + 127) / 128;
+            p.chunkBlocks = p.kBlocks;
+            auto plan = [&](const Operand& op, uint64_t mn, uint32_t rows, CUtensorMap* map, uint32_t* load3d, uint32_t* bytes, uint32_t* lbo, uint32_t* off)
+            {
+                if (op.mnMajor)
+                {
+                    const uint32_t atoms = rows / 64;
+                    *bytes = atoms * 128 * 128; *lbo = 128 * 128;
+                    for (uint32_t j = 0; j < 8; ++j) off[j] = (j * 16 * 128) >> 4;
+                    *load3d = box3d && mn % 64 == 0;
+                    return *load3d ? makeMap3d(map, type, op.base, mn, q.k, op.pitch * 2, 128, atoms) : makeMap(map, type, op.base, mn, q.k, op.pitch * 2, 64, 64);
+                }
+                *bytes = rows * 256; *lbo = 0;
+                for (uint32_t j = 0; j < 8; ++j) off[j] = ((j / 4) * rows * 128 + (j % 4) * 32) >> 4;
+                *load3d = box3d && q.k % 64 == 0;
+                return *load3d ? makeMapK3d(map, type, op.base, mn, q.k, op.pitch * 2, 64, rows) : makeMap(map, type, op.base, q.k, mn, op.pitch * 2, 64, rows);
+            };
+            if (!plan(a, q.m, kBlockM, &mapA, &p.aLoad3d, &p.pairABytes, &p.pairALbo, p.pairAOff)) return false;
+            if (!plan(b, q.n, bRows, &mapB, &p.bLoad3d, &p.pairBBytes, &p.pairBLbo, p.pairBOff)) return false;
         }
         mapA16 = mapA; mapB16 = mapB;                      // unused by 16-bit problems
         // instruction descriptor: D = f32, A/B = bf16 or f16, majors, N >> 3, M >> 4
@@ -1204,7 +1269,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     {
         // Split into K-major scratch (see splitF32Kernel). kPad is a multiple of 64 so that bf16 stages (64 elements)
         // and TF32 stages (32 elements) cover the same K ranges.
-        const uint32_t kPad = (p.k + 63) & ~63u;
+        const uint32_t kPad = (p.k + 127) & ~127u;
         float* hiA = static_cast<float*>(device.temporary(static_cast<size_t>(p.m) * kPad * 4));
         float* hiB = static_cast<float*>(device.temporary(static_cast<size_t>(p.n) * kPad * 4));
         uint16_t* pairA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
@@ -1213,19 +1278,40 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         // B is k x n: its "rows" for the split are the n columns
         launchSplit(ctx.stream, static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, hiB, pairB);
         if (ctx.launches) *ctx.launches += 2;
-        p.blockK = 32;
-        p.kBlocks = kPad / 32;
         p.kPhases = 3;
         p.kPerPhase = kPad;
-        p.chunkBlocks = 16;                                  // 512 elements of K per in-TMEM partial sum
+        if (!pair)
+        {
+            p.blockK = 32;
+            p.kBlocks = kPad / 32;
+            p.chunkBlocks = 16;                                  // 512 elements of K per in-TMEM partial sum
+            p.mmasPerStage = 4;
+            p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
+            p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.kAdvanceB = 32;
+            if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiA, kPad, q.m, static_cast<uint64_t>(kPad) * 4, 32, kBlockM)) return false;
+            if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiB, kPad, q.n, static_cast<uint64_t>(kPad) * 4, 32, bRows)) return false;
+            if (!makeMap(&mapA16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairA, 2ull * kPad, q.m, 2ull * kPad * 2, 64, kBlockM)) return false;
+            if (!makeMap(&mapB16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairB, 2ull * kPad, q.n, 2ull * kPad * 2, 64, bRows)) return false;
+        }
+        else
+        {
+            // stages of 64 TF32 elements (main pass) or 128 bf16 elements (cross passes), all K-major, one 3-D box each
+            p.atomK = 32;
+            p.kBlocks = kPad / 64;
+            p.chunkBlocks = 8;                                   // 512 elements of K per in-TMEM partial sum
+            p.aLoad3d = p.bLoad3d = 1;
+            p.pairABytes = kBlockM * 256; p.pairBBytes = bRows * 256;
+            for (uint32_t j = 0; j < 8; ++j)
+            {
+                p.pairAOff[j] = ((j / 4) * kBlockM * 128 + (j % 4) * 32) >> 4;
+                p.pairBOff[j] = ((j / 4) * bRows * 128 + (j % 4) * 32) >> 4;
+            }
+            if (!makeMapK3d(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiA, q.m, kPad, static_cast<uint64_t>(kPad) * 4, 32, kBlockM)) return false;
+            if (!makeMapK3d(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiB, q.n, kPad, static_cast<uint64_t>(kPad) * 4, 32, bRows)) return false;
+            if (!makeMapK3d(&mapA16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairA, q.m, 2ull * kPad, 2ull * kPad * 2, 64, kBlockM)) return false;
+            if (!makeMapK3d(&mapB16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairB, q.n, 2ull * kPad, 2ull * kPad * 2, 64, bRows)) return false;
+        }
         p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
-        p.mmasPerStage = 4;
-        p.aBoxes = 1; p.aBoxBytes = kStageBytesA; p.kAdvanceA = 32;
-        p.bBoxes = 1; p.bBoxBytes = bRows * 128; p.kAdvanceB = 32;
-        if (!makeMap(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiA, kPad, q.m, static_cast<uint64_t>(kPad) * 4, 32, kBlockM)) return false;
-        if (!makeMap(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, hiB, kPad, q.n, static_cast<uint64_t>(kPad) * 4, 32, bRows)) return false;
-        if (!makeMap(&mapA16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairA, 2ull * kPad, q.m, 2ull * kPad * 2, 64, kBlockM)) return false;
-        if (!makeMap(&mapB16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairB, 2ull * kPad, q.n, 2ull * kPad * 2, 64, bRows)) return false;
         const uint32_t shape = ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
         p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | shape;            // D f32, A/B tf32
         p.idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | shape;          // D f32, A/B bf16
