@@ -125,6 +125,14 @@ __device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatil
     }
     return true;
 }
+// After a wait has run out, the thread that issued TMA copies lingers for a bounded time before the CTA gives its
+// shared memory back, so that copies still in flight land in memory this CTA still owns.
+__device__ __forceinline__ void lingerAfterAbort(volatile uint32_t* abortFlag)
+{
+    if (!*abortFlag) return;
+    const uint64_t start = globalTimerNs();
+    while (globalTimerNs() - start < 1000000ull) { }          // 1 ms: orders of magnitude above a copy's latency
+}
 __device__ __forceinline__ void tmaLoad2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -439,6 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
         }
     }
 
+    if (threadIdx.x == 0) lingerAfterAbort(abortFlag);
     fenceBeforeSync();
     __syncthreads();
     if (warp == 1)
@@ -937,6 +946,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (captain) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // staging buffers are read, C is written
     }
 
+    if (threadIdx.x == 0) lingerAfterAbort(abortFlag);
     fenceBeforeSync();
     __syncthreads();
     clusterSync();                      // the leader's MMAs read the peer's shared memory until the very end
@@ -1013,7 +1023,7 @@ __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ 
     }
     else
     {
-        __shared__ __align__(16) float tile[64][68];          // [k][row]
+        __shared__ float tile[64][65];                        // [row][k]; odd pitch: both phases at most 2-way conflicts
         #pragma unroll
         for (uint32_t it = 0; it < 4; ++it)
         {
@@ -1033,18 +1043,20 @@ __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ 
                     if (r + 3 < rows) x.w = in[3 * rowStride];
                 }
             }
-            *reinterpret_cast<float4*>(&tile[kk][rg]) = x;
+            tile[rg][kk] = x.x; tile[rg + 1][kk] = x.y; tile[rg + 2][kk] = x.z; tile[rg + 3][kk] = x.w;
         }
         __syncthreads();
+        // same thread-to-output mapping as the in-place variant: 8 threads cover one row's 64 k, so the three output
+        // streams leave as 256- and 128-byte runs per row
         #pragma unroll
         for (uint32_t it = 0; it < 2; ++it)
         {
             const uint32_t idx = threadIdx.x + it * 256;
-            const uint32_t r = idx & 63u, kg = (idx >> 6) * 8;
+            const uint32_t r = idx >> 3, kg = (idx & 7u) * 8;
             if (r0 + r >= rows) continue;
             float v[8];
             #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j) v[j] = tile[kg + j][r];
+            for (uint32_t j = 0; j < 8; ++j) v[j] = tile[r][kg + j];
             splitEmit(v, r0 + r, c0 + kg, kPad, hi32, pair16);
         }
     }
