@@ -3,7 +3,7 @@ than the 126 MB L2 but hold well under a few GB on the device.
 
     python -m aix_b200.profile_cases <case> [repeats]
 
-cases: chain_f32 chain_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
+cases: chain_f32 chain_bf16 chain_sum_f32 chain_sum_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
        gemm_bf16_k1024 gemm_f32_4096 gemm_f32_k1024 adam_f32 mlp_f32
 Prints the device time per repeat measured with events on the device's stream.
 """
@@ -30,6 +30,11 @@ def build(dev, case):
     if case.startswith("chain_"):
         dt = C.F32 if case.endswith("f32") else C.BF16
         a, b, c = (_rand(dev, (1 << 16, 1024), dt, s) for s in range(3))
+        if case.startswith("chain_sum_"):
+            def both():                                   # the sum is recorded behind the chain: one kernel
+                z = chain(a, b, c)
+                return z, z.sum()
+            return both
         return lambda: chain(a, b, c)
     if case in ("sum_f32", "sum_bf16"):
         x = _rand(dev, (1 << 17, 1024), C.F32 if case.endswith("f32") else C.BF16, 0)

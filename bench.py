@@ -45,10 +45,16 @@ class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, enabled=True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
+        self.begin = self.end = None
+
+    def mark_begin(self): self.begin = time.time()
+    def mark_end(self): self.end = time.time()
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -60,7 +66,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([f.strip() for f in line.split(",")])
+            self.rows.append([time.time()] + [f.strip() for f in line.split(",")])
 
     def __exit__(self, *exc):
         if self.proc:
@@ -70,7 +76,11 @@ class ClockSampler:
 
     def summary(self):
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        rows = self.rows
+        if self.begin is not None and self.end is not None:
+            inside = [r for r in rows if self.begin - 0.15 <= r[0] <= self.end + 0.15]
+            rows = inside or rows            # a timed region shorter than the sampling period: fall back to all samples under load
+        for r in (x[1:] for x in rows):
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except (ValueError, IndexError):
@@ -206,6 +216,14 @@ def main():
         z = chain(a, b, c, scalar_like)
         return z, z.sum()
 
+    # One clock sampler, on rank 0 only, started well before anything is timed: nvidia-smi takes driver-wide locks
+    # while it starts (measured: with one sampler per rank starting at the head of the timed region, an 8-rank run
+    # stalled for ~100 ms inside its 7 ms of timed work). It keeps sampling through the warm-up (same kernels, same
+    # load) and the timed region; the summary prefers the samples that fall inside the timed region.
+    clocks = ClockSampler(local, enabled=(rank == 0))
+    clocks.__enter__()
+    if rank == 0:
+        time.sleep(0.5)
     warm0 = dev.stats()
     for _ in range(args.warmup):
         z, s = step()
@@ -221,22 +239,24 @@ def main():
     stats0 = dev.stats()
     barrier()
     dev.synchronize()
-    with ClockSampler(local) as clocks:
-        dev.recordEvent(ev0)
-        for k in range(args.steps):
-            dev.recordEvent(kev[k][0])
-            z = chain(a, b, c, scalar_like)
-            if sum_fused:
-                s = z.sum()                      # recorded behind the chain: same kernel
-            dev.recordEvent(kev[k][1])           # flushes: the fused chain kernel runs between the two events
-            if not sum_fused:
-                s = z.sum()
-        dev.recordEvent(ev1)
-        dev.synchronize()
-        barrier()
+    clocks.mark_begin()
+    dev.recordEvent(ev0)
+    for k in range(args.steps):
+        dev.recordEvent(kev[k][0])
+        z = chain(a, b, c, scalar_like)
+        if sum_fused:
+            s = z.sum()                      # recorded behind the chain: same kernel
+        dev.recordEvent(kev[k][1])           # flushes: the fused chain kernel runs between the two events
+        if not sum_fused:
+            s = z.sum()
+    dev.recordEvent(ev1)
+    dev.synchronize()
+    clocks.mark_end()
+    barrier()
+    clocks.__exit__(None, None, None)
     stats1 = dev.stats()
     ms_total = max_over_ranks(dev.elapsedMs(ev0, ev1))
-    chain_ms = float(np.mean([dev.elapsedMs(x, y) for x, y in kev]))
+    chain_ms = float(np.median([dev.elapsedMs(x, y) for x, y in kev]))
     result_sum = float(s.item())
     step_bytes = 4 * n * esize        # algorithmic bytes of one step, whether or not the sum runs as a kernel of its own
     value = world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9
