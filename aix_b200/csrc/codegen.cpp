@@ -341,7 +341,7 @@ KernelVariant chooseVariant(const KernelSpec& spec)
         for (auto& l : spec.loads) see(l.view.dtype);
         for (auto& st : spec.stores) see(st.view.dtype);
         for (auto& nd : spec.nodes) { see(nd.dtype); if (nd.op == Op::Cast) see(nd.srcDtype); }
-        v.packed16 = uniform && (common == F16 || common == BF16) && v.vec >= 2 && v.vec % 2 == 0 && spec.reductions.empty();
+        v.packed16 = uniform && (common == F16 || common == BF16) && v.vec >= 2 && v.vec % 2 == 0;
     }
     v.index64 = maxSpan >= (uint64_t(1) << 31);
     for (size_t i = 0; i < spec.loads.size(); ++i)
@@ -686,6 +686,13 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
             for (size_t i = 0; i < nS; ++i)
                 o << "                    y" << i << ".v[2 * e] = (u16_t)(v" << spec.stores[i].node << " & 0xffffu); y" << i
                   << ".v[2 * e + 1] = (u16_t)(v" << spec.stores[i].node << " >> 16);\n";
+            // reductions fold both halves of the packed register, widened to float
+            for (size_t r = 0; r < nR; ++r)
+            {
+                const std::string P = "P2<" + T(spec.reductions[r].dtype) + ">::", v = "v" + std::to_string(spec.reductions[r].node);
+                o << "                    racc" << r << " = " << redType(r) << "::step(" << redType(r) << "::step(racc" << r << ", " << P << "lo(" << v
+                  << ")), " << P << "hi(" << v << "));\n";
+            }
             o << "                }\n";
         }
         else

@@ -143,7 +143,7 @@ def run_reference(args, rank, world):
                                    f"(the reference CPU device is single-threaded) of {os.cpu_count()} host cores"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def emit(line):
