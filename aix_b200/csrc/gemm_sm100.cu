@@ -1310,7 +1310,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             // stages of 64 TF32 elements (main pass) or 128 bf16 elements (cross passes), all K-major, one 3-D box each
             p.atomK = 32;
             p.kBlocks = kPad / 64;
-            p.chunkBlocks = 8;                                   // 512 elements of K per in-TMEM partial sum
+            // 512 elements of K per in-TMEM partial sum (AIXB200_GEMM_CHUNK: in stages of 64, even; for measurements)
+            static const int chunkOverride = []{ const char* v = std::getenv("AIXB200_GEMM_CHUNK"); return v ? std::atoi(v) : 0; }();
+            p.chunkBlocks = (chunkOverride >= 2 && chunkOverride % 2 == 0) ? static_cast<uint32_t>(chunkOverride) : 8u;
             p.aLoad3d = p.bLoad3d = 1;
             p.pairABytes = kBlockM * 256; p.pairBBytes = bRows * 256;
             for (uint32_t j = 0; j < 8; ++j)
