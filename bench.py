@@ -49,6 +49,14 @@ class ClockSampler:
         self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
         self.begin = self.end = None
 
+    def wait_ready(self, timeout=8.0):
+        """Blocks until nvidia-smi has delivered its first sample: its start-up attaches to every GPU of the box under
+        driver-wide locks (measured: a kernel launch issued during it waited 90-110 ms)."""
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < timeout and self.proc.poll() is None:
+            time.sleep(0.02)
+        time.sleep(0.05)
+
     def mark_begin(self): self.begin = time.time()
     def mark_end(self): self.end = time.time()
 
@@ -216,14 +224,13 @@ def main():
         z = chain(a, b, c, scalar_like)
         return z, z.sum()
 
-    # One clock sampler, on rank 0 only, started well before anything is timed: nvidia-smi takes driver-wide locks
-    # while it starts (measured: with one sampler per rank starting at the head of the timed region, an 8-rank run
-    # stalled for ~100 ms inside its 7 ms of timed work). It keeps sampling through the warm-up (same kernels, same
-    # load) and the timed region; the summary prefers the samples that fall inside the timed region.
+    # One clock sampler, on rank 0 only, started before anything is timed and waited for until its first sample has
+    # arrived: nvidia-smi takes driver-wide locks while it starts (measured: a launch that fell into that window waited
+    # ~100 ms, inside 7 ms of timed work). It keeps sampling through the warm-up (same kernels, same load) and the timed
+    # region; the summary prefers the samples that fall inside the timed region.
     clocks = ClockSampler(local, enabled=(rank == 0))
     clocks.__enter__()
-    if rank == 0:
-        time.sleep(0.5)
+    clocks.wait_ready()
     warm0 = dev.stats()
     for _ in range(args.warmup):
         z, s = step()
