@@ -576,7 +576,7 @@ __device__ __forceinline__ void finishTile(const KernelParams& p, uint32_t taddr
 constexpr int kPairStages = 3;
 constexpr int kPairStageBytesA = 128 * 256;
 constexpr int kPairStageBytesB = 128 * 256;
-constexpr int kStagingBytes = 128 * 128;
+constexpr int kWarpStagingBytes = 32 * 128;
 
 struct PairStorage
 {
@@ -588,7 +588,7 @@ struct PairStorage
     uint64_t tmemEmpty[2];             // used in the leader CTA: 256 epilogue threads of the pair arrive
     uint32_t tmemBase;
     uint32_t abortFlag;
-    alignas(1024) uint8_t staging[2][kStagingBytes];   // epilogue: 128 rows x 128 bytes, swizzled, for TMA stores
+    alignas(1024) uint8_t staging[4][2 * kWarpStagingBytes];   // epilogue: per warp two buffers of 32 rows x 128 bytes, swizzled, for TMA stores
 };
 
 __device__ __forceinline__ uint32_t clusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -657,66 +657,88 @@ __device__ __forceinline__ void tmaStoreTile(const CUtensorMap* map, const void*
                      ::"l"(map), "r"(smemAddr(src)), "r"(x), "r"(y) : "memory");
 }
 
-__device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const CUtensorMap* mapC, uint8_t (*staging)[kStagingBytes],
-                                                    uint32_t& sliceCounter, uint32_t taddr, uint32_t rowInCta, int32_t tileRow0, int32_t colBase,
-                                                    uint32_t c, bool captain)
+// One 32-row x 128-byte slice of C leaves through this warp's own staging buffer: no barrier wider than the warp.
+__device__ __forceinline__ void emitSlice(const CUtensorMap* mapC, uint8_t* warpStaging, uint32_t& sliceCounter, const uint4 (&chunks)[8],
+                                          uint32_t lane, int32_t x, int32_t y, bool reduceAdd)
 {
-    const bool f32Out = p.outDtype == F32;
-    const uint32_t colsPerSlice = f32Out ? 32u : 64u;              // 128 bytes of C per row and slice
-    const uint32_t swizzle = rowInCta & 7u;
-    if (captain && c > 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // earlier partial sums of this tile have landed
-    #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < p.blockN; c0 += colsPerSlice)
+    uint8_t* buffer = warpStaging + (sliceCounter & 1u) * kWarpStagingBytes;
+    // the TMA operation that used this buffer two slices ago must have read it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+    uint8_t* rowPtr = buffer + lane * 128u;
+    const uint32_t swizzle = lane & 7u;
+    #pragma unroll
+    for (uint32_t v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) = chunks[v];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");          // generic-proxy writes -> visible to the TMA unit
+    __syncwarp();
+    if (lane == 0)
     {
-        uint8_t* buffer = staging[sliceCounter & 1u];
-        // the TMA operation that used this buffer two slices ago must have read it
-        if (captain) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        epilogueBarrier();
-        uint8_t* rowPtr = buffer + rowInCta * 128u;
-        if (f32Out)
+        tmaStoreTile(mapC, buffer, x, y, reduceAdd);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    ++sliceCounter;
+}
+
+__device__ __forceinline__ void packF32(const uint32_t (&r)[32], uint4 (&chunks)[8])
+{
+    #pragma unroll
+    for (int v = 0; v < 8; ++v) chunks[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+}
+
+// `taddr` addresses this warp's 32 TMEM lanes; (x0, y0) is the position in C of their first element.
+__device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const CUtensorMap* mapC, uint8_t* warpStaging, uint32_t& sliceCounter,
+                                                    uint32_t taddr, uint32_t lane, int32_t x0, int32_t y0, uint32_t c)
+{
+    const bool reduceAdd = c > 0;
+    if (lane == 0 && reduceAdd) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // earlier partial sums of these rows have landed
+    if (p.outDtype == F32)
+    {
+        // 32 columns per slice; the TMEM load of the next slice is in flight while this one is staged and handed over
+        uint32_t rA[32], rB[32];
+        uint4 chunks[8];
+        tmemLoad32(taddr, rA);
+        #pragma unroll 1
+        for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)
         {
-            uint32_t r[32];
-            tmemLoad32(taddr + c0, r);
             tmemLoadWait();
-            #pragma unroll
-            for (uint32_t v = 0; v < 8; ++v)
-                *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            tmemLoad32(taddr + c0 + 32, rB);
+            packF32(rA, chunks);
+            emitSlice(mapC, warpStaging, sliceCounter, chunks, lane, x0 + static_cast<int32_t>(c0), y0, reduceAdd);
+            tmemLoadWait();
+            if (c0 + 64 < p.blockN) tmemLoad32(taddr + c0 + 64, rA);
+            packF32(rB, chunks);
+            emitSlice(mapC, warpStaging, sliceCounter, chunks, lane, x0 + static_cast<int32_t>(c0 + 32), y0, reduceAdd);
         }
-        else
+        return;
+    }
+    #pragma unroll 1
+    for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)                    // 64 columns of 16-bit output per slice
+    {
+        uint32_t r0[32], r1[32];
+        tmemLoad32(taddr + c0, r0);
+        tmemLoad32(taddr + c0 + 32, r1);
+        tmemLoadWait();
+        uint32_t packed[32];
+        #pragma unroll
+        for (int v = 0; v < 16; ++v)
         {
-            uint32_t r0[32], r1[32];
-            tmemLoad32(taddr + c0, r0);
-            tmemLoad32(taddr + c0 + 32, r1);
-            tmemLoadWait();
-            uint32_t packed[32];
-            #pragma unroll
-            for (int v = 0; v < 16; ++v)
+            const float a0 = __uint_as_float(r0[2 * v]), a1 = __uint_as_float(r0[2 * v + 1]);
+            const float b0 = __uint_as_float(r1[2 * v]), b1 = __uint_as_float(r1[2 * v + 1]);
+            if (p.outDtype == BF16)
             {
-                const float a0 = __uint_as_float(r0[2 * v]), a1 = __uint_as_float(r0[2 * v + 1]);
-                const float b0 = __uint_as_float(r1[2 * v]), b1 = __uint_as_float(r1[2 * v + 1]);
-                if (p.outDtype == BF16)
-                {
-                    packed[v] = static_cast<uint32_t>(dev::f32ToBf16(a0)) | (static_cast<uint32_t>(dev::f32ToBf16(a1)) << 16);
-                    packed[16 + v] = static_cast<uint32_t>(dev::f32ToBf16(b0)) | (static_cast<uint32_t>(dev::f32ToBf16(b1)) << 16);
-                }
-                else
-                {
-                    packed[v] = static_cast<uint32_t>(dev::f32ToF16(a0)) | (static_cast<uint32_t>(dev::f32ToF16(a1)) << 16);
-                    packed[16 + v] = static_cast<uint32_t>(dev::f32ToF16(b0)) | (static_cast<uint32_t>(dev::f32ToF16(b1)) << 16);
-                }
+                packed[v] = static_cast<uint32_t>(dev::f32ToBf16(a0)) | (static_cast<uint32_t>(dev::f32ToBf16(a1)) << 16);
+                packed[16 + v] = static_cast<uint32_t>(dev::f32ToBf16(b0)) | (static_cast<uint32_t>(dev::f32ToBf16(b1)) << 16);
             }
-            #pragma unroll
-            for (uint32_t v = 0; v < 8; ++v)
-                *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            else
+            {
+                packed[v] = static_cast<uint32_t>(dev::f32ToF16(a0)) | (static_cast<uint32_t>(dev::f32ToF16(a1)) << 16);
+                packed[16 + v] = static_cast<uint32_t>(dev::f32ToF16(b0)) | (static_cast<uint32_t>(dev::f32ToF16(b1)) << 16);
+            }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy writes -> visible to the TMA unit
-        epilogueBarrier();
-        if (captain)
-        {
-            tmaStoreTile(mapC, buffer, colBase + static_cast<int32_t>(c0), tileRow0, c > 0);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-        ++sliceCounter;
+        uint4 chunks[8];
+        #pragma unroll
+        for (int v = 0; v < 8; ++v) chunks[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+        emitSlice(mapC, warpStaging, sliceCounter, chunks, lane, x0 + static_cast<int32_t>(c0), y0, false);
     }
 }
 
@@ -890,8 +912,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     fenceAfterSync();
                     const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16);
                     if (p.tmaEpilogue)
-                        drainAccumulatorTma(p, &mapC, s.staging, sliceCounter, taddr, rowInCta, static_cast<int32_t>(tm * 256 + rank * 128),
-                                            static_cast<int32_t>(tn * p.blockN), c, captain);
+                        drainAccumulatorTma(p, &mapC, s.staging[quarter], sliceCounter, taddr, lane, static_cast<int32_t>(tn * p.blockN),
+                                            static_cast<int32_t>(tm * 256 + rank * 128 + quarter * 32), c);
                     else
                         drainAccumulator(p, taddr, row, tn * p.blockN, c);
                     fenceBeforeSync();
@@ -943,7 +965,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             acc ^= 1u;
             if (acc == 0) accPhase ^= 1u;
         }
-        if (captain) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // staging buffers are read, C is written
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // staging buffers are read, C is written
     }
 
     if (threadIdx.x == 0) lingerAfterAbort(abortFlag);
@@ -1393,7 +1415,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             const CUtensorMapDataType ctype = q.dtype == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                             : (q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
             const size_t es = dtypeSize(q.dtype);
-            p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 128) ? 1u : 0u;
+            p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 32) ? 1u : 0u;
         }
         if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
         else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);

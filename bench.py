@@ -232,8 +232,11 @@ def main():
     clocks.__enter__()
     clocks.wait_ready()
     warm0 = dev.stats()
+    warm_marker = dev.createEvent()
     for _ in range(args.warmup):
         z, s = step()
+        dev.recordEvent(warm_marker)     # flush per step, exactly as in the timed loop: the recorder would otherwise merge the
+                                         # warm-up steps into one differently shaped kernel and leave the real one uncompiled
     dev.synchronize()
     # The device folds z.sum() into the chain's kernel when it is recorded behind it (one launch per step, z is still
     # written: 16 bytes per element); with that switched off the sum is a second kernel that reads z again (20 bytes).
