@@ -48,6 +48,7 @@ struct KernelParams
 {
     uint32_t m, n, k;
     uint32_t tilesM, tilesN, kBlocks;
+    uint32_t tileGroup;         // row-tiles walked together (tile order)
     uint32_t blockK;            // elements of K per stage (64 for 16-bit, 32 for tf32)
     uint32_t blockN;            // output tile width: 256, or 128 when that fills the last wave of tiles better
     uint32_t aMnMajor, bMnMajor;
@@ -201,9 +202,9 @@ struct SharedStorage
     uint32_t abortFlag;
 };
 
-__device__ __forceinline__ void tileCoordinates(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t& tm, uint32_t& tn)
+__device__ __forceinline__ void tileCoordinates(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t kGroup, uint32_t& tm, uint32_t& tn)
 {
-    constexpr uint32_t kGroup = 8;                     // 8 row-tiles share their B columns back to back
+    // kGroup row-tiles share their B columns back to back: a wave of tiles then covers a roughly square patch of C
     const uint32_t perGroup = kGroup * tilesN;
     const uint32_t group = t / perGroup;
     const uint32_t firstM = group * kGroup;
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
             for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
             {
                 uint32_t tm, tn;
-                tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+                tileCoordinates(t, p.tilesM, p.tilesN, p.tileGroup, tm, tn);
                 const int32_t m0 = static_cast<int32_t>(tm * kBlockM), n0 = static_cast<int32_t>(tn * p.blockN);
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
@@ -431,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
         for (uint32_t t = blockIdx.x; t < totalTiles && ok; t += gridDim.x)
         {
             uint32_t tm, tn;
-            tileCoordinates(t, p.tilesM, p.tilesN, tm, tn);
+            tileCoordinates(t, p.tilesM, p.tilesN, p.tileGroup, tm, tn);
             for (uint32_t c = 0; c < p.chunks && ok; ++c)
             {
             if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
@@ -787,7 +788,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             while (ok && work.get(w))
             {
                 uint32_t tm, tn;
-                tileCoordinates(w.tile, p.tilesM, p.tilesN, tm, tn);
+                tileCoordinates(w.tile, p.tilesM, p.tilesN, p.tileGroup, tm, tn);
                 const int32_t m0 = static_cast<int32_t>(tm * 256 + rank * 128), n0 = static_cast<int32_t>(tn * p.blockN + rank * (p.blockN >> 1));
                 for (uint32_t c = 0; c < p.chunks && ok; ++c)
                 {
@@ -901,7 +902,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         while (ok && work.get(w))
         {
             uint32_t tm, tn;
-            tileCoordinates(w.tile, p.tilesM, p.tilesN, tm, tn);
+            tileCoordinates(w.tile, p.tilesM, p.tilesN, p.tileGroup, tm, tn);
             const uint32_t row = tm * 256 + rank * 128 + rowInCta;
             const uint32_t leaderEmpty = mapToCta(smemAddr(&s.tmemEmpty[0]), 0);
             if (w.kind == kWorkWhole)
@@ -1225,6 +1226,10 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.blockN = (forced == 128 || forced == 256) ? static_cast<uint32_t>(forced) : (efficiency(128, 0.62) > efficiency(256, 1.0) ? 128u : 256u);
     }
     p.tilesN = (p.n + p.blockN - 1) / p.blockN;
+    {
+        static const int group = []{ const char* v = std::getenv("AIXB200_GEMM_GROUP"); return v ? std::atoi(v) : 0; }();
+        p.tileGroup = group > 0 ? static_cast<uint32_t>(group) : 8u;
+    }
     const uint32_t bRows = pair ? p.blockN / 2 : p.blockN;                   // B rows (N) each CTA loads per stage
     p.c = q.c;
     p.outDtype = q.dtype;
