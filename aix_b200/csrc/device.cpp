@@ -177,7 +177,12 @@ Device::~Device()
         cudaSetDevice(m_cfg.ordinal);
         if (m_commStream) cudaStreamSynchronize(m_commStream);
         m_comm.reset();
-        if (m_commStream) { cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork); cudaEventDestroy(m_commJoin); }
+        if (m_commStream)
+        {
+            cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork);
+            for (const CommInFlight& c : m_commInFlight) cudaEventDestroy(c.done);
+            for (cudaEvent_t e : m_commEventPool) cudaEventDestroy(e);
+        }
         if (m_stream) cudaStreamSynchronize(m_stream);
         for (auto& [key, k] : m_kernels)
             if (k.module) driver().moduleUnload(k.module);
@@ -223,6 +228,13 @@ void Device::deallocate(void* p)
     if (!p) return;
     if (!m_allocator->owns(p)) failInvalid("deallocate: pointer was not allocated by this device");
     if (m_released.count(p)) failInvalid("deallocate: pointer was already deallocated");
+    if (!m_commInFlight.empty())
+    {
+        // a collective on the side stream may still use the block: reuse is ordered on the device's stream only
+        aixb200_tensor whole{};
+        whole.data = p; whole.size = m_allocator->blockSize(p); whole.dtype = U8; whole.rank = 1; whole.shape[0] = whole.size; whole.strides[0] = 1;
+        orderAfterCollectives(makeView(&whole, "deallocate"));
+    }
     if (m_pending.empty() && m_deferredFrees.empty())
     {
         m_allocator->release(p);       // stream order makes immediate reuse safe
@@ -287,6 +299,7 @@ View Device::inputView(const aixb200_tensor* t, const char* what)
 {
     View v = makeView(t, what);
     if (v.size == 0 || dryRun()) return v;
+    if (!m_commInFlight.empty()) orderAfterCollectives(v);
     if (m_allocator->findBlock(v.base)) return v;
     if (!isHostPointer(v.base)) return v;                 // foreign device memory (another allocator in this process)
     // Host memory (the reference's getReadOnlyMTLBuffer path, aixDeviceMetal.cpp:1478-1490): copy the touched span
@@ -305,6 +318,7 @@ View Device::outputView(const aixb200_tensor* t, const char* what)
 {
     View v = makeView(t, what);
     if (v.size == 0 || dryRun()) return v;
+    if (!m_commInFlight.empty()) orderAfterCollectives(v);
     if (m_allocator->findBlock(v.base)) return v;
     if (isHostPointer(v.base)) failInvalid(std::string(what) + ": result must be device memory allocated by this device");
     return v;
@@ -759,6 +773,11 @@ void Device::copy(const void* src, uint32_t srcDtype, void* dst, uint32_t dstDty
     aixb200_tensor ts{}, td{};
     ts.data = const_cast<void*>(src); ts.size = count; ts.dtype = srcDtype; ts.rank = 1; ts.shape[0] = count; ts.strides[0] = 1;
     td.data = dst; td.size = count; td.dtype = dstDtype; td.rank = 1; td.shape[0] = count; td.strides[0] = 1;
+    if (!m_commInFlight.empty())
+    {
+        orderAfterCollectives(makeView(&ts, "copy"));      // plain memcpy paths below do not go through inputView / outputView
+        orderAfterCollectives(makeView(&td, "copy"));
+    }
 
     if (dstHost)
     {
@@ -934,32 +953,63 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 }
 
 // Overlapped form: the collective runs on a side stream, ordered after everything issued so far on the device's
-// stream; later work on the device's stream does NOT wait for it until commWait(). Between the two calls the caller
-// must leave `data` alone (the gradient of a parameter is final once its last contribution has been accumulated).
+// stream. Later work on the device's stream runs concurrently with it - except work that touches `data`: every op
+// whose operands or result overlap a collective in flight is ordered after that collective (and only that one), so
+// an optimizer step that walks the parameters starts on the first gradients while the last ones are still in flight.
 void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");
     const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
     if (scale != 1.0 && !average) failInvalid("all_reduce_async: scale must be 1 or 1/ranks on a floating type");
+    aixb200_tensor whole{};
+    whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
+    const View range = makeView(&whole, "all_reduce_async");
+    if (!m_commInFlight.empty()) orderAfterCollectives(range);       // two collectives on one buffer keep their order
     flush();
     if (!m_commStream)
     {
         check(cudaStreamCreateWithFlags(&m_commStream, cudaStreamNonBlocking), "cudaStreamCreate(comm)");
         check(cudaEventCreateWithFlags(&m_commFork, cudaEventDisableTiming), "cudaEventCreate(comm)");
-        check(cudaEventCreateWithFlags(&m_commJoin, cudaEventDisableTiming), "cudaEventCreate(comm)");
     }
     check(cudaEventRecord(m_commFork, m_stream), "cudaEventRecord(comm fork)");
     check(cudaStreamWaitEvent(m_commStream, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
     m_comm->allReduceSum(data, count, dtype, m_commStream, average);
-    m_commPending = true;
+    cudaEvent_t done = nullptr;
+    if (!m_commEventPool.empty()) { done = m_commEventPool.back(); m_commEventPool.pop_back(); }
+    else check(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate(comm)");
+    check(cudaEventRecord(done, m_commStream), "cudaEventRecord(comm done)");
+    const char* begin = static_cast<const char*>(data);
+    m_commInFlight.push_back({begin, begin + count * dtypeSize(dtype), done});
+}
+
+void Device::orderAfterCollectives(const View& v)
+{
+    const char* first = static_cast<const char*>(v.firstByte());
+    const char* last = first + v.span() * dtypeSize(v.dtype);
+    bool flushed = false;
+    for (size_t i = 0; i < m_commInFlight.size();)
+    {
+        const CommInFlight& c = m_commInFlight[i];
+        if (first < c.end && c.begin < last)
+        {
+            // what is recorded so far does not depend on the collective: launch it first, then make the stream wait
+            if (!flushed) { flush(); flushed = true; }
+            check(cudaStreamWaitEvent(m_stream, c.done, 0), "cudaStreamWaitEvent(comm done)");
+            m_commEventPool.push_back(c.done);
+            m_commInFlight.erase(m_commInFlight.begin() + static_cast<std::ptrdiff_t>(i));
+        }
+        else ++i;
+    }
 }
 
 void Device::commWait()
 {
-    if (!m_commPending) return;
-    m_commPending = false;
-    check(cudaEventRecord(m_commJoin, m_commStream), "cudaEventRecord(comm join)");
-    check(cudaStreamWaitEvent(m_stream, m_commJoin, 0), "cudaStreamWaitEvent(comm join)");
+    for (const CommInFlight& c : m_commInFlight)
+    {
+        check(cudaStreamWaitEvent(m_stream, c.done, 0), "cudaStreamWaitEvent(comm done)");
+        m_commEventPool.push_back(c.done);
+    }
+    m_commInFlight.clear();
 }
 
 void Device::commDestroy()
@@ -972,8 +1022,10 @@ void Device::commDestroy()
     }
     if (m_commStream)
     {
-        cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork); cudaEventDestroy(m_commJoin);
-        m_commStream = nullptr; m_commFork = m_commJoin = nullptr;
+        cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork);
+        for (cudaEvent_t e : m_commEventPool) cudaEventDestroy(e);
+        m_commEventPool.clear();
+        m_commStream = nullptr; m_commFork = nullptr;
     }
 }
 

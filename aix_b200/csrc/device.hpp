@@ -139,8 +139,11 @@ private:
     aixb200_stats m_stats{};
     std::unique_ptr<Comm> m_comm;
     cudaStream_t   m_commStream = nullptr;      // side stream of overlapped all-reduces
-    cudaEvent_t    m_commFork = nullptr, m_commJoin = nullptr;
-    bool           m_commPending = false;
+    cudaEvent_t    m_commFork = nullptr;
+    struct CommInFlight { const char* begin; const char* end; cudaEvent_t done; };
+    std::vector<CommInFlight> m_commInFlight;   // collectives started on the side stream and not yet joined
+    std::vector<cudaEvent_t>  m_commEventPool;
+    void orderAfterCollectives(const View& v);  // the device's stream waits for in-flight collectives that touch the view
     bool m_inFlush = false;
     bool m_checkErrorWord = false;
 };

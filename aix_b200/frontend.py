@@ -299,10 +299,13 @@ def all_reduce_gradients(device, parameters: Sequence[Tensor], world_size: int):
 
 
 class GradientExchange:
-    """The same exchange, overlapped with the rest of backward(): as soon as a parameter's gradient has been accumulated
-    (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side stream, so that the collectives
-    of the late layers run under the matmuls of the early ones; `finish()` orders the device's stream after all of
-    them and goes between backward() and step(). The reference would need one hook call at the end of defaultBackward.
+    """The same exchange, overlapped with the rest of backward() and with the optimizer step: as soon as a parameter's
+    gradient has been accumulated (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side
+    stream, so that the collectives of some layers run under the matmuls of the others. The device orders every later
+    op that touches a gradient after that gradient's collective (and only after that one), so `Adam::step` starts on
+    the first parameters while the last gradients are still being exchanged; `finish()` only closes the bookkeeping of
+    one backward pass and goes between backward() and step(). The reference would need one hook call at the end of
+    defaultBackward.
 
     Valid when every parameter receives exactly one gradient contribution per backward pass (true for a feed-forward
     stack); a second contribution to a gradient already in flight raises instead of racing with the collective."""
@@ -324,9 +327,7 @@ class GradientExchange:
         self.device.allReduceAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
 
     def finish(self):
-        if self.world_size > 1:
-            self.device.commWait()
-            self._inFlight.clear()
+        self._inFlight.clear()
 
     def detach(self):
         for p in self.parameters:

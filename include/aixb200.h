@@ -224,10 +224,11 @@ int aixb200_comm_init(aixb200_device* dev, int rank, int nranks, const void* id)
 /* In-place sum all-reduce over `count` elements of dtype (F32, F64, BF16, F16, I32, I64) followed by a
  * multiplication by `scale` (1/nranks averages). Ordered after all work recorded so far. */
 int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
-/* Overlapped form: the same collective on a side stream, ordered after all work recorded so far; work issued later on
- * the device's stream runs concurrently with it until aixb200_comm_wait() (also implied by synchronize and by the
- * blocking all-reduce) orders the device's stream after every collective started this way. `data` must not be read
- * or written in between. `scale` must be 1 or 1/nranks (floating types). */
+/* Overlapped form: the same collective on a side stream, ordered after all work recorded so far. Work issued later on
+ * the device's stream runs concurrently with it, except work that touches `data`: any later op whose operands or result
+ * overlap a collective in flight is ordered after that collective (and only that one). aixb200_comm_wait() orders the
+ * device's stream after every collective started this way (also implied by synchronize and by the blocking
+ * all-reduce). `scale` must be 1 or 1/nranks (floating types). */
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
 int aixb200_comm_wait(aixb200_device* dev);
 int aixb200_comm_destroy(aixb200_device* dev);

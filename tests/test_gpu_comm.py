@@ -57,9 +57,20 @@ def test_single_rank_overlapped_exchange_orders_both_streams(comm1):
     g = ta * tb                                          # recorded, not yet launched: the exchange must come after it
     comm1.allReduceAsync(g.storage.data, g.size, C.F32, 1.0)
     other = ta + tb                                      # runs on the device's stream next to the collective
-    comm1.commWait()
-    out = g + other                                      # must see the exchanged gradient
+    out = g + other                                      # touches g: the device orders it after g's collective by itself
     assert np.array_equal(out.numpy(), a * b + (a + b))
+    # several collectives in flight, consumed one by one in a different order, with an explicit join at the end
+    parts = [ta * float(k + 1) for k in range(4)]
+    for t in parts:
+        comm1.allReduceAsync(t.storage.data, t.size, C.F32, 1.0)
+    acc = parts[3] + parts[1]
+    comm1.commWait()
+    acc = acc + parts[0] + parts[2]
+    assert np.allclose(acc.numpy(), a * 10.0, rtol=1e-6)
+    # freeing a buffer whose collective is still in flight is safe
+    scratch = ta * 2.0
+    comm1.allReduceAsync(scratch.storage.data, scratch.size, C.F32, 1.0)
+    del scratch
     with pytest.raises(Exception, match="scale"):
         comm1.allReduceAsync(g.storage.data, g.size, C.F32, 0.25)
     # synchronize() joins the side stream on its own
