@@ -954,8 +954,8 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 
 // Overlapped form: the collective runs on a side stream, ordered after everything issued so far on the device's
 // stream. Later work on the device's stream runs concurrently with it - except work that touches `data`: every op
-// whose operands or result overlap a collective in flight is ordered after that collective (and only that one), so
-// an optimizer step that walks the parameters starts on the first gradients while the last ones are still in flight.
+// whose operands or result overlap a collective in flight is ordered after that collective (recorded work that does not
+// depend on it is launched first). commWait() joins all collectives at once.
 void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");

@@ -58,7 +58,7 @@ def worker(rank, world, port, out_dir, overlap=True):
     for _ in range(STEPS):
         trainer.step()
     if overlap:
-        assert dev.async_calls == STEPS * len(trainer.model.parameters())
+        assert dev.async_calls == STEPS * len(trainer.model.parameters()) and dev.waits == STEPS
     else:
         assert not hasattr(dev, "async_calls")
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *trainer.parameters_numpy())
