@@ -61,6 +61,8 @@ struct KernelParams
     uint32_t pairAOff[8], pairBOff[8]; // shared-memory descriptor start of the stage's 8 MMAs, in 16-byte units
     uint32_t pairALbo, pairBLbo;
     uint32_t atomK;             // K elements per swizzle atom in the main pass: 64 (16-bit) or 32 (TF32); cross passes: 64
+    uint32_t halfTerms;         // f32 problems as three fp16 passes over scaled two-term operands (see splitF16Kernel)
+    const uint32_t* scaleBits;  // halfTerms: bit patterns of max|A| and max|B| (device memory), for the output scale
     uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t idesc16;           // f32 problems: descriptor of the bf16 cross-term passes
     uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
@@ -680,10 +682,30 @@ __device__ __forceinline__ void emitSlice(const CUtensorMap* mapC, uint8_t* warp
     ++sliceCounter;
 }
 
-__device__ __forceinline__ void packF32(const uint32_t (&r)[32], uint4 (&chunks)[8])
+// Half-term scheme: an operand is multiplied by the power of two that brings its largest magnitude into [2^14, 2^15)
+// before it is cut into fp16 terms. `maxBits` is the bit pattern of max|x|. Zero, infinite or NaN maxima leave the
+// operand unscaled.
+__device__ __forceinline__ uint32_t halfTermScaleExponent(uint32_t maxBits)
 {
+    const uint32_t e = (maxBits >> 23) & 0xFFu;
+    if (e == 0u || e == 255u) return 127u;
+    const int32_t biased = 127 + 14 - (static_cast<int32_t>(e) - 127);
+    return static_cast<uint32_t>(min(max(biased, 1), 254));
+}
+__device__ __forceinline__ float halfTermScale(uint32_t maxBits) { return __uint_as_float(halfTermScaleExponent(maxBits) << 23); }
+__device__ __forceinline__ float halfTermInverseScale(uint32_t maxBits)
+{
+    const int32_t biased = 254 - static_cast<int32_t>(halfTermScaleExponent(maxBits));
+    return __uint_as_float(static_cast<uint32_t>(max(biased, 1)) << 23);
+}
+
+__device__ __forceinline__ void packF32(const uint32_t (&r)[32], uint4 (&chunks)[8], float scaleA, float scaleB)
+{
+    // the two factors are applied one after the other: their product may leave the float range when the result does not
     #pragma unroll
-    for (int v = 0; v < 8; ++v) chunks[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    for (int v = 0; v < 8; ++v)
+        chunks[v] = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) * scaleA * scaleB), __float_as_uint(__uint_as_float(r[4 * v + 1]) * scaleA * scaleB),
+                               __float_as_uint(__uint_as_float(r[4 * v + 2]) * scaleA * scaleB), __float_as_uint(__uint_as_float(r[4 * v + 3]) * scaleA * scaleB));
 }
 
 // `taddr` addresses this warp's 32 TMEM lanes; (x0, y0) is the position in C of their first element.
@@ -697,17 +719,19 @@ __device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const
         // 32 columns per slice; the TMEM load of the next slice is in flight while this one is staged and handed over
         uint32_t rA[32], rB[32];
         uint4 chunks[8];
+        const float scaleA = p.halfTerms ? halfTermInverseScale(p.scaleBits[0]) : 1.0f;      // multiplying by 1 is exact
+        const float scaleB = p.halfTerms ? halfTermInverseScale(p.scaleBits[1]) : 1.0f;
         tmemLoad32(taddr, rA);
         #pragma unroll 1
         for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)
         {
             tmemLoadWait();
             tmemLoad32(taddr + c0 + 32, rB);
-            packF32(rA, chunks);
+            packF32(rA, chunks, scaleA, scaleB);
             emitSlice(mapC, warpStaging, sliceCounter, chunks, lane, x0 + static_cast<int32_t>(c0), y0, reduceAdd);
             tmemLoadWait();
             if (c0 + 64 < p.blockN) tmemLoad32(taddr + c0 + 64, rA);
-            packF32(rB, chunks);
+            packF32(rB, chunks, scaleA, scaleB);
             emitSlice(mapC, warpStaging, sliceCounter, chunks, lane, x0 + static_cast<int32_t>(c0 + 32), y0, reduceAdd);
         }
         return;
@@ -795,8 +819,11 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const uint32_t kbBegin = w.kbBegin + c * p.chunkBlocks, kbCount = min(w.kbBegin + w.kbCount - kbBegin, p.chunkBlocks);
                     for (uint32_t passIndex = 0; passIndex < p.kPhases && ok; ++passIndex)
                     {
-                    const bool cross = Tf32 && passIndex < 2;          // see gemmKernel: bf16 cross terms first
-                    const uint32_t first = cross ? kbBegin >> 1 : kbBegin, count = cross ? kbCount >> 1 : kbCount;
+                    // hybrid scheme: two bf16 cross-term passes (stages of 128) before the TF32 main pass (stages of 64);
+                    // half-term scheme: three fp16 passes, all with stages of 128 (h1.h0', h0.h1', h0.h0')
+                    const bool cross = Tf32 && (passIndex < 2 || p.halfTerms);
+                    const bool halved = cross && !p.halfTerms;
+                    const uint32_t first = halved ? kbBegin >> 1 : kbBegin, count = halved ? kbCount >> 1 : kbCount;
                     const uint32_t atomK = cross ? 64u : p.atomK;
                     const CUtensorMap* ma = cross ? &mapA16 : &mapA;
                     const CUtensorMap* mb = cross ? &mapB16 : &mapB;
@@ -865,13 +892,13 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t kbCount = min(w.kbCount - c * p.chunkBlocks, p.chunkBlocks);
                 // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2 stages of 128), then kbCount
                 // TF32 stages of 64
-                const uint32_t stagesInChunk = Tf32 ? 2 * kbCount : kbCount;
+                const uint32_t stagesInChunk = Tf32 ? (p.halfTerms ? 3 * kbCount : 2 * kbCount) : kbCount;
                 for (uint32_t it = 0; it < stagesInChunk; ++it)
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
                     const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
-                    const bool cross = Tf32 && it < kbCount;
+                    const bool cross = Tf32 && (p.halfTerms || it < kbCount);
                     #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j)
                     {
@@ -1082,6 +1109,140 @@ __global__ void __launch_bounds__(256) splitF32Kernel(const float* __restrict__ 
             for (uint32_t j = 0; j < 8; ++j) v[j] = tile[r][kg + j];
             splitEmit(v, r0 + r, c0 + kg, kPad, hi32, pair16);
         }
+    }
+}
+
+// ---- half-term scheme: max|x| of a strided 2-D operand, then the scaled two-term fp16 split ---------------------------
+// slot: bit pattern of the running maximum (non-negative floats order like unsigned integers), zeroed by the launcher.
+__global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ src, uint64_t outer, uint64_t inner, uint64_t outerStride,
+                                                    uint64_t innerStride, uint32_t vectorLoads, uint32_t* slot)
+{
+    uint32_t best = 0;
+    const uint64_t perRow = vectorLoads ? inner / 4 : inner;
+    const uint64_t total = outer * perRow;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<uint64_t>(gridDim.x) * 256)
+    {
+        const uint64_t o = i / perRow, c = i - o * perRow;
+        if (vectorLoads)
+        {
+            const float4 x = *reinterpret_cast<const float4*>(src + o * outerStride + c * 4);
+            best = max(max(best, __float_as_uint(fabsf(x.x))), max(__float_as_uint(fabsf(x.y)), max(__float_as_uint(fabsf(x.z)), __float_as_uint(fabsf(x.w)))));
+        }
+        else best = max(best, __float_as_uint(fabsf(src[o * outerStride + c * innerStride])));
+    }
+    // NaNs carry the largest patterns: a NaN anywhere ends up as the maximum and switches the scaling off
+    #pragma unroll
+    for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_down_sync(0xffffffffu, best, d));
+    if ((threadIdx.x & 31) == 0 && best != 0) atomicMax(slot, best);
+}
+
+//   terms[rows][2*kPad]  [ h0 | h1 ] with h0 = fp16(s*a), h1 = fp16(s*a - h0), s = halfTermScale(max|a|):  s*a = h0 + h1 to 22 bits
+__device__ __forceinline__ void splitEmitHalf(const float (&v)[8], float scale, uint32_t r, uint32_t c, uint32_t kPad, uint16_t* __restrict__ terms)
+{
+    uint32_t h0[4], h1[4];
+    #pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const float x0 = v[2 * j] * scale, x1 = v[2 * j + 1] * scale;
+        const uint16_t a0 = dev::f32ToF16(x0), a1 = dev::f32ToF16(x1);
+        h0[j] = static_cast<uint32_t>(a0) | (static_cast<uint32_t>(a1) << 16);
+        h1[j] = static_cast<uint32_t>(dev::f32ToF16(x0 - dev::f16ToF32(a0))) | (static_cast<uint32_t>(dev::f32ToF16(x1 - dev::f16ToF32(a1))) << 16);
+    }
+    uint16_t* out = terms + static_cast<uint64_t>(r) * (2ull * kPad) + c;
+    *reinterpret_cast<uint4*>(out) = make_uint4(h0[0], h0[1], h0[2], h0[3]);
+    *reinterpret_cast<uint4*>(out + kPad) = make_uint4(h1[0], h1[1], h1[2], h1[3]);
+}
+
+template <bool Transposed>
+__global__ void __launch_bounds__(256) splitF16Kernel(const float* __restrict__ src, uint64_t rowStride, uint64_t colStride, uint32_t rows,
+                                                      uint32_t k, uint32_t kPad, uint16_t* __restrict__ terms, uint32_t vectorLoads,
+                                                      const uint32_t* __restrict__ maxBits)
+{
+    const float scale = halfTermScale(*maxBits);
+    const uint32_t r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    if (!Transposed)
+    {
+        #pragma unroll
+        for (uint32_t it = 0; it < 2; ++it)
+        {
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t r = r0 + (idx >> 3), c = c0 + (idx & 7u) * 8;
+            if (r >= rows) continue;
+            float v[8];
+            const float* in = src + static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride;
+            if (vectorLoads && c + 8 <= k)
+            {
+                const float4 x = reinterpret_cast<const float4*>(in)[0], y = reinterpret_cast<const float4*>(in)[1];
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+            }
+            else
+            {
+                #pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) v[j] = (c + j < k) ? in[j * colStride] : 0.f;
+            }
+            splitEmitHalf(v, scale, r, c, kPad, terms);
+        }
+    }
+    else
+    {
+        __shared__ float tile[64][65];                        // [row][k]
+        #pragma unroll
+        for (uint32_t it = 0; it < 4; ++it)
+        {
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t kk = idx >> 4, rg = (idx & 15u) * 4;
+            const uint32_t c = c0 + kk, r = r0 + rg;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < k)
+            {
+                const float* in = src + static_cast<uint64_t>(r) * rowStride + static_cast<uint64_t>(c) * colStride;
+                if (vectorLoads && r + 4 <= rows) x = *reinterpret_cast<const float4*>(in);
+                else
+                {
+                    if (r < rows) x.x = in[0];
+                    if (r + 1 < rows) x.y = in[rowStride];
+                    if (r + 2 < rows) x.z = in[2 * rowStride];
+                    if (r + 3 < rows) x.w = in[3 * rowStride];
+                }
+            }
+            tile[rg][kk] = x.x; tile[rg + 1][kk] = x.y; tile[rg + 2][kk] = x.z; tile[rg + 3][kk] = x.w;
+        }
+        __syncthreads();
+        #pragma unroll
+        for (uint32_t it = 0; it < 2; ++it)
+        {
+            const uint32_t idx = threadIdx.x + it * 256;
+            const uint32_t r = idx >> 3, kg = (idx & 7u) * 8;
+            if (r0 + r >= rows) continue;
+            float v[8];
+            #pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) v[j] = tile[r][kg + j];
+            splitEmitHalf(v, scale, r0 + r, c0 + kg, kPad, terms);
+        }
+    }
+}
+
+// max|x| of the operand into *slot (zeroed beforehand), then its two-term fp16 split.
+void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uint64_t rowStride, uint64_t colStride, uint32_t rows, uint32_t k,
+                         uint32_t kPad, uint16_t* terms, uint32_t* slot)
+{
+    const bool aligned = reinterpret_cast<uintptr_t>(src) % 16 == 0;
+    const unsigned maxGrid = static_cast<unsigned>(smCount) * 8;
+    if (colStride == 1 || rowStride != 1)
+    {
+        const uint32_t vec = colStride == 1 && aligned && rowStride % 4 == 0 && k % 4 == 0;
+        const uint64_t items = static_cast<uint64_t>(rows) * (vec ? k / 4 : k);
+        absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, rows, k, rowStride, colStride, vec, slot);
+        splitF16Kernel<false><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, terms,
+                                                                                      colStride == 1 && aligned && rowStride % 4 == 0, slot);
+    }
+    else
+    {
+        const uint32_t vec = aligned && colStride % 4 == 0 && rows % 4 == 0;
+        const uint64_t items = static_cast<uint64_t>(k) * (vec ? rows / 4 : rows);
+        absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, k, rows, colStride, rowStride, vec, slot);
+        splitF16Kernel<true><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, terms,
+                                                                                     aligned && colStride % 4 == 0, slot);
     }
 }
 
@@ -1309,6 +1470,38 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         // Split into K-major scratch (see splitF32Kernel). kPad is a multiple of 64 so that bf16 stages (64 elements)
         // and TF32 stages (32 elements) cover the same K ranges.
         const uint32_t kPad = (p.k + 127) & ~127u;
+        p.kPhases = 3;
+        p.kPerPhase = kPad;
+        // Pair kernel: three fp16 passes over scaled two-term operands (AIXB200_GEMM_F32=hybrid: TF32 + bf16 cross terms).
+        static const bool halfTerms = []{ const char* v = std::getenv("AIXB200_GEMM_F32"); return !(v && v[0] == 'h' && v[1] == 'y'); }();
+        if (pair && halfTerms)
+        {
+            uint16_t* termsA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
+            uint16_t* termsB = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.n) * 2 * kPad * 2));
+            uint32_t* slots = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + ctx.scratchBytes + 2048);   // behind the split-tile counters
+            if (cudaMemsetAsync(slots, 0, 8, ctx.stream) != cudaSuccess) return false;
+            launchHalfTermSplit(ctx.stream, ctx.smCount, static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, termsA, slots);
+            // B is k x n: its "rows" for the split are the n columns
+            launchHalfTermSplit(ctx.stream, ctx.smCount, static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, termsB, slots + 1);
+            if (ctx.launches) *ctx.launches += 4;
+            p.halfTerms = 1;
+            p.scaleBits = slots;
+            p.atomK = 64;
+            p.kBlocks = kPad / 128;                              // stages of 128 fp16 elements in all three passes
+            p.chunkBlocks = 4;                                   // 512 elements of K per in-TMEM partial sum
+            p.aLoad3d = p.bLoad3d = 1;
+            p.pairABytes = kBlockM * 256; p.pairBBytes = bRows * 256;
+            for (uint32_t j = 0; j < 8; ++j)
+            {
+                p.pairAOff[j] = ((j / 4) * kBlockM * 128 + (j % 4) * 32) >> 4;
+                p.pairBOff[j] = ((j / 4) * bRows * 128 + (j % 4) * 32) >> 4;
+            }
+            if (!makeMapK3d(&mapA16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, termsA, q.m, 2ull * kPad, 2ull * kPad * 2, 64, kBlockM)) return false;
+            if (!makeMapK3d(&mapB16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, termsB, q.n, 2ull * kPad, 2ull * kPad * 2, 64, bRows)) return false;
+            mapA = mapA16; mapB = mapB16;                        // no 32-bit pass
+        }
+        else
+        {
         float* hiA = static_cast<float*>(device.temporary(static_cast<size_t>(p.m) * kPad * 4));
         float* hiB = static_cast<float*>(device.temporary(static_cast<size_t>(p.n) * kPad * 4));
         uint16_t* pairA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
@@ -1317,8 +1510,6 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         // B is k x n: its "rows" for the split are the n columns
         launchSplit(ctx.stream, static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, hiB, pairB);
         if (ctx.launches) *ctx.launches += 2;
-        p.kPhases = 3;
-        p.kPerPhase = kPad;
         if (!pair)
         {
             p.blockK = 32;
@@ -1352,10 +1543,12 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             if (!makeMapK3d(&mapA16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairA, q.m, 2ull * kPad, 2ull * kPad * 2, 64, kBlockM)) return false;
             if (!makeMapK3d(&mapB16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pairB, q.n, 2ull * kPad, 2ull * kPad * 2, 64, bRows)) return false;
         }
+        }
         p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
         const uint32_t shape = ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
         p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | shape;            // D f32, A/B tf32
-        p.idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | shape;          // D f32, A/B bf16
+        p.idesc16 = p.halfTerms ? ((1u << 4) | shape)                    // D f32, A/B f16
+                                : ((1u << 4) | (1u << 7) | (1u << 10) | shape);   // D f32, A/B bf16
     }
 
     const size_t smemBytes = sizeof(SharedStorage) + 1024;
