@@ -216,6 +216,22 @@ __device__ __forceinline__ void tileCoordinates(uint32_t t, uint32_t tilesM, uin
     tn = local / groupRows;
 }
 
+// Half-term scheme: an operand is multiplied by the power of two that brings its largest magnitude into [2^14, 2^15)
+// before it is cut into fp16 terms. `maxBits` is the bit pattern of max|x|. Zero, infinite or NaN maxima leave the
+// operand unscaled.
+__device__ __forceinline__ uint32_t halfTermScaleExponent(uint32_t maxBits)
+{
+    const uint32_t e = (maxBits >> 23) & 0xFFu;
+    if (e == 0u || e == 255u) return 127u;
+    const int32_t biased = 127 + 14 - (static_cast<int32_t>(e) - 127);
+    return static_cast<uint32_t>(min(max(biased, 1), 253));      // 253: the reciprocal 2^(127 - biased) stays a normal number
+}
+__device__ __forceinline__ float halfTermScale(uint32_t maxBits) { return __uint_as_float(halfTermScaleExponent(maxBits) << 23); }
+__device__ __forceinline__ float halfTermInverseScale(uint32_t maxBits)
+{
+    return __uint_as_float((254u - halfTermScaleExponent(maxBits)) << 23);       // exact reciprocal: exponents 1 ... 253 map onto 253 ... 1
+}
+
 // Epilogue of one 32-column strip of one accumulator row: convert and store (first chunk) or add to what C already
 // holds (later chunks of the split-f32 scheme; `old` was fetched before the TMEM load).
 __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const uint32_t (&r)[32], const float4 (&old)[8], uint32_t row, uint32_t col, uint32_t c)
@@ -226,6 +242,9 @@ __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const
         if (p.outDtype == F32)
         {
             float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
+            // half-term scheme: undo the operands' scaling (two factors, one after the other; 1 when the scheme is off)
+            const float scaleA = p.halfTerms ? halfTermInverseScale(p.scaleBits[0]) : 1.0f;
+            const float scaleB = p.halfTerms ? halfTermInverseScale(p.scaleBits[1]) : 1.0f;
             // Partial results after the first are added to C with IEEE f32 additions: the tensor core's own
             // accumulation truncates, and that bias grows with the number of MMAs folded into one accumulator.
             if (fullRow && p.vectorStores)
@@ -233,14 +252,15 @@ __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const
                 #pragma unroll
                 for (int v = 0; v < 8; ++v)
                 {
-                    float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    float4 x = make_float4(__uint_as_float(r[4 * v]) * scaleA * scaleB, __uint_as_float(r[4 * v + 1]) * scaleA * scaleB,
+                                           __uint_as_float(r[4 * v + 2]) * scaleA * scaleB, __uint_as_float(r[4 * v + 3]) * scaleA * scaleB);
                     if (c > 0) { x.x += old[v].x; x.y += old[v].y; x.z += old[v].z; x.w += old[v].w; }
                     reinterpret_cast<float4*>(out)[v] = x;
                 }
             }
             else
             {
-                for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]) + (c > 0 ? out[e] : 0.f);
+                for (uint32_t e = 0; e < 32 && col + e < p.n; ++e) out[e] = __uint_as_float(r[e]) * scaleA * scaleB + (c > 0 ? out[e] : 0.f);
             }
         }
         else
@@ -682,23 +702,6 @@ __device__ __forceinline__ void emitSlice(const CUtensorMap* mapC, uint8_t* warp
     ++sliceCounter;
 }
 
-// Half-term scheme: an operand is multiplied by the power of two that brings its largest magnitude into [2^14, 2^15)
-// before it is cut into fp16 terms. `maxBits` is the bit pattern of max|x|. Zero, infinite or NaN maxima leave the
-// operand unscaled.
-__device__ __forceinline__ uint32_t halfTermScaleExponent(uint32_t maxBits)
-{
-    const uint32_t e = (maxBits >> 23) & 0xFFu;
-    if (e == 0u || e == 255u) return 127u;
-    const int32_t biased = 127 + 14 - (static_cast<int32_t>(e) - 127);
-    return static_cast<uint32_t>(min(max(biased, 1), 254));
-}
-__device__ __forceinline__ float halfTermScale(uint32_t maxBits) { return __uint_as_float(halfTermScaleExponent(maxBits) << 23); }
-__device__ __forceinline__ float halfTermInverseScale(uint32_t maxBits)
-{
-    const int32_t biased = 254 - static_cast<int32_t>(halfTermScaleExponent(maxBits));
-    return __uint_as_float(static_cast<uint32_t>(max(biased, 1)) << 23);
-}
-
 __device__ __forceinline__ void packF32(const uint32_t (&r)[32], uint4 (&chunks)[8], float scaleA, float scaleB)
 {
     // the two factors are applied one after the other: their product may leave the float range when the result does not
@@ -1120,15 +1123,29 @@ __global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ sr
     uint32_t best = 0;
     const uint64_t perRow = vectorLoads ? inner / 4 : inner;
     const uint64_t total = outer * perRow;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<uint64_t>(gridDim.x) * 256)
+    const uint64_t threads = static_cast<uint64_t>(gridDim.x) * 256;
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    auto fold4 = [&](const float4& x)
     {
-        const uint64_t o = i / perRow, c = i - o * perRow;
-        if (vectorLoads)
+        best = max(max(best, __float_as_uint(fabsf(x.x))), max(__float_as_uint(fabsf(x.y)), max(__float_as_uint(fabsf(x.z)), __float_as_uint(fabsf(x.w)))));
+    };
+    auto pack = [&](uint64_t idx) { const uint64_t o = idx / perRow, c = idx - o * perRow; return reinterpret_cast<const float4*>(src + o * outerStride + c * 4); };
+    if (vectorLoads)
+    {
+        for (; i + 3 * threads < total; i += 4 * threads)          // four independent 128-bit loads per thread
         {
-            const float4 x = *reinterpret_cast<const float4*>(src + o * outerStride + c * 4);
-            best = max(max(best, __float_as_uint(fabsf(x.x))), max(__float_as_uint(fabsf(x.y)), max(__float_as_uint(fabsf(x.z)), __float_as_uint(fabsf(x.w)))));
+            const float4 x0 = *pack(i), x1 = *pack(i + threads), x2 = *pack(i + 2 * threads), x3 = *pack(i + 3 * threads);
+            fold4(x0); fold4(x1); fold4(x2); fold4(x3);
         }
-        else best = max(best, __float_as_uint(fabsf(src[o * outerStride + c * innerStride])));
+        for (; i < total; i += threads) fold4(*pack(i));
+    }
+    else
+    {
+        for (; i < total; i += threads)
+        {
+            const uint64_t o = i / perRow, c = i - o * perRow;
+            best = max(best, __float_as_uint(fabsf(src[o * outerStride + c * innerStride])));
+        }
     }
     // NaNs carry the largest patterns: a NaN anywhere ends up as the maximum and switches the scaling off
     #pragma unroll

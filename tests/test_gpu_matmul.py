@@ -75,3 +75,26 @@ def test_medium_sizes_against_float64(b200, dtype):
             want = a.astype(np.float64) @ b.astype(np.float64)
             tol = 1e-5 if dtype == F32 else 1e-2
             assert normwise(got, want) <= tol, f"{m}x{k}x{n} ta={ta} tb={tb}: {normwise(got, want)}"
+
+
+def test_f32_operands_of_extreme_and_uneven_magnitude(b200, ref):
+    """The f32 product runs on the tensor cores from scaled fp16 terms: the scaling must be invisible - operands far from
+    1, operands whose rows differ by many decades, a zero operand - and the result must stay within the f32 bar."""
+    rng = np.random.default_rng(23)
+    m, k, n = 384, 640, 520
+    a = rng.normal(0, 0.5, (m, k)).astype(np.float32)
+    b = rng.normal(0, 0.5, (k, n)).astype(np.float32)
+    cases = {
+        "tiny x huge": (a * np.float32(1e-20), b * np.float32(1e15)),
+        "huge x tiny": (a * np.float32(3e30), b * np.float32(1e-35)),
+        "rows of different magnitude": ((a * np.exp(rng.uniform(-15, 15, (m, 1)))).astype(np.float32), b),
+        "17 decades inside one operand": ((a * np.exp(rng.uniform(-20, 20, a.shape))).astype(np.float32), b),
+        "same-sign products": (np.abs(a), np.abs(b)),
+    }
+    for what, (x, y) in cases.items():
+        want = x.astype(np.float64) @ y.astype(np.float64)
+        got = TensorValue.from_numpy(x, b200).matmul(TensorValue.from_numpy(y, b200)).numpy()
+        assert np.isfinite(got).all(), what
+        assert normwise(got, want) <= 1e-5, f"{what}: norm-wise error {normwise(got, want)}"
+    zero = TensorValue.from_numpy(np.zeros((m, k), np.float32), b200).matmul(TensorValue.from_numpy(b, b200)).numpy()
+    assert not zero.any()
