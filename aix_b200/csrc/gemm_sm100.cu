@@ -1150,7 +1150,15 @@ __global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ sr
     // NaNs carry the largest patterns: a NaN anywhere ends up as the maximum and switches the scaling off
     #pragma unroll
     for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_down_sync(0xffffffffu, best, d));
-    if ((threadIdx.x & 31) == 0 && best != 0) atomicMax(slot, best);
+    __shared__ uint32_t warpBest[8];
+    if ((threadIdx.x & 31) == 0) warpBest[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0)                                   // one atomic per CTA: they all hit the same word
+    {
+        #pragma unroll
+        for (int w = 1; w < 8; ++w) best = max(best, warpBest[w]);
+        if (best != 0) atomicMax(slot, best);
+    }
 }
 
 //   terms[rows][2*kPad]  [ h0 | h1 ] with h0 = fp16(s*a), h1 = fp16(s*a - h0), s = halfTermScale(max|a|):  s*a = h0 + h1 to 22 bits
