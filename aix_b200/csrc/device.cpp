@@ -740,6 +740,7 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
     p.b = vb.firstByte(); p.bRowStride = b->strides[0]; p.bColStride = b->strides[1];
     p.c = vr.firstByte();
     p.splitF32 = m_cfg.tf32x3_matmul != 0;
+    p.shareDevice = !m_commInFlight.empty();
     if (gemm::launchTensorCore(*this, ctx, p)) m_checkErrorWord = true;
     else
         kernels::matmulSimt(ctx, r->dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);

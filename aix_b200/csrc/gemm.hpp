@@ -20,6 +20,7 @@ struct Problem
     const void* b; uint64_t bRowStride, bColStride;
     void*       c;
     bool        splitF32;      // f32 operands: three-pass split so that the result keeps f32 accuracy
+    bool        shareDevice;   // another stream of this device has kernels in flight (a collective): leave it some SMs
 };
 
 // Runs the problem on the tensor cores when its element type, shape and alignment allow it.

@@ -1608,7 +1608,18 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                 maxClusters = ctx.smCount / 2;
             }
         });
-        uint32_t clusters = std::min<uint32_t>(tiles, static_cast<uint32_t>(maxClusters));
+        // A collective on the device's side stream needs SMs of its own. The persistent grid would otherwise either keep
+        // it out until the matmul ends or, if the collective got there first, start some of its clusters late - and
+        // with tiles dealt out statically those late clusters finish their whole share late. While a collective is in
+        // flight the grid therefore leaves a few SMs free (AIXB200_GEMM_RESERVE_SMS, default 24).
+        uint32_t usable = static_cast<uint32_t>(maxClusters);
+        if (q.shareDevice)
+        {
+            static const int reserve = []{ const char* v = std::getenv("AIXB200_GEMM_RESERVE_SMS"); return v ? std::atoi(v) : 24; }();
+            const uint32_t reservedClusters = static_cast<uint32_t>(std::max(0, reserve)) / 2;
+            usable = usable > reservedClusters + 8 ? usable - reservedClusters : usable;
+        }
+        uint32_t clusters = std::min<uint32_t>(tiles, usable);
         // Remainder tiles are cut along K and shared by all clusters (see WorkIterator) when that saves at least a few
         // stages of idle time per cluster; split-f32 problems keep whole tiles (their partial sums already go through C).
         // Off unless AIXB200_GEMM_SPLITK=1: measured on B200 it helps A^T.B at 4096^3 (+8 %) but costs A.B^T 6 % there
@@ -1616,7 +1627,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         // too long when K is short.
         static const bool splitEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_SPLITK"); return v && v[0] == '1'; }();
         const uint32_t remainder = tiles % static_cast<uint32_t>(maxClusters);
-        if (splitEnabled && !tf32 && remainder != 0 && p.kBlocks >= 8)
+        if (splitEnabled && !tf32 && !q.shareDevice && remainder != 0 && p.kBlocks >= 8)
         {
             const uint64_t units = static_cast<uint64_t>(remainder) * p.kBlocks;
             const uint64_t idleStages = (static_cast<uint64_t>(maxClusters) - remainder) * p.kBlocks / maxClusters;
