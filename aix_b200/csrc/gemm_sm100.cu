@@ -1611,11 +1611,11 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         // A collective on the device's side stream needs SMs of its own. The persistent grid would otherwise either keep
         // it out until the matmul ends or, if the collective got there first, start some of its clusters late - and
         // with tiles dealt out statically those late clusters finish their whole share late. While a collective is in
-        // flight the grid therefore leaves a few SMs free (AIXB200_GEMM_RESERVE_SMS, default 24).
+        // flight the grid can therefore leave a few SMs free (AIXB200_GEMM_RESERVE_SMS; default 0 = off until measured).
         uint32_t usable = static_cast<uint32_t>(maxClusters);
         if (q.shareDevice)
         {
-            static const int reserve = []{ const char* v = std::getenv("AIXB200_GEMM_RESERVE_SMS"); return v ? std::atoi(v) : 24; }();
+            static const int reserve = []{ const char* v = std::getenv("AIXB200_GEMM_RESERVE_SMS"); return v ? std::atoi(v) : 0; }();
             const uint32_t reservedClusters = static_cast<uint32_t>(std::max(0, reserve)) / 2;
             usable = usable > reservedClusters + 8 ? usable - reservedClusters : usable;
         }
