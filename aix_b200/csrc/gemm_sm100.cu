@@ -1121,6 +1121,7 @@ __global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ sr
                                                     uint64_t innerStride, uint32_t vectorLoads, uint32_t* slot)
 {
     uint32_t best = 0;
+    if (vectorLoads && outerStride == inner) { inner *= outer; outerStride = inner; outer = 1; }    // dense: one long row, no divisions
     const uint64_t perRow = vectorLoads ? inner / 4 : inner;
     const uint64_t total = outer * perRow;
     const uint64_t threads = static_cast<uint64_t>(gridDim.x) * 256;
@@ -1129,13 +1130,19 @@ __global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ sr
     {
         best = max(max(best, __float_as_uint(fabsf(x.x))), max(__float_as_uint(fabsf(x.y)), max(__float_as_uint(fabsf(x.z)), __float_as_uint(fabsf(x.w)))));
     };
-    auto pack = [&](uint64_t idx) { const uint64_t o = idx / perRow, c = idx - o * perRow; return reinterpret_cast<const float4*>(src + o * outerStride + c * 4); };
+    auto pack = [&](uint64_t idx)
+    {
+        if (outer == 1) return reinterpret_cast<const float4*>(src) + idx;
+        const uint64_t o = idx / perRow, c = idx - o * perRow;
+        return reinterpret_cast<const float4*>(src + o * outerStride + c * 4);
+    };
     if (vectorLoads)
     {
-        for (; i + 3 * threads < total; i += 4 * threads)          // four independent 128-bit loads per thread
+        for (; i + 7 * threads < total; i += 8 * threads)          // eight independent 128-bit loads per thread
         {
             const float4 x0 = *pack(i), x1 = *pack(i + threads), x2 = *pack(i + 2 * threads), x3 = *pack(i + 3 * threads);
-            fold4(x0); fold4(x1); fold4(x2); fold4(x3);
+            const float4 x4 = *pack(i + 4 * threads), x5 = *pack(i + 5 * threads), x6 = *pack(i + 6 * threads), x7 = *pack(i + 7 * threads);
+            fold4(x0); fold4(x1); fold4(x2); fold4(x3); fold4(x4); fold4(x5); fold4(x6); fold4(x7);
         }
         for (; i < total; i += threads) fold4(*pack(i));
     }
