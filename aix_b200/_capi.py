@@ -99,6 +99,7 @@ SIGNATURES = {
     "aixb200_all_reduce": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
     "aixb200_all_reduce_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
     "aixb200_comm_wait": ([_D], ctypes.c_int),
+    "aixb200_comm_wait_for": ([_D, ctypes.c_void_p, _SZ], ctypes.c_int),
     "aixb200_comm_destroy": ([_D], ctypes.c_int),
 }
 for _name in ("add", "sub", "mul", "div", "pow"):

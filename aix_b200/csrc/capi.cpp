@@ -232,6 +232,8 @@ int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t d
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale)
 { return guarded(dev, [&](Device& d) { d.allReduceAsync(data, count, dtype, scale); }); }
 int aixb200_comm_wait(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commWait(); }); }
+int aixb200_comm_wait_for(aixb200_device* dev, const void* data, size_t bytes)
+{ return guarded(dev, [&](Device& d) { d.commWaitFor(data, bytes); }); }
 int aixb200_comm_destroy(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commDestroy(); }); }
 
 }   // extern "C"

@@ -1003,6 +1003,16 @@ void Device::orderAfterCollectives(const View& v)
     }
 }
 
+// Joins only the collectives that touch [data, data + bytes): what an optimizer calls before it starts on one parameter,
+// so that the join falls between two parameters' recorded ops instead of inside an expression.
+void Device::commWaitFor(const void* data, size_t bytes)
+{
+    if (m_commInFlight.empty() || !data || bytes == 0) return;
+    aixb200_tensor whole{};
+    whole.data = const_cast<void*>(data); whole.size = bytes; whole.dtype = U8; whole.rank = 1; whole.shape[0] = bytes; whole.strides[0] = 1;
+    orderAfterCollectives(makeView(&whole, "comm_wait_for"));
+}
+
 void Device::commWait()
 {
     for (const CommInFlight& c : m_commInFlight)

@@ -87,6 +87,7 @@ public:
     void allReduce(void* data, size_t count, uint32_t dtype, double scale);
     void allReduceAsync(void* data, size_t count, uint32_t dtype, double scale);
     void commWait();
+    void commWaitFor(const void* data, size_t bytes);
     void commDestroy();
 
     // Scratch for fixed kernels (reduction partials, counters); lives as long as the device.

@@ -251,6 +251,8 @@ class DeviceB200:
 
     def commWait(self): self._check(self._lib.aixb200_comm_wait(self._h))
 
+    def commWaitFor(self, data: int, nbytes: int): self._check(self._lib.aixb200_comm_wait_for(self._h, data, nbytes))
+
     def commDestroy(self): self._check(self._lib.aixb200_comm_destroy(self._h))
 
     # Host <-> device helpers built on copy / copyImmediate (what TensorValue's host-pointer constructor and

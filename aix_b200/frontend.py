@@ -263,6 +263,7 @@ class Adam:
         self.parameters = list(parameters)
         self.lr, self.beta1, self.beta2, self.epsilon = lr, beta1, beta2, epsilon
         self.timestep = 0
+        self.beforeParameter: Optional[Callable] = None     # no counterpart in the reference; see GradientExchange.attach
         self.m = [TensorValue.full(0.0, p.shape, p.device, C.F32) for p in self.parameters]
         self.v = [TensorValue.full(0.0, p.shape, p.device, C.F32) for p in self.parameters]
 
@@ -278,6 +279,8 @@ class Adam:
         for i, p in enumerate(self.parameters):
             if not p.isRequireGrad():
                 continue
+            if self.beforeParameter is not None:
+                self.beforeParameter(p)
             g = p.grad().to(C.F32)
             self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
             self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
@@ -299,15 +302,19 @@ def all_reduce_gradients(device, parameters: Sequence[Tensor], world_size: int):
 
 
 class GradientExchange:
-    """The same exchange, overlapped with the rest of backward(): as soon as a parameter's gradient has been accumulated
-    (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side stream, so that the collectives
-    of some layers run under the matmuls of the others; `finish()` joins all of them at once and goes between backward()
-    and step(). The reference would need one hook call at the end of defaultBackward.
+    """The same exchange, overlapped with the rest of backward() and with the optimizer step: as soon as a parameter's
+    gradient has been accumulated (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side
+    stream, so that the collectives of some layers run under the matmuls of the others. `attach(optimizer)` makes the
+    optimizer join, before it starts on a parameter, only that parameter's collective: the front end produces the
+    weight gradients first-layer-first, so the largest exchanges are the last to start, and Adam already runs on the
+    first parameters while they finish. Without an attached optimizer, `finish()` joins everything at once; it goes
+    between backward() and step() either way. The reference would need one hook call at the end of defaultBackward
+    and one at the top of the optimizer's per-parameter loop.
 
-    The device itself orders any op that touches a gradient after that gradient's collective, so forgetting finish()
-    cannot race; joining explicitly keeps the optimizer's recorded ops in whole kernels (a join in the middle of
-    `beta1 * m + (1 - beta1) * g` would cut the expression in two launches - measured 81 instead of 69 launches per
-    step and no gain - and, with FMA contraction allowed, change last bits relative to the blocking form).
+    The device itself orders any op that touches a gradient after that gradient's collective, so a forgotten join
+    cannot race; joining explicitly at a parameter boundary keeps each parameter's recorded ops in one kernel (a join
+    in the middle of `beta1 * m + (1 - beta1) * g` would cut the expression in two launches and, with FMA contraction
+    allowed, change last bits relative to the blocking form).
 
     Valid when every parameter receives exactly one gradient contribution per backward pass (true for a feed-forward
     stack); a second contribution to a gradient already in flight raises instead of racing with the collective."""
@@ -328,8 +335,17 @@ class GradientExchange:
         g = node.grad()
         self.device.allReduceAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
 
-    def finish(self):
+    def attach(self, optimizer):
         if self.world_size > 1:
+            optimizer.beforeParameter = self._join
+            self._attached = True
+
+    def _join(self, p: "Tensor"):
+        g = p.grad()
+        self.device.commWaitFor(g.storage.data, g.size * C.DTYPE_SIZES[g.dtype])
+
+    def finish(self):
+        if self.world_size > 1 and not getattr(self, "_attached", False):
             self.device.commWait()
         self._inFlight.clear()
 

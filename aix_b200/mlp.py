@@ -48,6 +48,8 @@ class MlpTrainer:
         self.loss_fn = MSELoss()
         # overlap=True: each gradient's all-reduce starts inside backward(); False: all of them after it
         self.exchange = GradientExchange(device, self.model.parameters(), world_size) if overlap and world_size > 1 else None
+        if self.exchange is not None:
+            self.exchange.attach(self.optimizer)
         self.flops_per_step = 2.0 * batch * sum(a * b for a, b in zip(dims[:-1], dims[1:])) * 3 \
             - 2.0 * batch * dims[0] * dims[1]                        # forward + dW + dX (no dX for the first layer)
 

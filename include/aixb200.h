@@ -231,6 +231,9 @@ int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t d
  * all-reduce). `scale` must be 1 or 1/nranks (floating types). */
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
 int aixb200_comm_wait(aixb200_device* dev);
+/* Joins only the collectives that touch [data, data + bytes): recorded work that does not depend on them is launched
+ * first. An optimizer calls it before it starts on one parameter, so that the join falls between parameters. */
+int aixb200_comm_wait_for(aixb200_device* dev, const void* data, size_t bytes);
 int aixb200_comm_destroy(aixb200_device* dev);
 
 #ifdef __cplusplus

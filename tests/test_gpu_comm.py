@@ -67,6 +67,12 @@ def test_single_rank_overlapped_exchange_orders_both_streams(comm1):
     comm1.commWait()
     acc = acc + parts[0] + parts[2]
     assert np.allclose(acc.numpy(), a * 10.0, rtol=1e-6)
+    # joining one buffer's collective only
+    comm1.allReduceAsync(parts[0].storage.data, parts[0].size, C.F32, 1.0)
+    comm1.allReduceAsync(parts[1].storage.data, parts[1].size, C.F32, 1.0)
+    comm1.commWaitFor(parts[1].storage.data, parts[1].size * 4)
+    assert np.allclose((parts[1] * 2.0).numpy(), a * 4.0, rtol=1e-6)
+    comm1.commWaitFor(0, 0)                              # nothing to join: a no-op
     # freeing a buffer whose collective is still in flight is safe
     scratch = ta * 2.0
     comm1.allReduceAsync(scratch.storage.data, scratch.size, C.F32, 1.0)
