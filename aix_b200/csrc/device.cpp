@@ -937,13 +937,20 @@ void Device::commInit(int rank, int nranks, const void* id)
     m_comm = std::make_unique<Comm>(rank, nranks, id, m_cfg.ordinal);
 }
 
+// AIXB200_COMM_AVG=0: never use the collective's own averaging (sum, then a scaling pass) - for measurements.
+static bool ncclAverages()
+{
+    static const bool on = []{ const char* v = std::getenv("AIXB200_COMM_AVG"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
 void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
     flush();
     commWait();                 // collectives of one communicator are issued in one order on every rank
     // A scale of exactly 1/ranks on a floating type is the collective's own averaging: no extra pass over the data.
-    const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
+    const bool average = ncclAverages() && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
     m_comm->allReduceSum(data, count, dtype, m_stream, average);
     if (scale != 1.0 && !average)
     {
@@ -960,8 +967,7 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");
-    const bool average = isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
-    if (scale != 1.0 && !average) failInvalid("all_reduce_async: scale must be 1 or 1/ranks on a floating type");
+    const bool average = ncclAverages() && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
     aixb200_tensor whole{};
     whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
     const View range = makeView(&whole, "all_reduce_async");
@@ -975,6 +981,15 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
     check(cudaEventRecord(m_commFork, m_stream), "cudaEventRecord(comm fork)");
     check(cudaStreamWaitEvent(m_commStream, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
     m_comm->allReduceSum(data, count, dtype, m_commStream, average);
+    if (scale != 1.0 && !average)
+    {
+        // plain sum (the form in-switch reduction serves) followed by the scaling pass, both on the side stream
+        uint64_t launched = 0;
+        kernels::LaunchContext ctx{m_commStream, m_smCount, m_scratch, m_scratchBytes, &launched};
+        kernels::scaleInPlace(ctx, dtype, data, count, scale);
+        m_stats.static_kernel_launches += launched; m_stats.total_kernel_launches += launched;
+        checkLaunch("all_reduce_async scale");
+    }
     cudaEvent_t done = nullptr;
     if (!m_commEventPool.empty()) { done = m_commEventPool.back(); m_commEventPool.pop_back(); }
     else check(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate(comm)");

@@ -1,21 +1,26 @@
 // Dense matmul on the 5th-generation tensor cores of sm_100a.
 //
 // Replaces the reference's threadgroup-tiled Metal GEMM (matrixMulStridedTiled<16>, aixDeviceMetalShaders.hpp:1191-1275,
-// selected in aixDeviceMetal.cpp:569-656). Structure of the kernel:
-//   * persistent CTAs (one per SM) walk 128 x 256 output tiles in an L2-friendly order;
-//   * warp 0 streams operand tiles with TMA (cp.async.bulk.tensor, no multicast) into a 4-stage ring of
-//     128-byte-swizzled shared memory, signalling mbarriers;
-//   * warp 1 issues tcgen05.mma (cta_group::1, M=128, N=256, K=16 or 8) from one elected thread; the accumulators
-//     live in tensor memory (TMEM), two buffers of 256 columns so that the epilogue of one tile overlaps the
-//     main loop of the next; tcgen05.commit releases shared-memory stages and publishes finished accumulators;
-//   * warps 2-5 read the accumulator with tcgen05.ld, convert and store C.
+// selected in aixDeviceMetal.cpp:569-656). Two kernels share one structure:
+//   * persistent CTAs (one per SM) walk the output tiles in an L2-friendly order;
+//   * warp 0 streams operand tiles with TMA (cp.async.bulk.tensor, no multicast) into a ring of 128-byte-swizzled
+//     shared-memory stages, signalling mbarriers;
+//   * warp 1 issues tcgen05.mma from one elected thread; the accumulators live in tensor memory (TMEM), two buffers of
+//     256 columns so that the epilogue of one tile overlaps the main loop of the next; tcgen05.commit releases
+//     shared-memory stages and publishes finished accumulators;
+//   * warps 2-5 read the accumulator with tcgen05.ld, convert and write C.
+// gemmPairKernel (the default): clusters of two CTAs compute 256 x 256 tiles with cta_group::2 - each CTA loads its own
+// 128 rows of A and half of the B tile, the leader issues M=256 MMAs for both SMs; 3 stages of two swizzle atoms along K
+// (one 3-D TMA box per operand and stage); C leaves through shared memory and TMA stores. gemmKernel: one CTA per
+// 128 x 256 tile, 4 stages of one atom, row-per-thread epilogue; used for M <= 128 and as a cross-check.
 // Operands may be K-major or MN-major (row- or column-major views): the shared-memory matrix descriptors and the
 // TMA boxes are chosen per operand, so forward (A.B), dX (G.B^T) and dW (A^T.G) run without materialised transposes.
-// f32 problems are split as a = hi + lo with hi = a rounded to TF32: C = hi(A).hi(B) in TF32 plus the two cross terms
-// lo(A).hi(B) and hi(A).lo(B), which are 2^-11 of the result and therefore run as bf16 MMAs (twice the TF32 rate) at no
-// visible loss; lo.lo is dropped. The split pass also makes both operands K-major. Because the tensor core's f32
-// accumulation truncates, K is cut into chunks of 512 whose partial sums the epilogue adds into C with IEEE additions.
-// Every wait on an mbarrier is bounded in time; on expiry the kernel raises an error word and drains.
+// f32 problems run on the 16-bit pipes from split operands (pair kernel: two fp16 terms per scaled operand, three
+// passes; single-CTA kernel: a TF32 main pass plus two bf16 cross-term passes). Because the tensor core's f32
+// accumulation truncates, K is cut into chunks of 512 whose partial sums are added into C with IEEE additions
+// (TMA reduce-add in L2, or by the epilogue threads on the direct path).
+// Every wait on an mbarrier or on a flag of another cluster is bounded in time; on expiry the kernel raises an error
+// word and drains.
 #include "gemm.hpp"
 
 #include "device.hpp"

@@ -228,7 +228,7 @@ int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t d
  * the device's stream runs concurrently with it, except work that touches `data`: any later op whose operands or result
  * overlap a collective in flight is ordered after that collective (and only that one). aixb200_comm_wait() orders the
  * device's stream after every collective started this way (also implied by synchronize and by the blocking
- * all-reduce). `scale` must be 1 or 1/nranks (floating types). */
+ * all-reduce). */
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
 int aixb200_comm_wait(aixb200_device* dev);
 /* Joins only the collectives that touch [data, data + bytes): recorded work that does not depend on them is launched
