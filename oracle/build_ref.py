@@ -1,6 +1,6 @@
 """TEST INFRASTRUCTURE - builds the reference's own CPU device into oracle/_ref/libaixref.so.
 
-The reference sources are compiled where they lie (AIX_REFERENCE_ROOT, default /root/reference); nothing is copied
+The reference sources are compiled where they lie (the checkout named by AIX_REFERENCE_ROOT); nothing is copied
 into this repository and the output directory is git-ignored. Flags follow the reference's Release configuration
 (CMakeLists.txt:41,49: C++20, -O3, asserts left on). Only oracle/ref_shim.cpp (a thin C ABI, no arithmetic) is ours.
 
