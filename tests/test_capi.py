@@ -60,3 +60,17 @@ def test_contract_violations_raise_value_error(dry):
     dry.deallocate(p)
     with pytest.raises(ValueError):
         DeviceTensorParams(p, F32, 0, (1,) * 9, 1, (1,) * 9).to_c()
+
+
+def test_exchange_entry_points_without_a_communicator(dry):
+    """No communicator (and no GPU): the joins are no-ops, the collectives are refused with a message, nothing crashes."""
+    x = TensorValue.full(1.0, (16,), dry)
+    dry.commWait()
+    dry.commWaitFor(x.storage.data, 64)
+    dry.commWaitFor(0, 0)
+    for call in (dry.allReduce, dry.allReduceAsync):
+        with pytest.raises(Exception, match="comm_init"):
+            call(x.storage.data, 16, F32, 1.0)
+    with pytest.raises(Exception, match="GPU"):
+        dry.commInit(0, 1, bytes(C.COMM_ID_BYTES))
+    dry.synchronize()
