@@ -216,3 +216,27 @@ def test_fused_reduction_over_a_broadcast_chain_bf16(b200, ref):
             res.append((round_to(y.to(F32).sum().numpy(), BF16), y.max().numpy()))
     assert_close(res[0][1], res[1][1], BF16, "max")
     assert_close(res[0][0], res[1][0], BF16, "sum", scale=float(abs(res[1][0])))
+
+
+def test_fused_reduction_sees_the_values_at_its_place_in_program_order(b200, ref):
+    """A reduction folded into a kernel reads the producer's register at the point where it was recorded: a later in-place
+    update of the same tensor inside the same kernel must not leak into it. Also: a pending fill as the producer."""
+    rng = np.random.default_rng(12)
+    x = rng.normal(0, 1, (3, 4099)).astype(np.float32)
+    y = rng.normal(0, 1, (3, 4099)).astype(np.float32)
+    got, want = [], []
+    for dev, out in ((b200, got), (ref, want)):
+        a, b = TensorValue.from_numpy(x, dev), TensorValue.from_numpy(y, dev)
+        dev.synchronize()
+        t = a * b
+        before, peak = t.sum(), t.max()
+        t += a                                  # same storage, same kernel on the B200
+        after = t.sum()
+        ones = TensorValue.full(0.5, (7, 1000), dev)
+        out.extend([before.numpy(), peak.numpy(), after.numpy(), t.numpy(), ones.sum().numpy()])
+    scale = float(np.abs(x * y).sum())
+    assert_close(got[0], want[0], F32, "sum before the update", scale=scale)
+    assert_close(got[1], want[1], F32, "max before the update")
+    assert_close(got[2], want[2], F32, "sum after the update", scale=scale)
+    assert_close(got[3], want[3], F32, "updated tensor")
+    assert float(got[4]) == 3500.0 == float(want[4])

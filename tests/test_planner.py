@@ -214,3 +214,37 @@ def test_result_of_a_reduction_orders_later_writers_and_readers(dry):
     dry.synchronize()
     st = delta(dry, s0)
     assert st["reductions_fused"] == 1 and st["fused_kernels"] >= 2
+
+
+def test_reduction_epilogue_compiles_in_unusual_kernels(dry):
+    """Kernels whose only output is a reduction (no loads, or no stores), in-place updates of the reduced tensor after the
+    reduction, integer and 16-bit element types: every variant must plan and compile."""
+    s0 = dry.stats()
+    ones = TensorValue.full(1.0, (3, 1000), dry)
+    total = ones.sum()                                   # producer is a pending fill: no load, and (ones stays alive) one store
+    del ones
+    a = TensorValue.full(2.0, (4099,), dry, BF16)
+    b = TensorValue.full(3.0, (4099,), dry, BF16)
+    dry.synchronize()
+    t = a * b
+    s = t.sum()
+    m = t.max()
+    t += a                                               # in-place update after the reductions: they saw the old values
+    again = t.sum()
+    i = TensorValue.full(7, (513,), dry, I32)
+    dry.synchronize()
+    k = (i * i).max()
+    j = (i + i).sum()
+    dry.synchronize()
+    st = delta(dry, s0)
+    assert st["reductions_fused"] == 6 and st["static_kernel_launches"] == 0
+
+
+def test_reduction_is_not_recorded_with_fusion_off():
+    from aix_b200 import DeviceB200
+    dev = DeviceB200(0, dry_run=1, disk_cache=0, fusion=0)
+    a = TensorValue.full(1.0, (1000,), dev)
+    s = (a * a).sum()
+    dev.synchronize()
+    assert dev.stats()["reductions_fused"] == 0
+    dev.close()
