@@ -110,6 +110,14 @@ def tanhBackwardFunc(node, seed):
         node.inputs[0].backward((1.0 - t * t) * seed)
 
 
+def sinBackwardFunc(node, seed):
+    if node.inputs: node.inputs[0].backward(node.inputs[0].value.cos() * seed)       # aixCore.hpp:2123-2129
+
+
+def cosBackwardFunc(node, seed):
+    if node.inputs: node.inputs[0].backward(-node.inputs[0].value.sin() * seed)      # aixCore.hpp:2131-2137
+
+
 def matmulBackwardFunc(node, seed):
     if len(node.inputs) < 2: return
     a, b = node.inputs
@@ -189,6 +197,16 @@ class Tensor:
     def tanh(self) -> "Tensor":
         r = Tensor._result(self.value.tanh(), self.isRequireGrad())
         r.node.setBackward([self.node], tanhBackwardFunc)
+        return r
+
+    def sin(self) -> "Tensor":
+        r = Tensor._result(self.value.sin(), self.isRequireGrad())
+        r.node.setBackward([self.node], sinBackwardFunc)
+        return r
+
+    def cos(self) -> "Tensor":
+        r = Tensor._result(self.value.cos(), self.isRequireGrad())
+        r.node.setBackward([self.node], cosBackwardFunc)
         return r
 
     def matmul(self, other: "Tensor") -> "Tensor":
