@@ -31,6 +31,7 @@ int guarded(aixb200_device* dev, F&& body)
     try
     {
         if (!dev->impl->dryRun()) cudaSetDevice(dev->impl->ordinal());
+        dev->impl->beginCall();
         body(*dev->impl);
         return AIXB200_OK;
     }

@@ -223,6 +223,20 @@ void* Device::temporary(size_t bytes)
     return p;
 }
 
+// Staged host operands stay out of the deferred-release list while the call that staged them is still running: a flush
+// inside that call (ordering after a collective, the flush every immediate op starts with) returns deferred blocks to
+// the cache, and the call's own temporaries could then be handed the very block its operand sits in.
+void Device::retireStaged()
+{
+    for (void* p : m_staged)
+    {
+        m_released.insert(p);
+        m_deferredFrees.push_back(p);
+        m_deferredBytes += m_allocator->blockSize(p);
+    }
+    m_staged.clear();
+}
+
 void Device::deallocate(void* p)
 {
     if (!p) return;
@@ -273,15 +287,20 @@ void Device::synchronize()
     check(cudaGetLastError(), "asynchronous kernel failure");
     if (m_checkErrorWord)
     {
-        // Kernels with bounded waits (tensor-core GEMM) raise a word in scratch instead of hanging.
+        // Kernels never trap: one with a bounded wait (tensor-core GEMM) that ran out, or one that met an index outside
+        // its dimension, raises a word in scratch, skips the work it cannot do, and the failure surfaces here.
         m_checkErrorWord = false;
-        uint32_t word = 0;
-        check(cudaMemcpy(&word, static_cast<char*>(m_scratch) + 128, 4, cudaMemcpyDeviceToHost), "read error word");
-        if (word)
+        uint32_t words[2] = {0, 0};
+        check(cudaMemcpy(words, static_cast<char*>(m_scratch) + kernels::kScratchTimeoutOffset, 8, cudaMemcpyDeviceToHost), "read error words");
+        if (words[0] || words[1])
         {
-            cudaMemset(static_cast<char*>(m_scratch) + 128, 0, 4);
-            cudaMemset(static_cast<char*>(m_scratch) + m_scratchBytes, 0, kernels::kGemmCounterBytes);   // split-tile counters
-            throw Error(AIXB200_ERR_TIMEOUT, "a bounded device-side wait ran out inside the tensor-core matmul; its result is invalid");
+            cudaMemset(static_cast<char*>(m_scratch) + kernels::kScratchTimeoutOffset, 0, 8);
+            if (words[0])
+            {
+                cudaMemset(static_cast<char*>(m_scratch) + m_scratchBytes, 0, kernels::kGemmCounterBytes);   // split-tile counters
+                throw Error(AIXB200_ERR_TIMEOUT, "a bounded device-side wait ran out; the result of the kernel that waited is invalid");
+            }
+            throw Error(AIXB200_ERR_INVALID, "indexSelect / indexAdd: an index lies outside the indexed dimension; those elements were skipped");
         }
     }
 }
@@ -306,7 +325,8 @@ View Device::inputView(const aixb200_tensor* t, const char* what)
     // to a temporary device block now; program order on the stream keeps it ahead of the kernels that read it.
     const size_t es = dtypeSize(v.dtype);
     const size_t bytes = v.span() * es;
-    char* staged = static_cast<char*>(temporary(bytes));
+    char* staged = static_cast<char*>(m_allocator->allocate(bytes + 16));
+    m_staged.push_back(staged);
     check(cudaMemcpyAsync(staged, v.firstByte(), bytes, cudaMemcpyHostToDevice, m_stream), "host-to-device staging copy");
     m_stats.h2d_bytes += bytes;
     v.base = staged;
@@ -596,6 +616,16 @@ void Device::sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r)
     if (src.size == 0) failInvalid("sum_static_scratch: empty input");
     if ((!m_allocator->findBlock(src.base) && isHostPointer(src.base)) || (!m_allocator->findBlock(dst.base) && isHostPointer(dst.base)))
         failInvalid("sum_static_scratch: input and result must be device memory (host inputs would need a staging allocation)");
+    // An overlapped all-reduce may still be working on the operand or the result: the device's stream waits for it, as
+    // every other entry point does. Waiting on an event allocates nothing; the collective stays listed and is joined
+    // again by the next ordinary call, which is harmless.
+    for (const View* v : {&src, &dst})
+    {
+        const char* first = v->firstByte();
+        const char* last = v->endByte();
+        for (const CommInFlight& c : m_commInFlight)
+            if (first < c.end && c.begin < last) check(cudaStreamWaitEvent(m_stream, c.done, 0), "cudaStreamWaitEvent(comm done)");
+    }
     AIXB200_CTX();
     const char* error = kernels::sumWithStaticScratch(ctx, m_cfg.ordinal, src, dst.firstByte());
     m_stats.static_kernel_launches += launched_;
@@ -881,7 +911,8 @@ void Device::indexSelect(const aixb200_tensor* s, const aixb200_tensor* d, const
     const uint64_t dimSize = s->rank ? s->shape[dim] * sliceSize : 0;
     AIXB200_CTX();
     kernels::indexSelect(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), reinterpret_cast<const int32_t*>(ind.firstByte()),
-                         ind.size, sliceSize, dimSize, dst.size);
+                         layoutOf(idx), ind.size, sliceSize, dimSize, dst.size);
+    m_checkErrorWord = true;
     AIXB200_DONE("indexSelect");
 }
 
@@ -900,7 +931,8 @@ void Device::indexAdd(const aixb200_tensor* s, const aixb200_tensor* d, const ai
     const uint64_t dimSize = d->rank ? d->shape[dim] * sliceSize : 0;
     AIXB200_CTX();
     kernels::indexAdd(ctx, src.dtype, src.firstByte(), layoutOf(s), dst.firstByte(), reinterpret_cast<const int32_t*>(ind.firstByte()),
-                      ind.size, sliceSize, dimSize, src.size);
+                      layoutOf(idx), ind.size, sliceSize, dimSize, src.size);
+    m_checkErrorWord = true;
     AIXB200_DONE("indexAdd");
 }
 

@@ -104,6 +104,9 @@ public:
     void checkLaunch(const char* what);
     // Temporary device block that is returned to the cache after the next flush.
     void* temporary(size_t bytes);
+    // Called at the top of every C-ABI entry: the host operands the previous call staged are consumed by work that is
+    // recorded or enqueued by now, so their blocks may follow the usual deferred-release path.
+    void beginCall() { if (!m_staged.empty()) retireStaged(); }
 
 private:
     void record(OpRecord&& rec);
@@ -112,6 +115,7 @@ private:
     std::vector<char> compile(const std::string& source, const std::string& entry);
     bool isHostPointer(const void* p) const;
     void releaseDeferred();
+    void retireStaged();
 
     aixb200_config m_cfg;
     std::string    m_name;
@@ -128,6 +132,7 @@ private:
     std::vector<OpRecord> m_pending;
     std::unordered_set<const void*> m_released;        // storages deallocated while ops were pending
     std::vector<void*> m_deferredFrees;
+    std::vector<void*> m_staged;                       // staging copies of host operands of the call in progress
     uint64_t m_deferredBytes = 0;
     PlannerLimits  m_limits;
     CodegenOptions m_codegen;

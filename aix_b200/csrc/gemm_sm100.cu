@@ -1588,21 +1588,22 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                                 : ((1u << 4) | (1u << 7) | (1u << 10) | shape);   // D f32, A/B bf16
     }
 
+    // The opt-in to more than 48 KiB of dynamic shared memory and the cluster occupancy are properties of one device:
+    // kept per ordinal, so a second device handle on another GPU of the same process sets them up for itself.
+    constexpr int kMaxDevices = 64;
+    struct PerDevice { std::mutex lock; bool attributesSet = false; int maxClusters = 0; };
+    static PerDevice perDevice[kMaxDevices];
+    const int ordinal = device.ordinal();
+    if (ordinal < 0 || ordinal >= kMaxDevices) return false;
+    PerDevice& state = perDevice[ordinal];
     const size_t smemBytes = sizeof(SharedStorage) + 1024;
-    static std::once_flag attrOnce;
-    std::call_once(attrOnce, [&]
+    const size_t pairSmem = sizeof(PairStorage) + 1024;
     {
-        cudaFuncSetAttribute(gemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
-        cudaFuncSetAttribute(gemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
-    });
-    const uint32_t tiles = p.tilesM * p.tilesN;
-    if (pair)
-    {
-        const size_t pairSmem = sizeof(PairStorage) + 1024;
-        static int maxClusters = 0;
-        static std::once_flag pairOnce;
-        std::call_once(pairOnce, [&]
+        std::lock_guard<std::mutex> guard(state.lock);
+        if (!state.attributesSet)
         {
+            cudaFuncSetAttribute(gemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
+            cudaFuncSetAttribute(gemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
             cudaFuncSetAttribute(gemmPairKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaFuncSetAttribute(gemmPairKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaLaunchConfig_t cfg{};
@@ -1614,12 +1615,18 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
             cfg.attrs = &attr;
             cfg.numAttrs = 1;
-            if (cudaOccupancyMaxActiveClusters(&maxClusters, gemmPairKernel<false>, &cfg) != cudaSuccess || maxClusters <= 0)
+            if (cudaOccupancyMaxActiveClusters(&state.maxClusters, gemmPairKernel<false>, &cfg) != cudaSuccess || state.maxClusters <= 0)
             {
                 cudaGetLastError();
-                maxClusters = ctx.smCount / 2;
+                state.maxClusters = ctx.smCount / 2;
             }
-        });
+            state.attributesSet = true;
+        }
+    }
+    const int maxClusters = state.maxClusters;
+    const uint32_t tiles = p.tilesM * p.tilesN;
+    if (pair)
+    {
         // A collective on the device's side stream needs SMs of its own. The persistent grid would otherwise either keep
         // it out until the matmul ends or, if the collective got there first, start some of its clusters late - and
         // with tiles dealt out statically those late clusters finish their whole share late. While a collective is in

@@ -19,6 +19,8 @@ struct LaunchContext
 
 // Layout of the scratch block shared by the reduction kernels.
 constexpr size_t kScratchCounterBytes = 256;        // ticket counters at the start
+constexpr size_t kScratchTimeoutOffset  = 128;      // raised by a kernel whose bounded wait ran out
+constexpr size_t kScratchBadIndexOffset = 132;      // raised by indexSelect / indexAdd on an index outside the dimension
 constexpr size_t kMaxReduceBlocks     = 4096;       // upper bound of partials a full reduction may write
 // The device allocates this much beyond LaunchContext::scratchBytes: counters of the tensor-core matmul's split tiles.
 constexpr size_t kGemmCounterBytes    = 4096;
@@ -58,9 +60,9 @@ void sliceSet(const LaunchContext& ctx, uint32_t dtype, const void* src, const L
 void triangle(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& srcLayout, void* dst,
               const Layout& dstLayout, uint64_t count, uint64_t rows, uint64_t cols, int64_t diagonal, bool lower);
 void indexSelect(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& srcLayout, void* dst, const int32_t* indices,
-                 uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount);
+                 const Layout& indexLayout, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount);
 void indexAdd(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& srcLayout, void* dst, const int32_t* indices,
-              uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount);
+              const Layout& indexLayout, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount);
 void scaleInPlace(const LaunchContext& ctx, uint32_t dtype, void* data, uint64_t count, double scale);
 void flushL2(const LaunchContext& ctx, void* buffer, size_t bytes);
 

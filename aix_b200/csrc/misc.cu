@@ -29,6 +29,8 @@ __device__ __forceinline__ uint64_t layoutOffset(uint64_t i, const Layout& l)
     return off;
 }
 
+inline uint32_t* badIndexWord(const LaunchContext& ctx) { return reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + kScratchBadIndexOffset); }
+
 inline unsigned int gridFor(uint64_t count, int smCount)
 {
     const uint64_t blocks = (count + kBlock - 1) / kBlock;
@@ -266,34 +268,45 @@ __global__ void __launch_bounds__(kBlock) triangleKernel(const S* __restrict__ s
     }
 }
 
-// indexSelect (aixDeviceCPU.cpp:502-531)
+// indexSelect (aixDeviceCPU.cpp:502-531). An index outside [0, extent of the selected dimension) is not followed: the
+// element is skipped (its destination keeps what it held) and *badIndex is raised, which the next synchronize() reports
+// as an invalid argument. The reference's front end rejects such indices on the host before the device sees them
+// (aixCore.hpp:1242, 1640-1650); callers of the C ABI have no such guard.
 template <class S>
 __global__ void __launch_bounds__(kBlock) indexSelectKernel(const S* __restrict__ src, Layout srcLayout, S* __restrict__ dst,
-                                                            const int32_t* __restrict__ indices, uint64_t indexCount, uint64_t sliceSize,
-                                                            uint64_t dimSize, uint64_t dstCount)
+                                                            const int32_t* __restrict__ indices, Layout indexLayout, uint64_t indexCount,
+                                                            uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount, uint32_t* badIndex)
 {
+    const uint64_t extent = sliceSize ? dimSize / sliceSize : 0;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < dstCount; i += static_cast<uint64_t>(gridDim.x) * kBlock)
     {
         const uint64_t within = i % sliceSize, idx = (i / sliceSize) % indexCount, outer = i / (indexCount * sliceSize);
-        const uint64_t srcFlat = outer * dimSize + static_cast<uint64_t>(indices[idx]) * sliceSize + within;
+        const int64_t index = indices[layoutOffset(idx, indexLayout)];
+        if (index < 0 || static_cast<uint64_t>(index) >= extent) { *badIndex = 1u; continue; }
+        const uint64_t srcFlat = outer * dimSize + static_cast<uint64_t>(index) * sliceSize + within;
         dst[i] = src[layoutOffset(srcFlat, srcLayout)];
     }
 }
 
 // indexAdd (aixDeviceCPU.cpp:534-562). Several source slices may land on the same destination slice, so the kernel
 // is parallel over (outer, within) and sequential over the index list: same order as the reference, no atomics.
+// Out-of-range indices are skipped and reported like in indexSelect.
 template <int DT>
 __global__ void __launch_bounds__(kBlock) indexAddKernel(const typename Elem<DT>::S* __restrict__ src, Layout srcLayout,
                                                          typename Elem<DT>::S* __restrict__ dst, const int32_t* __restrict__ indices,
-                                                         uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t lanes)
+                                                         Layout indexLayout, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize,
+                                                         uint64_t lanes, uint32_t* badIndex)
 {
     typedef Reduce<DT, false> R;
+    const uint64_t extent = sliceSize ? dimSize / sliceSize : 0;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; t < lanes; t += static_cast<uint64_t>(gridDim.x) * kBlock)
     {
         const uint64_t within = t % sliceSize, outer = t / sliceSize;
         for (uint64_t idx = 0; idx < indexCount; ++idx)
         {
-            const uint64_t dstOff = outer * dimSize + static_cast<uint64_t>(indices[idx]) * sliceSize + within;
+            const int64_t index = indices[layoutOffset(idx, indexLayout)];
+            if (index < 0 || static_cast<uint64_t>(index) >= extent) { *badIndex = 1u; continue; }
+            const uint64_t dstOff = outer * dimSize + static_cast<uint64_t>(index) * sliceSize + within;
             const uint64_t srcFlat = outer * indexCount * sliceSize + idx * sliceSize + within;
             dst[dstOff] = R::finish(R::merge(R::liftStored(dst[dstOff]), R::liftStored(src[layoutOffset(srcFlat, srcLayout)])));
         }
@@ -335,18 +348,20 @@ template <int DT> void launchTriangle(const LaunchContext& ctx, const void* src,
     triangleKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, rows, cols, diagonal, lower);
 }
 template <int DT> void launchIndexSelect(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,
-                                         uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
+                                         const Layout& il, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
 {
     typedef typename Elem<DT>::S S;
-    indexSelectKernel<S><<<gridFor(dstCount, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, indexCount, sliceSize, dimSize, dstCount);
+    indexSelectKernel<S><<<gridFor(dstCount, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, il,
+                                                                                   indexCount, sliceSize, dimSize, dstCount, badIndexWord(ctx));
 }
 template <int DT> void launchIndexAdd(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,
-                                      uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
+                                      const Layout& il, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
 {
     typedef typename Elem<DT>::S S;
     const uint64_t lanes = indexCount ? srcCount / indexCount : 0;
     if (lanes == 0) return;
-    indexAddKernel<DT><<<gridFor(lanes, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, indexCount, sliceSize, dimSize, lanes);
+    indexAddKernel<DT><<<gridFor(lanes, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, il,
+                                                                                 indexCount, sliceSize, dimSize, lanes, badIndexWord(ctx));
 }
 template <int DT> void launchScale(const LaunchContext& ctx, void* data, uint64_t count, double scale)
 {
@@ -394,16 +409,16 @@ void triangle(const LaunchContext& ctx, uint32_t dtype, const void* src, const L
 }
 
 void indexSelect(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const int32_t* indices,
-                 uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
+                 const Layout& il, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
 {
-    AIXB200_DISPATCH_DTYPE(dtype, launchIndexSelect, ctx, src, sl, dst, indices, indexCount, sliceSize, dimSize, dstCount);
+    AIXB200_DISPATCH_DTYPE(dtype, launchIndexSelect, ctx, src, sl, dst, indices, il, indexCount, sliceSize, dimSize, dstCount);
     if (ctx.launches) ++*ctx.launches;
 }
 
 void indexAdd(const LaunchContext& ctx, uint32_t dtype, const void* src, const Layout& sl, void* dst, const int32_t* indices,
-              uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
+              const Layout& il, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount)
 {
-    AIXB200_DISPATCH_DTYPE(dtype, launchIndexAdd, ctx, src, sl, dst, indices, indexCount, sliceSize, dimSize, srcCount);
+    AIXB200_DISPATCH_DTYPE(dtype, launchIndexAdd, ctx, src, sl, dst, indices, il, indexCount, sliceSize, dimSize, srcCount);
     if (ctx.launches) ++*ctx.launches;
 }
 

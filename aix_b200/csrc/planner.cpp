@@ -53,6 +53,19 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
     std::vector<std::array<InputBinding, 2>> bindings(n);
     std::vector<Group> groups;
 
+    // Byte range every view touches, computed once: the hazard tests below compare ranges, not base pointers (two
+    // descriptors may reach one buffer through different bases, e.g. an interior pointer).
+    struct Range { const char* lo; const char* hi; };
+    auto rangeOf = [](const View& v) { return Range{v.firstByte(), v.endByte()}; };
+    auto meet = [](const Range& a, const Range& b) { return a.lo < b.hi && b.lo < a.hi; };
+    std::vector<Range> outRange(n);
+    std::vector<std::array<Range, 2>> inRange(n);
+    for (size_t j = 0; j < n; ++j)
+    {
+        outRange[j] = rangeOf(ops[j].out);
+        for (int k = 0; k < ops[j].numInputs; ++k) inRange[j][k] = rangeOf(ops[j].in[k]);
+    }
+
     // ---- pass 1: dependencies and group placement, in program order -------------------------------------------
     for (size_t j = 0; j < n; ++j)
     {
@@ -67,7 +80,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             for (size_t i = j; i-- > 0;)
             {
                 const View& w = ops[i].out;
-                if (w.base != in.base || !w.overlaps(in)) continue;
+                if (!meet(outRange[i], inRange[j][k])) continue;
                 if (isReduction(ops[i].op))
                 {
                     // written when the producing grid has finished: readable from the next kernel on
@@ -76,7 +89,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                     continue;
                 }
                 if (!shadowed && isOneElementFill(ops[i]) && in.isBroadcastScalar() && w.dtype == in.dtype &&
-                    w.offset == in.offset)
+                    outRange[i].lo == inRange[j][k].lo)
                 {
                     bind.kind = InputBinding::ImmediateFill;     // value known on the host: no ordering needed
                     bind.producer = i;
@@ -103,10 +116,10 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             for (int k = 0; k < ri.numInputs; ++k)
             {
                 const View& r = ri.in[k];
-                if (r.base != rj.out.base || !r.overlaps(rj.out)) continue;
+                if (!meet(inRange[i][k], outRange[j])) continue;
                 minGroup = std::max(minGroup, (r.sameElements(rj.out) && !jReduces) ? groupOf[i] : groupOf[i] + 1);
             }
-            if (ri.out.base == rj.out.base && ri.out.overlaps(rj.out))
+            if (meet(outRange[i], outRange[j]))
                 minGroup = std::max(minGroup, (ri.out.sameElements(rj.out) && !jReduces && !isReduction(ri.op)) ? groupOf[i] : groupOf[i] + 1);
         }
 
@@ -167,7 +180,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 // The reader goes to memory: every pending writer that overlaps the view must have stored by then.
                 for (size_t i = 0; i < j; ++i)
-                    if (ops[i].out.base == ops[j].in[k].base && ops[i].out.overlaps(ops[j].in[k])) readElsewhere[i] = 1;
+                    if (meet(outRange[i], inRange[j][k])) readElsewhere[i] = 1;
             }
         }
 

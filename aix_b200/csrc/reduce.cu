@@ -13,6 +13,7 @@
 #include "kernels.hpp"
 
 #include <algorithm>
+#include <atomic>
 
 namespace aixb200::kernels
 {
@@ -463,17 +464,16 @@ static __device__ __align__(256) unsigned char g_staticReduceScratch[kStaticScra
 const char* sumWithStaticScratch(const LaunchContext& ctx, int ordinal, const View& src, void* dst)
 {
     constexpr int kMaxDevices = 64;
-    static void* addresses[kMaxDevices] = {};
+    static std::atomic<void*> addresses[kMaxDevices] = {};      // two handles may make their first call from two threads
     if (ordinal < 0 || ordinal >= kMaxDevices) return "device ordinal out of range for the static scratch table";
-    if (!addresses[ordinal])
+    void* scratch = addresses[ordinal].load(std::memory_order_acquire);
+    if (!scratch)
     {
         // First call on this device (the device is current): resolve the array's device address.
-        void* p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_staticReduceScratch);
+        cudaError_t e = cudaGetSymbolAddress(&scratch, g_staticReduceScratch);
         if (e != cudaSuccess) return cudaGetErrorString(e);
-        addresses[ordinal] = p;
+        addresses[ordinal].store(scratch, std::memory_order_release);
     }
-    void* scratch = addresses[ordinal];
     // The ticket must start at zero; a launch that was cut short could have left it raised.
     cudaError_t e = cudaMemsetAsync(scratch, 0, kScratchCounterBytes, ctx.stream);
     if (e != cudaSuccess) return cudaGetErrorString(e);

@@ -31,7 +31,7 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 class MlpTrainer:
     def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
-                 overlap=True):
+                 overlap=True, data=None):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -41,7 +41,8 @@ class MlpTrainer:
             if i + 1 < len(weights):
                 layers.append(Tanh())
         self.model = Sequential(*layers)
-        x, y = synthetic_batch(dims, batch, rank, seed)
+        x, y = data if data is not None else synthetic_batch(dims, batch, rank, seed)
+        batch = x.shape[0]
         self.x = Tensor(TensorValue.from_numpy(x, device))
         self.y = Tensor(TensorValue.from_numpy(y, device))
         self.optimizer = Adam(self.model.parameters(), lr=lr)      # created after the parameters live on the device

@@ -88,7 +88,10 @@ typedef struct aixb200_config
     int32_t  disk_cache;         /* 1: keep compiled cubins in $AIXB200_CACHE_DIR (default ~/.cache/aixb200) */
     uint64_t cache_limit_bytes;  /* idle blocks kept by the allocator before it trims (0 = 3/4 of device memory) */
     void*    stream;             /* cudaStream_t to run on; NULL = the device creates its own non-blocking stream */
-    int32_t  tf32x3_matmul;      /* f32 matmul: 1 = split-precision TF32 + bf16 cross terms on tensor cores, 0 = CUDA-core f32 */
+    int32_t  tf32x3_matmul;      /* f32 matmul: 1 (default) = split precision on the tensor cores - every operand is scaled by a
+                                    power of two and cut into two fp16 terms, three fp16 passes accumulate in f32 (norm-wise error
+                                    <= 1e-5); 0 = plain f32 FMA on the CUDA cores. The field keeps the name of the first scheme
+                                    (TF32 main pass + bf16 cross terms), which remains behind AIXB200_GEMM_F32=hybrid. */
     int32_t  dry_run;            /* 1: no GPU is touched - ops are recorded, planned and compiled with NVRTC but not
                                     launched, and memory comes from malloc (host-logic tests on machines without a GPU) */
     int32_t  reserved[6];
@@ -149,7 +152,9 @@ int aixb200_max(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tens
  *  - the first call on a device resolves the array's address (cudaGetSymbolAddress); make that first call before any
  *    stream capture begins.
  *  - all calls on one GPU share the array: calls that overlap on the GPU (two streams, two device handles, two
- *    threads) race on it. Calls on one device handle are ordered by its stream and are safe. */
+ *    threads) race on it. Calls on one device handle are ordered by its stream and are safe.
+ *  - an aixb200_all_reduce_async still in flight on `a` or `result` is waited for on the device's stream first (an event
+ *    wait, no allocation), like in every other entry point. */
 #define AIXB200_SUM_STATIC_SCRATCH_MAX_ELEMENTS (1ull << 30)
 int aixb200_sum_static_scratch(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
 int aixb200_argmax(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* result);
@@ -160,7 +165,11 @@ int aixb200_max_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200
 int aixb200_argmax_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim);
 int aixb200_argmax_indices_to(aixb200_device* dev, const aixb200_tensor* src, const aixb200_tensor* dst, size_t dim);
 
-/* ---- contraction (aixDevice.hpp:63): result[M,N] = a[M,K] . b[K,N]; a and b may be arbitrary 2-D strided views ---- */
+/* ---- contraction (aixDevice.hpp:63): result[M,N] = a[M,K] . b[K,N]; a and b may be arbitrary 2-D strided views ----
+ * f32 on the tensor cores (tf32x3_matmul = 1) scales each operand by one power of two taken from its largest magnitude.
+ * An operand that contains an infinity or a NaN is left unscaled; its finite elements above 65504 then overflow the fp16
+ * terms, so rows and columns that the CPU device would still compute finitely can come out infinite or NaN as well.
+ * Operands with non-finite elements that must keep their finite part exact need tf32x3_matmul = 0. */
 int aixb200_matmul(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* result);
 
 /* ---- data movement (aixDevice.hpp:64-69, 74-81) ---- */

@@ -1,9 +1,11 @@
 """Child process of tests/test_gpu_comm.py: one data-parallel rank on its own GPU.
 
-    python tests/_dp_worker.py <rank> <world> <dir> <overlap 0|1> <steps>
+    python tests/_dp_worker.py <rank> <world> <dir> <overlap 0|1> <steps> [<ranks whose batches one process concatenates>]
 
 Rank 0 publishes the communicator id through a file in <dir>; every rank trains the small MLP and writes its parameters
-and losses to <dir>/rank<r>_<overlap>.npz."""
+and losses to <dir>/rank<r>_<overlap>.npz. With world = 1 and the last argument R, the single process trains on the
+concatenation of the batches ranks 0 .. R-1 would have drawn (the single-process result the data-parallel run must
+reproduce) and writes <dir>/single.npz."""
 import os
 import sys
 import time
@@ -13,7 +15,7 @@ import numpy as np
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from aix_b200 import DeviceB200                      # noqa: E402
-from aix_b200.mlp import MlpTrainer                  # noqa: E402
+from aix_b200.mlp import MlpTrainer, synthetic_batch  # noqa: E402
 
 DIMS = (256, 512, 512, 128)
 BATCH = 384
@@ -21,6 +23,17 @@ BATCH = 384
 
 def main():
     rank, world, out_dir, overlap, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4] == "1", int(sys.argv[5])
+    concat = int(sys.argv[6]) if len(sys.argv) > 6 else 0
+    if world == 1 and concat > 1:
+        parts = [synthetic_batch(DIMS, BATCH, r) for r in range(concat)]
+        data = (np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts]))
+        dev = DeviceB200(rank)
+        trainer = MlpTrainer(dev, DIMS, data=data)
+        losses = [float(trainer.step().value.numpy()) for _ in range(steps)]
+        dev.synchronize()
+        np.savez(os.path.join(out_dir, "single.npz"), *trainer.parameters_numpy(), losses=np.array(losses))
+        dev.close()
+        return
     id_path = os.path.join(out_dir, f"comm_id_{int(overlap)}")
     if rank == 0:
         unique = DeviceB200.commUniqueId()

@@ -4,11 +4,11 @@ with the reference's CPU device: same device calls, same descriptors, results co
 import numpy as np
 import pytest
 
-from aix_b200 import BF16, DTYPE_NAMES, F16, F32, F64, I8, I32, I64, U8, TensorValue
+from aix_b200 import BF16, DTYPE_NAMES, F16, F32, F64, I8, I16, I32, I64, U8, TensorValue
 from conftest import assert_close
 
 pytestmark = pytest.mark.gpu
-DTYPES = [F32, F64, BF16, F16, I32, I64, I8, U8]
+DTYPES = [F32, F64, BF16, F16, I32, I64, I16, I8, U8]      # all nine, as Tests/DeviceTests.cpp:30-33
 
 
 def values(rng, shape, dtype):

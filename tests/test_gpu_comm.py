@@ -107,3 +107,29 @@ def test_two_ranks_overlapped_equals_blocking(tmp_path):
             assert np.array_equal(results[0][0][k], results[1][0][k])
     losses = results[1][0]["losses"]
     assert losses[-1] < losses[0]
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_ranks_reproduce_the_single_process_run_on_the_concatenated_batch(tmp_path):
+    """Data parallelism must be invisible: two ranks with a batch each, gradients averaged over the ranks, end where one
+    process ends that trains on both batches at once (the loss is a mean over the batch, so the gradient of the
+    concatenated batch is the average of the two ranks' gradients). f32 tolerance: the sums are formed in a different
+    order, and Adam turns a relative perturbation of the gradient into the same relative perturbation of the update."""
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_dp_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    steps = 6
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", str(tmp_path), "1", str(steps)], env=env) for r in range(2)]
+    assert [p.wait(timeout=600) for p in procs] == [0, 0]
+    single = subprocess.Popen([sys.executable, worker, "0", "1", str(tmp_path), "0", str(steps), "2"], env=env)
+    assert single.wait(timeout=600) == 0
+    want = np.load(tmp_path / "single.npz")
+    for r in range(2):
+        got = np.load(tmp_path / f"rank{r}_1.npz")
+        for k in want.files:
+            if k == "losses":
+                continue
+            assert np.max(np.abs(got[k] - want[k])) <= 0.1 * steps * 1e-3, k      # single weights: a fraction of the total movement
+            assert np.mean(np.abs(got[k] - want[k])) <= 2e-6, k                   # the average weight: tightly
+    # each rank reports the loss of its own half; their mean is the loss of the concatenated batch
+    both = 0.5 * (np.load(tmp_path / "rank0_1.npz")["losses"] + np.load(tmp_path / "rank1_1.npz")["losses"])
+    assert np.allclose(both, want["losses"], rtol=2e-5)

@@ -248,3 +248,27 @@ def test_reduction_is_not_recorded_with_fusion_off():
     dev.synchronize()
     assert dev.stats()["reductions_fused"] == 0
     dev.close()
+
+
+def test_descriptors_that_alias_through_different_base_pointers_are_ordered(dry):
+    """Hazards are found on byte ranges, not on the `data` pointer: a descriptor whose base is an interior pointer of a
+    buffer written by a pending op must not be fused with that op as if it were independent."""
+    from aix_b200 import DeviceTensorParams
+    whole = TensorValue.full(1.0, (1024,), dry)
+    other = TensorValue.full(2.0, (512,), dry)
+    dry.synchronize()
+    s0 = dry.stats()
+    upper = DeviceTensorParams(whole.storage.data, F32, 512, (512,), 512, (1,))                   # elements 512 .. 1023
+    dry.add(upper, other.deviceParams(), upper)                                                  # pending in-place write
+    same_bytes = DeviceTensorParams(whole.storage.data + 512 * 4, F32, 0, (512,), 512, (1,))      # same bytes, other base
+    out = TensorValue.empty((512,), dry)
+    dry.add(same_bytes, other.deviceParams(), out.deviceParams())  # same element count: would join the writer's kernel
+    dry.synchronize()
+    assert delta(dry, s0)["fused_kernels"] == 2, "the aliasing read must wait for the writer's kernel"
+    s1 = dry.stats()
+    t = other + 1.0                                                 # reads `other` ...
+    shifted = DeviceTensorParams(other.storage.data + 4, F32, 0, (511,), 511, (1,))
+    dry.fill(0.0, F32, shifted)                                     # ... then part of it is overwritten through another base
+    u = other * 2.0
+    dry.synchronize()
+    assert delta(dry, s1)["fused_kernels"] == 3, "reader, overlapping writer, reader: three kernels in program order"

@@ -30,6 +30,11 @@ def test_static_scratch_sum_matches_regular_sum_twice_in_a_row(b200, dtype):
         scale = max(1.0, float(np.abs(np.asarray(x, dtype=np.float64)).sum()))
         assert_close(first.numpy(), want, dtype, f"first call n={n}", scale=scale)
         assert_close(second.numpy(), want, dtype, f"second call n={n}", scale=scale)
+        # and against the exact value of what the device holds: float64 for floats, the wrapping integer sum for i32
+        held = t.numpy()
+        exact = held.astype(np.int64).sum().astype(np.int32) if dtype == I32 else held.astype(np.float64).sum()
+        assert_close(first.numpy(), np.asarray(exact, dtype=first.numpy().dtype), dtype, f"against the exact sum n={n}", scale=scale)
+        assert np.array_equal(first.numpy(), second.numpy()), "same grid, same fold order: the two calls agree to the bit"
 
 
 def test_static_scratch_sum_refusals(b200):
@@ -48,3 +53,20 @@ def test_static_scratch_sum_refusals(b200):
     b200.synchronize()
     b200.sumStaticScratch(u.deviceParams(), out.deviceParams())
     assert out.numpy() == 32.0
+
+
+def test_static_scratch_sum_waits_for_a_collective_in_flight_on_its_operand(b200):
+    """An overlapped all-reduce may still be running on the operand: the sum is ordered after it, as every other entry
+    point is (one rank is enough to see the ordering - the collective and its scaling pass run on a side stream)."""
+    from aix_b200 import DeviceB200
+    b200.commInit(0, 1, DeviceB200.commUniqueId())
+    try:
+        host = np.full(1 << 22, 2.0, dtype=np.float32)
+        t = TensorValue.from_numpy(host, b200)
+        out = TensorValue.empty((), b200, F32)
+        b200.synchronize()
+        b200.allReduceAsync(t.storage.data, t.size, F32, 0.25)       # sum over one rank, then x 0.25 on the side stream
+        b200.sumStaticScratch(t.deviceParams(), out.deviceParams())
+        assert float(out.numpy()) == 0.5 * (1 << 22)
+    finally:
+        b200.commDestroy()
