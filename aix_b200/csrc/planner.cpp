@@ -9,7 +9,7 @@ namespace aixb200
 const char* opName(Op op)
 {
     static const char* names[] = {"add", "sub", "mul", "div", "neg", "sqrt", "sin", "cos", "tanh", "log", "exp", "pow",
-                                  "fill", "cast", "sumall", "maxall"};
+                                  "fill", "cast", "sumall", "maxall", "sumrows", "maxrows"};
     return names[static_cast<size_t>(op)];
 }
 
@@ -32,6 +32,7 @@ struct Group
     std::vector<View> loads;        // distinct views this group reads from memory
     size_t liveOutputs = 0;         // results whose storage is still alive (they will be stored)
     size_t reductions = 0;
+    uint64_t rowCols = 0;           // row length of the row reductions this group holds (they all share it)
 };
 
 // Where an input of a recorded op comes from.

@@ -30,8 +30,12 @@ namespace aixb200
 
 enum class Op : uint8_t { Add, Sub, Mul, Div, Neg, Sqrt, Sin, Cos, Tanh, Log, Exp, Pow, Fill, Cast,
                           SumAll, MaxAll,   // full reductions recorded behind a pending producer: in[0] -> one element
+                          SumRows, MaxRows, // reductions over the trailing dimension of a dense [rows, cols] operand recorded behind
+                                            // its pending producer: in[0] = operand, in[1] = out = the `rows` results, which
+                                            // accumulate into what the destination holds (reduceTo / maxTo contract)
                           COUNT };
-inline bool isReduction(Op op) { return op == Op::SumAll || op == Op::MaxAll; }
+inline bool isRowReduction(Op op) { return op == Op::SumRows || op == Op::MaxRows; }
+inline bool isReduction(Op op) { return op == Op::SumAll || op == Op::MaxAll || isRowReduction(op); }
 const char* opName(Op op);
 
 struct OpRecord
@@ -41,6 +45,7 @@ struct OpRecord
     View       in[2];
     View       out;
     ScalarBits scalar{};       // Fill: the value, already converted to out.dtype
+    uint64_t   rowCols = 0;    // SumRows / MaxRows: length of a row of in[0]
 };
 
 // How element i of the iteration space maps to an element of a view.
@@ -71,6 +76,10 @@ struct KernelNode
 struct KernelLoad  { View view; Access access; };
 struct KernelReduce { uint16_t node; bool isMax; uint8_t dtype; View out; };   // out: the one-element result
 struct KernelStore { View view; Access access; uint16_t node; };
+// One result per row of the kernel's [count / rowCols, rowCols] iteration space: out[row] = fold(initial, node over the row).
+// The initial value is what the destination holds, or - when the destination was filled by a pending op that nobody
+// else reads - that fill's value as a kernel scalar (the fill itself is then never stored).
+struct KernelRowReduce { uint16_t node; bool isMax; uint8_t dtype; View out; bool initImmediate; uint16_t scalarIndex; };
 
 // One fused kernel: loads, straight-line nodes, stores, all over `count` elements.
 struct KernelSpec
@@ -80,6 +89,8 @@ struct KernelSpec
     std::vector<KernelNode>  nodes;
     std::vector<KernelStore> stores;
     std::vector<KernelReduce> reductions;  // folded over all `count` elements of a node
+    std::vector<KernelRowReduce> rowReductions;   // folded over each row of rowCols elements
+    uint64_t                 rowCols = 0;  // non-zero: the kernel walks the elements row by row (one warp or CTA per row)
     std::vector<ScalarBits>  scalars;      // runtime values; not part of the kernel's identity
     std::vector<uint8_t>     scalarDtypes;
     uint32_t                 opsFolded = 0;    // recorded ops this kernel stands for

@@ -236,7 +236,8 @@ def test_host_operands_of_matmul_reduce_and_binary_ops(b200, ref):
         assert normwise(out.numpy(), want) <= 1e-5, f"matmul {m}x{k}x{n} from host operands"
         # mixed: one operand on the device
         out2 = TensorValue.empty((m, n), b200)
-        b200.matmul(TensorValue.from_numpy(a, b200).deviceParams(), pb, out2.deviceParams())
+        on_device = TensorValue.from_numpy(a, b200)                    # kept alive across the call
+        b200.matmul(on_device.deviceParams(), pb, out2.deviceParams())
         assert normwise(out2.numpy(), want) <= 1e-5
 
     x, px = host(rng.normal(0, 1, (300, 500)))
@@ -288,5 +289,6 @@ def test_index_ops_skip_and_report_out_of_range_indices(b200):
     every_other = TensorValue.from_numpy(np.array([0, 99, 2, 99, 4, 99]), b200, I32)
     view = TensorValue(every_other.storage, (3,), (2,), 0, I32, b200)
     sel = TensorValue.empty((3, 5), b200)
-    b200.indexSelect(TensorValue.from_numpy(x, b200).deviceParams(), sel.deviceParams(), view.deviceParams(), 0)
+    source = TensorValue.from_numpy(x, b200)
+    b200.indexSelect(source.deviceParams(), sel.deviceParams(), view.deviceParams(), 0)
     assert np.array_equal(sel.numpy(), x[[0, 2, 4]])
