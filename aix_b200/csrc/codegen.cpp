@@ -222,6 +222,7 @@ template <class D> struct Red<D, false>
     static __device__ __forceinline__ W widen(A a) { return (W)a; }
     static __device__ __forceinline__ W identity() { return (W)0; }
     static __device__ __forceinline__ W merge(W a, W b) { return a + b; }
+    static __device__ __forceinline__ W lift(S s) { return (W)(A)D::ld(s); }
     static __device__ __forceinline__ S finish(W w)
     {
         if constexpr (D::kind == 0 && D::id == 0) return w;
@@ -240,6 +241,7 @@ template <class D> struct Red<D, true>
     static __device__ __forceinline__ W widen(A a) { return (W)a; }
     static __device__ __forceinline__ W identity() { return (W)red_lowest<D>(); }
     static __device__ __forceinline__ W merge(W a, W b) { return b > a ? b : a; }
+    static __device__ __forceinline__ W lift(S s) { return (W)D::ld(s); }
     static __device__ __forceinline__ S finish(W w) { return D::st((A)w); }
 };
 template <class W> __device__ __forceinline__ W red_shfl(W v, int d)
@@ -262,6 +264,19 @@ template <class R> __device__ __forceinline__ typename R::W red_block(typename R
         for (int d = 16; d > 0; d >>= 1) v = R::merge(v, red_shfl<typename R::W>(v, d));
     }
     return v;
+}
+// Fold of one value per thread over a row's owners: the lanes of a warp (shuffles only) or the threads of the CTA.
+// The result is valid in lane 0 / thread 0.
+template <class R, bool WARP> __device__ __forceinline__ typename R::W row_fold(typename R::A acc, u64_t* smem)
+{
+    typename R::W w = R::widen(acc);
+    if constexpr (WARP)
+    {
+        #pragma unroll
+        for (int d = 16; d > 0; d >>= 1) w = R::merge(w, red_shfl<typename R::W>(w, d));
+        return w;
+    }
+    else return red_block<R>(w, (typename R::W*)smem);
 }
 template <class R> __device__ __forceinline__ void red_finish(typename R::A acc, u64_t* partials, unsigned* ticket, typename R::S* out)
 {
@@ -333,6 +348,13 @@ KernelVariant chooseVariant(const KernelSpec& spec)
         maxSpan = std::max(maxSpan, s.view.span());
     }
     v.vec = static_cast<int>(std::max<size_t>(1, std::min<size_t>(16 / minSize, 64 / maxSize)));
+    v.rowMode = spec.rowCols != 0;
+    if (v.rowMode)
+    {
+        if (spec.rowCols % static_cast<uint64_t>(v.vec) != 0) v.vec = 1;      // rows must start on a pack boundary
+        const uint64_t rows = spec.count / spec.rowCols;
+        v.warpPerRow = spec.rowCols * maxSize <= 65536 && rows >= 2048;
+    }
     // Packed two-per-register arithmetic needs one 16-bit float type throughout the kernel.
     {
         int common = -1;
@@ -352,8 +374,9 @@ KernelVariant chooseVariant(const KernelSpec& spec)
         {
             case Access::Dense:    fast = aligned(l.view, packBytes(l.view.dtype, v.vec)); break;
             case Access::Scalar:   fast = true; break;
-            case Access::RowBcast: fast = (l.view.shape[1] % v.vec == 0) && aligned(l.view, packBytes(l.view.dtype, v.vec)); break;
-            case Access::ColBcast: fast = (l.view.shape[1] % v.vec == 0); break;
+            case Access::RowBcast: fast = (l.view.shape[1] % v.vec == 0) && aligned(l.view, packBytes(l.view.dtype, v.vec)) &&
+                                          (!v.rowMode || l.view.shape[1] == spec.rowCols); break;
+            case Access::ColBcast: fast = (l.view.shape[1] % v.vec == 0) && (!v.rowMode || l.view.shape[1] == spec.rowCols); break;
             default: break;
         }
         if (fast) v.fastLoads |= (1u << i);
@@ -399,6 +422,11 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
         key += "R";
         for (const auto& r : spec.reductions) { put(r.node); put(r.isMax); put(r.dtype); }
     }
+    if (variant.rowMode)
+    {
+        key += "W"; put(variant.warpPerRow);
+        for (const auto& r : spec.rowReductions) { put(r.node); put(r.isMax); put(r.dtype); put(r.initImmediate); put(r.scalarIndex); }
+    }
     return key;
 }
 
@@ -432,6 +460,11 @@ std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVa
     {
         for (const auto& r : spec.reductions) a.push_back(reinterpret_cast<uint64_t>(r.out.firstByte()));
         a.push_back(reinterpret_cast<uint64_t>(scratch));
+    }
+    if (variant.rowMode)
+    {
+        a.push_back(spec.rowCols);
+        for (const auto& r : spec.rowReductions) a.push_back(reinterpret_cast<uint64_t>(r.out.firstByte()));
     }
     return a;
 }
@@ -471,6 +504,9 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
     slot += nR;
     const size_t slotScratch = slot;
     if (nR) ++slot;
+    const size_t nRR = spec.rowReductions.size();
+    const size_t slotRowCols = slot;
+    if (variant.rowMode) slot += 1 + nRR;
     o << "struct Params { u64_t a[" << std::max<size_t>(slot, 1) << "]; };\n\n";
 
     auto T = [&](uint8_t dt) { return std::string(kTraits[dt]); };
@@ -589,6 +625,194 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         for (size_t r = 0; r < nR; ++r)
             os << indent << "racc" << r << " = " << redType(r) << "::step(racc" << r << ", v" << spec.reductions[r].node << ");\n";
     };
+
+    // ---- row mode: one warp or one CTA per row of rowCols elements, per-row folds at the end of every row ------------
+    if (variant.rowMode)
+    {
+        const bool RW = variant.warpPerRow;
+        const int lanes = RW ? 32 : B;
+        auto rowRedType = [&](size_t r) { return "Red<" + T(spec.rowReductions[r].dtype) + ", " + (spec.rowReductions[r].isMax ? "true" : "false") + ">"; };
+        auto emitRowSteps = [&](std::ostream& os, const std::string& indent)
+        {
+            for (size_t r = 0; r < nRR; ++r)
+                os << indent << "rr" << r << " = " << rowRedType(r) << "::step(rr" << r << ", v" << spec.rowReductions[r].node << ");\n";
+        };
+        o << "    const idx_t cols = (idx_t)" << arg(slotRowCols) << ";\n";
+        o << "    const idx_t rows = n / cols;\n";
+        o << "    const int lane = " << (RW ? "threadIdx.x & 31" : "threadIdx.x") << ";\n";
+        o << "    __shared__ u64_t rsm[32];\n";
+        o << "    for (idx_t row0 = (idx_t)blockIdx.x * " << (RW ? B / 32 : 1) << "; row0 < rows; row0 += (idx_t)gridDim.x * " << (RW ? B / 32 : 1) << ")\n    {\n";
+        o << "        const idx_t row = row0 + " << (RW ? "(threadIdx.x >> 5)" : "0") << ";\n";
+        for (size_t r = 0; r < nRR; ++r)
+            o << "        " << rowRedType(r) << "::A rr" << r << " = " << rowRedType(r) << "::init();\n";
+        o << "        if (row < rows)\n        {\n";
+        o << "            const idx_t rowBase = row * cols;\n";
+        for (size_t i = 0; i < nL; ++i)
+            if (lp[i] == Path::ColWide)
+                o << "            const " << T(spec.loads[i].view.dtype) << "::S xc" << i << " = l" << i << "[row * (idx_t)" << arg(loadAux[i] + 1) << "];\n";
+        if (E > 1)
+        {
+            o << "            const idx_t cpk = cols / " << E << ";\n";
+            o << "            for (idx_t cp = lane; cp < cpk; cp += " << (lanes * U) << ")\n            {\n";
+            o << "                bool ok[" << U << "];\n";
+            for (size_t i = 0; i < nL; ++i)
+                if (lp[i] != Path::Scalar && lp[i] != Path::ColWide)
+                    o << "                Pack<" << T(spec.loads[i].view.dtype) << "::S, " << E << "> x" << i << "[" << U << "];\n";
+            o << "                #pragma unroll\n                for (int u = 0; u < " << U << "; ++u)\n                {\n";
+            o << "                    const idx_t q = cp + (idx_t)u * " << lanes << ";\n";
+            o << "                    ok[u] = q < cpk;\n";
+            o << "                    if (!ok[u]) continue;\n";
+            for (size_t i = 0; i < nL; ++i)
+            {
+                const std::string S = T(spec.loads[i].view.dtype) + "::S";
+                switch (lp[i])
+                {
+                    case Path::DenseWide:
+                        o << "                    x" << i << "[u] = *(const Pack<" << S << ", " << E << ">*)(l" << i << " + rowBase + q * " << E << ");\n";
+                        break;
+                    case Path::DenseElem:
+                        o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e) x" << i << "[u].v[e] = l" << i << "[rowBase + q * " << E << " + e];\n";
+                        break;
+                    case Path::RowWide:
+                        o << "                    x" << i << "[u] = *(const Pack<" << S << ", " << E << ">*)(l" << i << " + q * " << E << ");\n";
+                        break;
+                    case Path::General:
+                        o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e)\n                    {\n";
+                        emitGeneralOffset(o, "off_", "(rowBase + q * " + std::to_string(E) + " + e)", spec.loads[i].view.rank, loadAux[i], "                        ");
+                        o << "                        x" << i << "[u].v[e] = l" << i << "[off_];\n                    }\n";
+                        break;
+                    default: break;
+                }
+            }
+            o << "                }\n";
+            o << "                #pragma unroll\n                for (int u = 0; u < " << U << "; ++u)\n                {\n";
+            o << "                    if (!ok[u]) continue;\n";
+            o << "                    const idx_t q = cp + (idx_t)u * " << lanes << ";\n";
+            for (size_t i = 0; i < nS; ++i)
+                o << "                    Pack<" << T(spec.stores[i].view.dtype) << "::S, " << E << "> y" << i << ";\n";
+            if (variant.packed16)
+            {
+                o << "                    #pragma unroll\n                    for (int e = 0; e < " << (E / 2) << "; ++e)\n                    {\n";
+                emitNodesPacked(o, "                        ", [&](size_t l) -> std::string
+                {
+                    const std::string P = "P2<" + T(spec.loads[l].view.dtype) + ">::";
+                    if (lp[l] == Path::Scalar) return P + "splat(x" + std::to_string(l) + "s)";
+                    if (lp[l] == Path::ColWide) return P + "splat(xc" + std::to_string(l) + ")";
+                    return P + "join(x" + std::to_string(l) + "[u].v[2 * e], x" + std::to_string(l) + "[u].v[2 * e + 1])";
+                });
+                for (size_t i = 0; i < nS; ++i)
+                    o << "                        y" << i << ".v[2 * e] = (u16_t)(v" << spec.stores[i].node << " & 0xffffu); y" << i
+                      << ".v[2 * e + 1] = (u16_t)(v" << spec.stores[i].node << " >> 16);\n";
+                for (size_t r = 0; r < nR; ++r)
+                {
+                    const std::string P = "P2<" + T(spec.reductions[r].dtype) + ">::", v = "v" + std::to_string(spec.reductions[r].node);
+                    o << "                        racc" << r << " = " << redType(r) << "::step(" << redType(r) << "::step(racc" << r << ", " << P << "lo(" << v
+                      << ")), " << P << "hi(" << v << "));\n";
+                }
+                for (size_t r = 0; r < nRR; ++r)
+                {
+                    const std::string P = "P2<" + T(spec.rowReductions[r].dtype) + ">::", v = "v" + std::to_string(spec.rowReductions[r].node);
+                    o << "                        rr" << r << " = " << rowRedType(r) << "::step(" << rowRedType(r) << "::step(rr" << r << ", " << P << "lo(" << v
+                      << ")), " << P << "hi(" << v << "));\n";
+                }
+                o << "                    }\n";
+            }
+            else
+            {
+                o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e)\n                    {\n";
+                emitNodes(o, "                        ", [&](size_t l) -> std::string
+                {
+                    if (lp[l] == Path::Scalar) return "x" + std::to_string(l) + "s";
+                    if (lp[l] == Path::ColWide) return "xc" + std::to_string(l);
+                    return "x" + std::to_string(l) + "[u].v[e]";
+                });
+                for (size_t i = 0; i < nS; ++i)
+                    o << "                        y" << i << ".v[e] = " << T(spec.stores[i].view.dtype) << "::st(" << "v" << spec.stores[i].node << ");\n";
+                emitReduceSteps(o, "                        ");
+                emitRowSteps(o, "                        ");
+                o << "                    }\n";
+            }
+            for (size_t i = 0; i < nS; ++i)
+            {
+                const std::string S = T(spec.stores[i].view.dtype) + "::S";
+                if (sp[i] == Path::DenseWide)
+                    o << "                    *(Pack<" << S << ", " << E << ">*)(s" << i << " + rowBase + q * " << E << ") = y" << i << ";\n";
+                else if (sp[i] == Path::DenseElem)
+                    o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e) s" << i << "[rowBase + q * " << E << " + e] = y" << i << ".v[e];\n";
+                else
+                {
+                    o << "                    #pragma unroll\n                    for (int e = 0; e < " << E << "; ++e)\n                    {\n";
+                    emitGeneralOffset(o, "off_", "(rowBase + q * " + std::to_string(E) + " + e)", spec.stores[i].view.rank, storeAux[i], "                        ");
+                    o << "                        s" << i << "[off_] = y" << i << ".v[e];\n                    }\n";
+                }
+            }
+            o << "                }\n            }\n";
+        }
+        else
+        {
+            o << "            for (idx_t c = lane; c < cols; c += " << lanes << ")\n            {\n";
+            o << "                const idx_t i = rowBase + c;\n";
+            for (size_t l = 0; l < nL; ++l)
+            {
+                const View& v = spec.loads[l].view;
+                const std::string S = T(v.dtype) + "::S";
+                switch (lp[l])
+                {
+                    case Path::Scalar: case Path::ColWide: break;
+                    case Path::DenseWide: case Path::DenseElem:
+                        o << "                const " << S << " t" << l << " = l" << l << "[i];\n";
+                        break;
+                    case Path::RowWide:
+                        o << "                const " << S << " t" << l << " = l" << l << "[c];\n";
+                        break;
+                    case Path::General:
+                        emitGeneralOffset(o, "off" + std::to_string(l), "i", v.rank, loadAux[l], "                ");
+                        o << "                const " << S << " t" << l << " = l" << l << "[off" << l << "];\n";
+                        break;
+                }
+            }
+            emitNodes(o, "                ", [&](size_t l) -> std::string
+            {
+                if (lp[l] == Path::Scalar) return "x" + std::to_string(l) + "s";
+                if (lp[l] == Path::ColWide) return "xc" + std::to_string(l);
+                return "t" + std::to_string(l);
+            });
+            for (size_t i = 0; i < nS; ++i)
+            {
+                const std::string D = T(spec.stores[i].view.dtype);
+                if (sp[i] == Path::General)
+                {
+                    emitGeneralOffset(o, "so" + std::to_string(i), "i", spec.stores[i].view.rank, storeAux[i], "                ");
+                    o << "                s" << i << "[so" << i << "] = " << D << "::st(v" << spec.stores[i].node << ");\n";
+                }
+                else
+                    o << "                s" << i << "[i] = " << D << "::st(v" << spec.stores[i].node << ");\n";
+            }
+            emitReduceSteps(o, "                ");
+            emitRowSteps(o, "                ");
+            o << "            }\n";
+        }
+        o << "        }\n";
+        // per-row folds: every thread of the block takes part (the CTA-wide fold synchronises the block)
+        for (size_t r = 0; r < nRR; ++r)
+        {
+            const KernelRowReduce& rr = spec.rowReductions[r];
+            const std::string S = T(rr.dtype) + "::S";
+            o << "        {\n            const " << rowRedType(r) << "::W w_ = row_fold<" << rowRedType(r) << ", " << (RW ? "true" : "false") << ">(rr" << r << ", rsm);\n";
+            o << "            if (lane == 0 && row < rows)\n            {\n";
+            o << "                " << S << "* const o_ = (" << S << "*)" << arg(slotRowCols + 1 + r) << " + row;\n";
+            o << "                o_[0] = " << rowRedType(r) << "::finish(" << rowRedType(r) << "::merge(" << rowRedType(r) << "::lift("
+              << (rr.initImmediate ? "sc" + std::to_string(rr.scalarIndex) : std::string("o_[0]")) << "), w_));\n";
+            o << "            }\n        }\n";
+        }
+        o << "    }\n";
+        for (size_t r = 0; r < nR; ++r)
+            o << "    red_finish<" << redType(r) << " >(racc" << r << ", (u64_t*)(" << arg(slotScratch) << " + " << kReductionPartialsOffset
+              << "ull + " << (r * kReductionMaxBlocks * 8) << "ull), (unsigned*)(" << arg(slotScratch) << " + " << (4 * (r + 1)) << "ull), ("
+              << T(spec.reductions[r].dtype) << "::S*)" << arg(slotReductions + r) << ");\n";
+        o << "}\n";
+        return o.str();
+    }
 
     // ---- main loop: U packs of E elements per thread and iteration ----------------------------------------------
     if (E > 1)

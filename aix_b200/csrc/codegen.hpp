@@ -29,6 +29,8 @@ struct KernelVariant
     int      vec = 1;          // elements per pack (16 bytes of the narrowest element type)
     bool     packed16 = false; // one f16/bf16 type throughout: two elements per register on the packed pipes
     bool     index64 = false;  // element count does not fit 32 bits
+    bool     rowMode = false;  // the kernel walks [count / rowCols, rowCols] row by row and folds per-row results
+    bool     warpPerRow = false; // rowMode: one warp per row (short rows, many of them) instead of one CTA per row
     uint32_t fastLoads = 0;    // bit l: load l may use the wide / hoisted path
     uint32_t fastStores = 0;   // bit s: store s may use 128-bit stores
 };

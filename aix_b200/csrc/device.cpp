@@ -94,6 +94,8 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_codegen.unroll = std::max(1, std::min(8, envInt("AIXB200_EW_UNROLL", 2)));
     m_wavesPerSm = std::max(1, envInt("AIXB200_EW_WAVES", 8));
     m_fuseReductions = envInt("AIXB200_FUSE_REDUCTIONS", 1) != 0;
+    m_fuseRowReductions = envInt("AIXB200_FUSE_ROW_REDUCTIONS", 1) != 0;
+    m_termCacheEnabled = envInt("AIXB200_GEMM_TERM_CACHE", 1) != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -223,6 +225,70 @@ void* Device::temporary(size_t bytes)
     return p;
 }
 
+// ---- prepared f32 matmul operands (see device.hpp) --------------------------------------------------------------------
+const Device::PreparedTerms* Device::findPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch)
+{
+    for (PreparedTerms& e : m_preparedTerms)
+        if (e.lo == base && e.rows == rows && e.cols == cols && e.pitch == pitch) { e.stamp = ++m_preparedStamp; ++m_stats.reserved[0]; return &e; }
+    return nullptr;
+}
+
+const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch)
+{
+    constexpr uint32_t kSlots = 1024;
+    if (!m_termSlots)
+    {
+        m_termSlots = m_allocator->allocate(kSlots * sizeof(uint32_t));
+        for (uint32_t i = kSlots; i-- > 0;) m_freeTermSlots.push_back(i);
+    }
+    PreparedTerms e{};
+    e.lo = static_cast<const char*>(base);
+    e.hi = e.lo + ((rows - 1) * pitch + cols) * sizeof(float);
+    e.rows = rows; e.cols = cols; e.pitch = pitch;
+    e.paddedCols = (cols + 127) & ~uint64_t(127);
+    e.bytes = static_cast<size_t>(rows) * 2 * e.paddedCols * sizeof(uint16_t);
+    // budget: an eighth of the device memory, oldest entries go first
+    const uint64_t budget = std::max<uint64_t>(m_totalMemory / 8, e.bytes);
+    while (!m_preparedTerms.empty() && (m_preparedBytes + e.bytes > budget || m_freeTermSlots.empty()))
+    {
+        size_t oldest = 0;
+        for (size_t i = 1; i < m_preparedTerms.size(); ++i)
+            if (m_preparedTerms[i].stamp < m_preparedTerms[oldest].stamp) oldest = i;
+        const PreparedTerms& victim = m_preparedTerms[oldest];
+        invalidatePreparedTerms(victim.lo, victim.hi);
+    }
+    e.terms = m_allocator->allocate(e.bytes + 16);
+    e.slot = m_freeTermSlots.back();
+    m_freeTermSlots.pop_back();
+    e.stamp = ++m_preparedStamp;
+    m_preparedBytes += e.bytes;
+    ++m_stats.reserved[1];
+    m_preparedTerms.push_back(e);
+    return &m_preparedTerms.back();
+}
+
+// Every kernel that read a prepared form is already enqueued when this runs (matmuls launch at call time), so the block
+// can go back to the allocator at once: reuse is ordered behind those kernels on the device's stream.
+void Device::invalidatePreparedTerms(const void* lo, const void* hi)
+{
+    if (m_preparedTerms.empty()) return;
+    const char* first = static_cast<const char*>(lo);
+    const char* last = static_cast<const char*>(hi);
+    for (size_t i = 0; i < m_preparedTerms.size();)
+    {
+        PreparedTerms& e = m_preparedTerms[i];
+        if (first < e.hi && e.lo < last)
+        {
+            m_allocator->release(e.terms);
+            m_freeTermSlots.push_back(e.slot);
+            m_preparedBytes -= e.bytes;
+            m_preparedTerms[i] = m_preparedTerms.back();
+            m_preparedTerms.pop_back();
+        }
+        else ++i;
+    }
+}
+
 // Staged host operands stay out of the deferred-release list while the call that staged them is still running: a flush
 // inside that call (ordering after a collective, the flush every immediate op starts with) returns deferred blocks to
 // the cache, and the call's own temporaries could then be handed the very block its operand sits in.
@@ -242,6 +308,7 @@ void Device::deallocate(void* p)
     if (!p) return;
     if (!m_allocator->owns(p)) failInvalid("deallocate: pointer was not allocated by this device");
     if (m_released.count(p)) failInvalid("deallocate: pointer was already deallocated");
+    invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p));
     if (!m_commInFlight.empty())
     {
         // a collective on the side stream may still use the block: reuse is ordered on the device's stream only
@@ -338,6 +405,7 @@ View Device::outputView(const aixb200_tensor* t, const char* what)
 {
     View v = makeView(t, what);
     if (v.size == 0 || dryRun()) return v;
+    invalidatePreparedTerms(v.firstByte(), v.endByte());       // whatever is written here, its prepared matmul form is stale
     if (!m_commInFlight.empty()) orderAfterCollectives(v);
     if (m_allocator->findBlock(v.base)) return v;
     if (isHostPointer(v.base)) failInvalid(std::string(what) + ": result must be device memory allocated by this device");
@@ -524,7 +592,7 @@ void Device::launchSpec(const KernelSpec& spec)
     const std::string key = kernelKey(spec, variant, m_codegen);
     CompiledKernel& k = getKernel(spec, variant, key);
     m_lastSource = k.source;
-    m_stats.reductions_fused += spec.reductions.size();
+    m_stats.reductions_fused += spec.reductions.size() + spec.rowReductions.size();
     if (dryRun()) { countLaunch(true); return; }
 
     std::vector<uint64_t> args = packKernelArguments(spec, variant, m_scratch);
@@ -535,6 +603,11 @@ void Device::launchSpec(const KernelSpec& spec)
     const uint64_t tailElems = variant.vec > 1 ? spec.count - nvec * variant.vec : spec.count;
     const uint64_t tailBlocks = (tailElems + block - 1) / block;
     uint64_t grid = std::max<uint64_t>(1, std::max(mainBlocks, tailBlocks));
+    if (variant.rowMode)
+    {
+        const uint64_t rows = spec.count / spec.rowCols;
+        grid = variant.warpPerRow ? (rows + block / 32 - 1) / (block / 32) : rows;
+    }
     grid = std::min<uint64_t>(grid, static_cast<uint64_t>(m_smCount) * m_wavesPerSm);
     if (!spec.reductions.empty()) grid = std::min<uint64_t>(grid, kReductionMaxBlocks);    // one scratch partial per block
     void* params[] = {args.data()};
@@ -599,6 +672,29 @@ bool Device::recordReduction(Op op, const View& src, const View& dst)
     return true;
 }
 
+// reduceTo / maxTo over the trailing dimension of a dense [rows, cols] operand whose producer is still pending: recorded,
+// so that the producing kernel folds every row while its elements are in registers (one warp or CTA per row) and the
+// operand is not read back from memory. Rows must be plentiful enough to fill the GPU that way; anything else takes the
+// stand-alone kernels.
+bool Device::recordRowReduction(bool isMax, const View& src, const View& dst, uint64_t rows, uint64_t cols)
+{
+    if (!m_limits.fusion || !m_fuseReductions || !m_fuseRowReductions) return false;
+    if (rows < static_cast<uint64_t>(m_smCount) * 4 || cols < 128 || !src.isDense() || !dst.isDense() || dst.size != rows) return false;
+    bool producerPending = false;
+    for (size_t i = m_pending.size(); i-- > 0 && !producerPending;)
+        producerPending = !isReduction(m_pending[i].op) && m_pending[i].out.sameElements(src);
+    if (!producerPending) return false;
+    OpRecord rec;
+    rec.op = isMax ? Op::MaxRows : Op::SumRows;
+    rec.numInputs = 2;
+    rec.in[0] = src;
+    rec.in[1] = dst;
+    rec.out = dst;
+    rec.rowCols = cols;
+    record(std::move(rec));
+    return true;
+}
+
 // Sum for callers that must not allocate: no staging of host inputs, no flush of recorded work (a flush may
 // compile and load a kernel), scratch in the library's static device array.
 void Device::sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r)
@@ -614,6 +710,7 @@ void Device::sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r)
         failInvalid("sum_static_scratch: input has " + std::to_string(src.size) + " elements, the static scratch variant takes at most " +
                     std::to_string(kernels::kStaticScratchMaxElements));
     if (src.size == 0) failInvalid("sum_static_scratch: empty input");
+    invalidatePreparedTerms(dst.firstByte(), dst.endByte());
     if ((!m_allocator->findBlock(src.base) && isHostPointer(src.base)) || (!m_allocator->findBlock(dst.base) && isHostPointer(dst.base)))
         failInvalid("sum_static_scratch: input and result must be device memory (host inputs would need a staging allocation)");
     // An overlapped all-reduce may still be working on the operand or the result: the device's stream waits for it, as
@@ -705,14 +802,18 @@ void Device::reduceTo(const aixb200_tensor* s, const aixb200_tensor* d, bool isM
     View src = inputView(s, what);
     View dst = outputView(d, what);
     if (src.dtype != dst.dtype) failInvalid(std::string(what) + ": element types differ");
-    flush();
-    if (dryRun() || src.size == 0) return;
+    if (src.size == 0) { flush(); return; }
     kernels::ReduceDim dims[MAX_RANK];
     // inputView may have re-based a staged host tensor: the strides are unchanged, only base/offset moved.
     int rank = classifyReduction(s, d, dims);
     uint64_t outputs = 1;
     for (int i = 0; i < rank; ++i) if (dims[i].kept) outputs *= dims[i].extent;
     if (outputs != dst.size) failInvalid(std::string(what) + ": destination shape is not a reduction of the source shape");
+    if (rank == 2 && dims[0].kept && !dims[1].kept && dims[1].stride == 1 && dims[0].stride == dims[1].extent &&
+        recordRowReduction(isMax, src, dst, dims[0].extent, dims[1].extent))
+        return;
+    flush();
+    if (dryRun()) return;
     // canonical 2-D forms need an explicit partner dimension
     kernels::ReduceDim two[2];
     const kernels::ReduceDim* use = dims;
@@ -839,6 +940,7 @@ void Device::copy(const void* src, uint32_t srcDtype, void* dst, uint32_t dstDty
     if (srcHost && srcDtype == dstDtype)
     {
         flush();                            // ops already recorded against dst must run first
+        invalidatePreparedTerms(dst, static_cast<char*>(dst) + count * ds);
         check(cudaMemcpyAsync(dst, src, count * ss, cudaMemcpyHostToDevice, m_stream), "host-to-device copy");
         m_stats.h2d_bytes += count * ss;
     }
@@ -984,6 +1086,7 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
     flush();
+    invalidatePreparedTerms(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     commWait();                 // collectives of one communicator are issued in one order on every rank
     // A scale of exactly 1/ranks on a floating type is the collective's own averaging: no extra pass over the data.
     const bool average = ncclAverages(false) && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
@@ -1007,6 +1110,7 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
     aixb200_tensor whole{};
     whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
     const View range = makeView(&whole, "all_reduce_async");
+    invalidatePreparedTerms(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     if (!m_commInFlight.empty()) orderAfterCollectives(range);       // two collectives on one buffer keep their order
     flush();
     if (!m_commStream)

@@ -58,6 +58,7 @@ public:
     void recordFill(const void* scalar, uint32_t scalarDtype, const aixb200_tensor* r);
     void recordFillMin(const aixb200_tensor* r);
     bool recordReduction(Op op, const View& src, const View& dst);
+    bool recordRowReduction(bool isMax, const View& src, const View& dst, uint64_t rows, uint64_t cols);
     void flush();
 
     // immediate ops (flush first, then launch fixed kernels)
@@ -104,6 +105,28 @@ public:
     void checkLaunch(const char* what);
     // Temporary device block that is returned to the cache after the next flush.
     void* temporary(size_t bytes);
+
+    // ---- prepared f32 matmul operands ----------------------------------------------------------------------------------
+    // The tensor-core f32 product reads every operand as two scaled fp16 terms (gemm_sm100.cu). A tensor is prepared once,
+    // in its own row-major layout [rows][2 * paddedCols] = [h0 | h1] per row, and that form serves every orientation the
+    // tensor is used in (forward, dX and dW read the same activations, weights and gradients); it is kept until any op
+    // writes into the tensor's bytes, the tensor is deallocated, or the cache outgrows its budget.
+    struct PreparedTerms
+    {
+        const char* lo; const char* hi;     // bytes of the source tensor
+        uint64_t rows, cols, pitch;         // source layout: rows x cols f32, `pitch` elements between rows
+        uint64_t paddedCols;                // multiple of 128
+        void*    terms;                     // device block of rows * 2 * paddedCols fp16
+        uint32_t slot;                      // index of the bit pattern of max|x| in the slot block
+        size_t   bytes;
+        uint64_t stamp;
+    };
+    // Returns the cached form or nullptr; `fresh` receives a new entry (terms allocated, not yet filled) when absent.
+    const PreparedTerms* findPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch);
+    const PreparedTerms* addPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch);
+    uint32_t* preparedSlot(uint32_t slot) const { return static_cast<uint32_t*>(m_termSlots) + slot; }
+    void invalidatePreparedTerms(const void* lo, const void* hi);
+    bool preparedTermsEnabled() const { return m_termCacheEnabled; }
     // Called at the top of every C-ABI entry: the host operands the previous call staged are consumed by work that is
     // recorded or enqueued by now, so their blocks may follow the usual deferred-release path.
     void beginCall() { if (!m_staged.empty()) retireStaged(); }
@@ -138,6 +161,7 @@ private:
     CodegenOptions m_codegen;
     int            m_wavesPerSm = 8;
     bool           m_fuseReductions = true;     // AIXB200_FUSE_REDUCTIONS=0 keeps full reductions as kernels of their own
+    bool           m_fuseRowReductions = true;  // AIXB200_FUSE_ROW_REDUCTIONS=0 does the same for reduceTo / maxTo over rows
 
     std::unordered_map<std::string, CompiledKernel> m_kernels;
     std::string m_cacheDir;
@@ -150,6 +174,11 @@ private:
     std::vector<CommInFlight> m_commInFlight;   // collectives started on the side stream and not yet joined
     std::vector<cudaEvent_t>  m_commEventPool;
     void orderAfterCollectives(const View& v);  // the device's stream waits for in-flight collectives that touch the view
+    std::vector<PreparedTerms> m_preparedTerms;
+    std::vector<uint32_t> m_freeTermSlots;
+    void*    m_termSlots = nullptr;
+    uint64_t m_preparedBytes = 0, m_preparedStamp = 0;
+    bool     m_termCacheEnabled = true;     // AIXB200_GEMM_TERM_CACHE=0: every matmul prepares its operands afresh
     bool m_inFlush = false;
     bool m_checkErrorWord = false;
 };

@@ -53,6 +53,9 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
     std::vector<size_t> groupOf(n, 0);
     std::vector<std::array<InputBinding, 2>> bindings(n);
     std::vector<Group> groups;
+    // A fill of a row reduction's destination whose value the reduction takes as a kernel scalar: it is never stored
+    // (the reduction writes every element of it) and orders nothing.
+    std::vector<char> superseded(n, 0);
 
     // Byte range every view touches, computed once: the hazard tests below compare ranges, not base pointers (two
     // descriptors may reach one buffer through different bases, e.g. an interior pointer).
@@ -78,6 +81,31 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             const View& in = rj.in[k];
             InputBinding bind;
             bool shadowed = false;      // a more recent writer touches part of the view through a different view
+            if (k == 1 && isRowReduction(rj.op))
+            {
+                // The destination as the reduction's initial value. The usual caller has just filled it (zero, or the
+                // lowest value for a maximum): when that fill is still pending, defines every element and nobody has
+                // read the destination since, the value travels as a kernel scalar and the fill is dropped. Anything
+                // else is read from memory, after the kernels of all pending writers.
+                size_t writer = n;
+                for (size_t i = j; i-- > 0 && writer == n;)
+                    if (meet(outRange[i], inRange[j][1])) writer = i;
+                bool immediate = limits.fusion && writer != n && ops[writer].op == Op::Fill && ops[writer].out.sameElements(in);
+                for (size_t i = writer + 1; immediate && i < j; ++i)
+                    for (int q = 0; q < ops[i].numInputs; ++q)
+                        if (meet(inRange[i][q], inRange[j][1])) immediate = false;
+                if (immediate)
+                {
+                    bind.kind = InputBinding::ImmediateFill;
+                    bind.producer = writer;
+                    superseded[writer] = 1;
+                }
+                else
+                    for (size_t i = 0; i < j; ++i)
+                        if (meet(outRange[i], inRange[j][1])) minGroup = std::max(minGroup, groupOf[i] + 1);
+                bindings[j][k] = bind;
+                continue;
+            }
             for (size_t i = j; i-- > 0;)
             {
                 const View& w = ops[i].out;
@@ -120,7 +148,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                 if (!meet(inRange[i][k], outRange[j])) continue;
                 minGroup = std::max(minGroup, (r.sameElements(rj.out) && !jReduces) ? groupOf[i] : groupOf[i] + 1);
             }
-            if (meet(outRange[i], outRange[j]))
+            if (meet(outRange[i], outRange[j]) && !(superseded[i] && bindings[j][1].kind == InputBinding::ImmediateFill && bindings[j][1].producer == i))
                 minGroup = std::max(minGroup, (ri.out.sameElements(rj.out) && !jReduces && !isReduction(ri.op)) ? groupOf[i] : groupOf[i] + 1);
         }
 
@@ -134,6 +162,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 const InputBinding& b = bindings[j][k];
                 if (b.kind == InputBinding::ImmediateFill) continue;
+                if (k == 1 && isRowReduction(rj.op)) continue;      // the destination is read by one thread per row, not as an operand
                 if (b.kind == InputBinding::Producer && groupOf[b.producer] == g) continue;
                 bool known = false;
                 for (const View& v : groups[g].loads) if (v.sameElements(rj.in[k])) { known = true; break; }
@@ -149,6 +178,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 if (groups[g].count != count || groups[g].ops.size() + 2 > limits.maxNodesPerKernel) continue;
                 if (jReduces && groups[g].reductions + 1 > limits.maxReductionsPerKernel) continue;
+                if (isRowReduction(rj.op) && groups[g].rowCols != 0 && groups[g].rowCols != rj.rowCols) continue;
                 if (groups[g].loads.size() + groups[g].liveOutputs + newLoads(g, nullptr) + (liveOutput ? 1 : 0) > limits.maxTensorsPerKernel) continue;
                 chosen = g;
                 break;
@@ -164,6 +194,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
         for (const View* v : added) groups[chosen].loads.push_back(*v);
         groups[chosen].liveOutputs += liveOutput ? 1 : 0;
         groups[chosen].reductions += jReduces ? 1 : 0;
+        if (isRowReduction(rj.op)) groups[chosen].rowCols = rj.rowCols;
         groups[chosen].ops.push_back(j);
         groupOf[j] = chosen;
     }
@@ -181,7 +212,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             {
                 // The reader goes to memory: every pending writer that overlaps the view must have stored by then.
                 for (size_t i = 0; i < j; ++i)
-                    if (meet(outRange[i], inRange[j][k])) readElsewhere[i] = 1;
+                    if (meet(outRange[i], inRange[j][k]) && !superseded[i]) readElsewhere[i] = 1;
             }
         }
 
@@ -224,6 +255,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
             for (int k = 0; k < r.numInputs; ++k)
             {
                 const InputBinding& b = bindings[j][k];
+                if (k == 1 && isRowReduction(r.op)) continue;       // the destination: handled with the reduction below
                 if (b.kind == InputBinding::Producer && groupOf[b.producer] == g)
                 {
                     refs[k].kind = OperandRef::Reg;
@@ -255,7 +287,23 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                     spec.nodes.push_back(copy);
                     node = static_cast<uint16_t>(spec.nodes.size() - 1);
                 }
-                spec.reductions.push_back({node, r.op == Op::MaxAll, r.in[0].dtype, r.out});
+                if (isRowReduction(r.op))
+                {
+                    KernelRowReduce rr{node, r.op == Op::MaxRows, r.in[0].dtype, r.out, false, 0};
+                    if (bindings[j][1].kind == InputBinding::ImmediateFill)
+                    {
+                        const OpRecord& fill = ops[bindings[j][1].producer];
+                        rr.initImmediate = true;
+                        rr.scalarIndex = static_cast<uint16_t>(spec.scalars.size());
+                        spec.scalars.push_back(fill.scalar);
+                        spec.scalarDtypes.push_back(fill.out.dtype);
+                        ++spec.fillsAbsorbed;
+                    }
+                    spec.rowReductions.push_back(rr);
+                    spec.rowCols = r.rowCols;
+                }
+                else
+                    spec.reductions.push_back({node, r.op == Op::MaxAll, r.in[0].dtype, r.out});
                 continue;
             }
             if (r.op == Op::Fill)
@@ -280,7 +328,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                 overwrittenLater = ops[grp.ops[later]].out.sameElements(r.out);
 
             const bool alive = released.count(r.out.base) == 0;
-            const bool store = readElsewhere[j] || (alive && !overwrittenLater);
+            const bool store = readElsewhere[j] || (alive && !overwrittenLater && !superseded[j]);
             if (store)
             {
                 // Replace an earlier store of this kernel to the same elements: only the last value must land.
@@ -299,7 +347,7 @@ std::vector<KernelSpec> planKernels(const std::vector<OpRecord>& ops, const std:
                 if (r.op == Op::Fill) ++spec.fillsAbsorbed;
             }
         }
-        if (!spec.stores.empty() || !spec.reductions.empty()) kernels.push_back(std::move(spec));
+        if (!spec.stores.empty() || !spec.reductions.empty() || !spec.rowReductions.empty()) kernels.push_back(std::move(spec));
     }
     return kernels;
 }

@@ -55,6 +55,20 @@ def measure_reductions(dev, hbm_peak, rows=8192, cols=8192):
 
     y = relu(x * g + b)
     dev.synchronize()
+
+    def whole():
+        # configuration 1 exactly as the API issues it: the device folds the row sums, the row maxima and the global sum
+        # into the kernel that produces y (x read once, y written once); only the scalar division of the mean remains
+        yy = relu(x * g + b)
+        holder["all"] = (yy, yy.sum(1), yy.max(1), yy.mean())
+
+    api_bytes = 5 * n * 2 + 2 * cols * 2            # y written + read by each of the three reductions, x read: 640 MiB
+    moved_bytes = 2 * n * 2 + 2 * cols * 2          # what the fused form has to move: x in, y out
+    med, host_ms = _time(dev, whole)
+    out["config 1 whole (y, row sum, row max, mean) bf16"] = {
+        "ms": med, "GB/s_of_API_bytes": api_bytes / (med * 1e-3) / 1e9, "GB/s_of_bytes_moved": moved_bytes / (med * 1e-3) / 1e9,
+        "frac_of_measured_hbm_on_bytes_moved": moved_bytes / (med * 1e-3) / 1e9 / hbm_peak, "api_bytes": api_bytes,
+        "bytes_moved": moved_bytes, "host_ms_per_call": host_ms}
     cases = {
         "relu(x*g+bias) bf16 [fused, y written]": (lambda: holder.__setitem__("y", relu(x * g + b)), 2 * n * 2 + 2 * cols * 2),
         "row sum bf16 (reduceTo)": (lambda: holder.__setitem__("s", y.sum(1)), n * 2),

@@ -240,3 +240,83 @@ def test_fused_reduction_sees_the_values_at_its_place_in_program_order(b200, ref
     assert_close(got[2], want[2], F32, "sum after the update", scale=scale)
     assert_close(got[3], want[3], F32, "updated tensor")
     assert float(got[4]) == 3500.0 == float(want[4])
+
+
+# ---- reduceTo / maxTo over rows folded into the producing kernel ------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [F32, BF16, F16, F64, I32, I16, U8], ids=lambda d: DTYPE_NAMES[d])
+@pytest.mark.parametrize("shape", [(1000, 1000), (700, 1001), (4096, 256), (2500, 130)], ids=str)
+def test_row_reductions_fused_behind_their_producer(b200, ref, dtype, shape):
+    """`y.sum(1)`, `y.max(1)` and `y.sum()` with y's producer still pending: one generated kernel walks y row by row (a CTA
+    or a warp per row), stores it and leaves the per-row results; the fills of the destinations travel as kernel scalars.
+    Oracle: the CPU device on the same sequence (16-bit floats: reductions on the widened values, rounded once)."""
+    rng = np.random.default_rng(700 + dtype + shape[1])
+    x, g = values(rng, shape, dtype), values(rng, (shape[1],), dtype)
+    if dtype not in FLOATS:
+        x, g = x % 7, g % 5
+    before = b200.stats()
+    tx, tg = TensorValue.from_numpy(x, b200, dtype), TensorValue.from_numpy(g, b200, dtype)
+    b200.synchronize()
+    y = tx * tg + tx                                     # pending; kept alive, so it is stored as well
+    rows_sum, rows_max, total = y.sum(1), y.max(1), y.sum()
+    got_y, got_sum, got_max, got_total = y.numpy(), rows_sum.numpy(), rows_max.numpy(), total.numpy()
+    after = b200.stats()
+    assert after["reductions_fused"] - before["reductions_fused"] == 3, "row reductions were not folded into the producer"
+    assert after["fused_kernels"] - before["fused_kernels"] == 1
+
+    rx, rg = TensorValue.from_numpy(x, ref, dtype), TensorValue.from_numpy(g, ref, dtype)
+    ry = rx * rg + rx
+    want_y = ry.numpy()
+    assert_close(got_y, want_y, dtype, "y")
+    assert_close(got_max, ry.max(1).numpy(), dtype, "row max")
+    if dtype in FLOATS:
+        wide_y = ry.to(wide(dtype)) if dtype in (F16, BF16) else ry
+        scale = np.maximum(1.0, np.abs(np.asarray(want_y, dtype=np.float64)).sum(axis=1))
+        assert_close(got_sum, round_to(wide_y.sum(1).numpy(), dtype), dtype, "row sum", scale=scale)
+        exact = np.asarray(want_y, dtype=np.float64).sum()
+        bound = {F64: 1e-12, F32: 1e-5, F16: 1e-2, BF16: 1e-2}[dtype]
+        assert abs(float(got_total) - exact) <= bound * max(1.0, float(np.abs(np.asarray(want_y, dtype=np.float64)).sum()))
+    else:
+        assert_close(got_sum, ry.sum(1).numpy(), dtype, "row sum")
+        assert_close(got_total, ry.sum().numpy(), dtype, "sum")
+
+
+def test_fused_row_reduction_accumulates_into_what_the_destination_holds(b200, ref):
+    """The device contract is dst += sum(row), dst = max(dst, max(row)): a destination that holds data (not a pending
+    fill), and a fill that somebody reads before the reduction, must both be honoured by the fused form."""
+    rng = np.random.default_rng(31)
+    x = rng.normal(0, 1, (1200, 384)).astype(np.float32)
+    start = rng.normal(0, 5, (1200, 1)).astype(np.float32)
+    outs = []
+    for dev in (b200, ref):
+        t = TensorValue.from_numpy(x, dev)
+        held_sum, held_max = TensorValue.from_numpy(start, dev), TensorValue.from_numpy(start, dev)
+        dev.synchronize()
+        before = dev.stats()["reductions_fused"] if dev is b200 else 0
+        y = t * 2.0                                       # pending producer
+        dev.reduceTo(y.deviceParams(), held_sum.deviceParams())
+        dev.maxTo(y.deviceParams(), held_max.deviceParams())
+        filled = TensorValue.full(3.0, (1200, 1), dev)
+        peek = filled + 1.0                               # reads the fill before the reduction overwrites it
+        dev.reduceTo(y.deviceParams(), filled.deviceParams())
+        again = filled * 1.0                              # reads the reduction's result
+        outs.append((held_sum.numpy(), held_max.numpy(), peek.numpy(), filled.numpy(), again.numpy(), y.numpy()))
+        if dev is b200:
+            assert dev.stats()["reductions_fused"] - before == 3
+    scale = np.abs(x).sum(axis=1, keepdims=True) * 2 + 5
+    for k, what in enumerate(("sum into held data", "max into held data", "peek", "sum into a filled destination", "reader after", "y")):
+        assert_close(outs[0][k], outs[1][k], F32, what, scale=scale if k in (0, 3, 4) else None)
+    assert np.array_equal(outs[0][3], outs[0][4])
+
+
+def test_row_reduction_fusion_can_be_switched_off(b200):
+    """Layouts that do not fit (few rows, short rows, reduced leading dimension) take the stand-alone kernels."""
+    rng = np.random.default_rng(5)
+    for shape, dim in (((64, 4096), 1), ((4096, 64), 1), ((2048, 512), 0)):
+        x = rng.normal(0, 1, shape).astype(np.float32)
+        t = TensorValue.from_numpy(x, b200)
+        b200.synchronize()
+        before = b200.stats()["reductions_fused"]
+        got = (t + 1.0).sum(dim).numpy()
+        assert b200.stats()["reductions_fused"] == before
+        want = (x.astype(np.float64) + 1.0).sum(axis=dim)
+        assert np.max(np.abs(got - want)) <= 1e-5 * np.abs(x + 1).sum(axis=dim).max()
