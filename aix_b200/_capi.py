@@ -48,7 +48,8 @@ class Stats(ctypes.Structure):
         "kernel_cache_hits", "kernel_cache_misses", "nvrtc_compiles")] + [("nvrtc_ms", ctypes.c_double)] + [
         (n, ctypes.c_uint64) for n in (
         "static_kernel_launches", "total_kernel_launches", "bytes_in_use", "bytes_cached", "bytes_reserved",
-        "cuda_mallocs", "h2d_bytes", "d2h_bytes", "reductions_fused")] + [("reserved", ctypes.c_uint64 * 5)]
+        "cuda_mallocs", "h2d_bytes", "d2h_bytes", "reductions_fused", "prepared_operand_hits", "prepared_operand_builds")] + [
+        ("reserved", ctypes.c_uint64 * 3)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
@@ -98,6 +99,9 @@ SIGNATURES = {
     "aixb200_comm_init": ([_D, ctypes.c_int, ctypes.c_int, ctypes.c_void_p], ctypes.c_int),
     "aixb200_all_reduce": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
     "aixb200_all_reduce_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
+    "aixb200_reduce_scatter_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
+    "aixb200_all_gather_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32], ctypes.c_int),
+    "aixb200_comm_rank": ([_D, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
     "aixb200_comm_wait": ([_D], ctypes.c_int),
     "aixb200_comm_wait_for": ([_D, ctypes.c_void_p, _SZ], ctypes.c_int),
     "aixb200_comm_destroy": ([_D], ctypes.c_int),

@@ -232,6 +232,12 @@ int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t d
 { return guarded(dev, [&](Device& d) { d.allReduce(data, count, dtype, scale); }); }
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale)
 { return guarded(dev, [&](Device& d) { d.allReduceAsync(data, count, dtype, scale); }); }
+int aixb200_reduce_scatter_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale)
+{ return guarded(dev, [&](Device& d) { d.reduceScatterAsync(data, count, dtype, scale); }); }
+int aixb200_all_gather_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype)
+{ return guarded(dev, [&](Device& d) { d.allGatherAsync(data, count, dtype); }); }
+int aixb200_comm_rank(aixb200_device* dev, int* rank, int* nranks)
+{ return guarded(dev, [&](Device& d) { if (rank) *rank = d.commRank(); if (nranks) *nranks = d.commSize(); }); }
 int aixb200_comm_wait(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commWait(); }); }
 int aixb200_comm_wait_for(aixb200_device* dev, const void* data, size_t bytes)
 { return guarded(dev, [&](Device& d) { d.commWaitFor(data, bytes); }); }

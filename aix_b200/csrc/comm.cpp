@@ -21,6 +21,8 @@ struct NcclApi
     int (*commInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
     int (*commDestroy)(NcclComm) = nullptr;
     int (*allReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*reduceScatter)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*allGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
     const char* (*getErrorString)(int) = nullptr;
     void* handle = nullptr;
 };
@@ -41,6 +43,8 @@ NcclApi& nccl()
     api.commInitRank = reinterpret_cast<decltype(api.commInitRank)>(sym("ncclCommInitRank"));
     api.commDestroy = reinterpret_cast<decltype(api.commDestroy)>(sym("ncclCommDestroy"));
     api.allReduce = reinterpret_cast<decltype(api.allReduce)>(sym("ncclAllReduce"));
+    api.reduceScatter = reinterpret_cast<decltype(api.reduceScatter)>(sym("ncclReduceScatter"));
+    api.allGather = reinterpret_cast<decltype(api.allGather)>(sym("ncclAllGather"));
     api.getErrorString = reinterpret_cast<decltype(api.getErrorString)>(sym("ncclGetErrorString"));
     return api;
 }
@@ -76,20 +80,41 @@ Comm::~Comm()
     if (m_comm) nccl().commDestroy(m_comm);
 }
 
-void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average)
+static int ncclType(uint32_t dtype)
 {
-    int type;
     switch (dtype)
     {
-        case F64: type = kNcclDouble; break;
-        case F32: type = kNcclFloat; break;
-        case F16: type = kNcclHalf; break;
-        case BF16: type = kNcclBfloat16; break;
-        case I64: type = kNcclInt64; break;
-        case I32: type = kNcclInt32; break;
-        default: failInvalid("all_reduce: unsupported element type");
+        case F64: return kNcclDouble;
+        case F32: return kNcclFloat;
+        case F16: return kNcclHalf;
+        case BF16: return kNcclBfloat16;
+        case I64: return kNcclInt64;
+        case I32: return kNcclInt32;
+        default: failInvalid("collective: unsupported element type");
     }
-    checkNccl(nccl().allReduce(data, data, count, type, average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclAllReduce");
+}
+
+void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average)
+{
+    checkNccl(nccl().allReduce(data, data, count, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclAllReduce");
+}
+
+// In place: `data` holds count elements on every rank, count a multiple of the number of ranks; afterwards slice
+// [rank * count / ranks, (rank + 1) * count / ranks) of this rank's buffer holds the sum (NCCL's in-place form: the
+// receive buffer is the rank's own slice of the send buffer).
+void Comm::reduceScatterSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average)
+{
+    const size_t slice = count / static_cast<size_t>(m_nranks);
+    char* own = static_cast<char*>(data) + static_cast<size_t>(m_rank) * slice * dtypeSize(dtype);
+    checkNccl(nccl().reduceScatter(data, own, slice, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclReduceScatter");
+}
+
+// In place: every rank contributes its own slice of `data` and receives all the others'.
+void Comm::allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream)
+{
+    const size_t slice = count / static_cast<size_t>(m_nranks);
+    const char* own = static_cast<const char*>(data) + static_cast<size_t>(m_rank) * slice * dtypeSize(dtype);
+    checkNccl(nccl().allGather(own, data, slice, ncclType(dtype), m_comm, stream), "ncclAllGather");
 }
 
 }   // namespace aixb200

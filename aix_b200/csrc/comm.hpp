@@ -18,6 +18,8 @@ public:
     ~Comm();
     // Sum over the ranks; with `average` the sum is divided by the number of ranks inside the collective.
     void allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average = false);
+    void reduceScatterSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average = false);
+    void allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream);
     int rank() const { return m_rank; }
     int size() const { return m_nranks; }
 

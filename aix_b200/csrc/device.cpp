@@ -229,7 +229,7 @@ void* Device::temporary(size_t bytes)
 const Device::PreparedTerms* Device::findPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch)
 {
     for (PreparedTerms& e : m_preparedTerms)
-        if (e.lo == base && e.rows == rows && e.cols == cols && e.pitch == pitch) { e.stamp = ++m_preparedStamp; ++m_stats.reserved[0]; return &e; }
+        if (e.lo == base && e.rows == rows && e.cols == cols && e.pitch == pitch) { e.stamp = ++m_preparedStamp; ++m_stats.prepared_operand_hits; return &e; }
     return nullptr;
 }
 
@@ -254,7 +254,8 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
         size_t oldest = 0;
         for (size_t i = 1; i < m_preparedTerms.size(); ++i)
             if (m_preparedTerms[i].stamp < m_preparedTerms[oldest].stamp) oldest = i;
-        const PreparedTerms& victim = m_preparedTerms[oldest];
+        const PreparedTerms victim = m_preparedTerms[oldest];
+        if (victim.stamp == m_preparedStamp) break;         // the other operand of the matmul being launched: never evicted
         invalidatePreparedTerms(victim.lo, victim.hi);
     }
     e.terms = m_allocator->allocate(e.bytes + 16);
@@ -262,7 +263,7 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
     m_freeTermSlots.pop_back();
     e.stamp = ++m_preparedStamp;
     m_preparedBytes += e.bytes;
-    ++m_stats.reserved[1];
+    ++m_stats.prepared_operand_builds;
     m_preparedTerms.push_back(e);
     return &m_preparedTerms.back();
 }
@@ -296,6 +297,7 @@ void Device::retireStaged()
 {
     for (void* p : m_staged)
     {
+        invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p));     // the block will hold other data next
         m_released.insert(p);
         m_deferredFrees.push_back(p);
         m_deferredBytes += m_allocator->blockSize(p);
@@ -342,6 +344,7 @@ void Device::emptyCache()
 {
     flush();
     if (!dryRun()) check(cudaStreamSynchronize(m_stream), "synchronize");
+    invalidatePreparedTerms(nullptr, reinterpret_cast<const void*>(~uintptr_t(0)));
     m_allocator->trim(0);
 }
 
@@ -349,6 +352,9 @@ void Device::synchronize()
 {
     flush();
     if (dryRun()) return;
+    // With managed memory the host may write into any tensor through its pointer once the device is idle: nothing
+    // prepared from the tensors' contents survives a synchronisation.
+    if (m_cfg.managed_memory) invalidatePreparedTerms(nullptr, reinterpret_cast<const void*>(~uintptr_t(0)));
     commWait();
     check(cudaStreamSynchronize(m_stream), "cudaStreamSynchronize");
     check(cudaGetLastError(), "asynchronous kernel failure");
@@ -1072,10 +1078,9 @@ void Device::commInit(int rank, int nranks, const void* id)
 }
 
 // Whether a scale of 1/ranks is handed to the collective as its own averaging, or applied by a scaling pass after a
-// plain sum. Measured on 8 GPUs (MLP step, 168 MB of gradients): blocking form 4.98 ms with averaging against 5.07 ms
-// with sum + pass (the pass is on the critical path); overlapped form 4.72 ms against 4.60 ms (the plain sum is the
-// form the switch reduces in flight, and the pass hides on the side stream). Hence: averaging when blocking, sum + pass
-// when overlapped. AIXB200_COMM_AVG=1 / 0 forces one or the other.
+// plain sum. The blocking form averages inside the collective (a separate pass would sit on the critical path); the
+// overlapped forms ask for a plain sum - the form NVSwitch can reduce in flight - and run the pass on the side stream,
+// where it is hidden. AIXB200_COMM_AVG=1 / 0 forces one or the other.
 static bool ncclAverages(bool overlapped)
 {
     static const int forced = []{ const char* v = std::getenv("AIXB200_COMM_AVG"); return v ? (v[0] == '0' ? 0 : 1) : -1; }();
@@ -1107,9 +1112,55 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
 {
     if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");
     const bool average = ncclAverages(true) && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
+    startCollective(data, count, dtype, "all_reduce_async", [&]
+    {
+        m_comm->allReduceSum(data, count, dtype, m_commStream, average);
+        if (scale != 1.0 && !average) scaleOnCommStream(data, count, dtype, scale);      // plain sum (the form in-switch reduction serves), then the pass
+    });
+}
+
+// Reduce-scatter / all-gather pair of a sharded optimizer: after reduce_scatter_async rank r holds the (scaled) sum of
+// slice r of `data` - the other slices hold unspecified partial data until an all_gather_async on the same buffer, which
+// distributes every rank's slice to all. Both run on the side stream like all_reduce_async and are joined the same way.
+void Device::reduceScatterAsync(void* data, size_t count, uint32_t dtype, double scale)
+{
+    if (!m_comm) failInvalid("reduce_scatter_async: aixb200_comm_init was not called");
+    const size_t ranks = static_cast<size_t>(m_comm->size());
+    if (count % ranks != 0) failInvalid("reduce_scatter_async: the element count must be a multiple of the number of ranks");
+    const bool average = ncclAverages(true) && isFloatType(dtype) && ranks > 1 && scale == 1.0 / m_comm->size();
+    startCollective(data, count, dtype, "reduce_scatter_async", [&]
+    {
+        if (ranks > 1) m_comm->reduceScatterSum(data, count, dtype, m_commStream, average);
+        const size_t slice = count / ranks;
+        if (scale != 1.0 && !average)
+            scaleOnCommStream(static_cast<char*>(data) + static_cast<size_t>(m_comm->rank()) * slice * dtypeSize(dtype), slice, dtype, scale);
+    });
+}
+
+void Device::allGatherAsync(void* data, size_t count, uint32_t dtype)
+{
+    if (!m_comm) failInvalid("all_gather_async: aixb200_comm_init was not called");
+    const size_t ranks = static_cast<size_t>(m_comm->size());
+    if (count % ranks != 0) failInvalid("all_gather_async: the element count must be a multiple of the number of ranks");
+    startCollective(data, count, dtype, "all_gather_async", [&] { if (ranks > 1) m_comm->allGather(data, count, dtype, m_commStream); });
+}
+
+void Device::scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale)
+{
+    uint64_t launched = 0;
+    kernels::LaunchContext ctx{m_commStream, m_smCount, m_scratch, m_scratchBytes, &launched};
+    kernels::scaleInPlace(ctx, dtype, data, count, scale);
+    m_stats.static_kernel_launches += launched; m_stats.total_kernel_launches += launched;
+    checkLaunch("collective scale");
+}
+
+// Common frame of the overlapped collectives: order the side stream after everything issued so far on the device's
+// stream, run `issue` there, and remember the buffer so that later ops touching it are ordered after the collective.
+void Device::startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue)
+{
     aixb200_tensor whole{};
     whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
-    const View range = makeView(&whole, "all_reduce_async");
+    const View range = makeView(&whole, what);
     invalidatePreparedTerms(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     if (!m_commInFlight.empty()) orderAfterCollectives(range);       // two collectives on one buffer keep their order
     flush();
@@ -1120,16 +1171,7 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
     }
     check(cudaEventRecord(m_commFork, m_stream), "cudaEventRecord(comm fork)");
     check(cudaStreamWaitEvent(m_commStream, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
-    m_comm->allReduceSum(data, count, dtype, m_commStream, average);
-    if (scale != 1.0 && !average)
-    {
-        // plain sum (the form in-switch reduction serves) followed by the scaling pass, both on the side stream
-        uint64_t launched = 0;
-        kernels::LaunchContext ctx{m_commStream, m_smCount, m_scratch, m_scratchBytes, &launched};
-        kernels::scaleInPlace(ctx, dtype, data, count, scale);
-        m_stats.static_kernel_launches += launched; m_stats.total_kernel_launches += launched;
-        checkLaunch("all_reduce_async scale");
-    }
+    issue();
     cudaEvent_t done = nullptr;
     if (!m_commEventPool.empty()) { done = m_commEventPool.back(); m_commEventPool.pop_back(); }
     else check(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate(comm)");
@@ -1137,6 +1179,9 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
     const char* begin = static_cast<const char*>(data);
     m_commInFlight.push_back({begin, begin + count * dtypeSize(dtype), done});
 }
+
+int Device::commRank() const { return m_comm ? m_comm->rank() : 0; }
+int Device::commSize() const { return m_comm ? m_comm->size() : 1; }
 
 void Device::orderAfterCollectives(const View& v)
 {

@@ -9,6 +9,7 @@
 #include "planner.hpp"
 #include "scalar.hpp"
 
+#include <functional>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -87,6 +88,10 @@ public:
     void commInit(int rank, int nranks, const void* id);
     void allReduce(void* data, size_t count, uint32_t dtype, double scale);
     void allReduceAsync(void* data, size_t count, uint32_t dtype, double scale);
+    void reduceScatterAsync(void* data, size_t count, uint32_t dtype, double scale);
+    void allGatherAsync(void* data, size_t count, uint32_t dtype);
+    int  commRank() const;
+    int  commSize() const;
     void commWait();
     void commWaitFor(const void* data, size_t bytes);
     void commDestroy();
@@ -127,6 +132,7 @@ public:
     uint32_t* preparedSlot(uint32_t slot) const { return static_cast<uint32_t*>(m_termSlots) + slot; }
     void invalidatePreparedTerms(const void* lo, const void* hi);
     bool preparedTermsEnabled() const { return m_termCacheEnabled; }
+    bool ownsMemory(const void* p) const { return m_allocator->findBlock(p) != nullptr; }
     // Called at the top of every C-ABI entry: the host operands the previous call staged are consumed by work that is
     // recorded or enqueued by now, so their blocks may follow the usual deferred-release path.
     void beginCall() { if (!m_staged.empty()) retireStaged(); }
@@ -173,7 +179,9 @@ private:
     struct CommInFlight { const char* begin; const char* end; cudaEvent_t done; };
     std::vector<CommInFlight> m_commInFlight;   // collectives started on the side stream and not yet joined
     std::vector<cudaEvent_t>  m_commEventPool;
-    void orderAfterCollectives(const View& v);  // the device's stream waits for in-flight collectives that touch the view
+    void orderAfterCollectives(const View& v);
+    void startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue);
+    void scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale);  // the device's stream waits for in-flight collectives that touch the view
     std::vector<PreparedTerms> m_preparedTerms;
     std::vector<uint32_t> m_freeTermSlots;
     void*    m_termSlots = nullptr;

@@ -67,7 +67,10 @@ struct KernelParams
     uint32_t pairALbo, pairBLbo;
     uint32_t atomK;             // K elements per swizzle atom in the main pass: 64 (16-bit) or 32 (TF32); cross passes: 64
     uint32_t halfTerms;         // f32 problems as three fp16 passes over scaled two-term operands (see splitF16Kernel)
-    const uint32_t* scaleBits;  // halfTerms: bit patterns of max|A| and max|B| (device memory), for the output scale
+    const uint32_t* scaleA;     // halfTerms: bit pattern of max|A| (device memory), for the output scale
+    const uint32_t* scaleB;     //            and of max|B|
+    uint32_t aPlane, bPlane;    // distance in elements from an operand's first term (or `hi` part) to its second: along K for a
+                                // K-major operand, along M / N for an MN-major one
     uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t idesc16;           // f32 problems: descriptor of the bf16 cross-term passes
     uint32_t aLbo, bLbo;        // leading byte offsets (MN-major), 0 for K-major
@@ -248,8 +251,8 @@ __device__ __forceinline__ void storeAccumulatorRow(const KernelParams& p, const
         {
             float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n + col;
             // half-term scheme: undo the operands' scaling (two factors, one after the other; 1 when the scheme is off)
-            const float scaleA = p.halfTerms ? halfTermInverseScale(p.scaleBits[0]) : 1.0f;
-            const float scaleB = p.halfTerms ? halfTermInverseScale(p.scaleBits[1]) : 1.0f;
+            const float scaleA = p.halfTerms ? halfTermInverseScale(*p.scaleA) : 1.0f;
+            const float scaleB = p.halfTerms ? halfTermInverseScale(*p.scaleB) : 1.0f;
             // Partial results after the first are added to C with IEEE f32 additions: the tensor core's own
             // accumulation truncates, and that bias grows with the number of MMAs folded into one accumulator.
             if (fullRow && p.vectorStores)
@@ -727,8 +730,8 @@ __device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const
         // 32 columns per slice; the TMEM load of the next slice is in flight while this one is staged and handed over
         uint32_t rA[32], rB[32];
         uint4 chunks[8];
-        const float scaleA = p.halfTerms ? halfTermInverseScale(p.scaleBits[0]) : 1.0f;      // multiplying by 1 is exact
-        const float scaleB = p.halfTerms ? halfTermInverseScale(p.scaleBits[1]) : 1.0f;
+        const float scaleA = p.halfTerms ? halfTermInverseScale(*p.scaleA) : 1.0f;      // multiplying by 1 is exact
+        const float scaleB = p.halfTerms ? halfTermInverseScale(*p.scaleB) : 1.0f;
         tmemLoad32(taddr, rA);
         #pragma unroll 1
         for (uint32_t c0 = 0; c0 < p.blockN; c0 += 64)
@@ -835,17 +838,20 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const uint32_t atomK = cross ? 64u : p.atomK;
                     const CUtensorMap* ma = cross ? &mapA16 : &mapA;
                     const CUtensorMap* mb = cross ? &mapB16 : &mapB;
-                    const uint32_t offA = (cross && passIndex == 0) ? p.kPerPhase : 0u, offB = (cross && passIndex == 1) ? p.kPerPhase : 0u;
+                    // the second term (or `lo` part) of a split-f32 operand lies one plane further: along K when the operand
+                    // is K-major, along its M / N dimension when it is MN-major
+                    const uint32_t offA = (cross && passIndex == 0) ? p.aPlane : 0u, offB = (cross && passIndex == 1) ? p.bPlane : 0u;
+                    const uint32_t offKA = p.aMnMajor ? 0u : offA, offKB = p.bMnMajor ? 0u : offB;
+                    const int32_t m0p = m0 + static_cast<int32_t>(p.aMnMajor ? offA : 0u), n0p = n0 + static_cast<int32_t>(p.bMnMajor ? offB : 0u);
                     for (uint32_t kb = first; kb < first + count; ++kb)
                     {
                         if (!mbarWait(&s.empty[stage], phase ^ 1u, abortFlag)) { ok = false; break; }
                         const uint32_t leaderFull = leaderFull0 + stage * 8;
                         mbarExpectTxCluster(leaderFull, stageBytes);
-                        // K coordinate of the stage in elements; split-f32 operands keep their `lo` halves kPerPhase further
-                        const uint32_t kA = kb * 2 * atomK + offA, kB = kb * 2 * atomK + offB;
+                        const uint32_t kA = kb * 2 * atomK + offKA, kB = kb * 2 * atomK + offKB;
                         if (p.aMnMajor)
                         {
-                            if (p.aLoad3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, static_cast<int32_t>(kA), m0 >> 6);
+                            if (p.aLoad3d) tmaLoad3dPair(&s.a[stage][0], ma, leaderFull, 0, static_cast<int32_t>(kA), m0p >> 6);
                             else for (uint32_t at = 0; at < 2; ++at) for (uint32_t h = 0; h < 2; ++h)
                                 tmaLoad2dPair(&s.a[stage][at * 16384 + h * 8192], ma, leaderFull, m0 + static_cast<int32_t>(at * 64), static_cast<int32_t>(kA + h * 64));
                         }
@@ -857,7 +863,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         }
                         if (p.bMnMajor)
                         {
-                            if (p.bLoad3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, static_cast<int32_t>(kB), n0 >> 6);
+                            if (p.bLoad3d) tmaLoad3dPair(&s.b[stage][0], mb, leaderFull, 0, static_cast<int32_t>(kB), n0p >> 6);
                             else for (uint32_t at = 0; at < (p.blockN >> 7); ++at) for (uint32_t h = 0; h < 2; ++h)
                                 tmaLoad2dPair(&s.b[stage][at * 16384 + h * 8192], mb, leaderFull, n0 + static_cast<int32_t>(at * 64), static_cast<int32_t>(kB + h * 64));
                         }
@@ -1509,32 +1515,79 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         const uint32_t kPad = (p.k + 127) & ~127u;
         p.kPhases = 3;
         p.kPerPhase = kPad;
+        p.aPlane = p.bPlane = kPad;
         // Pair kernel: three fp16 passes over scaled two-term operands (AIXB200_GEMM_F32=hybrid: TF32 + bf16 cross terms).
         static const bool halfTerms = []{ const char* v = std::getenv("AIXB200_GEMM_F32"); return !(v && v[0] == 'h' && v[1] == 'y'); }();
         if (pair && halfTerms)
         {
-            uint16_t* termsA = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.m) * 2 * kPad * 2));
-            uint16_t* termsB = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(p.n) * 2 * kPad * 2));
-            uint32_t* slots = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + ctx.scratchBytes + 2048);   // behind the split-tile counters
-            if (cudaMemsetAsync(slots, 0, 8, ctx.stream) != cudaSuccess) return false;
-            launchHalfTermSplit(ctx.stream, ctx.smCount, static_cast<const float*>(q.a), q.aRowStride, q.aColStride, p.m, p.k, kPad, termsA, slots);
-            // B is k x n: its "rows" for the split are the n columns
-            launchHalfTermSplit(ctx.stream, ctx.smCount, static_cast<const float*>(q.b), q.bColStride, q.bRowStride, p.n, p.k, kPad, termsB, slots + 1);
-            if (ctx.launches) *ctx.launches += 4;
+            // Every operand as two scaled fp16 terms. A tensor that is dense along one of its two dimensions is prepared
+            // ONCE, in its own row-major layout [rows][h0 | h1] (Device::PreparedTerms), and read K-major or MN-major
+            // through the matching tensor map and descriptors: the forward product, dX and dW then share one prepared
+            // form of every activation, weight and gradient instead of splitting each of them once per orientation.
+            // Operands with two non-unit strides are split into a temporary K-major buffer for this call only.
+            struct Prepared { const uint16_t* terms; const uint32_t* scale; bool mnMajor; uint32_t plane; };
+            uint32_t* tempSlots = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + ctx.scratchBytes + 2048);   // behind the split-tile counters
+            uint64_t preparedLaunches = 0;
+            auto prepare = [&](const void* base, uint64_t mnStride, uint64_t kStride, uint64_t mn, uint32_t boxRows, uint32_t* tempSlot,
+                               CUtensorMap* map, Prepared* out) -> bool
+            {
+                const float* src = static_cast<const float*>(base);
+                const bool kDense = (kStride == 1 || p.k == 1) && (mn == 1 || mnStride >= p.k);
+                const bool mnDense = (mnStride == 1 || mn == 1) && (p.k == 1 || kStride >= mn);
+                // only tensors of this device's allocator: writes into foreign memory cannot be seen, so nothing is kept of it
+                if (device.preparedTermsEnabled() && (kDense || mnDense) && device.ownsMemory(base))
+                {
+                    const uint64_t rows = kDense ? mn : p.k, cols = kDense ? p.k : mn;
+                    const uint64_t pitch = rows == 1 ? cols : (kDense ? mnStride : kStride);
+                    const Device::PreparedTerms* e = device.findPreparedTerms(base, rows, cols, pitch);
+                    if (!e)
+                    {
+                        e = device.addPreparedTerms(base, rows, cols, pitch);
+                        if (cudaMemsetAsync(device.preparedSlot(e->slot), 0, 4, ctx.stream) != cudaSuccess) return false;
+                        launchHalfTermSplit(ctx.stream, ctx.smCount, src, pitch, 1, static_cast<uint32_t>(rows), static_cast<uint32_t>(cols),
+                                            static_cast<uint32_t>(e->paddedCols), static_cast<uint16_t*>(e->terms), device.preparedSlot(e->slot));
+                        preparedLaunches += 2;
+                    }
+                    out->terms = static_cast<const uint16_t*>(e->terms);
+                    out->scale = device.preparedSlot(e->slot);
+                    out->mnMajor = !kDense;
+                    out->plane = static_cast<uint32_t>(e->paddedCols);
+                    const uint64_t rowBytes = 2ull * e->paddedCols * 2;
+                    return kDense ? makeMapK3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, e->terms, mn, 2ull * e->paddedCols, rowBytes, 64, boxRows)
+                                  : makeMap3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, e->terms, 2ull * e->paddedCols, p.k, rowBytes, 128, boxRows / 64);
+                }
+                uint16_t* terms = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(mn) * 2 * kPad * 2));
+                if (cudaMemsetAsync(tempSlot, 0, 4, ctx.stream) != cudaSuccess) return false;
+                launchHalfTermSplit(ctx.stream, ctx.smCount, src, mnStride, kStride, static_cast<uint32_t>(mn), p.k, kPad, terms, tempSlot);
+                preparedLaunches += 2;
+                out->terms = terms; out->scale = tempSlot; out->mnMajor = false; out->plane = kPad;
+                return makeMapK3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, terms, mn, 2ull * kPad, 2ull * kPad * 2, 64, boxRows);
+            };
+            Prepared pa{}, pb{};
+            if (!prepare(q.a, q.aRowStride, q.aColStride, q.m, kBlockM, tempSlots, &mapA16, &pa)) return false;
+            // B is k x n: its M/N dimension are the n columns
+            if (!prepare(q.b, q.bColStride, q.bRowStride, q.n, bRows, tempSlots + 1, &mapB16, &pb)) return false;
+            if (ctx.launches) *ctx.launches += preparedLaunches;
             p.halfTerms = 1;
-            p.scaleBits = slots;
+            p.scaleA = pa.scale; p.scaleB = pb.scale;
+            p.aPlane = pa.plane; p.bPlane = pb.plane;
+            p.aMnMajor = pa.mnMajor; p.bMnMajor = pb.mnMajor;
             p.atomK = 64;
             p.kBlocks = kPad / 128;                              // stages of 128 fp16 elements in all three passes
-            p.chunkBlocks = 4;                                   // 512 elements of K per in-TMEM partial sum
+            {
+                // 512 elements of K per in-TMEM partial sum (AIXB200_GEMM_HCHUNK: stages per partial sum, for measurements only -
+                // longer partial sums leave the f32 error bar)
+                static const int chunkOverride = []{ const char* v = std::getenv("AIXB200_GEMM_HCHUNK"); return v ? std::atoi(v) : 0; }();
+                p.chunkBlocks = chunkOverride > 0 ? static_cast<uint32_t>(chunkOverride) : 4u;
+            }
             p.aLoad3d = p.bLoad3d = 1;
             p.pairABytes = kBlockM * 256; p.pairBBytes = bRows * 256;
+            p.pairALbo = pa.mnMajor ? 128 * 128 : 0; p.pairBLbo = pb.mnMajor ? 128 * 128 : 0;
             for (uint32_t j = 0; j < 8; ++j)
             {
-                p.pairAOff[j] = ((j / 4) * kBlockM * 128 + (j % 4) * 32) >> 4;
-                p.pairBOff[j] = ((j / 4) * bRows * 128 + (j % 4) * 32) >> 4;
+                p.pairAOff[j] = pa.mnMajor ? (j * 16 * 128) >> 4 : ((j / 4) * kBlockM * 128 + (j % 4) * 32) >> 4;
+                p.pairBOff[j] = pb.mnMajor ? (j * 16 * 128) >> 4 : ((j / 4) * bRows * 128 + (j % 4) * 32) >> 4;
             }
-            if (!makeMapK3d(&mapA16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, termsA, q.m, 2ull * kPad, 2ull * kPad * 2, 64, kBlockM)) return false;
-            if (!makeMapK3d(&mapB16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, termsB, q.n, 2ull * kPad, 2ull * kPad * 2, 64, bRows)) return false;
             mapA = mapA16; mapB = mapB16;                        // no 32-bit pass
         }
         else
@@ -1584,7 +1637,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         p.chunks = (p.kBlocks + p.chunkBlocks - 1) / p.chunkBlocks;
         const uint32_t shape = ((p.blockN >> 3) << 17) | (((pair ? 256u : 128u) >> 4) << 24);
         p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | shape;            // D f32, A/B tf32
-        p.idesc16 = p.halfTerms ? ((1u << 4) | shape)                    // D f32, A/B f16
+        p.idesc16 = p.halfTerms ? ((1u << 4) | ((p.aMnMajor ? 1u : 0u) << 15) | ((p.bMnMajor ? 1u : 0u) << 16) | shape)   // D f32, A/B f16
                                 : ((1u << 4) | (1u << 7) | (1u << 10) | shape);   // D f32, A/B bf16
     }
 

@@ -249,6 +249,17 @@ class DeviceB200:
     def allReduceAsync(self, data: int, count: int, dtype: int, scale: float = 1.0):
         self._check(self._lib.aixb200_all_reduce_async(self._h, data, count, dtype, scale))
 
+    def reduceScatterAsync(self, data: int, count: int, dtype: int, scale: float = 1.0):
+        self._check(self._lib.aixb200_reduce_scatter_async(self._h, data, count, dtype, scale))
+
+    def allGatherAsync(self, data: int, count: int, dtype: int):
+        self._check(self._lib.aixb200_all_gather_async(self._h, data, count, dtype))
+
+    def commRank(self):
+        rank, size = ctypes.c_int(), ctypes.c_int()
+        self._check(self._lib.aixb200_comm_rank(self._h, ctypes.byref(rank), ctypes.byref(size)))
+        return rank.value, size.value
+
     def commWait(self): self._check(self._lib.aixb200_comm_wait(self._h))
 
     def commWaitFor(self, data: int, nbytes: int): self._check(self._lib.aixb200_comm_wait_for(self._h, data, nbytes))

@@ -370,3 +370,69 @@ class GradientExchange:
     def detach(self):
         for p in self.parameters:
             p.node.gradReadyHook = None
+
+
+def _flat_slice(t: TensorValue, rank: int, world_size: int) -> TensorValue:
+    """Slice `rank` of `world_size` of a dense tensor, as a 1-D view of its storage."""
+    n = t.size // world_size
+    return TensorValue(t.storage, (n,), (1,), t.offset + rank * n, t.dtype, t.device)
+
+
+class ShardedGradientExchange(GradientExchange):
+    """Gradient exchange of the sharded optimizer: a reduce-scatter instead of an all-reduce, started from the same
+    gradient-ready hook. Afterwards rank r holds the averaged gradient only in slice r of every gradient buffer, which
+    is all ShardedAdam reads. Parameters whose size is not a multiple of the number of ranks keep the all-reduce."""
+
+    def _ready(self, node: TensorNode):
+        if id(node) in self._inFlight:
+            raise RuntimeError("GradientExchange: a parameter received a second gradient contribution while its "
+                               "collective was in flight; use all_reduce_gradients for this model")
+        self._inFlight.add(id(node))
+        g = node.grad()
+        if g.size % self.world_size == 0:
+            self.device.reduceScatterAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
+        else:
+            self.device.allReduceAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
+
+
+class ShardedAdam(Adam):
+    """optim::Adam (aixOptimizer.hpp:93-159) with its work and its state split over the data-parallel ranks: rank r keeps
+    the moments of slice r of every parameter only, updates that slice from slice r of the reduce-scattered gradient
+    with exactly the reference's expression sequence, and an all-gather hands every rank the other slices. The
+    all-gather runs on the device's side stream; the device orders the first later use of the parameter (the next
+    forward pass) after it. Elementwise the update is the reference's, so the parameters equal those of the unsharded
+    optimizer given the same averaged gradients. A parameter whose size is not a multiple of the number of ranks is
+    updated in full on every rank (its gradient was all-reduced)."""
+
+    def __init__(self, parameters: Sequence[Tensor], rank: int, world_size: int, lr=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8):
+        self.parameters = list(parameters)
+        self.lr, self.beta1, self.beta2, self.epsilon = lr, beta1, beta2, epsilon
+        self.timestep = 0
+        self.rank, self.world_size = rank, world_size
+        self.beforeParameter: Optional[Callable] = None
+        self.sharded = [world_size > 1 and p.value.size % world_size == 0 and p.value.isContiguous() for p in self.parameters]
+        shape = lambda p, s: (p.value.size // world_size,) if s else p.shape
+        self.m = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
+        self.v = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
+
+    def step(self):
+        self.timestep += 1
+        b1, b2 = float(np.float32(self.beta1)), float(np.float32(self.beta2))
+        narrow = lambda x: float(np.float32(x))
+        for i, p in enumerate(self.parameters):
+            if not p.isRequireGrad():
+                continue
+            if self.beforeParameter is not None:
+                self.beforeParameter(p)
+            value, grad = p.value, p.grad()
+            if self.sharded[i]:
+                value, grad = _flat_slice(value, self.rank, self.world_size), _flat_slice(grad, self.rank, self.world_size)
+            g = grad.to(C.F32)
+            self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
+            self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
+            mHat = self.m[i] / narrow(1.0 - math.pow(b1, self.timestep))
+            vHat = self.v[i] / narrow(1.0 - math.pow(b2, self.timestep))
+            value -= (self.lr * mHat / (vHat.sqrt() + self.epsilon)).to(p.dtype)
+            if self.sharded[i]:
+                whole = p.value
+                whole.device.allGatherAsync(whole.storage.data, whole.size, whole.dtype)

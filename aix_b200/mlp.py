@@ -4,7 +4,8 @@ all-reduce over the ranks) + optimizer step, issued through the mirrored front e
 import numpy as np
 
 from . import _capi as C
-from .frontend import Adam, GradientExchange, Linear, MSELoss, Sequential, Tanh, Tensor, all_reduce_gradients
+from .frontend import (Adam, GradientExchange, Linear, MSELoss, Sequential, ShardedAdam, ShardedGradientExchange, Tanh, Tensor,
+                       all_reduce_gradients)
 from .tensor import TensorValue
 
 DEFAULT_DIMS = (1024, 4096, 4096, 4096, 1024)
@@ -31,7 +32,7 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 class MlpTrainer:
     def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
-                 overlap=True, data=None):
+                 overlap=True, data=None, sharded=False):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -45,10 +46,15 @@ class MlpTrainer:
         batch = x.shape[0]
         self.x = Tensor(TensorValue.from_numpy(x, device))
         self.y = Tensor(TensorValue.from_numpy(y, device))
-        self.optimizer = Adam(self.model.parameters(), lr=lr)      # created after the parameters live on the device
+        # sharded=True: reduce-scatter the gradients, update 1/world_size of every parameter (and keep that share of the
+        # Adam state) per rank, all-gather the parameters; needs the overlapped exchange
+        sharded = sharded and overlap and world_size > 1
+        params = self.model.parameters()
+        self.optimizer = ShardedAdam(params, rank, world_size, lr=lr) if sharded else Adam(params, lr=lr)   # after the parameters live on the device
         self.loss_fn = MSELoss()
-        # overlap=True: each gradient's all-reduce starts inside backward(); False: all of them after it
-        self.exchange = GradientExchange(device, self.model.parameters(), world_size) if overlap and world_size > 1 else None
+        # overlap=True: each gradient's collective starts inside backward(); False: all of them after it
+        exchange_type = ShardedGradientExchange if sharded else GradientExchange
+        self.exchange = exchange_type(device, params, world_size) if overlap and world_size > 1 else None
         if self.exchange is not None:
             self.exchange.attach(self.optimizer)
         self.flops_per_step = 2.0 * batch * sum(a * b for a, b in zip(dims[:-1], dims[1:])) * 3 \

@@ -9,8 +9,8 @@ elements per GPU (synthetic U(-1,1) inputs, seed 0), issued op by op through the
 issue it: 16 recorded device calls that the device fuses into one generated kernel, plus the sum kernel.
 The line also carries `mlp_train` (steps/s of the data-parallel MLP configuration at this N) and, at N = 1, `extras`
 (reductions at 8192^2 bf16, matmul 4096^3) and `cpu_baseline`.
-`value` counts the algorithmic bytes of the step (3 reads + 1 write for the chain, 1 read for the sum: 20*n for
-f32) over the device time of K steps with inputs resident in HBM; `e2e` is the same step with the inputs copied from
+`value` counts the algorithmic bytes of the step (a, b, c read and z written once: 16*n for f32; the sum is folded into the
+chain's kernel and moves nothing of its own) over the device time of K steps with inputs resident in HBM; `e2e` is the same step with the inputs copied from
 pinned host memory and the sum read back every step. Rank 0 prints one JSON line.
 """
 import argparse
@@ -122,6 +122,24 @@ def cpu_reference_chain(n_sample, repeats=1):
         _, _, secs = ref.chain_f32(a, b, c)
         best = secs if best is None else min(best, secs)
     return STEP_BYTES_PER_ELEMENT_F32 * rows * 1024 / best / 1e9, best
+
+
+def cpp_front_end(dev):
+    """The drop-in path proper: the reference's unmodified C++ front end on aix::DeviceB200 (managed memory), timed by the
+    program tests/cpp/adapter_bench.cpp. The binary is built from the reference's headers where they are present and
+    travels with the repository; without it the entry says so."""
+    binary = os.path.join(ROOT, "oracle", "_ref", "adapter_bench")
+    if not os.path.isfile(binary):
+        return {"unavailable": "adapter_bench was not built (the reference's headers were absent at build time)"}
+    dev.emptyCache()
+    try:
+        run = subprocess.run([binary], capture_output=True, text=True, timeout=600)
+        last = [l for l in run.stdout.splitlines() if l.startswith("{")]
+        if run.returncode != 0 or not last:
+            return {"error": (run.stdout + run.stderr)[-400:]}
+        return json.loads(last[-1])
+    except Exception as exc:
+        return {"error": str(exc)}
 
 
 def run_reference(args, rank, world):
@@ -323,7 +341,8 @@ def main():
                                                       "reductions_fused", "kernel_cache_hits", "kernel_cache_misses")},
     }
 
-    # ---- the data-parallel MLP training configuration, at every N (gradient all-reduce over NCCL for N > 1) --------------
+    # ---- the data-parallel MLP training configuration, at every N (gradient exchange over NCCL for N > 1) ----------------
+    mlp_train = None
     if not args.no_mlp:
         # free the sweep tensors first: the MLP step needs its own few GB
         del a, b, c
@@ -334,16 +353,19 @@ def main():
                 dist.broadcast_object_list(ids, src=0)
                 dev.commInit(rank, world, ids[0])
             from aix_b200.extras import measure_mlp
-            line["mlp_train"] = measure_mlp(dev, tensor_peak, steps=max(3, min(args.steps, 10)), warmup=3, rank=rank, world_size=world,
-                                            barrier=barrier, reduce_max=max_over_ranks)
-            if world > 1:
-                # the same steps with every all-reduce issued after backward(), to show what the overlap buys
-                plain = measure_mlp(dev, tensor_peak, steps=max(3, min(args.steps, 10)), warmup=3, rank=rank, world_size=world,
-                                    barrier=barrier, reduce_max=max_over_ranks, overlap=False)
-                line["mlp_train"]["ms_per_step_exchange_after_backward"] = plain["ms_per_step"]
+            mlp_steps = 100                              # the configuration is "100 steps from seed 0"
+            common = dict(steps=mlp_steps, warmup=3, rank=rank, world_size=world, barrier=barrier, reduce_max=max_over_ranks)
+            if world == 1:
+                mlp_train = measure_mlp(dev, tensor_peak, **common)
+            else:
+                # default form: sharded optimizer (reduce-scatter, 1/N of Adam per rank, all-gather); beside it the two
+                # all-reduce forms, to show what each step of the design buys
+                mlp_train = measure_mlp(dev, tensor_peak, sharded=True, **common)
+                mlp_train["ms_per_step_all_reduce_inside_backward"] = measure_mlp(dev, tensor_peak, **common)["ms_per_step"]
+                mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]
                 dev.commDestroy()
         except Exception as exc:
-            line["mlp_train"] = {"error": str(exc)}
+            mlp_train = {"error": str(exc)}
 
     if rank == 0 and world == 1:
         try:
@@ -359,6 +381,9 @@ def main():
                 line["extras"] = measure_extras(dev, hbm_peak, tensor_peak)
             except Exception as exc:
                 line["extras"] = {"error": str(exc)}
+            line["extras"]["cpp_front_end"] = cpp_front_end(dev)
+    if mlp_train is not None:
+        line["mlp_train"] = mlp_train                    # last key: the step time of this N stays in the tail of the line
     if rank == 0:
         emit(line)
     dev.close()

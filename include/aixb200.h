@@ -211,7 +211,9 @@ typedef struct aixb200_stats
     uint64_t h2d_bytes;             /* staged host->device */
     uint64_t d2h_bytes;
     uint64_t reductions_fused;      /* full sums / maxima folded into the kernel that produces their operand */
-    uint64_t reserved[5];
+    uint64_t prepared_operand_hits; /* f32 matmul operands whose two-term fp16 form was still cached */
+    uint64_t prepared_operand_builds; /* ... and those that had to be prepared (max pass + split) */
+    uint64_t reserved[3];
 } aixb200_stats;
 int aixb200_get_stats(aixb200_device* dev, aixb200_stats* out);
 /* CUDA C source of the most recently generated kernel (for inspection and tests); NULL if none yet. */
@@ -239,6 +241,16 @@ int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t d
  * device's stream after every collective started this way (also implied by synchronize and by the blocking
  * all-reduce). */
 int aixb200_all_reduce_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
+/* Sharded-optimizer pair, both in place on a buffer of `count` elements (a multiple of the number of ranks) and both
+ * overlapped like aixb200_all_reduce_async. reduce_scatter: afterwards slice [r*count/R, (r+1)*count/R) of rank r's buffer
+ * holds the sum over the ranks times `scale`; the other slices hold unspecified data. all_gather: every rank contributes
+ * its own slice r and receives the others', so that all ranks hold identical buffers. A rank that updates only its slice
+ * of a parameter between the two (its share of the optimizer state) does 1/R of the optimizer's work and moves half the
+ * bytes of an all-reduce before the update can start. */
+int aixb200_reduce_scatter_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);
+int aixb200_all_gather_async(aixb200_device* dev, void* data, size_t count, uint32_t dtype);
+/* Rank and size of the device's communicator (0 and 1 without one). */
+int aixb200_comm_rank(aixb200_device* dev, int* rank, int* nranks);
 int aixb200_comm_wait(aixb200_device* dev);
 /* Joins only the collectives that touch [data, data + bytes): recorded work that does not depend on them is launched
  * first. An optimizer calls it before it starts on one parameter, so that the join falls between parameters. */

@@ -13,7 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libaixref.so")
-REF_ROOT = os.environ.get("AIX_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: AIX_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REF_ROOT = os.environ.get("AIX_REFERENCE_ROOT") or os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
 LIB_DIR = os.path.join(REF_ROOT, "Targets", "AIXLib")
 REF_SOURCES = ["aixDeviceCPU.cpp", "aixDevices.cpp", "aixFuse.cpp"]
 
@@ -38,31 +39,43 @@ def build(force: bool = False) -> str | None:
 
 
 ADAPTER_OUT = os.path.join(OUT_DIR, "adapter_check")
+ADAPTER_BENCH_OUT = os.path.join(OUT_DIR, "adapter_bench")
 
 
-def build_adapter_check(force: bool = False) -> str | None:
-    """Builds the drop-in check: the reference's unmodified front end + aix_b200/adapter/aixDeviceB200.hpp, linked
-    against libaixb200.so. Needs the reference headers, hence lives with the oracle artefacts."""
+def _build_front_end_program(source_name: str, out: str, force: bool) -> str | None:
+    """Compiles tests/cpp/<source_name>: the reference's unmodified front end + aix_b200/adapter/aixDeviceB200.hpp, linked
+    against libaixb200.so. Needs the reference headers, hence the binary lives with the oracle artefacts."""
     if not reference_available():
-        return ADAPTER_OUT if os.path.isfile(ADAPTER_OUT) else None
+        return out if os.path.isfile(out) else None
     root = os.path.join(HERE, "..")
     adapter_dir = os.path.join(root, "aix_b200", "adapter")
     lib_dir = os.path.join(root, "aix_b200", "lib")
-    src = os.path.join(adapter_dir, "adapter_check.cpp")
+    src = os.path.join(root, "tests", "cpp", source_name)
     deps = [src, os.path.join(adapter_dir, "aixDeviceB200.hpp"), os.path.join(root, "include", "aixb200.h")]
     if not os.path.isfile(os.path.join(lib_dir, "libaixb200.so")):
         return None
-    if not force and os.path.isfile(ADAPTER_OUT) and all(os.path.getmtime(ADAPTER_OUT) >= os.path.getmtime(d) for d in deps):
-        return ADAPTER_OUT
+    if not force and os.path.isfile(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = ["g++", "-std=c++20", "-O2", "-w", "-I", LIB_DIR, "-I", os.path.join(root, "include"), "-I", adapter_dir, src]
     cmd += [os.path.join(LIB_DIR, s) for s in REF_SOURCES]
-    cmd += ["-L", lib_dir, "-laixb200", "-Wl,-rpath,$ORIGIN/../../aix_b200/lib", "-o", ADAPTER_OUT]
+    cmd += ["-L", lib_dir, "-laixb200", "-Wl,-rpath,$ORIGIN/../../aix_b200/lib", "-o", out]
     subprocess.run(cmd, check=True)
-    return ADAPTER_OUT
+    return out
+
+
+def build_adapter_check(force: bool = False) -> str | None:
+    """The drop-in correctness check (tests/test_gpu_adapter.py runs it)."""
+    return _build_front_end_program("adapter_check.cpp", ADAPTER_OUT, force)
+
+
+def build_adapter_bench(force: bool = False) -> str | None:
+    """The drop-in timing program (bench.py runs it and reports its line as extras.cpp_front_end)."""
+    return _build_front_end_program("adapter_bench.cpp", ADAPTER_BENCH_OUT, force)
 
 
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv)
     print(path if path else "reference sources not found; nothing built")
     print(build_adapter_check(force="--force" in sys.argv))
+    print(build_adapter_bench(force="--force" in sys.argv))

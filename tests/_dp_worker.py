@@ -1,6 +1,9 @@
 """Child process of tests/test_gpu_comm.py: one data-parallel rank on its own GPU.
 
-    python tests/_dp_worker.py <rank> <world> <dir> <overlap 0|1> <steps> [<ranks whose batches one process concatenates>]
+    python tests/_dp_worker.py <rank> <world> <dir> <exchange 0|1|2> <steps> [<ranks whose batches one process concatenates>]
+
+exchange: 0 = all-reduces after backward, 1 = all-reduces started inside backward, 2 = sharded optimizer (reduce-scatter,
+per-rank slice of Adam, all-gather).
 
 Rank 0 publishes the communicator id through a file in <dir>; every rank trains the small MLP and writes its parameters
 and losses to <dir>/rank<r>_<overlap>.npz. With world = 1 and the last argument R, the single process trains on the
@@ -22,7 +25,8 @@ BATCH = 384
 
 
 def main():
-    rank, world, out_dir, overlap, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4] == "1", int(sys.argv[5])
+    rank, world, out_dir, mode, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4]), int(sys.argv[5])
+    overlap, sharded = mode >= 1, mode == 2
     concat = int(sys.argv[6]) if len(sys.argv) > 6 else 0
     if world == 1 and concat > 1:
         parts = [synthetic_batch(DIMS, BATCH, r) for r in range(concat)]
@@ -34,7 +38,7 @@ def main():
         np.savez(os.path.join(out_dir, "single.npz"), *trainer.parameters_numpy(), losses=np.array(losses))
         dev.close()
         return
-    id_path = os.path.join(out_dir, f"comm_id_{int(overlap)}")
+    id_path = os.path.join(out_dir, f"comm_id_{mode}")
     if rank == 0:
         unique = DeviceB200.commUniqueId()
         with open(id_path + ".tmp", "wb") as f:
@@ -50,12 +54,12 @@ def main():
             unique = f.read()
     dev = DeviceB200(rank)
     dev.commInit(rank, world, unique)
-    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, overlap=overlap)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, overlap=overlap, sharded=sharded)
     losses = []
     for _ in range(steps):
         losses.append(float(trainer.step().value.numpy()))
     dev.synchronize()
-    np.savez(os.path.join(out_dir, f"rank{rank}_{int(overlap)}.npz"), *trainer.parameters_numpy(), losses=np.array(losses))
+    np.savez(os.path.join(out_dir, f"rank{rank}_{mode}.npz"), *trainer.parameters_numpy(), losses=np.array(losses))
     dev.commDestroy()
     dev.close()
 

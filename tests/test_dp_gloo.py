@@ -38,6 +38,33 @@ class GlooDevice(DeviceNumpyOracle):
         self.async_calls = getattr(self, "async_calls", 0) + 1
         self.allReduce(data, count, dtype, scale)
 
+    def _write(self, p, values):
+        """The sharded optimizer updates a slice of a parameter in place, i.e. it hands the device a RESULT view with an
+        offset. The B200 device writes through the result view; the reference's CPU device writes res[i] from the
+        storage base whatever the view's offset (aixDeviceCPU.cpp:36-40), which is why this test double honours the
+        offset of dense results (identical for offset 0, the only case the reference's own callers produce)."""
+        self._raw(p.data, p.dtype, p.offset + len(values))[p.offset:] = values
+
+    def reduceScatterAsync(self, data, count, dtype, scale=1.0):
+        """Slice `rank` of the buffer receives the scaled sum; the other slices are scribbled over on purpose - nothing
+        may read them before the all-gather."""
+        self.scatter_calls = getattr(self, "scatter_calls", 0) + 1
+        view = self._raw(data, dtype, count)
+        t = torch.from_numpy(view.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        n, r = count // dist.get_world_size(), dist.get_rank()
+        reduced = (t.numpy() * np.float32(scale)).astype(np.float32)
+        view[:] = np.float32(np.nan)
+        view[r * n:(r + 1) * n] = reduced[r * n:(r + 1) * n]
+
+    def allGatherAsync(self, data, count, dtype):
+        self.gather_calls = getattr(self, "gather_calls", 0) + 1
+        view = self._raw(data, dtype, count)
+        n, r = count // dist.get_world_size(), dist.get_rank()
+        parts = [torch.empty(n, dtype=torch.float32) for _ in range(dist.get_world_size())]
+        dist.all_gather(parts, torch.from_numpy(view[r * n:(r + 1) * n].copy()))
+        view[:] = torch.cat(parts).numpy()
+
     def commWait(self):
         self.waits = getattr(self, "waits", 0) + 1
 
@@ -50,17 +77,22 @@ def set_batch(trainer, dev, x, y):
     trainer.y = Tensor(TensorValue.from_numpy(y, dev))
 
 
-def worker(rank, world, port, out_dir, overlap=True):
+def worker(rank, world, port, out_dir, overlap=True, sharded=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     dev = GlooDevice()
     weights, biases = xavier_parameters(DIMS, seed=0)
-    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases, overlap=overlap)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases, overlap=overlap, sharded=sharded)
     x, y = synthetic_batch(DIMS, BATCH, rank)
     set_batch(trainer, dev, x, y)
     for _ in range(STEPS):
         trainer.step()
-    if overlap:
+    if sharded:
+        # one reduce-scatter, one join and one all-gather per parameter and step; the optimizer state is 1/world of a replica's
+        count = STEPS * len(trainer.model.parameters())
+        assert dev.scatter_calls == count == dev.gather_calls == dev.joins and not hasattr(dev, "async_calls")
+        assert sum(m.size for m in trainer.optimizer.m) * world == sum(p.value.size for p in trainer.model.parameters())
+    elif overlap:
         # one collective and one join per parameter and step; no global join when the optimizer is attached
         assert dev.async_calls == STEPS * len(trainer.model.parameters()) == dev.joins and not hasattr(dev, "waits")
     else:
@@ -69,12 +101,12 @@ def worker(rank, world, port, out_dir, overlap=True):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("overlap", [True, False], ids=["overlapped", "after_backward"])
-def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path, overlap):
+@pytest.mark.parametrize("overlap,sharded", [(True, False), (False, False), (True, True)], ids=["overlapped", "after_backward", "sharded_optimizer"])
+def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path, overlap, sharded):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(worker, args=(2, port, str(tmp_path), overlap), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, port, str(tmp_path), overlap, sharded), nprocs=2, join=True)
     r0 = np.load(tmp_path / "rank0.npz")
     r1 = np.load(tmp_path / "rank1.npz")
     for k in r0.files:

@@ -86,6 +86,34 @@ def test_single_rank_overlapped_exchange_orders_both_streams(comm1):
     assert np.array_equal(g.numpy(), a * b)
 
 
+def test_single_rank_reduce_scatter_and_all_gather(comm1):
+    """One rank: the whole buffer is the rank's own slice - the pair must leave sum x scale there, ordered like any other
+    overlapped collective, and refuse counts that do not divide by the number of ranks only when there are several."""
+    rng = np.random.default_rng(4)
+    host = rng.normal(size=1 << 18).astype(np.float32)
+    x = TensorValue.from_numpy(host, comm1)
+    y = x * 3.0                                          # pending producer: the collective comes after it
+    comm1.reduceScatterAsync(y.storage.data, y.size, C.F32, 0.5)
+    z = y + 1.0                                          # touches y: ordered after the collective and its scaling pass
+    comm1.allGatherAsync(y.storage.data, y.size, C.F32)
+    assert np.array_equal(z.numpy(), host * np.float32(3.0) * np.float32(0.5) + np.float32(1.0))
+    assert np.array_equal(y.numpy(), host * np.float32(3.0) * np.float32(0.5))
+    assert comm1.commRank() == (0, 1)
+
+
+def test_sharded_optimizer_on_one_rank_is_the_plain_optimizer(b200):
+    from aix_b200.mlp import MlpTrainer
+    dims, batch = (64, 128, 32), 48
+    plain = MlpTrainer(b200, dims, batch)
+    losses = [float(plain.step().value.item()) for _ in range(3)]
+    from aix_b200.frontend import ShardedAdam
+    again = MlpTrainer(b200, dims, batch)
+    again.optimizer = ShardedAdam(again.model.parameters(), 0, 1)
+    assert [float(again.step().value.item()) for _ in range(3)] == losses
+    for p, q in zip(plain.parameters_numpy(), again.parameters_numpy()):
+        assert np.array_equal(p, q)
+
+
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
 def test_two_ranks_overlapped_equals_blocking(tmp_path):
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_dp_worker.py")
@@ -118,18 +146,18 @@ def test_two_ranks_reproduce_the_single_process_run_on_the_concatenated_batch(tm
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_dp_worker.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     steps = 6
-    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", str(tmp_path), "1", str(steps)], env=env) for r in range(2)]
-    assert [p.wait(timeout=600) for p in procs] == [0, 0]
     single = subprocess.Popen([sys.executable, worker, "0", "1", str(tmp_path), "0", str(steps), "2"], env=env)
     assert single.wait(timeout=600) == 0
     want = np.load(tmp_path / "single.npz")
-    for r in range(2):
-        got = np.load(tmp_path / f"rank{r}_1.npz")
+    for mode in ("1", "2"):                               # overlapped all-reduce; sharded optimizer
+        procs = [subprocess.Popen([sys.executable, worker, str(r), "2", str(tmp_path), mode, str(steps)], env=env) for r in range(2)]
+        assert [p.wait(timeout=600) for p in procs] == [0, 0]
+        ranks = [np.load(tmp_path / f"rank{r}_{mode}.npz") for r in range(2)]
         for k in want.files:
             if k == "losses":
                 continue
-            assert np.max(np.abs(got[k] - want[k])) <= 0.1 * steps * 1e-3, k      # single weights: a fraction of the total movement
-            assert np.mean(np.abs(got[k] - want[k])) <= 2e-6, k                   # the average weight: tightly
-    # each rank reports the loss of its own half; their mean is the loss of the concatenated batch
-    both = 0.5 * (np.load(tmp_path / "rank0_1.npz")["losses"] + np.load(tmp_path / "rank1_1.npz")["losses"])
-    assert np.allclose(both, want["losses"], rtol=2e-5)
+            assert np.array_equal(ranks[0][k], ranks[1][k]), f"ranks diverged (exchange {mode})"
+            assert np.max(np.abs(ranks[0][k] - want[k])) <= 0.1 * steps * 1e-3, k      # single weights: a fraction of the total movement
+            assert np.mean(np.abs(ranks[0][k] - want[k])) <= 2e-6, k                   # the average weight: tightly
+        # each rank reports the loss of its own half; their mean is the loss of the concatenated batch
+        assert np.allclose(0.5 * (ranks[0]["losses"] + ranks[1]["losses"]), want["losses"], rtol=2e-5)

@@ -98,3 +98,47 @@ def test_f32_operands_of_extreme_and_uneven_magnitude(b200, ref):
         assert normwise(got, want) <= 1e-5, f"{what}: norm-wise error {normwise(got, want)}"
     zero = TensorValue.from_numpy(np.zeros((m, k), np.float32), b200).matmul(TensorValue.from_numpy(b, b200)).numpy()
     assert not zero.any()
+
+
+def test_f32_operands_prepared_once_and_never_stale(b200):
+    """The tensor-core f32 product keeps the two-term fp16 form of an operand until the operand is written: every
+    orientation of one tensor shares it (forward, G.B^T, A^T.G), and any write - a recorded op, an upload, an in-place
+    update - must drop it."""
+    rng = np.random.default_rng(3)
+    m, k, n = 512, 384, 640
+    a, b = rng.normal(0, 0.5, (m, k)).astype(np.float32), rng.normal(0, 0.5, (k, n)).astype(np.float32)
+    A, B = TensorValue.from_numpy(a, b200), TensorValue.from_numpy(b, b200)
+    G = TensorValue.from_numpy(rng.normal(0, 0.5, (m, n)).astype(np.float32), b200)
+    g = G.numpy()
+    s0 = b200.stats()
+    c = A.matmul(B).numpy()
+    da = G.matmul(B.transpose(0, 1)).numpy()            # B again, now K-major instead of MN-major
+    db = A.transpose(0, 1).matmul(G).numpy()            # A and G again, both MN-major
+    s1 = b200.stats()
+    assert s1["prepared_operand_builds"] - s0["prepared_operand_builds"] == 3, "A, B and G are prepared once each"
+    assert s1["prepared_operand_hits"] - s0["prepared_operand_hits"] == 3
+    a64, b64, g64 = a.astype(np.float64), b.astype(np.float64), g.astype(np.float64)
+    assert normwise(c, a64 @ b64) <= 1e-5 and normwise(da, g64 @ b64.T) <= 1e-5 and normwise(db, a64.T @ g64) <= 1e-5
+    # a recorded in-place update of B, an upload into A, a full overwrite of G: every later product sees the new values
+    B *= 2.0
+    a2 = rng.normal(0, 0.5, (m, k)).astype(np.float32)
+    b200.copy(a2.ctypes.data, F32, A.storage.data, F32, a2.size)
+    assert normwise(A.matmul(B).numpy(), a2.astype(np.float64) @ (2.0 * b64)) <= 1e-5
+    b200.fill(1.0, F32, G.deviceParams())
+    assert normwise(A.transpose(0, 1).matmul(G).numpy(), a2.astype(np.float64).T @ np.ones((m, n))) <= 1e-5
+    # a view of part of a tensor, and a write into another part of the same storage
+    big = TensorValue.from_numpy(rng.normal(0, 0.5, (2 * m, k)).astype(np.float32), b200)
+    upper = TensorValue(big.storage, (m, k), (k, 1), 0, F32, b200)
+    lower = TensorValue(big.storage, (m, k), (k, 1), m * k, F32, b200)
+    want = big.numpy().astype(np.float64)
+    first = upper.matmul(B).numpy()
+    lower *= 0.0                                         # does not touch `upper`
+    again = upper.matmul(B).numpy()
+    assert np.array_equal(first, again) and normwise(first, want[:m] @ (2.0 * b64)) <= 1e-5
+    upper += 1.0
+    assert normwise(upper.matmul(B).numpy(), (want[:m] + 1.0) @ (2.0 * b64)) <= 1e-5
+    # freed and reused storage: a new tensor in the old block is a new operand
+    for scale in (1.0, 3.0):
+        t = TensorValue.from_numpy(a * np.float32(scale), b200)
+        assert normwise(t.matmul(B).numpy(), (a64 * scale) @ (2.0 * b64)) <= 1e-5
+        del t
