@@ -38,7 +38,9 @@ class Config(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("tf32x3_matmul", ctypes.c_int32),
         ("dry_run", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 6),
+        ("inject_alloc_limit_bytes", ctypes.c_uint64),
+        ("inject_nvrtc_failures", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 3),
     ]
 
 
@@ -95,6 +97,7 @@ SIGNATURES = {
     "aixb200_event_elapsed_ms": ([_D, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)], ctypes.c_int),
     "aixb200_event_destroy": ([_D, ctypes.c_void_p], ctypes.c_int),
     "aixb200_flush_l2": ([_D], ctypes.c_int),
+    "aixb200_self_test_bounded_wait": ([_D, ctypes.c_uint64], ctypes.c_int),
     "aixb200_comm_unique_id": ([ctypes.c_void_p], ctypes.c_int),
     "aixb200_comm_init": ([_D, ctypes.c_int, ctypes.c_int, ctypes.c_void_p], ctypes.c_int),
     "aixb200_all_reduce": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),

@@ -217,6 +217,7 @@ int aixb200_event_destroy(aixb200_device* dev, aixb200_event* ev)
 }
 
 int aixb200_flush_l2(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.flushL2(); }); }
+int aixb200_self_test_bounded_wait(aixb200_device* dev, uint64_t limitNs) { return guarded(dev, [&](Device& d) { d.selfTestBoundedWait(limitNs); }); }
 
 int aixb200_comm_unique_id(void* idOut)
 {

@@ -114,7 +114,12 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     {
         m_name = "B200 (dry run, no GPU)";
         RawMemoryOps raw;
-        raw.allocate = [](size_t bytes) { return std::malloc(bytes); };
+        const uint64_t injected = m_cfg.inject_alloc_limit_bytes;
+        raw.allocate = [injected, this](size_t bytes) -> void*
+        {
+            if (injected && m_allocator && m_allocator->bytesReserved() + bytes > injected) return nullptr;     // injected out-of-memory
+            return std::malloc(bytes);
+        };
         raw.free = [](void* p) { std::free(p); };
         m_allocator = std::make_unique<CachingAllocator>(raw, uint64_t(1) << 30);
         return;
@@ -144,8 +149,10 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     const bool managed = m_cfg.managed_memory != 0;
     const int ordinal = m_cfg.ordinal;
     RawMemoryOps raw;
-    raw.allocate = [managed, ordinal, this](size_t bytes) -> void*
+    const uint64_t injected = m_cfg.inject_alloc_limit_bytes;
+    raw.allocate = [managed, ordinal, injected, this](size_t bytes) -> void*
     {
+        if (injected && m_allocator && m_allocator->bytesReserved() + bytes > injected) return nullptr;         // injected out-of-memory
         void* p = nullptr;
         cudaError_t e = managed ? cudaMallocManaged(&p, bytes) : cudaMalloc(&p, bytes);
         if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return nullptr; }
@@ -246,7 +253,10 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
     e.hi = e.lo + ((rows - 1) * pitch + cols) * sizeof(float);
     e.rows = rows; e.cols = cols; e.pitch = pitch;
     e.paddedCols = (cols + 127) & ~uint64_t(127);
-    e.bytes = static_cast<size_t>(rows) * 2 * e.paddedCols * sizeof(uint16_t);
+    // AIXB200_GEMM_TERM_PAD: extra fp16 elements per row (a multiple of 8), so that rows do not sit a power of two apart
+    static const uint64_t pad = []{ const char* v = std::getenv("AIXB200_GEMM_TERM_PAD"); return v ? (std::strtoull(v, nullptr, 10) & ~uint64_t(7)) : uint64_t(0); }();
+    e.termPitch = 2 * e.paddedCols + pad;
+    e.bytes = static_cast<size_t>(rows) * e.termPitch * sizeof(uint16_t);
     // budget: an eighth of the device memory, oldest entries go first
     const uint64_t budget = std::max<uint64_t>(m_totalMemory / 8, e.bytes);
     while (!m_preparedTerms.empty() && (m_preparedBytes + e.bytes > budget || m_freeTermSlots.empty()))
@@ -538,6 +548,12 @@ std::vector<char> Device::compile(const std::string& source, const std::string& 
         }
     }
 
+    if (m_cfg.inject_nvrtc_failures > 0)
+    {
+        --m_cfg.inject_nvrtc_failures;
+        m_lastSource = source;
+        failRuntime("NVRTC failed to compile a fused kernel: injected failure (aixb200_config.inject_nvrtc_failures)");
+    }
     const auto t0 = std::chrono::steady_clock::now();
     nvrtcProgram prog = nullptr;
     if (nvrtcCreateProgram(&prog, source.c_str(), (entry + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
@@ -1059,6 +1075,16 @@ void Device::flushL2()
     AIXB200_CTX();
     kernels::flushL2(ctx, m_l2Flush, m_l2FlushBytes);
     AIXB200_DONE("flushL2");
+}
+
+void Device::selfTestBoundedWait(uint64_t limitNs)
+{
+    if (dryRun()) failInvalid("the bounded-wait self-test needs a GPU");
+    flush();
+    AIXB200_CTX();
+    gemm::launchBoundedWaitSelfTest(ctx, limitNs);
+    m_checkErrorWord = true;
+    AIXB200_DONE("bounded-wait self-test");
 }
 
 void Device::fillStats(aixb200_stats* out) const

@@ -81,6 +81,7 @@ public:
 
     // timing / diagnostics
     void flushL2();
+    void selfTestBoundedWait(uint64_t limitNs);
     void fillStats(aixb200_stats* out) const;
     const char* lastKernelSource() const { return m_lastSource.empty() ? nullptr : m_lastSource.c_str(); }
 
@@ -121,6 +122,7 @@ public:
         const char* lo; const char* hi;     // bytes of the source tensor
         uint64_t rows, cols, pitch;         // source layout: rows x cols f32, `pitch` elements between rows
         uint64_t paddedCols;                // multiple of 128
+        uint64_t termPitch;                 // fp16 elements between rows of `terms`: 2 * paddedCols plus an optional pad
         void*    terms;                     // device block of rows * 2 * paddedCols fp16
         uint32_t slot;                      // index of the bit pattern of max|x| in the slot block
         size_t   bytes;

@@ -27,4 +27,8 @@ struct Problem
 // Returns false (having launched nothing) when the caller must use the CUDA-core kernel instead.
 bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& problem);
 
+// One tiny kernel that waits, with the matmul's own bounded-wait routine, on an mbarrier nobody arrives at, gives up after
+// limitNs and raises the device's error word (LaunchContext::scratch + kScratchTimeoutOffset). No TMA, no tensor-core work.
+void launchBoundedWaitSelfTest(const kernels::LaunchContext& ctx, uint64_t limitNs);
+
 }   // namespace aixb200::gemm

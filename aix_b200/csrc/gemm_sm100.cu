@@ -121,7 +121,7 @@ __device__ __forceinline__ uint64_t globalTimerNs()
 }
 // Bounded wait: returns false (and raises *abortFlag) when the barrier did not flip within kWaitLimitNs or when
 // another role already gave up.
-__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag)
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag, uint64_t limitNs = kWaitLimitNs)
 {
     if (mbarTest(bar, parity)) return true;
     const uint64_t start = globalTimerNs();
@@ -131,7 +131,7 @@ __device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatil
         if ((++spins & 63u) == 0)
         {
             if (*abortFlag) return false;
-            if (globalTimerNs() - start > kWaitLimitNs) { *abortFlag = 1; return false; }
+            if (globalTimerNs() - start > limitNs) { *abortFlag = 1; return false; }
         }
     }
     return true;
@@ -778,11 +778,15 @@ __device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const
     }
 }
 
-template <bool Tf32>
+// Mode 0: 16-bit operands, one pass. Mode 1: f32 as a TF32 main pass plus two bf16 cross-term passes. Mode 2: f32 as three
+// fp16 passes over two-term operands - every pass is a 16-bit pass, so nothing in the issue loops depends on the pass.
+template <int Mode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
                const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ KernelParams p)
 {
+    constexpr bool Tf32 = Mode != 0;
+    constexpr bool HalfTerms = Mode == 2;
     extern __shared__ uint8_t rawSmem[];
     PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -832,8 +836,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     {
                     // hybrid scheme: two bf16 cross-term passes (stages of 128) before the TF32 main pass (stages of 64);
                     // half-term scheme: three fp16 passes, all with stages of 128 (h1.h0', h0.h1', h0.h0')
-                    const bool cross = Tf32 && (passIndex < 2 || p.halfTerms);
-                    const bool halved = cross && !p.halfTerms;
+                    const bool cross = Tf32 && (passIndex < 2 || HalfTerms);
+                    const bool halved = cross && !HalfTerms;
                     const uint32_t first = halved ? kbBegin >> 1 : kbBegin, count = halved ? kbCount >> 1 : kbCount;
                     const uint32_t atomK = cross ? 64u : p.atomK;
                     const CUtensorMap* ma = cross ? &mapA16 : &mapA;
@@ -906,20 +910,20 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t kbCount = min(w.kbCount - c * p.chunkBlocks, p.chunkBlocks);
                 // f32 problems: kbCount bf16 stages (two cross-term passes of kbCount / 2 stages of 128), then kbCount
                 // TF32 stages of 64
-                const uint32_t stagesInChunk = Tf32 ? (p.halfTerms ? 3 * kbCount : 2 * kbCount) : kbCount;
+                const uint32_t stagesInChunk = Tf32 ? (HalfTerms ? 3 * kbCount : 2 * kbCount) : kbCount;
                 for (uint32_t it = 0; it < stagesInChunk; ++it)
                 {
                     if (!mbarWait(&s.full[stage], phase, abortFlag)) { ok = false; break; }
                     fenceAfterSync();
                     const uint32_t aLo = descLoA + stage * (aStageBytes >> 4), bLo = descLoB + stage * (bStageBytes >> 4);
-                    const bool cross = Tf32 && (p.halfTerms || it < kbCount);
+                    const bool cross = Tf32 && (HalfTerms || it < kbCount);
                     #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j)
                     {
                         const uint64_t da = descHiA | static_cast<uint64_t>(aLo + aOff[j]);
                         const uint64_t db = descHiB | static_cast<uint64_t>(bLo + bOff[j]);
-                        if (cross) ummaPair<false>(tmemD, da, db, idesc16, (it | j) != 0 ? 1u : 0u);
-                        else       ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
+                        if (HalfTerms || cross) ummaPair<false>(tmemD, da, db, idesc16, (it | j) != 0 ? 1u : 0u);
+                        else                    ummaPair<Tf32>(tmemD, da, db, idesc, (it | j) != 0 ? 1u : 0u);
                     }
                     ummaCommitPair(&s.empty[stage]);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
@@ -1180,7 +1184,7 @@ __global__ void __launch_bounds__(256) absMaxKernel(const float* __restrict__ sr
 }
 
 //   terms[rows][2*kPad]  [ h0 | h1 ] with h0 = fp16(s*a), h1 = fp16(s*a - h0), s = halfTermScale(max|a|):  s*a = h0 + h1 to 22 bits
-__device__ __forceinline__ void splitEmitHalf(const float (&v)[8], float scale, uint32_t r, uint32_t c, uint32_t kPad, uint16_t* __restrict__ terms)
+__device__ __forceinline__ void splitEmitHalf(const float (&v)[8], float scale, uint32_t r, uint32_t c, uint32_t kPad, uint32_t outPitch, uint16_t* __restrict__ terms)
 {
     uint32_t h0[4], h1[4];
     #pragma unroll
@@ -1191,14 +1195,14 @@ __device__ __forceinline__ void splitEmitHalf(const float (&v)[8], float scale, 
         h0[j] = static_cast<uint32_t>(a0) | (static_cast<uint32_t>(a1) << 16);
         h1[j] = static_cast<uint32_t>(dev::f32ToF16(x0 - dev::f16ToF32(a0))) | (static_cast<uint32_t>(dev::f32ToF16(x1 - dev::f16ToF32(a1))) << 16);
     }
-    uint16_t* out = terms + static_cast<uint64_t>(r) * (2ull * kPad) + c;
+    uint16_t* out = terms + static_cast<uint64_t>(r) * outPitch + c;
     *reinterpret_cast<uint4*>(out) = make_uint4(h0[0], h0[1], h0[2], h0[3]);
     *reinterpret_cast<uint4*>(out + kPad) = make_uint4(h1[0], h1[1], h1[2], h1[3]);
 }
 
 template <bool Transposed>
 __global__ void __launch_bounds__(256) splitF16Kernel(const float* __restrict__ src, uint64_t rowStride, uint64_t colStride, uint32_t rows,
-                                                      uint32_t k, uint32_t kPad, uint16_t* __restrict__ terms, uint32_t vectorLoads,
+                                                      uint32_t k, uint32_t kPad, uint32_t outPitch, uint16_t* __restrict__ terms, uint32_t vectorLoads,
                                                       const uint32_t* __restrict__ maxBits)
 {
     const float scale = halfTermScale(*maxBits);
@@ -1223,7 +1227,7 @@ __global__ void __launch_bounds__(256) splitF16Kernel(const float* __restrict__ 
                 #pragma unroll
                 for (uint32_t j = 0; j < 8; ++j) v[j] = (c + j < k) ? in[j * colStride] : 0.f;
             }
-            splitEmitHalf(v, scale, r, c, kPad, terms);
+            splitEmitHalf(v, scale, r, c, kPad, outPitch, terms);
         }
     }
     else
@@ -1260,14 +1264,14 @@ __global__ void __launch_bounds__(256) splitF16Kernel(const float* __restrict__ 
             float v[8];
             #pragma unroll
             for (uint32_t j = 0; j < 8; ++j) v[j] = tile[r][kg + j];
-            splitEmitHalf(v, scale, r0 + r, c0 + kg, kPad, terms);
+            splitEmitHalf(v, scale, r0 + r, c0 + kg, kPad, outPitch, terms);
         }
     }
 }
 
 // max|x| of the operand into *slot (zeroed beforehand), then its two-term fp16 split.
 void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uint64_t rowStride, uint64_t colStride, uint32_t rows, uint32_t k,
-                         uint32_t kPad, uint16_t* terms, uint32_t* slot)
+                         uint32_t kPad, uint32_t outPitch, uint16_t* terms, uint32_t* slot)
 {
     const bool aligned = reinterpret_cast<uintptr_t>(src) % 16 == 0;
     const unsigned maxGrid = static_cast<unsigned>(smCount) * 8;
@@ -1276,7 +1280,7 @@ void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uin
         const uint32_t vec = colStride == 1 && aligned && rowStride % 4 == 0 && k % 4 == 0;
         const uint64_t items = static_cast<uint64_t>(rows) * (vec ? k / 4 : k);
         absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, rows, k, rowStride, colStride, vec, slot);
-        splitF16Kernel<false><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, terms,
+        splitF16Kernel<false><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, outPitch, terms,
                                                                                       colStride == 1 && aligned && rowStride % 4 == 0, slot);
     }
     else
@@ -1284,7 +1288,7 @@ void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uin
         const uint32_t vec = aligned && colStride % 4 == 0 && rows % 4 == 0;
         const uint64_t items = static_cast<uint64_t>(k) * (vec ? rows / 4 : rows);
         absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, k, rows, colStride, rowStride, vec, slot);
-        splitF16Kernel<true><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, terms,
+        splitF16Kernel<true><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, outPitch, terms,
                                                                                      aligned && colStride % 4 == 0, slot);
     }
 }
@@ -1395,6 +1399,38 @@ bool classify(const void* base, uint64_t rowStride, uint64_t colStride, uint64_t
 }
 
 }   // namespace
+
+namespace
+{
+// The give-up path of mbarWait on its own: thread 0 waits for a phase that never completes, the wait runs out after
+// limitNs, and the kernel reports it the way the matmul kernels do. The limit is capped so that a wrong argument cannot
+// park the kernel for long.
+__global__ void boundedWaitSelfTestKernel(uint64_t limitNs, uint32_t* errorWord)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abortFlag;
+    if (threadIdx.x == 0)
+    {
+        mbarInit(&bar, 1);
+        abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        const uint64_t limit = limitNs < 100000000ull ? limitNs : 100000000ull;
+        mbarWait(&bar, 0, &abortFlag, limit);           // nobody arrives: returns false once the limit has passed
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && abortFlag) atomicExch(errorWord, 1u);
+}
+}   // namespace
+
+void launchBoundedWaitSelfTest(const kernels::LaunchContext& ctx, uint64_t limitNs)
+{
+    boundedWaitSelfTestKernel<<<1, 32, 0, ctx.stream>>>(limitNs, reinterpret_cast<uint32_t*>(static_cast<char*>(ctx.scratch) + kernels::kScratchTimeoutOffset));
+    if (ctx.launches) ++*ctx.launches;
+}
 
 bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& q)
 {
@@ -1545,20 +1581,21 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                         e = device.addPreparedTerms(base, rows, cols, pitch);
                         if (cudaMemsetAsync(device.preparedSlot(e->slot), 0, 4, ctx.stream) != cudaSuccess) return false;
                         launchHalfTermSplit(ctx.stream, ctx.smCount, src, pitch, 1, static_cast<uint32_t>(rows), static_cast<uint32_t>(cols),
-                                            static_cast<uint32_t>(e->paddedCols), static_cast<uint16_t*>(e->terms), device.preparedSlot(e->slot));
+                                            static_cast<uint32_t>(e->paddedCols), static_cast<uint32_t>(e->termPitch), static_cast<uint16_t*>(e->terms),
+                                            device.preparedSlot(e->slot));
                         preparedLaunches += 2;
                     }
                     out->terms = static_cast<const uint16_t*>(e->terms);
                     out->scale = device.preparedSlot(e->slot);
                     out->mnMajor = !kDense;
                     out->plane = static_cast<uint32_t>(e->paddedCols);
-                    const uint64_t rowBytes = 2ull * e->paddedCols * 2;
+                    const uint64_t rowBytes = e->termPitch * 2;
                     return kDense ? makeMapK3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, e->terms, mn, 2ull * e->paddedCols, rowBytes, 64, boxRows)
                                   : makeMap3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, e->terms, 2ull * e->paddedCols, p.k, rowBytes, 128, boxRows / 64);
                 }
                 uint16_t* terms = static_cast<uint16_t*>(device.temporary(static_cast<size_t>(mn) * 2 * kPad * 2));
                 if (cudaMemsetAsync(tempSlot, 0, 4, ctx.stream) != cudaSuccess) return false;
-                launchHalfTermSplit(ctx.stream, ctx.smCount, src, mnStride, kStride, static_cast<uint32_t>(mn), p.k, kPad, terms, tempSlot);
+                launchHalfTermSplit(ctx.stream, ctx.smCount, src, mnStride, kStride, static_cast<uint32_t>(mn), p.k, kPad, 2 * kPad, terms, tempSlot);
                 preparedLaunches += 2;
                 out->terms = terms; out->scale = tempSlot; out->mnMajor = false; out->plane = kPad;
                 return makeMapK3d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, terms, mn, 2ull * kPad, 2ull * kPad * 2, 64, boxRows);
@@ -1657,8 +1694,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
         {
             cudaFuncSetAttribute(gemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
             cudaFuncSetAttribute(gemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes));
-            cudaFuncSetAttribute(gemmPairKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
-            cudaFuncSetAttribute(gemmPairKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(static_cast<unsigned>(ctx.smCount) & ~1u);
             cfg.blockDim = dim3(kThreads);
@@ -1668,7 +1706,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
             cfg.attrs = &attr;
             cfg.numAttrs = 1;
-            if (cudaOccupancyMaxActiveClusters(&state.maxClusters, gemmPairKernel<false>, &cfg) != cudaSuccess || state.maxClusters <= 0)
+            if (cudaOccupancyMaxActiveClusters(&state.maxClusters, gemmPairKernel<0>, &cfg) != cudaSuccess || state.maxClusters <= 0)
             {
                 cudaGetLastError();
                 state.maxClusters = ctx.smCount / 2;
@@ -1723,8 +1761,9 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             const size_t es = dtypeSize(q.dtype);
             p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 32) ? 1u : 0u;
         }
-        if (tf32) gemmPairKernel<true><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
-        else      gemmPairKernel<false><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        if (!tf32)            gemmPairKernel<0><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        else                  gemmPairKernel<1><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
         if (ctx.launches) ++*ctx.launches;
         return true;
     }

@@ -107,6 +107,8 @@ class DeviceB200:
         if status == C.OK:
             return
         msg = self._lib.aixb200_last_error(self._h).decode()
+        if status == C.ERR_TIMEOUT:
+            raise TimeoutError(msg)
         raise (ValueError if status == C.ERR_INVALID else RuntimeError)(msg)
 
     @staticmethod
@@ -218,6 +220,9 @@ class DeviceB200:
         return s.decode() if s else None
 
     def flushL2(self):  self._check(self._lib.aixb200_flush_l2(self._h))
+
+    def selfTestBoundedWait(self, limit_ns: int = 1_000_000):
+        self._check(self._lib.aixb200_self_test_bounded_wait(self._h, limit_ns))
 
     def createEvent(self) -> int:
         ev = ctypes.c_void_p()

@@ -4,7 +4,7 @@ than the 126 MB L2 but hold well under a few GB on the device.
     python -m aix_b200.profile_cases <case> [repeats]
 
 cases: chain_f32 chain_bf16 chain_sum_f32 chain_sum_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
-       gemm_bf16_k1024 gemm_f32_4096 gemm_f32_k1024 adam_f32 mlp_f32
+       gemm_bf16_k1024 gemm_f32_4096 gemm_f32_4096_nt gemm_f32_4096_tn gemm_f32_k1024 adam_f32 mlp_f32
 Prints the device time per repeat measured with events on the device's stream.
 """
 import sys
@@ -45,6 +45,16 @@ def build(dev, case):
     if case == "colsum_f32":
         x = _rand(dev, (16384, 4096), C.F32, 0)
         return lambda: x.sum(0)
+    if case in ("gemm_f32_4096_nt", "gemm_f32_4096_tn"):
+        # the backward forms of the 4096^3 f32 product: G . B^T (all K-major) and A^T . G (both operands MN-major)
+        a, b = _rand(dev, (4096, 4096), C.F32, 0, 0.05), _rand(dev, (4096, 4096), C.F32, 1, 0.05)
+        return (lambda: a.matmul(b.transpose(0, 1))) if case.endswith("_nt") else (lambda: a.transpose(0, 1).matmul(b))
+    if case in ("gemm_f16_4096", "gemm_bf16_k12288"):
+        # probes: the f16 form of the 16-bit kernel, and a contraction three times as long (the depth of the three f32 passes)
+        dt = C.F16 if case.startswith("gemm_f16") else C.BF16
+        k = 12288 if case.endswith("k12288") else 4096
+        a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (4096, k), dt, 1, 0.05)
+        return lambda: a.matmul(b.transpose(0, 1))
     if case in ("gemm_bf16_k1024", "gemm_f32_k1024", "gemm_f32_4096"):
         # the MLP's shapes: batch 4096, a 1024-wide or 4096-wide contraction
         dt = C.BF16 if "bf16" in case else C.F32
@@ -79,7 +89,8 @@ def main():
     dev = DeviceB200(0)
     fn = build(dev, case)
     dev.synchronize()
-    out = fn()
+    for _ in range(3):                   # warm-up: kernels compiled and loaded, allocator cache populated
+        out = fn()
     dev.synchronize()
     e0, e1 = dev.createEvent(), dev.createEvent()
     dev.flushL2()

@@ -94,7 +94,10 @@ typedef struct aixb200_config
                                     (TF32 main pass + bf16 cross terms), which remains behind AIXB200_GEMM_F32=hybrid. */
     int32_t  dry_run;            /* 1: no GPU is touched - ops are recorded, planned and compiled with NVRTC but not
                                     launched, and memory comes from malloc (host-logic tests on machines without a GPU) */
-    int32_t  reserved[6];
+    /* Host-side fault injection for tests of the failure paths (nothing on the GPU faults): */
+    uint64_t inject_alloc_limit_bytes; /* non-zero: the raw allocator reports out-of-memory once this many bytes are reserved */
+    int32_t  inject_nvrtc_failures;    /* the next n kernel compilations fail as if NVRTC had returned an error */
+    int32_t  reserved[3];
 } aixb200_config;
 
 void aixb200_default_config(aixb200_config* cfg);
@@ -227,6 +230,11 @@ int aixb200_event_elapsed_ms(aixb200_device* dev, aixb200_event* start, aixb200_
 int aixb200_event_destroy(aixb200_device* dev, aixb200_event* ev);
 /* Writes `bytes` of device memory so that nothing useful stays in L2 (timing hygiene between iterations). */
 int aixb200_flush_l2(aixb200_device* dev);
+/* Self-test of the bounded device-side waits: launches one tiny kernel (no TMA, no tensor-core work) that waits on an
+ * mbarrier nobody arrives at and gives up after `limit_ns`. The kernel returns normally; it raises the device's error
+ * word, and the next aixb200_synchronize returns AIXB200_ERR_TIMEOUT once, after which the device works as before.
+ * This is the path the tensor-core matmul takes if one of its waits ever runs out. */
+int aixb200_self_test_bounded_wait(aixb200_device* dev, uint64_t limit_ns);
 
 /* ---- data-parallel exchange (no reference counterpart: the reference has no multi-device code) ---- */
 #define AIXB200_COMM_ID_BYTES 128
