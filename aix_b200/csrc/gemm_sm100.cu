@@ -46,6 +46,7 @@ constexpr int kStageBytesA = kBlockM * 128;              // 128 rows (or 2 MN at
 constexpr int kStageBytesB = kBlockN * 128;
 constexpr int kStages = 4;
 constexpr int kThreads = 192;
+constexpr int kThreadsHalfTerms = 320;                   // three-fp16-pass f32 kernel: eight epilogue warps (see its epilogue)
 constexpr int kTmemColumns = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;         // 2 s: far beyond any legitimate wait
 
@@ -183,6 +184,14 @@ __device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32])
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -781,7 +790,7 @@ __device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const
 // Mode 0: 16-bit operands, one pass. Mode 1: f32 as a TF32 main pass plus two bf16 cross-term passes. Mode 2: f32 as three
 // fp16 passes over two-term operands - every pass is a 16-bit pass, so nothing in the issue loops depends on the pass.
 template <int Mode>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Mode == 2 ? kThreadsHalfTerms : kThreads, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
                const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ KernelParams p)
 {
@@ -797,7 +806,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < kPairStages; ++i) { mbarInit(&s.full[i], 2); mbarInit(&s.empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], 256); }
+        for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], HalfTerms ? 512 : 256); }   // epilogue threads of the pair
         s.abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -936,6 +945,98 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     else
     {
+        if constexpr (HalfTerms)
+        {
+            // f32 as three fp16 passes: K is cut into chunks whose partial sums must be added in IEEE f32 (the tensor core's
+            // own accumulation truncates). The running sum of the tile lives in REGISTERS: eight epilogue warps - two per
+            // TMEM lane quarter, each owning half of the tile's columns - read every finished chunk from TMEM and add it to
+            // 32 rows x (blockN / 2) columns of sums, one row per thread. Nothing leaves the SM until the tile is complete;
+            // then the sums are scaled back and stored once through shared memory and TMA (or directly when C's rows are
+            // not 16-byte aligned). Per chunk the epilogue costs four TMEM loads and 128 additions per thread, so it never
+            // holds an accumulator long enough to stall the MMA issue.
+            const uint32_t ewarp = warp - 2u, quarter = warp & 3u, half = ewarp >> 2;
+            const uint32_t halfCols = p.blockN >> 1;                         // 128, or 64 for narrow tiles
+            uint8_t* staging = &s.staging[0][0] + ewarp * kWarpStagingBytes; // one 32 x 128-byte buffer per warp
+            float sum[128];
+            uint32_t acc = 0, accPhase = 0;
+            bool ok = true;
+            WorkIterator work(p, clusterId, clusters);
+            WorkItem w;
+            while (ok && work.get(w))
+            {
+                uint32_t tm, tn;
+                tileCoordinates(w.tile, p.tilesM, p.tilesN, p.tileGroup, tm, tn);
+                const uint32_t leaderEmpty = mapToCta(smemAddr(&s.tmemEmpty[0]), 0);
+                for (uint32_t c = 0; c < p.chunks && ok; ++c)
+                {
+                    if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag)) { ok = false; break; }
+                    fenceAfterSync();
+                    const uint32_t taddr = tmemBase + acc * kBlockN + ((quarter * 32u) << 16) + half * halfCols;
+                    #pragma unroll
+                    for (uint32_t strip = 0; strip < 8; ++strip)         // 16 columns per TMEM load: the sums leave few registers to spare
+                    {
+                        if (strip * 16 < halfCols)
+                        {
+                            uint32_t r[16];
+                            tmemLoad16(taddr + strip * 16, r);
+                            tmemLoadWait();
+                            #pragma unroll
+                            for (int i = 0; i < 16; ++i) sum[strip * 16 + i] = (c == 0) ? __uint_as_float(r[i]) : sum[strip * 16 + i] + __uint_as_float(r[i]);
+                        }
+                    }
+                    fenceBeforeSync();
+                    mbarArriveCluster(leaderEmpty + acc * 8);
+                    acc ^= 1u;
+                    if (acc == 0) accPhase ^= 1u;
+                }
+                if (!ok) break;
+                // the tile is complete: undo the operands' scaling (two exact factors, one after the other) and store
+                const float scaleA = halfTermInverseScale(*p.scaleA), scaleB = halfTermInverseScale(*p.scaleB);
+                const uint32_t col0 = tn * p.blockN + half * halfCols;
+                const uint32_t row0 = tm * 256 + rank * 128 + quarter * 32;
+                #pragma unroll
+                for (uint32_t strip = 0; strip < 4; ++strip)
+                {
+                    if (strip * 32 >= halfCols) continue;
+                    if (p.tmaEpilogue)
+                    {
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the buffer's previous slice has been read
+                        __syncwarp();
+                        uint8_t* rowPtr = staging + lane * 128u;
+                        const uint32_t swizzle = lane & 7u;
+                        #pragma unroll
+                        for (uint32_t v = 0; v < 8; ++v)
+                            *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) =
+                                make_uint4(__float_as_uint(sum[strip * 32 + 4 * v] * scaleA * scaleB), __float_as_uint(sum[strip * 32 + 4 * v + 1] * scaleA * scaleB),
+                                           __float_as_uint(sum[strip * 32 + 4 * v + 2] * scaleA * scaleB), __float_as_uint(sum[strip * 32 + 4 * v + 3] * scaleA * scaleB));
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0)
+                        {
+                            tmaStoreTile(&mapC, staging, static_cast<int32_t>(col0 + strip * 32), static_cast<int32_t>(row0), false);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                    else
+                    {
+                        const uint32_t row = row0 + lane;
+                        if (row < p.m)
+                        {
+                            float* out = static_cast<float*>(p.c) + static_cast<size_t>(row) * p.n;
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 32; ++i)
+                            {
+                                const uint32_t col = col0 + strip * 32 + i;
+                                if (col < p.n) out[col] = sum[strip * 32 + i] * scaleA * scaleB;
+                            }
+                        }
+                    }
+                }
+            }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // staging buffers are read, C is written
+        }
+        else
+        {
         const uint32_t quarter = warp & 3u;
         const bool captain = threadIdx.x == 64;                          // first thread of the epilogue warps
         const uint32_t rowInCta = quarter * 32 + lane;
@@ -1012,6 +1113,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (acc == 0) accPhase ^= 1u;
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // staging buffers are read, C is written
+        }
     }
 
     if (threadIdx.x == 0) lingerAfterAbort(abortFlag);
@@ -1612,10 +1714,12 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             p.atomK = 64;
             p.kBlocks = kPad / 128;                              // stages of 128 fp16 elements in all three passes
             {
-                // 512 elements of K per in-TMEM partial sum (AIXB200_GEMM_HCHUNK: stages per partial sum, for measurements only -
-                // longer partial sums leave the f32 error bar)
+                // 256 elements of K per in-TMEM partial sum: the tensor core's accumulation truncates, an error that grows with
+                // the number of MMAs folded into one accumulator, and with the running sums kept in registers a short chunk
+                // costs nothing (measured: 2, 4 and 96 stages per chunk run 4096^3 within 1 % of each other).
+                // AIXB200_GEMM_HCHUNK: stages per partial sum, for measurements only - long chunks leave the f32 error bar.
                 static const int chunkOverride = []{ const char* v = std::getenv("AIXB200_GEMM_HCHUNK"); return v ? std::atoi(v) : 0; }();
-                p.chunkBlocks = chunkOverride > 0 ? static_cast<uint32_t>(chunkOverride) : 4u;
+                p.chunkBlocks = chunkOverride > 0 ? static_cast<uint32_t>(chunkOverride) : 2u;
             }
             p.aLoad3d = p.bLoad3d = 1;
             p.pairABytes = kBlockM * 256; p.pairBBytes = bRows * 256;
@@ -1762,7 +1866,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 32) ? 1u : 0u;
         }
         if (!tf32)            gemmPairKernel<0><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
-        else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
         else                  gemmPairKernel<1><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
         if (ctx.launches) ++*ctx.launches;
         return true;
