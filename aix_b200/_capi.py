@@ -105,6 +105,8 @@ SIGNATURES = {
     "aixb200_reduce_scatter_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32, ctypes.c_double], ctypes.c_int),
     "aixb200_all_gather_async": ([_D, ctypes.c_void_p, _SZ, ctypes.c_uint32], ctypes.c_int),
     "aixb200_comm_rank": ([_D, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "aixb200_comm_inject_backend": ([ctypes.c_int, ctypes.c_int], ctypes.c_int),
+    "aixb200_comm_injected_counters": ([ctypes.POINTER(ctypes.c_int)] * 3, ctypes.c_int),
     "aixb200_comm_wait": ([_D], ctypes.c_int),
     "aixb200_comm_wait_for": ([_D, ctypes.c_void_p, _SZ], ctypes.c_int),
     "aixb200_comm_destroy": ([_D], ctypes.c_int),

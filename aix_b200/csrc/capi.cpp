@@ -239,6 +239,13 @@ int aixb200_all_gather_async(aixb200_device* dev, void* data, size_t count, uint
 { return guarded(dev, [&](Device& d) { d.allGatherAsync(data, count, dtype); }); }
 int aixb200_comm_rank(aixb200_device* dev, int* rank, int* nranks)
 { return guarded(dev, [&](Device& d) { if (rank) *rank = d.commRank(); if (nranks) *nranks = d.commSize(); }); }
+int aixb200_comm_inject_backend(int mode, int errorAfterPolls)
+{
+    if (mode < 0 || mode > 2) return AIXB200_ERR_INVALID;
+    Comm::injectBackend(mode, errorAfterPolls);
+    return AIXB200_OK;
+}
+int aixb200_comm_injected_counters(int* inits, int* polls, int* aborts) { Comm::injectedCounters(inits, polls, aborts); return AIXB200_OK; }
 int aixb200_comm_wait(aixb200_device* dev) { return guarded(dev, [&](Device& d) { d.commWait(); }); }
 int aixb200_comm_wait_for(aixb200_device* dev, const void* data, size_t bytes)
 { return guarded(dev, [&](Device& d) { d.commWaitFor(data, bytes); }); }

@@ -3,6 +3,15 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <chrono>
+#include <cstdlib>
+#include <thread>
+
+#if __has_include(<nccl.h>)
+#include <nccl.h>              // only for ncclConfig_t and its initializer (non-blocking initialisation)
+#define AIXB200_HAVE_NCCL_CONFIG 1
+#endif
+
 namespace aixb200
 {
 
@@ -13,12 +22,16 @@ namespace
 typedef struct { char internal[128]; } NcclUniqueId;
 typedef void* NcclComm;
 enum { kNcclSum = 0, kNcclAvg = 4 };
+enum { kNcclSuccess = 0, kNcclRemoteError = 6, kNcclInProgress = 7 };
 enum { kNcclInt32 = 2, kNcclInt64 = 4, kNcclHalf = 6, kNcclFloat = 7, kNcclDouble = 8, kNcclBfloat16 = 9 };
 
 struct NcclApi
 {
     int (*getUniqueId)(NcclUniqueId*) = nullptr;
     int (*commInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
+    int (*commInitRankConfig)(NcclComm*, int, NcclUniqueId, int, void*) = nullptr;
+    int (*commGetAsyncError)(NcclComm, int*) = nullptr;
+    int (*commAbort)(NcclComm) = nullptr;
     int (*commDestroy)(NcclComm) = nullptr;
     int (*allReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*reduceScatter)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
@@ -27,8 +40,41 @@ struct NcclApi
     void* handle = nullptr;
 };
 
+// ---- injected back end for host-side tests of the failure paths: no library, no GPU, no network -------------------------
+// mode 1: initialisation never completes (the communicator stays "in progress"); mode 2: initialisation and collectives
+// succeed, and from the (errorAfterPolls + 1)-th status query on the communicator reports a remote error.
+struct Injected { int mode = 0; int errorAfterPolls = 0; int inits = 0, polls = 0, aborts = 0, destroys = 0; };
+Injected g_injected;
+int fakeGetUniqueId(NcclUniqueId* id) { std::memset(id, 0, sizeof(*id)); return kNcclSuccess; }
+int fakeInitRank(NcclComm* comm, int, NcclUniqueId, int) { ++g_injected.inits; *comm = &g_injected; return kNcclSuccess; }
+int fakeInitRankConfig(NcclComm* comm, int, NcclUniqueId, int, void*)
+{
+    ++g_injected.inits;
+    *comm = &g_injected;
+    return g_injected.mode == 1 ? kNcclInProgress : kNcclSuccess;
+}
+int fakeGetAsyncError(NcclComm, int* state)
+{
+    ++g_injected.polls;
+    *state = g_injected.mode == 1 ? kNcclInProgress : ((g_injected.mode == 2 && g_injected.polls > g_injected.errorAfterPolls) ? kNcclRemoteError : kNcclSuccess);
+    return kNcclSuccess;
+}
+int fakeAbort(NcclComm) { ++g_injected.aborts; return kNcclSuccess; }
+int fakeDestroy(NcclComm) { ++g_injected.destroys; return kNcclSuccess; }
+int fakeAllReduce(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) { return kNcclSuccess; }
+int fakeAllGather(const void*, void*, size_t, int, NcclComm, cudaStream_t) { return kNcclSuccess; }
+const char* fakeErrorString(int code) { return code == kNcclRemoteError ? "remote process exited or there was a network error (injected)" : "injected back end"; }
+
 NcclApi& nccl()
 {
+    static NcclApi fake;
+    if (g_injected.mode != 0)
+    {
+        fake.getUniqueId = fakeGetUniqueId; fake.commInitRank = fakeInitRank; fake.commInitRankConfig = fakeInitRankConfig;
+        fake.commGetAsyncError = fakeGetAsyncError; fake.commAbort = fakeAbort; fake.commDestroy = fakeDestroy;
+        fake.allReduce = fakeAllReduce; fake.reduceScatter = fakeAllReduce; fake.allGather = fakeAllGather; fake.getErrorString = fakeErrorString;
+        return fake;
+    }
     static NcclApi api;
     if (api.handle) return api;
     const char* names[] = {"libnccl.so.2", "libnccl.so"};
@@ -42,6 +88,9 @@ NcclApi& nccl()
     api.getUniqueId = reinterpret_cast<decltype(api.getUniqueId)>(sym("ncclGetUniqueId"));
     api.commInitRank = reinterpret_cast<decltype(api.commInitRank)>(sym("ncclCommInitRank"));
     api.commDestroy = reinterpret_cast<decltype(api.commDestroy)>(sym("ncclCommDestroy"));
+    api.commInitRankConfig = reinterpret_cast<decltype(api.commInitRankConfig)>(sym("ncclCommInitRankConfig"));
+    api.commGetAsyncError = reinterpret_cast<decltype(api.commGetAsyncError)>(sym("ncclCommGetAsyncError"));
+    api.commAbort = reinterpret_cast<decltype(api.commAbort)>(sym("ncclCommAbort"));
     api.allReduce = reinterpret_cast<decltype(api.allReduce)>(sym("ncclAllReduce"));
     api.reduceScatter = reinterpret_cast<decltype(api.reduceScatter)>(sym("ncclReduceScatter"));
     api.allGather = reinterpret_cast<decltype(api.allGather)>(sym("ncclAllGather"));
@@ -64,20 +113,103 @@ void Comm::uniqueId(void* out128)
     std::memcpy(out128, &id, sizeof(id));
 }
 
+void Comm::injectBackend(int mode, int errorAfterPolls)
+{
+    g_injected = Injected{};
+    g_injected.mode = mode;
+    g_injected.errorAfterPolls = errorAfterPolls;
+}
+bool Comm::backendInjected() { return g_injected.mode != 0; }
+void Comm::injectedCounters(int* inits, int* polls, int* aborts)
+{
+    if (inits) *inits = g_injected.inits;
+    if (polls) *polls = g_injected.polls;
+    if (aborts) *aborts = g_injected.aborts;
+}
+
+// Blocking initialisation by default. With AIXB200_COMM_INIT_TIMEOUT_MS set, the communicator is created non-blocking
+// (ncclCommInitRankConfig, config.blocking = 0) and polled with ncclCommGetAsyncError until it is ready or the deadline
+// has passed - a rank that never joins then costs a timeout and an ncclCommAbort instead of a hang. A communicator created
+// that way stays non-blocking: every later call may report "in progress" and is polled to completion the same way.
 Comm::Comm(int rank, int nranks, const void* id128, int ordinal) : m_rank(rank), m_nranks(nranks)
 {
     if (nranks < 1 || rank < 0 || rank >= nranks) failInvalid("comm_init: bad rank / nranks");
     NcclUniqueId id;
     std::memcpy(&id, id128, sizeof(id));
-    cudaSetDevice(ordinal);
+    if (!backendInjected()) cudaSetDevice(ordinal);
+    const char* limit = std::getenv("AIXB200_COMM_INIT_TIMEOUT_MS");
+    m_timeoutMs = (limit && *limit) ? std::atol(limit) : 0;
     NcclComm comm = nullptr;
+#ifdef AIXB200_HAVE_NCCL_CONFIG
+    if (m_timeoutMs > 0)
+    {
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.blocking = 0;
+        m_nonBlocking = true;
+        const int r = nccl().commInitRankConfig(&comm, nranks, id, rank, &config);
+        m_comm = comm;
+        if (r != kNcclSuccess && r != kNcclInProgress) { abortOnce(); checkNccl(r, "ncclCommInitRankConfig"); }
+        waitUntilReady("ncclCommInitRankConfig");
+        return;
+    }
+#endif
     checkNccl(nccl().commInitRank(&comm, nranks, id, rank), "ncclCommInitRank");
     m_comm = comm;
 }
 
 Comm::~Comm()
 {
-    if (m_comm) nccl().commDestroy(m_comm);
+    if (m_comm && !m_aborted) nccl().commDestroy(m_comm);
+}
+
+void Comm::abortOnce()
+{
+    if (m_comm && !m_aborted) nccl().commAbort(m_comm);
+    m_aborted = true;
+}
+
+// Polls the communicator's state until it leaves "in progress". A deadline that passes aborts the communicator and
+// reports a timeout; an error state aborts it and reports the error.
+void Comm::waitUntilReady(const char* what)
+{
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(m_timeoutMs > 0 ? m_timeoutMs : 120000);
+    for (;;)
+    {
+        int state = kNcclSuccess;
+        const int r = nccl().commGetAsyncError(m_comm, &state);
+        if (r != kNcclSuccess) { abortOnce(); checkNccl(r, "ncclCommGetAsyncError"); }
+        if (state == kNcclSuccess) return;
+        if (state != kNcclInProgress)
+        {
+            abortOnce();
+            failRuntime(std::string(what) + ": asynchronous NCCL error: " + nccl().getErrorString(state) + "; the communicator was aborted");
+        }
+        if (std::chrono::steady_clock::now() > deadline)
+        {
+            abortOnce();
+            throw Error(AIXB200_ERR_TIMEOUT, std::string(what) + " did not complete within " + std::to_string(m_timeoutMs > 0 ? m_timeoutMs : 120000) +
+                                             " ms (a rank that never joined?); the communicator was aborted");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+}
+
+// One status query: an asynchronous error (a peer that died, a network fault) surfaces at the next call instead of as a
+// hang in a later collective.
+void Comm::checkAsyncError(const char* what)
+{
+    if (m_aborted) failRuntime(std::string(what) + ": the communicator was aborted after an earlier failure");
+    int state = kNcclSuccess;
+    if (nccl().commGetAsyncError(m_comm, &state) != kNcclSuccess) return;
+    if (state == kNcclSuccess || state == kNcclInProgress) return;
+    abortOnce();
+    failRuntime(std::string(what) + ": asynchronous NCCL error: " + nccl().getErrorString(state) + "; the communicator was aborted");
+}
+
+void Comm::finishCall(int r, const char* what)
+{
+    if (r == kNcclInProgress && m_nonBlocking) { waitUntilReady(what); return; }
+    checkNccl(r, what);
 }
 
 static int ncclType(uint32_t dtype)
@@ -96,7 +228,8 @@ static int ncclType(uint32_t dtype)
 
 void Comm::allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average)
 {
-    checkNccl(nccl().allReduce(data, data, count, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclAllReduce");
+    checkAsyncError("all_reduce");
+    finishCall(nccl().allReduce(data, data, count, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclAllReduce");
 }
 
 // In place: `data` holds count elements on every rank, count a multiple of the number of ranks; afterwards slice
@@ -106,7 +239,8 @@ void Comm::reduceScatterSum(void* data, size_t count, uint32_t dtype, cudaStream
 {
     const size_t slice = count / static_cast<size_t>(m_nranks);
     char* own = static_cast<char*>(data) + static_cast<size_t>(m_rank) * slice * dtypeSize(dtype);
-    checkNccl(nccl().reduceScatter(data, own, slice, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclReduceScatter");
+    checkAsyncError("reduce_scatter");
+    finishCall(nccl().reduceScatter(data, own, slice, ncclType(dtype), average ? kNcclAvg : kNcclSum, m_comm, stream), "ncclReduceScatter");
 }
 
 // In place: every rank contributes its own slice of `data` and receives all the others'.
@@ -114,7 +248,8 @@ void Comm::allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stre
 {
     const size_t slice = count / static_cast<size_t>(m_nranks);
     const char* own = static_cast<const char*>(data) + static_cast<size_t>(m_rank) * slice * dtypeSize(dtype);
-    checkNccl(nccl().allGather(own, data, slice, ncclType(dtype), m_comm, stream), "ncclAllGather");
+    checkAsyncError("all_gather");
+    finishCall(nccl().allGather(own, data, slice, ncclType(dtype), m_comm, stream), "ncclAllGather");
 }
 
 }   // namespace aixb200

@@ -22,10 +22,23 @@ public:
     void allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream);
     int rank() const { return m_rank; }
     int size() const { return m_nranks; }
+    // One query of the communicator's asynchronous state; an error aborts the communicator (once) and throws.
+    void checkAsyncError(const char* what);
+    bool aborted() const { return m_aborted; }
+
+    // Host-side fault injection (tests): replaces the NCCL entry points by stand-ins. mode 0 restores NCCL.
+    static void injectBackend(int mode, int errorAfterPolls);
+    static bool backendInjected();
+    static void injectedCounters(int* inits, int* polls, int* aborts);
 
 private:
+    void waitUntilReady(const char* what);
+    void finishCall(int result, const char* what);
+    void abortOnce();
     void* m_comm = nullptr;
     int   m_rank, m_nranks;
+    long  m_timeoutMs = 0;
+    bool  m_nonBlocking = false, m_aborted = false;
 };
 
 }   // namespace aixb200

@@ -361,7 +361,7 @@ void Device::emptyCache()
 void Device::synchronize()
 {
     flush();
-    if (dryRun()) return;
+    if (dryRun()) { if (m_comm && !m_comm->aborted()) m_comm->checkAsyncError("synchronize"); return; }
     // With managed memory the host may write into any tensor through its pointer once the device is idle: nothing
     // prepared from the tensors' contents survives a synchronisation.
     if (m_cfg.managed_memory) invalidatePreparedTerms(nullptr, reinterpret_cast<const void*>(~uintptr_t(0)));
@@ -1098,8 +1098,9 @@ void Device::fillStats(aixb200_stats* out) const
 
 void Device::commInit(int rank, int nranks, const void* id)
 {
-    if (dryRun()) failInvalid("communication needs a GPU");
+    if (dryRun() && !Comm::backendInjected()) failInvalid("communication needs a GPU");
     flush();
+    m_comm.reset();
     m_comm = std::make_unique<Comm>(rank, nranks, id, m_cfg.ordinal);
 }
 
@@ -1122,7 +1123,7 @@ void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
     // A scale of exactly 1/ranks on a floating type is the collective's own averaging: no extra pass over the data.
     const bool average = ncclAverages(false) && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
     m_comm->allReduceSum(data, count, dtype, m_stream, average);
-    if (scale != 1.0 && !average)
+    if (scale != 1.0 && !average && !dryRun())
     {
         AIXB200_CTX();
         kernels::scaleInPlace(ctx, dtype, data, count, scale);
@@ -1241,6 +1242,7 @@ void Device::commWaitFor(const void* data, size_t bytes)
 
 void Device::commWait()
 {
+    if (m_comm && !m_comm->aborted()) m_comm->checkAsyncError("comm_wait");      // a peer that died surfaces here instead of as a hang later
     for (const CommInFlight& c : m_commInFlight)
     {
         check(cudaStreamWaitEvent(m_stream, c.done, 0), "cudaStreamWaitEvent(comm done)");

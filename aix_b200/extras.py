@@ -138,3 +138,44 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
 
 def measure_extras(dev, hbm_peak, tensor_peak):
     return {"reductions_8192x8192_bf16": measure_reductions(dev, hbm_peak), "matmul": measure_matmul(dev, tensor_peak)}
+
+
+def measure_config1_sharded(dev, hbm_peak, rank, world_size, rows=8192, cols=8192, barrier=None, reduce_max=None):
+    """Configuration 1 with the rows split across the ranks (weak scaling: every rank holds rows x cols): y, the row sums
+    and the row maxima are local - one generated kernel - and the global mean takes one scalar all-reduce over NCCL.
+    Returns per-GPU and aggregate rates; the mean is checked against the ranks' local means."""
+    from .frontend import global_mean
+    rng = np.random.default_rng(rank)
+    x = TensorValue.from_numpy(rng.normal(0, 1, (rows, cols)).astype(np.float32), dev, C.BF16)
+    g = TensorValue.from_numpy(np.random.default_rng(1000).uniform(0.5, 1.5, cols).astype(np.float32), dev, C.BF16)
+    b = TensorValue.from_numpy(np.random.default_rng(1001).normal(0, 0.1, cols).astype(np.float32), dev, C.BF16)
+    dev.synchronize()
+    holder = {}
+
+    def whole():
+        y = relu(x * g + b)
+        holder["all"] = (y, y.sum(1), y.max(1), global_mean(y, world_size))
+
+    for _ in range(3):
+        whole()
+    dev.synchronize()
+    if barrier: barrier()
+    iters = 10
+    e0, e1 = dev.createEvent(), dev.createEvent()
+    for _ in range(8):
+        dev.flushL2()                      # keeps the device busy while the host queues the timed calls
+    dev.recordEvent(e0)
+    for _ in range(iters):
+        whole()
+    dev.recordEvent(e1)
+    ms = dev.elapsedMs(e0, e1) / iters
+    if reduce_max: ms = reduce_max(ms)
+    y, _, _, mean = holder["all"]
+    local_mean = float(y.numpy().astype(np.float64).mean())
+    moved = 2 * rows * cols * 2 + 2 * cols * 2
+    api = 5 * rows * cols * 2 + 2 * cols * 2
+    return {"rows_per_gpu": rows, "cols": cols, "ms": ms, "GB/s_per_gpu_of_bytes_moved": moved / (ms * 1e-3) / 1e9,
+            "GB/s_aggregate_of_bytes_moved": world_size * moved / (ms * 1e-3) / 1e9,
+            "GB/s_aggregate_of_API_bytes": world_size * api / (ms * 1e-3) / 1e9,
+            "frac_of_measured_hbm_per_gpu": moved / (ms * 1e-3) / 1e9 / hbm_peak,
+            "global_mean": float(mean.numpy()), "local_mean_of_this_rank": local_mean, "exchange": "one scalar all-reduce per evaluation"}

@@ -372,6 +372,17 @@ class GradientExchange:
             p.node.gradReadyHook = None
 
 
+def global_mean(value: TensorValue, world_size: int) -> TensorValue:
+    """Mean over a tensor whose rows are split across `world_size` ranks (equal shards): the local `sum()` - folded into
+    the producing kernel when that is still pending - one scalar all-reduce that averages the partial sums over the
+    ranks, and the reference's `sum() / size` division (aixCore.hpp:2498-2501) by the LOCAL size. Row-wise results of a
+    row-sharded tensor need no exchange at all."""
+    total = value.sum()
+    if world_size > 1:
+        value.device.allReduce(total.storage.data, 1, total.dtype, 1.0 / world_size)
+    return total / float(value.size)
+
+
 def _flat_slice(t: TensorValue, rank: int, world_size: int) -> TensorValue:
     """Slice `rank` of `world_size` of a dense tensor, as a 1-D view of its storage."""
     n = t.size // world_size

@@ -363,6 +363,12 @@ def main():
                 mlp_train = measure_mlp(dev, tensor_peak, sharded=True, **common)
                 mlp_train["ms_per_step_all_reduce_inside_backward"] = measure_mlp(dev, tensor_peak, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]
+                # the broadcast + reduction configuration with its rows split over the ranks (one scalar all-reduce for the mean)
+                from aix_b200.extras import measure_config1_sharded
+                line["config1_sharded"] = measure_config1_sharded(dev, hbm_peak, rank, world, barrier=barrier, reduce_max=max_over_ranks)
+                means = [None] * world
+                dist.all_gather_object(means, line["config1_sharded"]["local_mean_of_this_rank"])
+                line["config1_sharded"]["mean_of_local_means"] = float(np.mean(means))
                 dev.commDestroy()
         except Exception as exc:
             mlp_train = {"error": str(exc)}

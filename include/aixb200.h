@@ -239,7 +239,19 @@ int aixb200_self_test_bounded_wait(aixb200_device* dev, uint64_t limit_ns);
 /* ---- data-parallel exchange (no reference counterpart: the reference has no multi-device code) ---- */
 #define AIXB200_COMM_ID_BYTES 128
 int aixb200_comm_unique_id(void* id_out /* AIXB200_COMM_ID_BYTES */);
+/* Creates the communicator (NCCL over NVLink / NVSwitch). Blocking by default. With the environment variable
+ * AIXB200_COMM_INIT_TIMEOUT_MS set, initialisation is non-blocking and polled: if it has not completed by then (a rank
+ * that never joins) the communicator is aborted and the call returns AIXB200_ERR_TIMEOUT instead of hanging. Every
+ * collective, aixb200_comm_wait and aixb200_synchronize also query the communicator's asynchronous state first: an error
+ * reported there (a peer that died, a network fault) aborts the communicator once and returns AIXB200_ERR_RUNTIME; later
+ * collectives on it fail at once. */
 int aixb200_comm_init(aixb200_device* dev, int rank, int nranks, const void* id);
+/* Host-side fault injection for tests of those paths; process-wide, no GPU or NCCL involved. mode 0: the real NCCL;
+ * 1: initialisation never completes; 2: everything succeeds until the communicator's state has been queried
+ * `error_after_polls` times, then it reports a remote error. With a back end injected, aixb200_comm_init also works on a
+ * dry-run device. aixb200_comm_injected_counters reads how often the stand-ins were initialised, polled and aborted. */
+int aixb200_comm_inject_backend(int mode, int error_after_polls);
+int aixb200_comm_injected_counters(int* inits, int* polls, int* aborts);
 /* In-place sum all-reduce over `count` elements of dtype (F32, F64, BF16, F16, I32, I64) followed by a
  * multiplication by `scale` (1/nranks averages). Ordered after all work recorded so far. */
 int aixb200_all_reduce(aixb200_device* dev, void* data, size_t count, uint32_t dtype, double scale);

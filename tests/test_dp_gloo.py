@@ -123,6 +123,40 @@ def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path, overlap, shar
         assert np.allclose(got, want, rtol=1e-4, atol=2e-5), np.max(np.abs(got - want))
 
 
+def mean_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from aix_b200.frontend import global_mean
+    dev = GlooDevice()
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (12, 40)).astype(np.float32)           # every rank draws the same matrix and keeps its own rows
+    g = rng.uniform(0.5, 1.5, 40).astype(np.float32)
+    rows = x.shape[0] // world
+    tx, tg = TensorValue.from_numpy(x[rank * rows:(rank + 1) * rows], dev), TensorValue.from_numpy(g, dev)
+    y = tx * tg
+    np.savez(os.path.join(out_dir, f"mean{rank}.npz"), mean=global_mean(y, world).numpy(), row_sum=y.sum(1).numpy(), row_max=y.max(1).numpy())
+    dist.destroy_process_group()
+
+
+def test_row_sharded_reductions_need_one_scalar_exchange(tmp_path):
+    """Configuration 1 split by rows over two ranks: row sums and row maxima are local, the global mean takes one scalar
+    all-reduce and equals the single-process mean."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(mean_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (12, 40)).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, 40).astype(np.float32)
+    dev = DeviceNumpyOracle()
+    y = TensorValue.from_numpy(x, dev) * TensorValue.from_numpy(g, dev)
+    parts = [np.load(tmp_path / f"mean{r}.npz") for r in range(2)]
+    assert np.array_equal(parts[0]["mean"], parts[1]["mean"])
+    assert abs(float(parts[0]["mean"]) - float(y.mean().numpy())) <= 1e-6 * max(1.0, abs(float(y.mean().numpy())))
+    assert np.array_equal(np.concatenate([p["row_sum"] for p in parts]), y.sum(1).numpy())
+    assert np.array_equal(np.concatenate([p["row_max"] for p in parts]), y.max(1).numpy())
+
+
 def test_shards_are_disjoint_and_deterministic():
     a0, _ = synthetic_batch(DIMS, BATCH, rank=0)
     a1, _ = synthetic_batch(DIMS, BATCH, rank=1)

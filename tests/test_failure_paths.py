@@ -70,3 +70,69 @@ def test_a_bounded_device_wait_that_runs_out_is_reported_once_and_the_device_rec
     assert np.array_equal(y.numpy(), np.arange(1000, dtype=np.float32) + 1.0)
     m = TensorValue.from_numpy(np.ones((256, 256), np.float32), b200).matmul(TensorValue.from_numpy(np.ones((256, 256), np.float32), b200))
     assert np.all(m.numpy() == 256.0)                    # the tensor-core path (which shares the error word) is unaffected
+
+
+# ---- communicator failures, injected on the host (no NCCL, no GPU): aixb200_comm_inject_backend -----------------------
+@pytest.fixture()
+def injected():
+    from aix_b200 import _capi as C
+    lib = C.load()
+
+    def counters():
+        import ctypes
+        a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        lib.aixb200_comm_injected_counters(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        return {"inits": a.value, "polls": b.value, "aborts": c.value}
+    yield lib, counters
+    lib.aixb200_comm_inject_backend(0, 0)
+    import os
+    os.environ.pop("AIXB200_COMM_INIT_TIMEOUT_MS", None)
+
+
+def test_a_rank_that_never_joins_costs_a_timeout_and_one_abort(injected, monkeypatch):
+    import time
+    lib, counters = injected
+    monkeypatch.setenv("AIXB200_COMM_INIT_TIMEOUT_MS", "150")
+    assert lib.aixb200_comm_inject_backend(1, 0) == 0                   # initialisation stays "in progress" for ever
+    dev = DeviceB200(0, dry_run=1, disk_cache=0)
+    t0 = time.time()
+    with pytest.raises(TimeoutError, match="did not complete within 150 ms"):
+        dev.commInit(0, 2, b"\0" * 128)
+    assert 0.1 <= time.time() - t0 < 5.0
+    seen = counters()
+    assert seen["inits"] == 1 and seen["aborts"] == 1 and seen["polls"] > 10
+    x = TensorValue.full(1.0, (100,), dev)                              # the device itself is unaffected
+    dev.synchronize()
+    with pytest.raises(Exception, match="comm_init"):
+        dev.allReduce(x.storage.data, x.size, F32, 1.0)                 # no communicator came into being; nothing is aborted twice
+    assert counters()["aborts"] == 1
+    dev.commDestroy()
+    dev.close()
+
+
+def test_an_asynchronous_error_aborts_the_communicator_once(injected, monkeypatch):
+    lib, counters = injected
+    monkeypatch.setenv("AIXB200_COMM_INIT_TIMEOUT_MS", "2000")
+    assert lib.aixb200_comm_inject_backend(2, 3) == 0                   # healthy for three status queries, then a remote error
+    dev = DeviceB200(0, dry_run=1, disk_cache=0)
+    dev.commInit(0, 2, b"\0" * 128)                                     # query 1: ready
+    x = TensorValue.full(1.0, (100,), dev)
+    dev.allReduce(x.storage.data, x.size, F32, 1.0)                     # query 2 (comm_wait) and 3 (all_reduce): still healthy
+    with pytest.raises(RuntimeError, match="asynchronous NCCL error.*aborted"):
+        dev.synchronize()                                               # query 4: the error surfaces at the next call
+    assert counters()["aborts"] == 1
+    with pytest.raises(RuntimeError, match="aborted after an earlier failure"):
+        dev.allReduce(x.storage.data, x.size, F32, 1.0)
+    dev.commDestroy()                                                   # no second abort, no destroy of an aborted communicator
+    assert counters()["aborts"] == 1
+    dev.close()
+
+
+def test_blocking_initialisation_stays_the_default(injected):
+    lib, counters = injected
+    assert lib.aixb200_comm_inject_backend(2, 1000) == 0
+    dev = DeviceB200(0, dry_run=1, disk_cache=0)
+    dev.commInit(0, 1, b"\0" * 128)
+    assert counters() == {"inits": 1, "polls": 0, "aborts": 0}          # plain ncclCommInitRank: nothing to poll
+    dev.commDestroy()
+    dev.close()
