@@ -242,11 +242,16 @@ class Tanh:
 
 
 class Sequential:
-    def __init__(self, *modules): self.modules = list(modules)
+    def __init__(self, *modules):
+        self.modules = list(modules)
+        self.beforeModule: Optional[Callable] = None    # no counterpart in the reference; see ShardedAdam.attach_model
+
     def parameters(self): return [p for m in self.modules for p in m.parameters()]
 
     def forward(self, x: Tensor) -> Tensor:
-        for m in self.modules:
+        for index, m in enumerate(self.modules):
+            if self.beforeModule is not None:
+                self.beforeModule(index)
             x = m.forward(x)
         return x
 
@@ -426,24 +431,64 @@ class ShardedAdam(Adam):
         self.m = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
         self.v = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
 
+    def attach_model(self, model: "Sequential", lookahead: int = 1):
+        """Deferred form: `step()` only notes that an update is due, and every parameter is updated when the next forward
+        pass reaches the module `lookahead` parametrised modules before its own (the first module's at once). The
+        front end finishes the weight gradients first-layer-first, so the reduce-scatters of the LAST layers are still
+        running when backward() returns; issued eagerly, their updates would hold up the in-order stream - and the next
+        forward pass behind them. Deferred, the first layers of the next forward pass run under those collectives, and each
+        late layer's update and all-gather run under the layer before it. Every parameter is still updated before its
+        next use; `finish()` applies whatever is outstanding (before reading parameters on the host)."""
+        self._owners = []                                   # per module: indices of its parameters in self.parameters
+        index_of = {id(p.node): i for i, p in enumerate(self.parameters)}
+        for m in model.modules:
+            self._owners.append([index_of[id(p.node)] for p in m.parameters() if id(p.node) in index_of])
+        self._with_params = [j for j, own in enumerate(self._owners) if own]
+        self._lookahead = lookahead
+        self._due = set()
+        model.beforeModule = self._before_module
+
+    def _before_module(self, module_index: int):
+        if not self._due or module_index not in self._with_params:
+            return
+        at = self._with_params.index(module_index)
+        for j in self._with_params[:at + 1 + self._lookahead]:
+            for i in self._owners[j]:
+                if i in self._due:
+                    self._due.discard(i)
+                    self._update(i)
+
+    def finish(self):
+        for i in sorted(getattr(self, "_due", ())):
+            self._update(i)
+        if hasattr(self, "_due"):
+            self._due.clear()
+
     def step(self):
+        self.finish()                                       # nothing of the previous step may be left when the gradients change
         self.timestep += 1
+        if hasattr(self, "_owners"):
+            self._due = {i for i, p in enumerate(self.parameters) if p.isRequireGrad()}
+            return
+        for i, p in enumerate(self.parameters):
+            if p.isRequireGrad():
+                self._update(i)
+
+    def _update(self, i: int):
+        p = self.parameters[i]
         b1, b2 = float(np.float32(self.beta1)), float(np.float32(self.beta2))
         narrow = lambda x: float(np.float32(x))
-        for i, p in enumerate(self.parameters):
-            if not p.isRequireGrad():
-                continue
-            if self.beforeParameter is not None:
-                self.beforeParameter(p)
-            value, grad = p.value, p.grad()
-            if self.sharded[i]:
-                value, grad = _flat_slice(value, self.rank, self.world_size), _flat_slice(grad, self.rank, self.world_size)
-            g = grad.to(C.F32)
-            self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
-            self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
-            mHat = self.m[i] / narrow(1.0 - math.pow(b1, self.timestep))
-            vHat = self.v[i] / narrow(1.0 - math.pow(b2, self.timestep))
-            value -= (self.lr * mHat / (vHat.sqrt() + self.epsilon)).to(p.dtype)
-            if self.sharded[i]:
-                whole = p.value
-                whole.device.allGatherAsync(whole.storage.data, whole.size, whole.dtype)
+        if self.beforeParameter is not None:
+            self.beforeParameter(p)
+        value, grad = p.value, p.grad()
+        if self.sharded[i]:
+            value, grad = _flat_slice(value, self.rank, self.world_size), _flat_slice(grad, self.rank, self.world_size)
+        g = grad.to(C.F32)
+        self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
+        self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
+        mHat = self.m[i] / narrow(1.0 - math.pow(b1, self.timestep))
+        vHat = self.v[i] / narrow(1.0 - math.pow(b2, self.timestep))
+        value -= (self.lr * mHat / (vHat.sqrt() + self.epsilon)).to(p.dtype)
+        if self.sharded[i]:
+            whole = p.value
+            whole.device.allGatherAsync(whole.storage.data, whole.size, whole.dtype)

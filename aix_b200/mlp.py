@@ -32,7 +32,7 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 class MlpTrainer:
     def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
-                 overlap=True, data=None, sharded=False):
+                 overlap=True, data=None, sharded=False, deferred=True):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -51,6 +51,8 @@ class MlpTrainer:
         sharded = sharded and overlap and world_size > 1
         params = self.model.parameters()
         self.optimizer = ShardedAdam(params, rank, world_size, lr=lr) if sharded else Adam(params, lr=lr)   # after the parameters live on the device
+        if sharded and deferred:
+            self.optimizer.attach_model(self.model)         # updates applied layer by layer inside the next forward pass
         self.loss_fn = MSELoss()
         # overlap=True: each gradient's collective starts inside backward(); False: all of them after it
         exchange_type = ShardedGradientExchange if sharded else GradientExchange
@@ -78,4 +80,6 @@ class MlpTrainer:
         return loss
 
     def parameters_numpy(self):
+        if hasattr(self.optimizer, "finish"):
+            self.optimizer.finish()                         # a deferred optimizer may still owe the last step's updates
         return [p.value.numpy() for p in self.model.parameters()]
