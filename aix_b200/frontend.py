@@ -431,20 +431,23 @@ class ShardedAdam(Adam):
         self.m = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
         self.v = [TensorValue.full(0.0, shape(p, s), p.device, C.F32) for p, s in zip(self.parameters, self.sharded)]
 
-    def attach_model(self, model: "Sequential", lookahead: int = 1):
-        """Deferred form: `step()` only notes that an update is due, and every parameter is updated when the next forward
-        pass reaches the module `lookahead` parametrised modules before its own (the first module's at once). The
-        front end finishes the weight gradients first-layer-first, so the reduce-scatters of the LAST layers are still
-        running when backward() returns; issued eagerly, their updates would hold up the in-order stream - and the next
-        forward pass behind them. Deferred, the first layers of the next forward pass run under those collectives, and each
-        late layer's update and all-gather run under the layer before it. Every parameter is still updated before its
-        next use; `finish()` applies whatever is outstanding (before reading parameters on the host)."""
+    def attach_model(self, model: "Sequential", lookahead: int = 1, eager_modules: Optional[int] = None):
+        """Deferred form. The front end finishes the weight gradients first-layer-first, so the reduce-scatters of the LAST
+        layers are still running when backward() returns; issued eagerly, their updates hold up the in-order stream - and
+        the next forward pass behind them. With a model attached, `step()` updates only the first `eager_modules`
+        parametrised modules at once (default: the first half - their gradients arrived long ago, and their all-gathers
+        then run under the rest of step()); the others are noted as due and updated when the next forward pass reaches
+        the module `lookahead` parametrised modules before their own, so that the first layers of that pass run under the
+        late collectives and each late layer's update and all-gather run under the layer before it. Every parameter is
+        still updated before its next use; `finish()` applies whatever is outstanding (before the host reads
+        parameters)."""
         self._owners = []                                   # per module: indices of its parameters in self.parameters
         index_of = {id(p.node): i for i, p in enumerate(self.parameters)}
         for m in model.modules:
             self._owners.append([index_of[id(p.node)] for p in m.parameters() if id(p.node) in index_of])
         self._with_params = [j for j, own in enumerate(self._owners) if own]
         self._lookahead = lookahead
+        self._eager = len(self._with_params) // 2 if eager_modules is None else eager_modules
         self._due = set()
         model.beforeModule = self._before_module
 
@@ -469,6 +472,11 @@ class ShardedAdam(Adam):
         self.timestep += 1
         if hasattr(self, "_owners"):
             self._due = {i for i, p in enumerate(self.parameters) if p.isRequireGrad()}
+            for j in self._with_params[:self._eager]:
+                for i in self._owners[j]:
+                    if i in self._due:
+                        self._due.discard(i)
+                        self._update(i)
             return
         for i, p in enumerate(self.parameters):
             if p.isRequireGrad():
