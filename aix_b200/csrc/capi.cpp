@@ -196,7 +196,7 @@ int aixb200_event_record(aixb200_device* dev, aixb200_event* ev)
     return guarded(dev, [&](Device& d)
     {
         if (!ev) failInvalid("null event");
-        d.flush();
+        d.flushAll();
         if (cudaEventRecord(ev->event, d.stream()) != cudaSuccess) failRuntime("cudaEventRecord failed");
     });
 }

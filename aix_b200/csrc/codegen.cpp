@@ -244,6 +244,20 @@ template <class D> struct Red<D, true>
     static __device__ __forceinline__ W lift(S s) { return (W)D::ld(s); }
     static __device__ __forceinline__ S finish(W w) { return D::st((A)w); }
 };
+// max|x| of f32 values as a bit pattern (non-negative floats order like unsigned integers; a NaN carries the largest
+// patterns and so ends up as the maximum): the scale source of a prepared matmul operand.
+struct RedAbsBits
+{
+    typedef unsigned S;
+    typedef unsigned A;
+    typedef u64_t W;
+    static __device__ __forceinline__ A init() { return 0u; }
+    static __device__ __forceinline__ A step(A acc, float v) { const unsigned b = __float_as_uint(fabsf(v)); return b > acc ? b : acc; }
+    static __device__ __forceinline__ W widen(A a) { return (W)a; }
+    static __device__ __forceinline__ W identity() { return (W)0; }
+    static __device__ __forceinline__ W merge(W a, W b) { return b > a ? b : a; }
+    static __device__ __forceinline__ S finish(W w) { return (unsigned)w; }
+};
 template <class W> __device__ __forceinline__ W red_shfl(W v, int d)
 {
     i64_t bits = __shfl_down_sync(0xffffffffu, *(i64_t*)&v, d);
@@ -420,7 +434,7 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
     if (!spec.reductions.empty())
     {
         key += "R";
-        for (const auto& r : spec.reductions) { put(r.node); put(r.isMax); put(r.dtype); }
+        for (const auto& r : spec.reductions) { put(r.node); put(r.isMax); put(r.dtype); put(r.absBits); }
     }
     if (variant.rowMode)
     {
@@ -617,7 +631,8 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
     for (size_t i = 0; i < nL; ++i)
         if (lp[i] == Path::Scalar) o << "    const " << T(spec.loads[i].view.dtype) << "::S x" << i << "s = l" << i << "[0];\n";
 
-    auto redType = [&](size_t r) { return "Red<" + T(spec.reductions[r].dtype) + ", " + (spec.reductions[r].isMax ? "true" : "false") + ">"; };
+    auto redType = [&](size_t r) { return spec.reductions[r].absBits ? std::string("RedAbsBits")
+                                                                        : "Red<" + T(spec.reductions[r].dtype) + ", " + (spec.reductions[r].isMax ? "true" : "false") + ">"; };
     for (size_t r = 0; r < nR; ++r)
         o << "    " << redType(r) << "::A racc" << r << " = " << redType(r) << "::init();\n";
     auto emitReduceSteps = [&](std::ostream& os, const std::string& indent)
@@ -809,7 +824,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         for (size_t r = 0; r < nR; ++r)
             o << "    red_finish<" << redType(r) << " >(racc" << r << ", (u64_t*)(" << arg(slotScratch) << " + " << kReductionPartialsOffset
               << "ull + " << (r * kReductionMaxBlocks * 8) << "ull), (unsigned*)(" << arg(slotScratch) << " + " << (4 * (r + 1)) << "ull), ("
-              << T(spec.reductions[r].dtype) << "::S*)" << arg(slotReductions + r) << ");\n";
+              << redType(r) << "::S*)" << arg(slotReductions + r) << ");\n";
         o << "}\n";
         return o.str();
     }
@@ -997,7 +1012,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
     for (size_t r = 0; r < nR; ++r)
         o << "    red_finish<" << redType(r) << " >(racc" << r << ", (u64_t*)(" << arg(slotScratch) << " + " << kReductionPartialsOffset
           << "ull + " << (r * kReductionMaxBlocks * 8) << "ull), (unsigned*)(" << arg(slotScratch) << " + " << (4 * (r + 1)) << "ull), ("
-          << T(spec.reductions[r].dtype) << "::S*)" << arg(slotReductions + r) << ");\n";
+          << redType(r) << "::S*)" << arg(slotReductions + r) << ");\n";
     o << "}\n";
     return o.str();
 }

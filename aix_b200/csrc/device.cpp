@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <nvrtc.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -96,6 +97,8 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_fuseReductions = envInt("AIXB200_FUSE_REDUCTIONS", 1) != 0;
     m_fuseRowReductions = envInt("AIXB200_FUSE_ROW_REDUCTIONS", 1) != 0;
     m_termCacheEnabled = envInt("AIXB200_GEMM_TERM_CACHE", 1) != 0;
+    m_keepIdleFills = envInt("AIXB200_KEEP_IDLE_FILLS", 1) != 0;
+    m_fuseOperandMax = envInt("AIXB200_FUSE_OPERAND_MAX", 1) != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -218,7 +221,7 @@ void* Device::allocate(size_t bytes)
         // Out of memory with dead buffers still parked behind recorded ops: emit those ops (which returns the buffers
         // to the cache), then try once more.
         if (m_deferredFrees.empty() || m_inFlush) throw;
-        flush();
+        flushAll();
         return m_allocator->allocate(bytes + 16);
     }
 }
@@ -246,7 +249,8 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
     if (!m_termSlots)
     {
         m_termSlots = m_allocator->allocate(kSlots * sizeof(uint32_t));
-        for (uint32_t i = kSlots; i-- > 0;) m_freeTermSlots.push_back(i);
+        for (uint32_t i = kSlots; i-- > 1;) m_freeTermSlots.push_back(i);
+        m_dummySlot = 0;
     }
     PreparedTerms e{};
     e.lo = static_cast<const char*>(base);
@@ -269,8 +273,15 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
         invalidatePreparedTerms(victim.lo, victim.hi);
     }
     e.terms = m_allocator->allocate(e.bytes + 16);
-    e.slot = m_freeTermSlots.back();
-    m_freeTermSlots.pop_back();
+    const int produced = freshOperandMax(e.lo, e.hi);
+    if (produced >= 0) { e.slot = static_cast<uint32_t>(produced); e.ownsSlot = false; ++m_stats.prepared_operand_max_known; }
+    else
+    {
+        e.slot = m_freeTermSlots.back();
+        m_freeTermSlots.pop_back();
+        e.ownsSlot = true;
+    }
+    rememberOperandRegion(e.lo, e.hi, true);
     e.stamp = ++m_preparedStamp;
     m_preparedBytes += e.bytes;
     ++m_stats.prepared_operand_builds;
@@ -280,8 +291,80 @@ const Device::PreparedTerms* Device::addPreparedTerms(const void* base, uint64_t
 
 // Every kernel that read a prepared form is already enqueued when this runs (matmuls launch at call time), so the block
 // can go back to the allocator at once: reuse is ordered behind those kernels on the device's stream.
+int Device::freshOperandMax(const void* lo, const void* hi) const
+{
+    for (const OperandRegion& r : m_operandRegions)
+        if (r.lo == lo && r.hi == hi) return r.fresh ? static_cast<int>(r.slot) : -1;
+    return -1;
+}
+
+// Returns the index of the range's entry (created if need be), or -1. `operandNow`: the range is being prepared as a matmul
+// operand - its size joins the sizes whose producers are asked for max|x|.
+int Device::rememberOperandRegion(const char* lo, const char* hi, bool operandNow)
+{
+    const size_t bytes = static_cast<size_t>(hi - lo);
+    if (!m_fuseOperandMax || bytes < (size_t(1) << 20)) return -1;          // small operands: the max pass is noise
+    if (operandNow && std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) == m_operandSizes.end() && m_operandSizes.size() < 32)
+        m_operandSizes.push_back(bytes);
+    for (size_t i = 0; i < m_operandRegions.size(); ++i)
+        if (m_operandRegions[i].lo == lo && m_operandRegions[i].hi == hi) { m_operandRegions[i].stamp = ++m_preparedStamp; return static_cast<int>(i); }
+    if (m_operandRegions.size() >= 64 || m_freeTermSlots.size() < 64)
+    {
+        // forget the range used longest ago, unless a prepared form still reads its slot
+        size_t oldest = m_operandRegions.size();
+        for (size_t i = 0; i < m_operandRegions.size(); ++i)
+        {
+            bool inUse = false;
+            for (const PreparedTerms& e : m_preparedTerms) inUse = inUse || (!e.ownsSlot && e.slot == m_operandRegions[i].slot);
+            if (!inUse && (oldest == m_operandRegions.size() || m_operandRegions[i].stamp < m_operandRegions[oldest].stamp)) oldest = i;
+        }
+        if (oldest == m_operandRegions.size()) return -1;
+        m_freeTermSlots.push_back(m_operandRegions[oldest].slot);
+        m_operandRegions[oldest] = m_operandRegions.back();
+        m_operandRegions.pop_back();
+    }
+    if (m_freeTermSlots.empty()) return -1;
+    m_operandRegions.push_back({lo, hi, m_freeTermSlots.back(), false, ++m_preparedStamp});
+    m_freeTermSlots.pop_back();
+    return static_cast<int>(m_operandRegions.size() - 1);
+}
+
+// Every generated kernel that stores a dense f32 tensor of a size matmul operands have had folds max|x| of the stored values
+// into a slot of that tensor's range (the choice depends on sizes only, so a kernel's identity does not change with the
+// addresses the allocator happens to hand out). regionsOf[k] lists the ranges kernel k refreshes.
+void Device::appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::vector<std::vector<std::pair<const char*, const char*>>>& regionsOf)
+{
+    regionsOf.assign(kernels.size(), {});
+    if (m_operandSizes.empty() || !m_fuseReductions || !m_termSlots) return;
+    for (size_t k = 0; k < kernels.size(); ++k)
+    {
+        KernelSpec& spec = kernels[k];
+        for (const KernelStore& st : spec.stores)
+        {
+            if (st.view.dtype != F32 || !st.view.isDense() || st.view.size != spec.count) continue;
+            if (spec.reductions.size() >= m_limits.maxReductionsPerKernel) break;
+            const size_t bytes = static_cast<size_t>(st.view.endByte() - st.view.firstByte());
+            if (std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) == m_operandSizes.end()) continue;
+            const int region = rememberOperandRegion(st.view.firstByte(), st.view.endByte(), false);
+            View slot;
+            slot.base = reinterpret_cast<char*>(preparedSlot(region >= 0 ? m_operandRegions[static_cast<size_t>(region)].slot : m_dummySlot));
+            slot.size = 1;
+            slot.dtype = F32;
+            spec.reductions.push_back({st.node, true, static_cast<uint8_t>(F32), slot, true});
+            if (region >= 0) regionsOf[k].push_back({st.view.firstByte(), st.view.endByte()});
+        }
+    }
+}
+
 void Device::invalidatePreparedTerms(const void* lo, const void* hi)
 {
+    {
+        // whatever is written into an operand's range, the maximum its producer left is stale
+        const char* first = static_cast<const char*>(lo);
+        const char* last = static_cast<const char*>(hi);
+        for (OperandRegion& r : m_operandRegions)
+            if (first < r.hi && r.lo < last) r.fresh = false;
+    }
     if (m_preparedTerms.empty()) return;
     const char* first = static_cast<const char*>(lo);
     const char* last = static_cast<const char*>(hi);
@@ -291,7 +374,7 @@ void Device::invalidatePreparedTerms(const void* lo, const void* hi)
         if (first < e.hi && e.lo < last)
         {
             m_allocator->release(e.terms);
-            m_freeTermSlots.push_back(e.slot);
+            if (e.ownsSlot) m_freeTermSlots.push_back(e.slot);
             m_preparedBytes -= e.bytes;
             m_preparedTerms[i] = m_preparedTerms.back();
             m_preparedTerms.pop_back();
@@ -326,6 +409,7 @@ void Device::deallocate(void* p)
         // a collective on the side stream may still use the block: reuse is ordered on the device's stream only
         aixb200_tensor whole{};
         whole.data = p; whole.size = m_allocator->blockSize(p); whole.dtype = U8; whole.rank = 1; whole.shape[0] = whole.size; whole.strides[0] = 1;
+        noteCallRange(p, static_cast<char*>(p) + whole.size);
         orderAfterCollectives(makeView(&whole, "deallocate"));
     }
     if (m_pending.empty() && m_deferredFrees.empty())
@@ -339,7 +423,7 @@ void Device::deallocate(void* p)
     // Memory pressure: do not let dead buffers pile up behind a long recorded chain
     // (the reference commits when half its working-set budget is queued, aixDeviceMetal.cpp:1438-1444).
     const uint64_t budget = dryRun() ? (uint64_t(1) << 30) : m_totalMemory / 2;
-    if (m_deferredBytes > budget) flush();
+    if (m_deferredBytes > budget) flushAll();
 }
 
 void Device::releaseDeferred()
@@ -352,7 +436,7 @@ void Device::releaseDeferred()
 
 void Device::emptyCache()
 {
-    flush();
+    flushAll();
     if (!dryRun()) check(cudaStreamSynchronize(m_stream), "synchronize");
     invalidatePreparedTerms(nullptr, reinterpret_cast<const void*>(~uintptr_t(0)));
     m_allocator->trim(0);
@@ -360,7 +444,7 @@ void Device::emptyCache()
 
 void Device::synchronize()
 {
-    flush();
+    flushAll();
     if (dryRun()) { if (m_comm && !m_comm->aborted()) m_comm->checkAsyncError("synchronize"); return; }
     // With managed memory the host may write into any tensor through its pointer once the device is idle: nothing
     // prepared from the tensors' contents survives a synchronisation.
@@ -400,6 +484,7 @@ bool Device::isHostPointer(const void* p) const
 View Device::inputView(const aixb200_tensor* t, const char* what)
 {
     View v = makeView(t, what);
+    if (v.size != 0) noteCallRange(v.firstByte(), v.endByte());
     if (v.size == 0 || dryRun()) return v;
     if (!m_commInFlight.empty()) orderAfterCollectives(v);
     if (m_allocator->findBlock(v.base)) return v;
@@ -420,6 +505,7 @@ View Device::inputView(const aixb200_tensor* t, const char* what)
 View Device::outputView(const aixb200_tensor* t, const char* what)
 {
     View v = makeView(t, what);
+    if (v.size != 0) noteCallRange(v.firstByte(), v.endByte());
     if (v.size == 0 || dryRun()) return v;
     invalidatePreparedTerms(v.firstByte(), v.endByte());       // whatever is written here, its prepared matmul form is stale
     if (!m_commInFlight.empty()) orderAfterCollectives(v);
@@ -499,7 +585,7 @@ void Device::recordFillMin(const aixb200_tensor* r)
 // ----------------------------------------------------------------------------------------------------------------
 // flush: plan, generate, compile, launch
 // ----------------------------------------------------------------------------------------------------------------
-void Device::flush()
+void Device::flush(bool keepIdleFills)
 {
     if (m_inFlush) return;
     if (m_pending.empty()) { releaseDeferred(); return; }
@@ -507,13 +593,50 @@ void Device::flush()
     struct Reset { bool& f; ~Reset() { f = false; } } reset{m_inFlush};
     std::vector<OpRecord> ops;
     ops.swap(m_pending);
+    if (keepIdleFills && m_keepIdleFills && m_limits.fusion)
+    {
+        // Idle fills stay recorded (see the declaration). "Idle": alive storage, untouched by every other op of the batch
+        // and by the call in progress.
+        auto meet = [](const char* alo, const char* ahi, const char* blo, const char* bhi) { return alo < bhi && blo < ahi; };
+        std::vector<char> idle(ops.size(), 0);
+        size_t idleCount = 0;
+        for (size_t i = 0; i < ops.size(); ++i)
+        {
+            if (ops[i].op != Op::Fill || m_released.count(ops[i].out.base)) continue;
+            const char* lo = ops[i].out.firstByte();
+            const char* hi = ops[i].out.endByte();
+            bool touched = false;
+            for (const auto& r : m_callRanges) touched = touched || meet(lo, hi, r.first, r.second);
+            for (size_t j = 0; j < ops.size() && !touched; ++j)
+            {
+                if (j == i) continue;
+                touched = meet(lo, hi, ops[j].out.firstByte(), ops[j].out.endByte());
+                for (int k = 0; k < ops[j].numInputs && !touched; ++k) touched = meet(lo, hi, ops[j].in[k].firstByte(), ops[j].in[k].endByte());
+            }
+            if (!touched) { idle[i] = 1; ++idleCount; }
+        }
+        if (idleCount > 0 && idleCount <= 64)
+        {
+            std::vector<OpRecord> rest;
+            rest.reserve(ops.size() - idleCount);
+            for (size_t i = 0; i < ops.size(); ++i) (idle[i] ? m_pending : rest).push_back(ops[i]);
+            ops.swap(rest);
+            if (ops.empty()) { releaseDeferred(); return; }
+        }
+    }
     ++m_stats.flushes;
     try
     {
         std::vector<KernelSpec> kernels = planKernels(ops, m_released, m_limits);
-        for (const KernelSpec& spec : kernels)
+        std::vector<std::vector<std::pair<const char*, const char*>>> refreshed;
+        appendOperandMaxEpilogues(kernels, refreshed);
+        for (size_t k = 0; k < kernels.size(); ++k)
         {
+            const KernelSpec& spec = kernels[k];
             launchSpec(spec);
+            for (const auto& range : refreshed[k])
+                for (OperandRegion& r : m_operandRegions)
+                    if (r.lo == range.first && r.hi == range.second) r.fresh = !dryRun();
             ++m_stats.fused_kernels;
             m_stats.fused_ops += spec.opsFolded;
             m_stats.fills_absorbed += spec.fillsAbsorbed;
@@ -614,7 +737,8 @@ void Device::launchSpec(const KernelSpec& spec)
     const std::string key = kernelKey(spec, variant, m_codegen);
     CompiledKernel& k = getKernel(spec, variant, key);
     m_lastSource = k.source;
-    m_stats.reductions_fused += spec.reductions.size() + spec.rowReductions.size();
+    for (const KernelReduce& r : spec.reductions) m_stats.reductions_fused += r.absBits ? 0 : 1;      // the caller's reductions only
+    m_stats.reductions_fused += spec.rowReductions.size();
     if (dryRun()) { countLaunch(true); return; }
 
     std::vector<uint64_t> args = packKernelArguments(spec, variant, m_scratch);
@@ -919,6 +1043,8 @@ void Device::copy(const void* src, uint32_t srcDtype, void* dst, uint32_t dstDty
     const size_t ss = dtypeSize(srcDtype), ds = dtypeSize(dstDtype);
     if (count == 0) { if (immediate) synchronize(); return; }
     if (!src || !dst) failInvalid("copy: null pointer");
+    noteCallRange(src, static_cast<const char*>(src) + count * ss);
+    noteCallRange(dst, static_cast<char*>(dst) + count * ds);
     if (dryRun()) { flush(); return; }
     const bool srcHost = !m_allocator->findBlock(src) && isHostPointer(src);
     const bool dstHost = !m_allocator->findBlock(dst) && isHostPointer(dst);
@@ -1065,7 +1191,7 @@ void Device::indexAdd(const aixb200_tensor* s, const aixb200_tensor* d, const ai
 // ----------------------------------------------------------------------------------------------------------------
 void Device::flushL2()
 {
-    flush();
+    flushAll();
     if (dryRun()) return;
     if (!m_l2Flush)
     {
@@ -1117,6 +1243,7 @@ static bool ncclAverages(bool overlapped)
 void Device::allReduce(void* data, size_t count, uint32_t dtype, double scale)
 {
     if (!m_comm) failInvalid("all_reduce: aixb200_comm_init was not called");
+    noteCallRange(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     flush();
     invalidatePreparedTerms(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     commWait();                 // collectives of one communicator are issued in one order on every rank
@@ -1188,6 +1315,7 @@ void Device::startCollective(void* data, size_t count, uint32_t dtype, const cha
     aixb200_tensor whole{};
     whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
     const View range = makeView(&whole, what);
+    noteCallRange(range.firstByte(), range.endByte());
     invalidatePreparedTerms(data, static_cast<char*>(data) + count * dtypeSize(dtype));
     if (!m_commInFlight.empty()) orderAfterCollectives(range);       // two collectives on one buffer keep their order
     flush();
@@ -1237,6 +1365,7 @@ void Device::commWaitFor(const void* data, size_t bytes)
     if (m_commInFlight.empty() || !data || bytes == 0) return;
     aixb200_tensor whole{};
     whole.data = const_cast<void*>(data); whole.size = bytes; whole.dtype = U8; whole.rank = 1; whole.shape[0] = bytes; whole.strides[0] = 1;
+    noteCallRange(data, static_cast<const char*>(data) + bytes);
     orderAfterCollectives(makeView(&whole, "comm_wait_for"));
 }
 

@@ -60,7 +60,12 @@ public:
     void recordFillMin(const aixb200_tensor* r);
     bool recordReduction(Op op, const View& src, const View& dst);
     bool recordRowReduction(bool isMax, const View& src, const View& dst, uint64_t rows, uint64_t cols);
-    void flush();
+    // Emits the recorded ops. A fill that nothing else in the batch touches, whose storage is alive and which the call in
+    // progress does not touch either stays recorded (the reference keeps such fills deferred too, aixFuse.cpp:891-916):
+    // the op that eventually uses the buffer - typically an in-place accumulation a few matmuls later - then absorbs it.
+    // flushAll() emits everything (synchronize, event records, memory pressure).
+    void flush(bool keepIdleFills = true);
+    void flushAll() { flush(false); }
 
     // immediate ops (flush first, then launch fixed kernels)
     void sum(const aixb200_tensor* a, const aixb200_tensor* r);
@@ -125,6 +130,7 @@ public:
         uint64_t termPitch;                 // fp16 elements between rows of `terms`: 2 * paddedCols plus an optional pad
         void*    terms;                     // device block of rows * 2 * paddedCols fp16
         uint32_t slot;                      // index of the bit pattern of max|x| in the slot block
+        bool     ownsSlot;                  // false: the slot belongs to the operand's region (its producer left the maximum there)
         size_t   bytes;
         uint64_t stamp;
     };
@@ -134,10 +140,17 @@ public:
     uint32_t* preparedSlot(uint32_t slot) const { return static_cast<uint32_t*>(m_termSlots) + slot; }
     void invalidatePreparedTerms(const void* lo, const void* hi);
     bool preparedTermsEnabled() const { return m_termCacheEnabled; }
+    // max|x| of a matmul operand, left by the kernel that produced it. Tensors that were f32 matmul operands are remembered
+    // by address range; when a generated kernel stores exactly such a range, it folds max|x| of what it stores as one more
+    // reduction epilogue into the range's slot, and the next preparation of that operand skips its max pass. Returns the
+    // slot index, or -1 when no fresh maximum is known.
+    int freshOperandMax(const void* lo, const void* hi) const;
     bool ownsMemory(const void* p) const { return m_allocator->findBlock(p) != nullptr; }
     // Called at the top of every C-ABI entry: the host operands the previous call staged are consumed by work that is
     // recorded or enqueued by now, so their blocks may follow the usual deferred-release path.
-    void beginCall() { if (!m_staged.empty()) retireStaged(); }
+    void beginCall() { if (!m_staged.empty()) retireStaged(); m_callRanges.clear(); }
+    // Byte range the call in progress reads or writes outside the recorder's view (immediate kernels, copies, collectives).
+    void noteCallRange(const void* lo, const void* hi) { m_callRanges.push_back({static_cast<const char*>(lo), static_cast<const char*>(hi)}); }
 
 private:
     void record(OpRecord&& rec);
@@ -164,6 +177,8 @@ private:
     std::unordered_set<const void*> m_released;        // storages deallocated while ops were pending
     std::vector<void*> m_deferredFrees;
     std::vector<void*> m_staged;                       // staging copies of host operands of the call in progress
+    std::vector<std::pair<const char*, const char*>> m_callRanges;
+    bool m_keepIdleFills = true;                       // AIXB200_KEEP_IDLE_FILLS=0: every flush emits every recorded fill
     uint64_t m_deferredBytes = 0;
     PlannerLimits  m_limits;
     CodegenOptions m_codegen;
@@ -184,6 +199,13 @@ private:
     void orderAfterCollectives(const View& v);
     void startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue);
     void scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale);  // the device's stream waits for in-flight collectives that touch the view
+    struct OperandRegion { const char* lo; const char* hi; uint32_t slot; bool fresh; uint64_t stamp; };
+    std::vector<OperandRegion> m_operandRegions;
+    std::vector<size_t> m_operandSizes;     // byte sizes of tensors that have been f32 matmul operands
+    uint32_t m_dummySlot = 0;               // where an epilogue writes when no region could be had
+    int  rememberOperandRegion(const char* lo, const char* hi, bool operandNow);
+    void appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::vector<std::vector<std::pair<const char*, const char*>>>& regionsOf);
+    bool m_fuseOperandMax = true;           // AIXB200_FUSE_OPERAND_MAX=0: every preparation runs its own max pass
     std::vector<PreparedTerms> m_preparedTerms;
     std::vector<uint32_t> m_freeTermSlots;
     void*    m_termSlots = nullptr;

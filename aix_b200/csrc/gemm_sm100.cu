@@ -16,9 +16,12 @@
 // Operands may be K-major or MN-major (row- or column-major views): the shared-memory matrix descriptors and the
 // TMA boxes are chosen per operand, so forward (A.B), dX (G.B^T) and dW (A^T.G) run without materialised transposes.
 // f32 problems run on the 16-bit pipes from split operands (pair kernel: two fp16 terms per scaled operand, three
-// passes; single-CTA kernel: a TF32 main pass plus two bf16 cross-term passes). Because the tensor core's f32
-// accumulation truncates, K is cut into chunks of 512 whose partial sums are added into C with IEEE additions
-// (TMA reduce-add in L2, or by the epilogue threads on the direct path).
+// passes, in an instantiation of its own whose issue loops do not depend on the pass; single-CTA kernel and the
+// AIXB200_GEMM_F32=hybrid form: a TF32 main pass plus two bf16 cross-term passes). Because the tensor core's f32
+// accumulation truncates, K is cut into chunks whose partial sums are added with IEEE additions: in the three-pass
+// kernel in registers of eight epilogue warps (C is stored once per tile), in the hybrid form by TMA reduce-add in L2 or
+// by the epilogue threads on the direct path. A tensor's two-term form is prepared once and cached by the device
+// (Device::PreparedTerms); it is read K-major or MN-major, whichever the view asks for.
 // Every wait on an mbarrier or on a flag of another cluster is bounded in time; on expiry the kernel raises an error
 // word and drains.
 #include "gemm.hpp"
@@ -1373,7 +1376,7 @@ __global__ void __launch_bounds__(256) splitF16Kernel(const float* __restrict__ 
 
 // max|x| of the operand into *slot (zeroed beforehand), then its two-term fp16 split.
 void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uint64_t rowStride, uint64_t colStride, uint32_t rows, uint32_t k,
-                         uint32_t kPad, uint32_t outPitch, uint16_t* terms, uint32_t* slot)
+                         uint32_t kPad, uint32_t outPitch, uint16_t* terms, uint32_t* slot, bool maxKnown = false)
 {
     const bool aligned = reinterpret_cast<uintptr_t>(src) % 16 == 0;
     const unsigned maxGrid = static_cast<unsigned>(smCount) * 8;
@@ -1381,7 +1384,8 @@ void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uin
     {
         const uint32_t vec = colStride == 1 && aligned && rowStride % 4 == 0 && k % 4 == 0;
         const uint64_t items = static_cast<uint64_t>(rows) * (vec ? k / 4 : k);
-        absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, rows, k, rowStride, colStride, vec, slot);
+        if (!maxKnown)
+            absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, rows, k, rowStride, colStride, vec, slot);
         splitF16Kernel<false><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, outPitch, terms,
                                                                                       colStride == 1 && aligned && rowStride % 4 == 0, slot);
     }
@@ -1389,7 +1393,8 @@ void launchHalfTermSplit(cudaStream_t stream, int smCount, const float* src, uin
     {
         const uint32_t vec = aligned && colStride % 4 == 0 && rows % 4 == 0;
         const uint64_t items = static_cast<uint64_t>(k) * (vec ? rows / 4 : rows);
-        absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, k, rows, colStride, rowStride, vec, slot);
+        if (!maxKnown)
+            absMaxKernel<<<static_cast<unsigned>(std::min<uint64_t>(maxGrid, (items + 255) / 256)), 256, 0, stream>>>(src, k, rows, colStride, rowStride, vec, slot);
         splitF16Kernel<true><<<dim3(kPad / 64, (rows + 63) / 64), 256, 0, stream>>>(src, rowStride, colStride, rows, k, kPad, outPitch, terms,
                                                                                      aligned && colStride % 4 == 0, slot);
     }
@@ -1681,11 +1686,12 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                     if (!e)
                     {
                         e = device.addPreparedTerms(base, rows, cols, pitch);
-                        if (cudaMemsetAsync(device.preparedSlot(e->slot), 0, 4, ctx.stream) != cudaSuccess) return false;
+                        // the kernel that wrote the tensor may have left max|x| in the slot already (e->ownsSlot == false)
+                        if (e->ownsSlot && cudaMemsetAsync(device.preparedSlot(e->slot), 0, 4, ctx.stream) != cudaSuccess) return false;
                         launchHalfTermSplit(ctx.stream, ctx.smCount, src, pitch, 1, static_cast<uint32_t>(rows), static_cast<uint32_t>(cols),
                                             static_cast<uint32_t>(e->paddedCols), static_cast<uint32_t>(e->termPitch), static_cast<uint16_t*>(e->terms),
-                                            device.preparedSlot(e->slot));
-                        preparedLaunches += 2;
+                                            device.preparedSlot(e->slot), !e->ownsSlot);
+                        preparedLaunches += e->ownsSlot ? 2 : 1;
                     }
                     out->terms = static_cast<const uint16_t*>(e->terms);
                     out->scale = device.preparedSlot(e->slot);

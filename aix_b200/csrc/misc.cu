@@ -6,6 +6,8 @@
 #include "kernels.hpp"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace aixb200::kernels
 {
@@ -37,59 +39,111 @@ inline unsigned int gridFor(uint64_t count, int smCount)
     return static_cast<unsigned int>(std::max<uint64_t>(1, std::min<uint64_t>(blocks, static_cast<uint64_t>(smCount) * 16)));
 }
 
-// ---- argmax over everything: one CTA, first maximal index wins (aixDeviceCPU.cpp:258-272) -------------------
+// ---- argmax over everything: first maximal index wins (aixDeviceCPU.cpp:258-272) ----------------------------------
+// Stage 1: every CTA scans a grid-strided share (each thread sees its indices in increasing order and keeps the first
+// strictly greater value), folds it with the tie rule "equal value -> smaller index" and leaves one (value, index)
+// partial in scratch; the CTA that draws the last ticket folds the partials with the same rule, so the result is the
+// one the reference's sequential loop finds, whatever the grid. The one-hot form needs the winner in every CTA and
+// takes a second launch. (The reference runs a multi-pass tree, aixDeviceMetalShaders.hpp:1667-1800.)
+constexpr int kArgmaxBlock = 256;
+constexpr size_t kArgmaxTicketOffset = 64, kArgmaxWinnerOffset = 72;
+constexpr unsigned kArgmaxMaxBlocks = 1024;
+
+template <class V> __device__ __forceinline__ void argmaxFold(V& bestV, uint64_t& bestI, V otherV, uint64_t otherI)
+{
+    if (otherI != ~0ull && (bestI == ~0ull || otherV > bestV || (otherV == bestV && otherI < bestI))) { bestV = otherV; bestI = otherI; }
+}
+
 template <int DT>
-__global__ void __launch_bounds__(1024) argmaxAllKernel(const typename Elem<DT>::S* __restrict__ src, Layout layout, uint64_t n,
-                                                        int32_t* dst, bool oneHot)
+__global__ void __launch_bounds__(kArgmaxBlock) argmaxAllKernel(const typename Elem<DT>::S* __restrict__ src, Layout layout, uint64_t n,
+                                                                typename Elem<DT>::V* partialV, uint64_t* partialI, unsigned int* ticket,
+                                                                uint64_t* winnerSlot, int32_t* dst, bool oneHot)
 {
     typedef Elem<DT> E;
     typedef typename E::V V;
-    __shared__ V bestV[1024];
-    __shared__ uint64_t bestI[1024];
+    __shared__ V sharedV[kArgmaxBlock];
+    __shared__ uint64_t sharedI[kArgmaxBlock];
+    __shared__ bool isLast;
     V best = E::lowest();
     uint64_t bestIdx = ~0ull;
-    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x)
+    const bool dense = layout.rank <= 1 && (layout.rank == 0 || layout.strides[0] == 1);
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kArgmaxBlock + threadIdx.x; i < n; i += static_cast<uint64_t>(gridDim.x) * kArgmaxBlock)
     {
-        const V v = E::load(src[layoutOffset(i, layout)]);
+        const V v = E::load(src[dense ? i : layoutOffset(i, layout)]);
         if (bestIdx == ~0ull || v > best) { best = v; bestIdx = i; }
     }
-    bestV[threadIdx.x] = best;
-    bestI[threadIdx.x] = bestIdx;
-    __syncthreads();
-    for (int s = blockDim.x / 2; s > 0; s >>= 1)
+    auto blockFold = [&]()
     {
-        if (threadIdx.x < s)
-        {
-            const V ov = bestV[threadIdx.x + s];
-            const uint64_t oi = bestI[threadIdx.x + s];
-            const uint64_t mi = bestI[threadIdx.x];
-            if (oi != ~0ull && (mi == ~0ull || ov > bestV[threadIdx.x] || (ov == bestV[threadIdx.x] && oi < mi)))
-            {
-                bestV[threadIdx.x] = ov;
-                bestI[threadIdx.x] = oi;
-            }
-        }
+        sharedV[threadIdx.x] = best;
+        sharedI[threadIdx.x] = bestIdx;
         __syncthreads();
-    }
-    // The sequential loop of the reference keeps index 0 unless a strictly greater value appears, so NaN-free data
-    // gives the first maximal index; that is what the tie rule above reproduces.
-    const uint64_t winner = bestI[0] == ~0ull ? 0 : bestI[0];
-    if (!oneHot)
+        for (int s = kArgmaxBlock / 2; s > 0; s >>= 1)
+        {
+            if (threadIdx.x < s)
+            {
+                V v = sharedV[threadIdx.x];
+                uint64_t i = sharedI[threadIdx.x];
+                argmaxFold(v, i, sharedV[threadIdx.x + s], sharedI[threadIdx.x + s]);
+                sharedV[threadIdx.x] = v;
+                sharedI[threadIdx.x] = i;
+            }
+            __syncthreads();
+        }
+    };
+    blockFold();
+    if (threadIdx.x == 0)
     {
-        if (threadIdx.x == 0) dst[0] = static_cast<int32_t>(winner);
-        return;
+        partialV[blockIdx.x] = sharedV[0];
+        partialI[blockIdx.x] = sharedI[0];
+        __threadfence();
+        isLast = atomicAdd(ticket, 1u) == gridDim.x - 1;
     }
-    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = (i == winner) ? 1 : 0;
+    __syncthreads();
+    if (!isLast) return;
+    __threadfence();
+    best = E::lowest();
+    bestIdx = ~0ull;
+    for (unsigned b = threadIdx.x; b < gridDim.x; b += kArgmaxBlock)
+        argmaxFold(best, bestIdx, *const_cast<volatile V*>(partialV + b), *const_cast<volatile uint64_t*>(partialI + b));
+    blockFold();
+    if (threadIdx.x == 0)
+    {
+        // The sequential loop of the reference keeps index 0 unless a strictly greater value appears.
+        const uint64_t winner = sharedI[0] == ~0ull ? 0 : sharedI[0];
+        if (oneHot) *winnerSlot = winner; else dst[0] = static_cast<int32_t>(winner);
+        *ticket = 0;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) oneHotKernel(int32_t* dst, uint64_t n, const uint64_t* winnerSlot)
+{
+    const uint64_t winner = *winnerSlot;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+        dst[i] = (i == winner) ? 1 : 0;
 }
 
 template <int DT>
 void launchArgmaxAll(const LaunchContext& ctx, const View& src, int32_t* dst, bool oneHot, uint64_t count)
 {
+    typedef typename Elem<DT>::V V;
     Layout l{};
     l.rank = src.rank;
     for (int d = 0; d < src.rank; ++d) { l.shape[d] = src.shape[d]; l.strides[d] = src.strides[d]; }
-    argmaxAllKernel<DT><<<1, 1024, 0, ctx.stream>>>(reinterpret_cast<const typename Elem<DT>::S*>(src.firstByte()), l, count, dst, oneHot);
+    char* scratch = static_cast<char*>(ctx.scratch);
+    auto partialV = reinterpret_cast<V*>(scratch + kScratchCounterBytes);
+    auto partialI = reinterpret_cast<uint64_t*>(scratch + kScratchCounterBytes + kArgmaxMaxBlocks * 8);
+    auto ticket = reinterpret_cast<unsigned int*>(scratch + kArgmaxTicketOffset);
+    auto winner = reinterpret_cast<uint64_t*>(scratch + kArgmaxWinnerOffset);
+    const uint64_t wanted = (count + kArgmaxBlock * 8 - 1) / (kArgmaxBlock * 8);
+    const unsigned grid = static_cast<unsigned>(std::max<uint64_t>(1, std::min<uint64_t>(wanted, std::min<uint64_t>(kArgmaxMaxBlocks, static_cast<uint64_t>(ctx.smCount) * 4))));
+    argmaxAllKernel<DT><<<grid, kArgmaxBlock, 0, ctx.stream>>>(reinterpret_cast<const typename Elem<DT>::S*>(src.firstByte()), l, count, partialV, partialI,
+                                                               ticket, winner, dst, oneHot);
     if (ctx.launches) ++*ctx.launches;
+    if (oneHot)
+    {
+        oneHotKernel<<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(dst, count, winner);
+        if (ctx.launches) ++*ctx.launches;
+    }
 }
 
 // ---- argmax along one dimension: one thread per output (aixDeviceCPU.cpp:275-352) ---------------------------
@@ -313,6 +367,57 @@ __global__ void __launch_bounds__(kBlock) indexAddKernel(const typename Elem<DT>
     }
 }
 
+// indexAdd with few (outer, within) lanes and a long index list: parallel over every source element, colliding
+// destinations resolved by atomics (the reference's Metal kernels do the same, aixDeviceMetalShaders.hpp:2289-2314).
+// Integer sums wrap, so any order gives the reference's bits; floating sums depend on the order of colliding adds within
+// rounding. f32 / f64 / i32 / i64 use the native atomics; 16- and 8-bit types a compare-and-swap on the enclosing 32-bit
+// word, rounding to the storage type after every add like the sequential form.
+template <int DT> __device__ __forceinline__ void atomicAccumulate(typename Elem<DT>::S* dst, uint64_t off, typename Elem<DT>::S value)
+{
+    typedef Elem<DT> E;
+    typedef typename E::S S;
+    typedef Reduce<DT, false> R;
+    if constexpr (DT == 0) atomicAdd(reinterpret_cast<double*>(dst) + off, static_cast<double>(value));
+    else if constexpr (DT == 1) atomicAdd(reinterpret_cast<float*>(dst) + off, static_cast<float>(value));
+    else if constexpr (DT == 4) atomicAdd(reinterpret_cast<unsigned long long*>(dst) + off, static_cast<unsigned long long>(value));
+    else if constexpr (DT == 5) atomicAdd(reinterpret_cast<int*>(dst) + off, static_cast<int>(value));
+    else
+    {
+        const uintptr_t address = reinterpret_cast<uintptr_t>(dst + off);
+        unsigned int* word = reinterpret_cast<unsigned int*>(address & ~uintptr_t(3));
+        const unsigned shift = static_cast<unsigned>(address & 3u) * 8u;
+        const unsigned mask = (sizeof(S) == 2 ? 0xFFFFu : 0xFFu) << shift;
+        unsigned int seen = *word, assumed;
+        do
+        {
+            assumed = seen;
+            S held;
+            if constexpr (sizeof(S) == 2) { const uint16_t bits = static_cast<uint16_t>((assumed & mask) >> shift); memcpy(&held, &bits, 2); }
+            else { const uint8_t bits = static_cast<uint8_t>((assumed & mask) >> shift); memcpy(&held, &bits, 1); }
+            const S sum = R::finish(R::merge(R::liftStored(held), R::liftStored(value)));
+            unsigned int bits = 0;
+            memcpy(&bits, &sum, sizeof(S));
+            seen = atomicCAS(word, assumed, (assumed & ~mask) | ((bits << shift) & mask));
+        } while (seen != assumed);
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kBlock) indexAddAtomicKernel(const typename Elem<DT>::S* __restrict__ src, Layout srcLayout,
+                                                               typename Elem<DT>::S* dst, const int32_t* __restrict__ indices, Layout indexLayout,
+                                                               uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t srcCount,
+                                                               uint32_t* badIndex)
+{
+    const uint64_t extent = sliceSize ? dimSize / sliceSize : 0;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; t < srcCount; t += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        const uint64_t within = t % sliceSize, idx = (t / sliceSize) % indexCount, outer = t / (indexCount * sliceSize);
+        const int64_t index = indices[layoutOffset(idx, indexLayout)];
+        if (index < 0 || static_cast<uint64_t>(index) >= extent) { *badIndex = 1u; continue; }
+        atomicAccumulate<DT>(dst, outer * dimSize + static_cast<uint64_t>(index) * sliceSize + within, src[layoutOffset(t, srcLayout)]);
+    }
+}
+
 template <int DT>
 __global__ void __launch_bounds__(kBlock) scaleKernel(typename Elem<DT>::S* data, uint64_t count, double scale)
 {
@@ -360,6 +465,15 @@ template <int DT> void launchIndexAdd(const LaunchContext& ctx, const void* src,
     typedef typename Elem<DT>::S S;
     const uint64_t lanes = indexCount ? srcCount / indexCount : 0;
     if (lanes == 0) return;
+    // Enough (outer, within) lanes to fill the GPU: one thread per lane walks the index list in order (deterministic,
+    // coalesced). Fewer lanes and a longer list: one thread per source element with atomics.
+    static const bool atomicsAllowed = []{ const char* v = std::getenv("AIXB200_INDEX_ADD_ATOMICS"); return !(v && v[0] == '0'); }();
+    if (atomicsAllowed && lanes < static_cast<uint64_t>(ctx.smCount) * 512 && indexCount >= 8)
+    {
+        indexAddAtomicKernel<DT><<<gridFor(srcCount, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, il,
+                                                                                          indexCount, sliceSize, dimSize, srcCount, badIndexWord(ctx));
+        return;
+    }
     indexAddKernel<DT><<<gridFor(lanes, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, il,
                                                                                  indexCount, sliceSize, dimSize, lanes, badIndexWord(ctx));
 }

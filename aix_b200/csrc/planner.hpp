@@ -74,7 +74,8 @@ struct KernelNode
 };
 
 struct KernelLoad  { View view; Access access; };
-struct KernelReduce { uint16_t node; bool isMax; uint8_t dtype; View out; };   // out: the one-element result
+struct KernelReduce { uint16_t node; bool isMax; uint8_t dtype; View out; bool absBits = false; };   // out: the one-element result;
+                                            // absBits (f32 only): the result is the bit pattern of max|x| (a matmul operand's scale)
 struct KernelStore { View view; Access access; uint16_t node; };
 // One result per row of the kernel's [count / rowCols, rowCols] iteration space: out[row] = fold(initial, node over the row).
 // The initial value is what the destination holds, or - when the destination was filled by a pending op that nobody

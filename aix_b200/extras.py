@@ -137,8 +137,46 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
             "loss_after_warmup": first, "loss_at_end": last}
 
 
+def measure_cold_ops(dev, hbm_peak, n=10_000_000):
+    """The remaining aix::Device virtuals at the size the reference's own device benchmarks use (10 M f32 elements,
+    Targets/AIXBenchmarks/Device.cpp; transpose at its 5000 x 5000): device time per call and the rate of the bytes each
+    call has to move. They are off the hot path; the figures say how far."""
+    rng = np.random.default_rng(0)
+    out, holder = {}, {}
+    x = TensorValue.from_numpy(rng.normal(0, 1, n).astype(np.float32), dev)
+    sq = TensorValue.from_numpy(rng.normal(0, 1, (5000, 5000)).astype(np.float32), dev)
+    rows = TensorValue.from_numpy(rng.normal(0, 1, (10000, 1000)).astype(np.float32), dev)
+    idx = TensorValue.from_numpy(rng.integers(0, 10000, 10000), dev, C.I32)
+    few = TensorValue.from_numpy(rng.normal(0, 1, (64, 1000)).astype(np.float32), dev)
+    idx_few = TensorValue.from_numpy(rng.integers(0, 64, 10000), dev, C.I32)
+    r32 = TensorValue.empty((), dev, C.I32)
+    onehot = TensorValue.empty((n,), dev, C.I32)
+    sq_t = TensorValue.empty((5000, 5000), dev)
+    sel = TensorValue.empty((10000, 1000), dev)
+    tri = TensorValue.empty((5000, 5000), dev)
+    dev.synchronize()
+    cases = {
+        "argmax 10M f32": (lambda: dev.argmax(x.deviceParams(), r32.deviceParams()), 4 * n),
+        "argmaxIndices 10M f32": (lambda: dev.argmaxIndices(x.deviceParams(), onehot.deviceParams()), 8 * n),
+        "max 10M f32": (lambda: holder.__setitem__("m", x.max()), 4 * n),
+        "transpose 5000x5000 f32 (materialised)": (lambda: dev.transpose(sq.deviceParams(), sq_t.deviceParams(), 0, 1), 8 * 25_000_000),
+        "contiguous of a transposed 5000x5000 view": (lambda: holder.__setitem__("c", sq.transpose(0, 1).contiguous()), 8 * 25_000_000),
+        "tril 5000x5000 f32": (lambda: dev.tril(sq.deviceParams(), tri.deviceParams(), 0), 8 * 25_000_000),
+        "indexSelect 10000 rows of 1000 f32": (lambda: dev.indexSelect(rows.deviceParams(), sel.deviceParams(), idx.deviceParams(), 0), 8 * n),
+        "indexAdd 10000 rows of 1000 f32 into 10000 (lane-parallel form)": (lambda: dev.indexAdd(sel.deviceParams(), rows.deviceParams(), idx.deviceParams(), 0), 12 * n),
+        "indexAdd 10000 rows of 1000 f32 into 64 (atomic form)": (lambda: dev.indexAdd(sel.deviceParams(), few.deviceParams(), idx_few.deviceParams(), 0), 4 * n),
+        "sliceSet 5000x2500 into every other column": (lambda: dev.sliceSet(TensorValue(sq.storage, (5000, 2500), (2500, 1), 0, C.F32, dev).deviceParams(),
+                                                                              tri.deviceParams(), 1, 0, 5000, 2), 8 * 12_500_000),
+    }
+    for name, (fn, nbytes) in cases.items():
+        ms, _host = _time(dev, fn, iters=5, warmup=2)
+        out[name] = {"ms": ms, "GB/s": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm_peak}
+    return out
+
+
 def measure_extras(dev, hbm_peak, tensor_peak):
-    return {"reductions_8192x8192_bf16": measure_reductions(dev, hbm_peak), "matmul": measure_matmul(dev, tensor_peak)}
+    return {"reductions_8192x8192_bf16": measure_reductions(dev, hbm_peak), "matmul": measure_matmul(dev, tensor_peak),
+            "cold_ops_10M": measure_cold_ops(dev, hbm_peak)}
 
 
 def measure_config1_sharded(dev, hbm_peak, rank, world_size, rows=8192, cols=8192, barrier=None, reduce_max=None):

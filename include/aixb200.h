@@ -216,7 +216,8 @@ typedef struct aixb200_stats
     uint64_t reductions_fused;      /* full sums / maxima folded into the kernel that produces their operand */
     uint64_t prepared_operand_hits; /* f32 matmul operands whose two-term fp16 form was still cached */
     uint64_t prepared_operand_builds; /* ... and those that had to be prepared (max pass + split) */
-    uint64_t reserved[3];
+    uint64_t prepared_operand_max_known; /* ... of which the max pass was skipped: the producing kernel had left max|x| */
+    uint64_t reserved[2];
 } aixb200_stats;
 int aixb200_get_stats(aixb200_device* dev, aixb200_stats* out);
 /* CUDA C source of the most recently generated kernel (for inspection and tests); NULL if none yet. */

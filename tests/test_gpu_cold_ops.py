@@ -117,3 +117,66 @@ def test_index_select_and_index_add(b200, ref, dtype):
         got, want = both(b200, ref, run)
         assert np.array_equal(got[0], want[0]), f"indexSelect {DTYPE_NAMES[dtype]} {shape} dim {dim}"
         assert_close(got[1], want[1], dtype, f"indexAdd {DTYPE_NAMES[dtype]} {shape} dim {dim}", scale=np.maximum(1.0, np.abs(want[1]) * 4))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, I32, I16, U8], ids=lambda d: DTYPE_NAMES[d])
+def test_argmax_over_many_blocks_keeps_the_first_maximum(b200, ref, dtype):
+    """Sizes that take many CTAs: the two-stage fold must still return the FIRST maximal index
+    (aixDeviceCPU.cpp:263-272), also when the maximum occurs thousands of times."""
+    rng = np.random.default_rng(900 + dtype)
+    for n in (100003, (1 << 21) + 5):
+        x = rng.integers(0, 9, n)                       # few distinct values: the maximum 8 appears everywhere
+        first = int(np.argmax(x))
+        t = TensorValue.from_numpy(x, b200, dtype)
+        r = TensorValue.empty((), b200, I32)
+        b200.argmax(t.deviceParams(), r.deviceParams())
+        assert int(r.numpy()) == first
+        oh = TensorValue.empty((n,), b200, I32)
+        b200.argmaxIndices(t.deviceParams(), oh.deviceParams())
+        got = oh.numpy()
+        assert got.sum() == 1 and got[first] == 1
+    x = values(rng, (300, 700), dtype)
+    got, want = both(b200, ref, lambda dev: _argmax_pair(dev, x, dtype))
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+
+
+def _argmax_pair(dev, x, dtype):
+    t = TensorValue.from_numpy(x, dev, dtype).transpose(0, 1)          # strided source
+    r = TensorValue.empty((), dev, I32)
+    dev.argmax(t.deviceParams(), r.deviceParams())
+    oh = TensorValue.empty(t.shape, dev, I32)
+    dev.argmaxIndices(t.deviceParams(), oh.deviceParams())
+    return r.numpy(), oh.numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
+def test_index_add_with_a_long_index_list_and_collisions(b200, ref, dtype):
+    """Few lanes and a long index list take the atomic form: integer results must equal the sequential ones bit for
+    bit (wrapping sums commute); floating results within the type's tolerance of the per-add rounding."""
+    rng = np.random.default_rng(950 + dtype)
+    for shape, dim, count in [((50, 8), 0, 4000), ((3, 64, 4), 1, 1000), ((257,), 0, 5000)]:
+        idx = rng.integers(0, shape[dim], count)
+        src_shape = list(shape)
+        src_shape[dim] = count
+        base = values(rng, shape, dtype)
+        add = values(rng, src_shape, dtype)
+        if dtype in (F32, F64, BF16, F16):
+            add = np.round(add / 8.0, 3)                # keep 16-bit running sums in range
+
+        def run(dev):
+            acc = TensorValue.from_numpy(base, dev, dtype)
+            source = TensorValue.from_numpy(add, dev, dtype)
+            indices = TensorValue.from_numpy(idx, dev, I32)
+            dev.indexAdd(source.deviceParams(), acc.deviceParams(), indices.deviceParams(), dim)
+            return acc.numpy()
+        got, want = both(b200, ref, run)
+        if dtype in (F32, F64):
+            assert_close(got, want, dtype, f"indexAdd {shape}", scale=np.maximum(1.0, np.abs(want)) * 64)
+        elif dtype in (BF16, F16):
+            # every add rounds to the 16-bit type, in a different order than the sequential loop: compare with the exact sum
+            exact = np.array(base, dtype=np.float64)
+            np.add.at(np.moveaxis(exact, dim, 0), idx, np.moveaxis(np.array(add, dtype=np.float64), dim, 0))      # a view: adds land in `exact`
+            tol = 0.05 * np.maximum(1.0, np.abs(exact)) + 0.3
+            assert np.all(np.abs(got - exact) <= tol), f"indexAdd {DTYPE_NAMES[dtype]} {shape}"
+        else:
+            assert np.array_equal(got, want), f"indexAdd {DTYPE_NAMES[dtype]} {shape}"

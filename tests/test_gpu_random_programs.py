@@ -56,3 +56,34 @@ def test_random_program_matches_the_cpu_device(b200, ref, seed):
         assert_close(g, w, F32, f"seed {seed}: tensor {k}", scale=max(1.0, float(np.abs(w).max())) * 4.0)
     for k, (g, w) in enumerate(zip(got_s, want_s)):
         assert abs(g - w) <= 4e-5 * max(1.0, abs(w), ROWS * COLS * 0.25), f"seed {seed}: scalar {k}: {g} vs {w}"
+
+
+def test_fills_kept_across_flushes_land_in_program_order(b200, ref):
+    """A fill whose buffer nothing uses yet stays recorded over later flushes. Whatever comes next - an accumulation, a
+    read through another call, a second fill, a host read, a deallocation - must see it exactly where it was issued."""
+    import numpy as np
+    from aix_b200 import F32, TensorValue
+    rng = np.random.default_rng(77)
+    a = rng.normal(0, 1, (256, 192)).astype(np.float32)
+    b = rng.normal(0, 1, (192, 256)).astype(np.float32)
+    outs = []
+    for dev in (b200, ref):
+        ta, tb = TensorValue.from_numpy(a, dev), TensorValue.from_numpy(b, dev)
+        g1 = TensorValue.full(0.0, (256, 256), dev)          # accumulated into after two matmuls
+        g2 = TensorValue.full(5.0, (256, 256), dev)          # read by a reduction (an immediate call) later
+        g3 = TensorValue.full(1.0, (256, 256), dev)          # overwritten by a second fill, then read on the host
+        g4 = TensorValue.full(9.0, (256, 256), dev)          # dropped without ever being used
+        c = ta.matmul(tb)
+        d = c.matmul(ta.matmul(tb))
+        g1 += d
+        g1 += c
+        del g4
+        s = g2.sum(0)
+        g3.fill(2.0)
+        e = ta.matmul(tb)
+        g2 += e
+        outs.append([g1.numpy(), s.numpy(), g3.numpy(), g2.numpy()])
+    from conftest import assert_close
+    for k, what in enumerate(("accumulated", "column sums of a filled buffer", "refilled", "filled then accumulated")):
+        # matmul results are compared norm-wise (the CPU device's own sequential f32 dot products carry that much error)
+        assert_close(outs[0][k], outs[1][k], F32, what, scale=float(np.max(np.abs(outs[1][k]))) if k in (0, 3) else None)

@@ -272,3 +272,33 @@ def test_descriptors_that_alias_through_different_base_pointers_are_ordered(dry)
     u = other * 2.0
     dry.synchronize()
     assert delta(dry, s1)["fused_kernels"] == 3, "reader, overlapping writer, reader: three kernels in program order"
+
+
+def test_idle_fills_stay_recorded_until_something_uses_their_buffer(dry):
+    """zeroGrad() fills every gradient, and the accumulation `grad += dW` comes several matmuls later: a fill that nothing
+    else touches survives the flushes in between (the reference defers such fills too, aixFuse.cpp:891-916) and is then
+    absorbed by the accumulation instead of costing a kernel and a pass over the buffer."""
+    a, b = TensorValue.full(1.0, (128, 128), dry), TensorValue.full(2.0, (128, 128), dry)
+    dry.synchronize()
+    s0 = dry.stats()
+    g = TensorValue.full(0.0, (128, 128), dry)           # idle fill
+    c = a.matmul(b)                                      # flushes the recorder; the fill has nothing to do with it
+    d1 = delta(dry, s0)
+    assert d1["fused_kernels"] == 0, "the idle fill must not be launched by the matmul's flush"
+    g += c                                               # the accumulation absorbs it: g = 0 + c in one kernel, no load of g
+    dry.synchronize()
+    d2 = delta(dry, s0)
+    assert d2["fused_kernels"] == 1 and d2["fills_absorbed"] >= 1
+    assert dry.lastKernelSource().count("const Df32::S* const l") == 1       # one load (c), not two
+    # synchronize() emits whatever is still recorded: the host may read the buffer afterwards
+    s1 = dry.stats()
+    h = TensorValue.full(3.0, (64,), dry)
+    e = a.matmul(b)
+    assert delta(dry, s1)["fused_kernels"] == 0
+    dry.synchronize()
+    assert delta(dry, s1)["fused_kernels"] == 1
+    # a call that touches the buffer itself flushes the fill first
+    s2 = dry.stats()
+    k = TensorValue.full(0.0, (128, 128), dry)
+    dry.matmul(a.deviceParams(), b.deviceParams(), k.deviceParams())          # k is the result: its fill must not come after
+    assert delta(dry, s2)["fused_kernels"] == 1
