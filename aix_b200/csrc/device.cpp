@@ -307,7 +307,12 @@ int Device::rememberOperandRegion(const char* lo, const char* hi, bool operandNo
     if (operandNow && std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) == m_operandSizes.end() && m_operandSizes.size() < 32)
         m_operandSizes.push_back(bytes);
     for (size_t i = 0; i < m_operandRegions.size(); ++i)
-        if (m_operandRegions[i].lo == lo && m_operandRegions[i].hi == hi) { m_operandRegions[i].stamp = ++m_preparedStamp; return static_cast<int>(i); }
+        if (m_operandRegions[i].lo == lo && m_operandRegions[i].hi == hi)
+        {
+            m_operandRegions[i].stamp = ++m_preparedStamp;
+            m_operandRegions[i].operand = m_operandRegions[i].operand || operandNow;
+            return static_cast<int>(i);
+        }
     if (m_operandRegions.size() >= 64 || m_freeTermSlots.size() < 64)
     {
         // forget the range used longest ago, unless a prepared form still reads its slot
@@ -324,14 +329,15 @@ int Device::rememberOperandRegion(const char* lo, const char* hi, bool operandNo
         m_operandRegions.pop_back();
     }
     if (m_freeTermSlots.empty()) return -1;
-    m_operandRegions.push_back({lo, hi, m_freeTermSlots.back(), false, ++m_preparedStamp});
+    m_operandRegions.push_back({lo, hi, m_freeTermSlots.back(), false, ++m_preparedStamp, operandNow});
     m_freeTermSlots.pop_back();
     return static_cast<int>(m_operandRegions.size() - 1);
 }
 
-// Every generated kernel that stores a dense f32 tensor of a size matmul operands have had folds max|x| of the stored values
-// into a slot of that tensor's range (the choice depends on sizes only, so a kernel's identity does not change with the
-// addresses the allocator happens to hand out). regionsOf[k] lists the ranges kernel k refreshes.
+// A generated kernel folds max|x| of a dense f32 tensor it stores into that tensor's slot when the tensor has the size of
+// earlier matmul operands and either is the kernel's only such store (activations, gradients: fresh allocations whose
+// addresses vary - the choice then depends on sizes only, so the kernel's identity is stable) or lives where a matmul operand
+// lives (weights updated in place next to optimizer state of the same size). regionsOf[k] lists the ranges kernel k refreshes.
 void Device::appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::vector<std::vector<std::pair<const char*, const char*>>>& regionsOf)
 {
     regionsOf.assign(kernels.size(), {});
@@ -339,12 +345,25 @@ void Device::appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::ve
     for (size_t k = 0; k < kernels.size(); ++k)
     {
         KernelSpec& spec = kernels[k];
+        auto qualifies = [&](const KernelStore& st)
+        {
+            if (st.view.dtype != F32 || !st.view.isDense() || st.view.size != spec.count) return false;
+            const size_t bytes = static_cast<size_t>(st.view.endByte() - st.view.firstByte());
+            return std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) != m_operandSizes.end();
+        };
+        size_t candidates = 0;
+        for (const KernelStore& st : spec.stores) candidates += qualifies(st) ? 1 : 0;
         for (const KernelStore& st : spec.stores)
         {
-            if (st.view.dtype != F32 || !st.view.isDense() || st.view.size != spec.count) continue;
+            if (!qualifies(st)) continue;
             if (spec.reductions.size() >= m_limits.maxReductionsPerKernel) break;
-            const size_t bytes = static_cast<size_t>(st.view.endByte() - st.view.firstByte());
-            if (std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) == m_operandSizes.end()) continue;
+            if (candidates > 1)
+            {
+                bool operandLivesThere = false;
+                for (const OperandRegion& r : m_operandRegions)
+                    operandLivesThere = operandLivesThere || (r.operand && r.lo == st.view.firstByte() && r.hi == st.view.endByte());
+                if (!operandLivesThere) continue;
+            }
             const int region = rememberOperandRegion(st.view.firstByte(), st.view.endByte(), false);
             View slot;
             slot.base = reinterpret_cast<char*>(preparedSlot(region >= 0 ? m_operandRegions[static_cast<size_t>(region)].slot : m_dummySlot));
@@ -356,14 +375,15 @@ void Device::appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::ve
     }
 }
 
-void Device::invalidatePreparedTerms(const void* lo, const void* hi)
+void Device::invalidatePreparedTerms(const void* lo, const void* hi, bool freed)
 {
     {
-        // whatever is written into an operand's range, the maximum its producer left is stale
+        // whatever is written into an operand's range, the maximum its producer left is stale; once the memory is freed,
+        // whatever lives there next is not the operand any more
         const char* first = static_cast<const char*>(lo);
         const char* last = static_cast<const char*>(hi);
         for (OperandRegion& r : m_operandRegions)
-            if (first < r.hi && r.lo < last) r.fresh = false;
+            if (first < r.hi && r.lo < last) { r.fresh = false; if (freed) r.operand = false; }
     }
     if (m_preparedTerms.empty()) return;
     const char* first = static_cast<const char*>(lo);
@@ -390,7 +410,7 @@ void Device::retireStaged()
 {
     for (void* p : m_staged)
     {
-        invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p));     // the block will hold other data next
+        invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p), true);     // the block will hold other data next
         m_released.insert(p);
         m_deferredFrees.push_back(p);
         m_deferredBytes += m_allocator->blockSize(p);
@@ -403,7 +423,7 @@ void Device::deallocate(void* p)
     if (!p) return;
     if (!m_allocator->owns(p)) failInvalid("deallocate: pointer was not allocated by this device");
     if (m_released.count(p)) failInvalid("deallocate: pointer was already deallocated");
-    invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p));
+    invalidatePreparedTerms(p, static_cast<char*>(p) + m_allocator->blockSize(p), true);
     if (!m_commInFlight.empty())
     {
         // a collective on the side stream may still use the block: reuse is ordered on the device's stream only

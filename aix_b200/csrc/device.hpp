@@ -138,7 +138,7 @@ public:
     const PreparedTerms* findPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch);
     const PreparedTerms* addPreparedTerms(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch);
     uint32_t* preparedSlot(uint32_t slot) const { return static_cast<uint32_t*>(m_termSlots) + slot; }
-    void invalidatePreparedTerms(const void* lo, const void* hi);
+    void invalidatePreparedTerms(const void* lo, const void* hi, bool freed = false);
     bool preparedTermsEnabled() const { return m_termCacheEnabled; }
     // max|x| of a matmul operand, left by the kernel that produced it. Tensors that were f32 matmul operands are remembered
     // by address range; when a generated kernel stores exactly such a range, it folds max|x| of what it stores as one more
@@ -199,7 +199,7 @@ private:
     void orderAfterCollectives(const View& v);
     void startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue);
     void scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale);  // the device's stream waits for in-flight collectives that touch the view
-    struct OperandRegion { const char* lo; const char* hi; uint32_t slot; bool fresh; uint64_t stamp; };
+    struct OperandRegion { const char* lo; const char* hi; uint32_t slot; bool fresh; uint64_t stamp; bool operand; };   // operand: the tensor living there has been a matmul operand
     std::vector<OperandRegion> m_operandRegions;
     std::vector<size_t> m_operandSizes;     // byte sizes of tensors that have been f32 matmul operands
     uint32_t m_dummySlot = 0;               // where an epilogue writes when no region could be had

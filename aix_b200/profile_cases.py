@@ -3,7 +3,7 @@ than the 126 MB L2 but hold well under a few GB on the device.
 
     python -m aix_b200.profile_cases <case> [repeats]
 
-cases: chain_f32 chain_bf16 chain_sum_f32 chain_sum_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
+cases: chain_f32 chain_bf16 chain_sum_f32 chain_sum_bf16 config1_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32 gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32
        gemm_bf16_k1024 gemm_f32_4096 gemm_f32_4096_nt gemm_f32_4096_tn gemm_f32_k1024 adam_f32 mlp_f32
 Prints the device time per repeat measured with events on the device's stream.
 """
@@ -36,6 +36,16 @@ def build(dev, case):
                 return z, z.sum()
             return both
         return lambda: chain(a, b, c)
+    if case == "config1_bf16":
+        # configuration 1 as the API issues it: y = relu(x*g + bias), y.sum(1), y.max(1), y.mean() - one row-form kernel
+        x = _rand(dev, (8192, 8192), C.BF16, 0)
+        g, b = _rand(dev, (8192,), C.BF16, 1), _rand(dev, (8192,), C.BF16, 2, 0.1)
+
+        def whole():
+            v = x * g + b
+            y = (v + (v * v).sqrt()) * 0.5
+            return y, y.sum(1), y.max(1), y.mean()
+        return whole
     if case in ("sum_f32", "sum_bf16"):
         x = _rand(dev, (1 << 17, 1024), C.F32 if case.endswith("f32") else C.BF16, 0)
         return lambda: x.sum()
@@ -89,8 +99,10 @@ def main():
     dev = DeviceB200(0)
     fn = build(dev, case)
     dev.synchronize()
+    marker = dev.createEvent()
     for _ in range(3):                   # warm-up: kernels compiled and loaded, allocator cache populated
         out = fn()
+        dev.recordEvent(marker)          # emits the recorded work per call, as the timed loop does (else the calls merge into other kernels)
     dev.synchronize()
     e0, e1 = dev.createEvent(), dev.createEvent()
     dev.flushL2()
