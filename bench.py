@@ -352,7 +352,7 @@ def main():
                 ids = [DeviceB200.commUniqueId() if rank == 0 else None]
                 dist.broadcast_object_list(ids, src=0)
                 dev.commInit(rank, world, ids[0])
-            from aix_b200.extras import measure_mlp
+            from bench_cases import measure_mlp
             mlp_steps = 100                              # the configuration is "100 steps from seed 0"
             common = dict(steps=mlp_steps, warmup=3, rank=rank, world_size=world, barrier=barrier, reduce_max=max_over_ranks)
             if world == 1:
@@ -365,7 +365,7 @@ def main():
                 mlp_train["ms_per_step_all_reduce_inside_backward"] = measure_mlp(dev, tensor_peak, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]
                 # the broadcast + reduction configuration with its rows split over the ranks (one scalar all-reduce for the mean)
-                from aix_b200.extras import measure_config1_sharded
+                from bench_cases import measure_config1_sharded
                 line["config1_sharded"] = measure_config1_sharded(dev, hbm_peak, rank, world, barrier=barrier, reduce_max=max_over_ranks)
                 means = [None] * world
                 dist.all_gather_object(means, line["config1_sharded"]["local_mean_of_this_rank"])
@@ -384,7 +384,7 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 1, "kind": "reference", "sample": f"unavailable: {exc}"}
         if not args.no_extras:
             try:
-                from aix_b200.extras import measure_extras
+                from bench_cases import measure_extras
                 line["extras"] = measure_extras(dev, hbm_peak, tensor_peak)
             except Exception as exc:
                 line["extras"] = {"error": str(exc)}

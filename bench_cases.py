@@ -1,13 +1,37 @@
-"""Secondary measurements printed beside the headline benchmark: the reduction kernels on the broadcast+reduction
-configuration (x [8192,8192] bf16) and the dense matmul configuration (4096^3, bf16 and f32). Device time by CUDA
-events on the device's stream, L2 flushed between iterations when the working set could fit in it."""
+#!/usr/bin/env python
+"""Measurement cases beside bench.py: the secondary kernel-class measurements its JSON line carries (`extras`, `mlp_train`,
+`config1_sharded`), the small fixed workloads the profiler captures under profiles/ were taken on, and the bandwidth sweep
+of the fused chain. Nothing of the device library imports this file.
+
+    python bench_cases.py <case> [repeats]         one kernel class a few times on inputs larger than L2 but well under a few GB;
+                                                   prints the device time per repeat (events on the device's stream). Cases:
+        chain_f32 chain_bf16 chain_sum_f32 chain_sum_bf16 config1_bf16 sum_f32 sum_bf16 rowsum_bf16 rowmax_bf16 colsum_f32
+        gemm_bf16_nt gemm_bf16_nn gemm_bf16_tn gemm_f32 gemm_bf16_k1024 gemm_f32_4096 gemm_f32_4096_nt gemm_f32_4096_tn
+        gemm_f32_k1024 gemm_f16_4096 gemm_bf16_k12288 adam_f32 mlp_f32
+    python bench_cases.py sweep [max_log2n] [min_log2n]    chain bandwidth for n = 2^min ... 2^max, f32 and bf16
+"""
+import json
+import os
+import sys
+import time
+
 import numpy as np
 
-from . import _capi as C
-from .device import to_storage
-from .tensor import TensorValue
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from aix_b200 import _capi as C                                      # noqa: E402
+from aix_b200.device import DeviceB200, to_storage                  # noqa: E402
+from aix_b200.tensor import TensorValue, scalar_like                # noqa: E402
+
+def chain(a, b, c):
+    """z = (a*b + c) * sigmoid(a) - tanh(b) / (1 + exp(-c)) as the front end issues it (16 device calls)."""
+    one = lambda t: scalar_like(1.0, t)
+    return (a * b + c) * (one(a) / (one(a) + (-a).exp())) - b.tanh() / (one(c) + (-c).exp())
 
 
+# ---- measurements carried by bench.py's JSON line --------------------------------------------------------------------
 def _time(dev, fn, iters=10, warmup=3, flush_l2=True):
     """Device time of one call of fn. The calls are issued from Python, whose per-call cost (tens of microseconds) can
     exceed a kernel's duration; to keep the interval between the two events free of host time, enough L2-flush kernels
@@ -102,7 +126,7 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
                 sharded=False, deferred=True):
     """MLP training configuration: device time of `steps` steps (forward, backward, gradient all-reduce when
     world_size > 1, Adam), loss not read inside the timed region."""
-    from .mlp import MlpTrainer
+    from aix_b200.mlp import MlpTrainer
     trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size, overlap=overlap, sharded=sharded, deferred=deferred)
     for _ in range(warmup):
         loss = trainer.step()
@@ -183,7 +207,7 @@ def measure_config1_sharded(dev, hbm_peak, rank, world_size, rows=8192, cols=819
     """Configuration 1 with the rows split across the ranks (weak scaling: every rank holds rows x cols): y, the row sums
     and the row maxima are local - one generated kernel - and the global mean takes one scalar all-reduce over NCCL.
     Returns per-GPU and aggregate rates; the mean is checked against the ranks' local means."""
-    from .frontend import global_mean
+    from aix_b200.frontend import global_mean
     rng = np.random.default_rng(rank)
     x = TensorValue.from_numpy(rng.normal(0, 1, (rows, cols)).astype(np.float32), dev, C.BF16)
     g = TensorValue.from_numpy(np.random.default_rng(1000).uniform(0.5, 1.5, cols).astype(np.float32), dev, C.BF16)
@@ -218,3 +242,176 @@ def measure_config1_sharded(dev, hbm_peak, rank, world_size, rows=8192, cols=819
             "GB/s_aggregate_of_API_bytes": world_size * api / (ms * 1e-3) / 1e9,
             "frac_of_measured_hbm_per_gpu": moved / (ms * 1e-3) / 1e9 / hbm_peak,
             "global_mean": float(mean.numpy()), "local_mean_of_this_rank": local_mean, "exchange": "one scalar all-reduce per evaluation"}
+
+
+# ---- fixed workloads for profiler captures -----------------------------------------------------------------------------
+def _rand(dev, shape, dtype, seed, scale=1.0):
+    rng = np.random.default_rng(seed)
+    return TensorValue.from_numpy((rng.uniform(-1, 1, shape) * scale).astype(np.float32), dev, dtype)
+
+
+def build_case(dev, case):
+    if case.startswith("chain_"):
+        dt = C.F32 if case.endswith("f32") else C.BF16
+        a, b, c = (_rand(dev, (1 << 16, 1024), dt, s) for s in range(3))
+        if case.startswith("chain_sum_"):
+            def both():                                   # the sum is recorded behind the chain: one kernel
+                z = chain(a, b, c)
+                return z, z.sum()
+            return both
+        return lambda: chain(a, b, c)
+    if case == "config1_bf16":
+        # configuration 1 as the API issues it: y = relu(x*g + bias), y.sum(1), y.max(1), y.mean() - one row-form kernel
+        x = _rand(dev, (8192, 8192), C.BF16, 0)
+        g, b = _rand(dev, (8192,), C.BF16, 1), _rand(dev, (8192,), C.BF16, 2, 0.1)
+
+        def whole():
+            v = x * g + b
+            y = (v + (v * v).sqrt()) * 0.5
+            return y, y.sum(1), y.max(1), y.mean()
+        return whole
+    if case in ("sum_f32", "sum_bf16"):
+        x = _rand(dev, (1 << 17, 1024), C.F32 if case.endswith("f32") else C.BF16, 0)
+        return lambda: x.sum()
+    if case in ("rowsum_bf16", "rowmax_bf16"):
+        x = _rand(dev, (16384, 8192), C.BF16, 0)
+        return (lambda: x.sum(1)) if case.startswith("rowsum") else (lambda: x.max(1))
+    if case == "colsum_f32":
+        x = _rand(dev, (16384, 4096), C.F32, 0)
+        return lambda: x.sum(0)
+    if case in ("gemm_f32_4096_nt", "gemm_f32_4096_tn"):
+        # the backward forms of the 4096^3 f32 product: G . B^T (all K-major) and A^T . G (both operands MN-major)
+        a, b = _rand(dev, (4096, 4096), C.F32, 0, 0.05), _rand(dev, (4096, 4096), C.F32, 1, 0.05)
+        return (lambda: a.matmul(b.transpose(0, 1))) if case.endswith("_nt") else (lambda: a.transpose(0, 1).matmul(b))
+    if case in ("gemm_f16_4096", "gemm_bf16_k12288"):
+        # probes: the f16 form of the 16-bit kernel, and a contraction three times as long (the depth of the three f32 passes)
+        dt = C.F16 if case.startswith("gemm_f16") else C.BF16
+        k = 12288 if case.endswith("k12288") else 4096
+        a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (4096, k), dt, 1, 0.05)
+        return lambda: a.matmul(b.transpose(0, 1))
+    if case in ("gemm_bf16_k1024", "gemm_f32_k1024", "gemm_f32_4096"):
+        # the MLP's shapes: batch 4096, a 1024-wide or 4096-wide contraction
+        dt = C.BF16 if "bf16" in case else C.F32
+        k = 1024 if case.endswith("k1024") else 4096
+        a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (k, 4096), dt, 1, 0.05)
+        return lambda: a.matmul(b)
+    if case == "mlp_f32":
+        from aix_b200.mlp import MlpTrainer
+        trainer = MlpTrainer(dev)
+        return trainer.step
+    if case.startswith("gemm_"):
+        dt = C.F32 if case == "gemm_f32" else C.BF16
+        n = 2048 if dt == C.F32 else 4096
+        a, b = _rand(dev, (n, n), dt, 0, 0.05), _rand(dev, (n, n), dt, 1, 0.05)
+        if case.endswith("_nt"): return lambda: a.matmul(b.transpose(0, 1))
+        if case.endswith("_tn"): return lambda: a.transpose(0, 1).matmul(b)
+        return lambda: a.matmul(b)
+    if case == "adam_f32":
+        p, g, m, v = (_rand(dev, (1 << 16, 1024), C.F32, s) for s in range(4))
+
+        def step():
+            m2 = 0.9 * m + 0.1 * g
+            v2 = 0.999 * v * v + 0.001 * g * g
+            return p - (0.001 * (m2 / 0.1) / ((v2 / 0.001).sqrt() + 1e-8)), m2, v2
+        return step
+    raise SystemExit(f"unknown case {case}")
+
+
+def run_case(argv):
+    case = argv[0] if argv else "chain_f32"
+    repeats = int(argv[1]) if len(argv) > 1 else 4
+    dev = DeviceB200(0)
+    fn = build_case(dev, case)
+    dev.synchronize()
+    marker = dev.createEvent()
+    for _ in range(3):                   # warm-up: kernels compiled and loaded, allocator cache populated
+        out = fn()
+        dev.recordEvent(marker)          # emits the recorded work per call, as the timed loop does (else the calls merge into other kernels)
+    dev.synchronize()
+    e0, e1 = dev.createEvent(), dev.createEvent()
+    dev.flushL2()
+    dev.recordEvent(e0)
+    for _ in range(repeats):
+        out = fn()
+        dev.recordEvent(e1)
+    ms = dev.elapsedMs(e0, e1) / repeats
+    stats = dev.stats()
+    print(f"{case}: {ms:.4f} ms per repeat over {repeats} repeats (one event pair around all repeats: the device queue stays "
+          f"full); launches so far {stats['total_kernel_launches']}")
+    del out
+    dev.close()
+
+
+# ---- bandwidth sweep of the fused chain (configuration 4) -----------------------------------------------------------------
+PATTERN = 1 << 20
+
+
+def tiled(dev, pattern: TensorValue, repeats: int) -> TensorValue:
+    if repeats == 1:
+        return pattern.reshape((1, PATTERN))
+    return pattern.reshape((1, PATTERN)).broadcastTo((repeats, PATTERN)).contiguous()
+
+
+def sweep_point(dev, log2n, dtype, iters=10):
+    n = 1 << log2n
+    repeats = n // PATTERN
+    esize = C.DTYPE_SIZES[dtype]
+    rng = np.random.default_rng(0)
+    patterns = [TensorValue.from_numpy(rng.uniform(-1, 1, PATTERN).astype(np.float32), dev, dtype) for _ in range(3)]
+    zp = chain(*[p.reshape((1, PATTERN)) for p in patterns])
+    pattern_sum = float(zp.numpy().astype(np.float64).sum())
+    a, b, c = (tiled(dev, p, repeats) for p in patterns)
+    dev.synchronize()
+    for _ in range(2):                       # warm-up: compile, populate the allocator cache
+        z = chain(a, b, c)
+        dev.synchronize()
+    t0 = time.perf_counter()
+    z = chain(a, b, c)
+    host_s = time.perf_counter() - t0        # host cost of issuing one evaluation
+    s = z.sum()
+    checksum = float(s.item())
+    del s
+    events = [(dev.createEvent(), dev.createEvent()) for _ in range(iters)]
+    blockers = int(1.5 * iters * (host_s + 60e-6) / 45e-6) + 4
+    for _ in range(blockers):
+        dev.flushL2()
+    for e0, e1 in events:
+        dev.recordEvent(e0)
+        z = chain(a, b, c)
+        dev.recordEvent(e1)
+        dev.flushL2()
+    ms = [dev.elapsedMs(e0, e1) for e0, e1 in events]
+    for e0, e1 in events:
+        dev.destroyEvent(e0); dev.destroyEvent(e1)
+    best, med = float(np.min(ms)), float(np.median(ms))
+    stats = dev.stats()
+    del z, a, b, c
+    dev.emptyCache()
+    nbytes = 4 * n * esize
+    want = pattern_sum * repeats
+    return {"log2n": log2n, "dtype": C.DTYPE_NAMES[dtype], "bytes": nbytes, "ms_median": med, "ms_best": best,
+            "GB/s_median": nbytes / (med * 1e-3) / 1e9, "GB/s_best": nbytes / (best * 1e-3) / 1e9,
+            "host_us_per_evaluation": host_s * 1e6, "checksum": checksum, "checksum_expected": want,
+            "checksum_rel_err": abs(checksum - want) / max(1.0, abs(want)), "kernels_total": stats["fused_kernels"]}
+
+
+def run_sweep(dev, max_log2n=31, min_log2n=20, dtypes=(C.F32, C.BF16)):
+    out = []
+    for dtype in dtypes:
+        for log2n in range(min_log2n, max_log2n + 1):
+            if (4 + 13) * (1 << log2n) * C.DTYPE_SIZES[dtype] > 150 * (1 << 30):
+                continue                     # would not fit next to the dead intermediates of one evaluation
+            out.append(sweep_point(dev, log2n, dtype, iters=10 if log2n < 28 else 5))
+    return out
+
+
+if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "sweep":
+        hi = int(sys.argv[2]) if len(sys.argv) > 2 else 31
+        lo = int(sys.argv[3]) if len(sys.argv) > 3 else 20
+        device = DeviceB200(0)
+        for rec in run_sweep(device, hi, lo):
+            print(json.dumps(rec), flush=True)
+        device.close()
+    else:
+        run_case(sys.argv[1:])
