@@ -82,6 +82,9 @@ class DeviceTensorParams:
         return True
 
 
+_FILL_SCALARS: dict = {}
+
+
 class DeviceB200:
     """One B200 GPU behind the aix::Device interface."""
 
@@ -113,7 +116,10 @@ class DeviceB200:
 
     @staticmethod
     def _t(p: DeviceTensorParams):
-        return ctypes.byref(p.to_c())
+        ref = p.__dict__.get("_ref")
+        if ref is None:
+            ref = p.__dict__["_ref"] = ctypes.byref(p.to_c())      # descriptors are immutable: one reference object per descriptor
+        return ref
 
     def close(self):
         if getattr(self, "_h", None):
@@ -155,8 +161,14 @@ class DeviceB200:
     def unary(self, a1, result):    self._check(self._lib.aixb200_unary(self._h, self._t(a1), self._t(result)))
 
     def fill(self, scalar, scalarDType: int, result):
-        raw = to_storage(np.array([scalar]), scalarDType)
-        self._check(self._lib.aixb200_fill(self._h, raw.ctypes.data, scalarDType, self._t(result)))
+        key = (scalar, scalarDType)
+        held = _FILL_SCALARS.get(key)
+        if held is None:                   # the same few constants recur every step: keep their one-element buffers
+            raw = to_storage(np.array([scalar]), scalarDType)
+            held = (raw, raw.ctypes.data)
+            if len(_FILL_SCALARS) < 4096:
+                _FILL_SCALARS[key] = held
+        self._check(self._lib.aixb200_fill(self._h, held[1], scalarDType, self._t(result)))
 
     def fillMin(self, result):      self._check(self._lib.aixb200_fill_min(self._h, self._t(result)))
     def sum(self, a, result):       self._check(self._lib.aixb200_sum(self._h, self._t(a), self._t(result)))

@@ -34,12 +34,21 @@ def promote(a: int, b: int) -> int:
     return _PROMOTE[a][b]
 
 
+_STRIDES: dict = {}
+
+
 def contiguous_strides(shape: Sequence[int]) -> tuple:
-    strides, acc = [], 1
-    for s in reversed(shape):
-        strides.append(acc)
-        acc *= s
-    return tuple(reversed(strides))
+    shape = tuple(shape)
+    known = _STRIDES.get(shape)
+    if known is None:
+        strides, acc = [], 1
+        for s in reversed(shape):
+            strides.append(acc)
+            acc *= s
+        known = tuple(reversed(strides))
+        if len(_STRIDES) < 4096:
+            _STRIDES[shape] = known
+    return known
 
 
 def numel(shape: Sequence[int]) -> int:
