@@ -50,8 +50,8 @@ class Stats(ctypes.Structure):
         "kernel_cache_hits", "kernel_cache_misses", "nvrtc_compiles")] + [("nvrtc_ms", ctypes.c_double)] + [
         (n, ctypes.c_uint64) for n in (
         "static_kernel_launches", "total_kernel_launches", "bytes_in_use", "bytes_cached", "bytes_reserved",
-        "cuda_mallocs", "h2d_bytes", "d2h_bytes", "reductions_fused", "prepared_operand_hits", "prepared_operand_builds", "prepared_operand_max_known")] + [
-        ("reserved", ctypes.c_uint64 * 2)]
+        "cuda_mallocs", "h2d_bytes", "d2h_bytes", "reductions_fused", "prepared_operand_hits", "prepared_operand_builds", "prepared_operand_max_known", "matmul_consumers_folded")] + [
+        ("reserved", ctypes.c_uint64 * 1)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}

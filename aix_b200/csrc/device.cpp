@@ -99,6 +99,7 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_termCacheEnabled = envInt("AIXB200_GEMM_TERM_CACHE", 1) != 0;
     m_keepIdleFills = envInt("AIXB200_KEEP_IDLE_FILLS", 1) != 0;
     m_fuseOperandMax = envInt("AIXB200_FUSE_OPERAND_MAX", 1) != 0;
+    m_foldMatmulEpilogue = envInt("AIXB200_GEMM_EPILOGUE", 1) != 0 && m_cfg.strict_math == 0 && m_cfg.fusion != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -432,7 +433,7 @@ void Device::deallocate(void* p)
         noteCallRange(p, static_cast<char*>(p) + whole.size);
         orderAfterCollectives(makeView(&whole, "deallocate"));
     }
-    if (m_pending.empty() && m_deferredFrees.empty())
+    if (m_pending.empty() && m_deferredFrees.empty() && !m_deferred.active)
     {
         m_allocator->release(p);       // stream order makes immediate reuse safe
         return;
@@ -549,6 +550,7 @@ void Device::record(OpRecord&& rec)
     if (rec.out.size == 0) return;
     m_pending.push_back(std::move(rec));
     ++m_stats.ops_recorded;
+    if (m_deferred.active) advanceDeferredMatmul(m_pending.size() - 1);
     if (m_pending.size() >= m_cfg.flush_threshold) flush();
 }
 
@@ -608,6 +610,7 @@ void Device::recordFillMin(const aixb200_tensor* r)
 void Device::flush(bool keepIdleFills)
 {
     if (m_inFlush) return;
+    if (m_deferred.active) launchDeferredMatmul();        // issued before everything recorded after it
     if (m_pending.empty()) { releaseDeferred(); return; }
     m_inFlush = true;
     struct Reset { bool& f; ~Reset() { f = false; } } reset{m_inFlush};
@@ -866,7 +869,7 @@ bool Device::recordRowReduction(bool isMax, const View& src, const View& dst, ui
 void Device::sumStaticScratch(const aixb200_tensor* a, const aixb200_tensor* r)
 {
     if (dryRun()) failInvalid("sum_static_scratch needs a GPU");
-    if (!m_pending.empty() || !m_deferredFrees.empty())
+    if (!m_pending.empty() || !m_deferredFrees.empty() || m_deferred.active)
         failInvalid("sum_static_scratch: recorded work is pending; call aixb200_synchronize() first (flushing here could allocate)");
     View src = makeView(a, "sum_static_scratch");
     View dst = makeView(r, "sum_static_scratch");
@@ -1024,24 +1027,169 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
     if (a->rank != 2 || b->rank != 2 || r->rank != 2) failInvalid("matmul: operands and result must be 2-D");
     if (a->shape[1] != b->shape[0] || r->shape[0] != a->shape[0] || r->shape[1] != b->shape[1]) failInvalid("matmul: shapes do not chain");
     if (a->dtype != r->dtype || b->dtype != r->dtype) failInvalid("matmul: element types differ");
-    View va = inputView(a, "matmul"), vb = inputView(b, "matmul");
-    View vr = outputView(r, "matmul");
+    DeferredMatmul d;
+    d.a = *a; d.b = *b; d.r = *r;
+    d.va = inputView(a, "matmul"); d.vb = inputView(b, "matmul");
+    d.vr = outputView(r, "matmul");
     flush();
-    if (dryRun() || vr.size == 0) return;
-    const uint64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
+    if (dryRun() || d.vr.size == 0) return;
+    // Products whose consumers the kernel can fold wait for the ops that follow (see DeferredMatmul). Operands staged from
+    // host memory live only until the next call, so those products are launched at once.
+    if (m_foldMatmulEpilogue && m_staged.empty() && d.vr.isDense())
+    {
+        gemm::Problem probe{};
+        probe.dtype = r->dtype;
+        probe.m = a->shape[0]; probe.k = a->shape[1]; probe.n = b->shape[1];
+        probe.c = d.vr.firstByte();
+        probe.splitF32 = m_cfg.tf32x3_matmul != 0;
+        if (gemm::canFoldEpilogue(probe)) { m_deferred = d; m_deferred.active = true; return; }
+    }
+    launchMatmul(d, 0);
+}
+
+void Device::launchMatmul(const DeferredMatmul& d, int folded)
+{
+    const uint64_t m = d.a.shape[0], k = d.a.shape[1], n = d.b.shape[1];
     AIXB200_CTX();
     gemm::Problem p{};
-    p.dtype = r->dtype;
+    p.dtype = d.r.dtype;
     p.m = m; p.n = n; p.k = k;
-    p.a = va.firstByte(); p.aRowStride = a->strides[0]; p.aColStride = a->strides[1];
-    p.b = vb.firstByte(); p.bRowStride = b->strides[0]; p.bColStride = b->strides[1];
-    p.c = vr.firstByte();
+    p.a = d.va.firstByte(); p.aRowStride = d.a.strides[0]; p.aColStride = d.a.strides[1];
+    p.b = d.vb.firstByte(); p.bRowStride = d.b.strides[0]; p.bColStride = d.b.strides[1];
+    p.c = d.vr.firstByte();
     p.splitF32 = m_cfg.tf32x3_matmul != 0;
     p.shareDevice = !m_commInFlight.empty();
-    if (gemm::launchTensorCore(*this, ctx, p)) m_checkErrorWord = true;
-    else
-        kernels::matmulSimt(ctx, r->dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);
+    int region = -1;
+    if (folded > 0)
+    {
+        // exactly one output leaves the kernel: the sum, or its tanh (launchDeferredMatmul folds no further than that)
+        p.bias = reinterpret_cast<const float*>(d.bias.firstByte());
+        p.storeC = false;
+        p.biasOut = folded == 2 ? nullptr : d.biasOut.firstByte();
+        p.tanhOut = folded == 2 ? d.tanhOut.firstByte() : nullptr;
+        // max|x| of that output for the matmul it will feed, as generated kernels leave it (appendOperandMaxEpilogues)
+        const View& last = folded == 2 ? d.tanhOut : d.biasOut;
+        const size_t bytes = static_cast<size_t>(last.endByte() - last.firstByte());
+        if (m_termSlots && std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) != m_operandSizes.end())
+            region = rememberOperandRegion(last.firstByte(), last.endByte(), false);
+        if (region >= 0) p.maxSlot = preparedSlot(m_operandRegions[static_cast<size_t>(region)].slot);
+    }
+    const bool tensorCore = gemm::launchTensorCore(*this, ctx, p);
+    if (tensorCore) m_checkErrorWord = true;
+    else if (folded == 0)
+        kernels::matmulSimt(ctx, d.r.dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);
     AIXB200_DONE("matmul");
+    if (folded > 0 && !tensorCore) { launchMatmul(d, 0); return; }       // the consumers stay recorded and run as kernels
+    if (folded > 0)
+    {
+        if (region >= 0) m_operandRegions[static_cast<size_t>(region)].fresh = true;
+        if (folded == 2) m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(d.tanhIndex));
+        m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(d.addIndex));
+        m_stats.matmul_consumers_folded += static_cast<uint64_t>(folded);
+    }
+}
+
+void Device::launchDeferredMatmul()
+{
+    const DeferredMatmul d = m_deferred;
+    m_deferred = DeferredMatmul{};
+    // A consumer is folded only when that leaves the kernel with ONE output: the value it consumes must be dead - its storage
+    // deallocated and no other recorded op touching it. Measured on B200 (4096 x 4096 outputs): the product alone 83 us (K =
+    // 1024); product, then add + tanh as a generated kernel 117 us; all three results written by the product's epilogue 135 us -
+    // every CTA finishes its tile at the same moment, and a burst of three tiles per CTA cannot drain while the tensor
+    // cores run the two chunks of K ahead that TMEM has room for. With one output the epilogue costs what it always did.
+    auto dead = [&](const View& v, size_t skipA, size_t skipB)
+    {
+        if (!m_released.count(v.base)) return false;
+        for (size_t i = 0; i < m_pending.size(); ++i)
+        {
+            if (i == skipA || i == skipB) continue;
+            const OpRecord& op = m_pending[i];
+            if (op.out.overlaps(v)) return false;
+            for (int q = 0; q < op.numInputs; ++q) if (op.in[q].overlaps(v)) return false;
+        }
+        return true;
+    };
+    int folded = d.folded;
+    if (folded == 2 && !dead(d.biasOut, d.addIndex, d.tanhIndex)) folded = 1;
+    if (folded >= 1 && !dead(d.vr, d.addIndex, d.addIndex)) folded = 0;
+    launchMatmul(d, folded);
+    // Ops recorded while the product waited announced their writes (outputView) before the launch prepared the operands and
+    // left the output's maximum: what they are going to overwrite is stale from their point in program order on.
+    for (const OpRecord& op : m_pending)
+        if (op.out.overlaps(d.va) || op.out.overlaps(d.vb) || (folded >= 1 && op.out.overlaps(d.biasOut)) || (folded == 2 && op.out.overlaps(d.tanhOut)))
+            invalidatePreparedTerms(op.out.firstByte(), op.out.endByte());
+}
+
+void Device::advanceDeferredMatmul(size_t index)
+{
+    DeferredMatmul& d = m_deferred;
+    const OpRecord& op = m_pending[index];
+    auto touches = [](const OpRecord& o, const View& v)
+    {
+        if (o.out.overlaps(v)) return true;
+        for (int q = 0; q < o.numInputs; ++q) if (o.in[q].overlaps(v)) return true;
+        return false;
+    };
+    // The product is launched ahead of everything recorded: an output it writes must not be touched by an earlier recorded
+    // op (one that stayed recorded across flushes), and its bias must not be written by one.
+    auto untouchedBefore = [&](const View& v, size_t except)
+    {
+        for (size_t i = 0; i < index; ++i)
+            if (i != except && touches(m_pending[i], v)) return false;
+        return true;
+    };
+    auto denseLikeResult = [&](const View& v)
+    {
+        return v.dtype == F32 && v.isDense() && v.size == d.vr.size && reinterpret_cast<uintptr_t>(v.firstByte()) % 16 == 0 &&
+               !v.overlaps(d.vr) && !v.overlaps(d.va) && !v.overlaps(d.vb);
+    };
+    if (d.folded == 0)
+    {
+        if (!touches(op, d.vr)) return;                         // unrelated (a fill of some gradient, say): keep waiting
+        const uint64_t m = d.r.shape[0], n = d.r.shape[1];
+        auto isRowVector = [&](const View& v)
+        {
+            return v.dtype == F32 && v.rank == 2 && v.shape[0] == m && v.shape[1] == n && v.strides[0] == 0 && v.strides[1] == 1 &&
+                   reinterpret_cast<uintptr_t>(v.firstByte()) % 16 == 0;
+        };
+        if (op.op == Op::Add && op.numInputs == 2 && denseLikeResult(op.out))
+        {
+            const int product = op.in[0].sameElements(d.vr) ? 0 : (op.in[1].sameElements(d.vr) ? 1 : -1);
+            if (product >= 0 && isRowVector(op.in[1 - product]) && !op.in[1 - product].overlaps(op.out) && untouchedBefore(op.out, index))
+            {
+                bool biasWritten = false;
+                for (size_t i = 0; i < index; ++i) biasWritten = biasWritten || m_pending[i].out.overlaps(op.in[1 - product]);
+                if (!biasWritten)
+                {
+                    d.folded = 1;
+                    d.addIndex = index;
+                    d.bias = op.in[1 - product];
+                    d.biasOut = op.out;
+                    return;
+                }
+            }
+        }
+        launchDeferredMatmul();
+        return;
+    }
+    if (d.folded == 2)
+    {
+        // both consumers are candidates; the call that recorded the tanh still held the sum, which is why the product was not
+        // launched there and then: whether the sum is dead shows once that call has returned
+        if (touches(op, d.tanhOut) || touches(op, d.biasOut)) launchDeferredMatmul();
+        return;
+    }
+    if (!touches(op, d.biasOut)) return;
+    if (op.op == Op::Tanh && op.numInputs == 1 && op.in[0].sameElements(d.biasOut) && denseLikeResult(op.out) && !op.out.overlaps(d.biasOut) &&
+        !op.out.overlaps(d.bias) && untouchedBefore(op.out, d.addIndex))
+    {
+        d.folded = 2;
+        d.tanhIndex = index;
+        d.tanhOut = op.out;
+        return;
+    }
+    launchDeferredMatmul();
 }
 
 void Device::transpose(const aixb200_tensor* a, const aixb200_tensor* r, size_t dim0, size_t dim1)

@@ -154,6 +154,30 @@ public:
 
 private:
     void record(OpRecord&& rec);
+    // ---- matmul with folded consumers ----------------------------------------------------------------------------------
+    // nn::Linear is matmul(x, W) + b, usually followed by tanh (aixNeuralNetwork.hpp:150-153). An f32 product the tensor-core
+    // kernel can fold consumers into is therefore not launched by the matmul call itself: it waits for the recorded ops
+    // that follow. If the first op that touches its result is `result + row vector`, that add is a candidate for the
+    // product's epilogue; if the first op that touches the sum is its tanh, that one too. When the wait ends - the tanh
+    // has arrived, some other op touches the sum, or anything flushes - the consumers are folded as far as the values they
+    // consume are dead (temporaries already deallocated, read by nothing else): the kernel then writes only the sum, or
+    // only its tanh, and the folded ops are dropped from the record. Values that stay alive (autograd keeps the product and
+    // the sum of every layer) are written by the kernels that always wrote them: see launchDeferredMatmul for the
+    // measurement behind that rule. The product is always launched ahead of the ops recorded after it.
+    struct DeferredMatmul
+    {
+        bool active = false;
+        aixb200_tensor a{}, b{}, r{};
+        View va, vb, vr;
+        int folded = 0;                         // recorded consumers matched so far: 0, 1 (the add), 2 (add and tanh)
+        size_t addIndex = 0, tanhIndex = 0;     // their positions in m_pending
+        View bias, biasOut, tanhOut;
+    };
+    DeferredMatmul m_deferred;
+    bool m_foldMatmulEpilogue = true;           // AIXB200_GEMM_EPILOGUE=0: every product is launched by its own call
+    void advanceDeferredMatmul(size_t index);   // looks at the op just recorded at m_pending[index]
+    void launchDeferredMatmul();
+    void launchMatmul(const DeferredMatmul& d, int folded);
     void launchSpec(const KernelSpec& spec);
     CompiledKernel& getKernel(const KernelSpec& spec, const KernelVariant& variant, const std::string& key);
     std::vector<char> compile(const std::string& source, const std::string& entry);

@@ -93,6 +93,10 @@ struct KernelParams
     uint32_t* errorWord;
     float*   splitWorkspace;    // one 256 x 256 f32 partial accumulator per cluster
     uint32_t* splitCounters;    // per (split tile, CTA rank): partial accumulators published so far; left at zero
+    // Elementwise consumers folded into the epilogue of the three-fp16-pass f32 kernel (see Problem::bias):
+    uint32_t outputs;           // bit 0: C itself, bit 1: C + bias (through mapC1), bit 2: tanh(C + bias) (through mapC2)
+    const float* bias;          // n values, added to every row
+    uint32_t* maxSlot;          // max|x| of the last output as a bit pattern (atomic maximum; zeroed before the launch), or null
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -790,15 +794,39 @@ __device__ __forceinline__ void drainAccumulatorTma(const KernelParams& p, const
     }
 }
 
+// tanh of the folded epilogue: the same routine the generated elementwise kernels use in their default math mode, so a
+// product whose bias and tanh are folded into the matmul gives the bits the separate kernels would give.
+// |x| < 0.6: x + x^3 * p(x^2), a degree-4 fit of (tanh(x) - x) / x^3 (max relative error 9e-8); otherwise
+// 1 - 2 / (exp(2|x|) + 1) with the sign of x.
+__device__ __forceinline__ float epilogueTanh(float x)
+{
+    const float t = fabsf(x), u = x * x;
+    float q = -0.006276384927332401f;
+    q = fmaf(q, u, 0.021116212010383606f);
+    q = fmaf(q, u, -0.053875137120485306f);
+    q = fmaf(q, u, 0.13332924246788025f);
+    q = fmaf(q, u, -0.3333333134651184f);
+    const float small = fmaf(x * u, q, x);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * 2.885390081777927f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    const float large = copysignf(fmaf(-2.0f, r, 1.0f), x);
+    return t < 0.6f ? small : large;
+}
+
 // Mode 0: 16-bit operands, one pass. Mode 1: f32 as a TF32 main pass plus two bf16 cross-term passes. Mode 2: f32 as three
 // fp16 passes over two-term operands - every pass is a 16-bit pass, so nothing in the issue loops depends on the pass.
+// Mode 3: mode 2 with elementwise consumers folded into the epilogue (an instantiation of its own, so that the plain
+// product keeps its register allocation).
 template <int Mode>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Mode == 2 ? kThreadsHalfTerms : kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Mode >= 2 ? kThreadsHalfTerms : kThreads, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
-               const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ KernelParams p)
+               const __grid_constant__ CUtensorMap mapB16, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapC1,
+               const __grid_constant__ CUtensorMap mapC2, const __grid_constant__ KernelParams p)
 {
     constexpr bool Tf32 = Mode != 0;
-    constexpr bool HalfTerms = Mode == 2;
+    constexpr bool HalfTerms = Mode >= 2;
+    constexpr bool Fold = Mode == 3;             // bias / tanh consumers folded into the epilogue
     extern __shared__ uint8_t rawSmem[];
     PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -993,31 +1021,66 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (acc == 0) accPhase ^= 1u;
                 }
                 if (!ok) break;
-                // the tile is complete: undo the operands' scaling (two exact factors, one after the other) and store
+                // the tile is complete: undo the operands' scaling (two exact factors, one after the other) and store.
+                // Elementwise consumers folded into this epilogue (p.outputs) take the values from the same registers:
+                // C + bias and tanh(C + bias) leave through their own tensor maps, and C itself only if somebody reads it.
                 const float scaleA = halfTermInverseScale(*p.scaleA), scaleB = halfTermInverseScale(*p.scaleB);
                 const uint32_t col0 = tn * p.blockN + half * halfCols;
                 const uint32_t row0 = tm * 256 + rank * 128 + quarter * 32;
+                const uint32_t outputs = Fold ? p.outputs : 1u;
+                uint32_t maxBits = 0;
                 #pragma unroll
                 for (uint32_t strip = 0; strip < 4; ++strip)
                 {
                     if (strip * 32 >= halfCols) continue;
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i) sum[strip * 32 + i] = sum[strip * 32 + i] * scaleA * scaleB;
                     if (p.tmaEpilogue)
                     {
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the buffer's previous slice has been read
-                        __syncwarp();
-                        uint8_t* rowPtr = staging + lane * 128u;
-                        const uint32_t swizzle = lane & 7u;
-                        #pragma unroll
-                        for (uint32_t v = 0; v < 8; ++v)
-                            *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) =
-                                make_uint4(__float_as_uint(sum[strip * 32 + 4 * v] * scaleA * scaleB), __float_as_uint(sum[strip * 32 + 4 * v + 1] * scaleA * scaleB),
-                                           __float_as_uint(sum[strip * 32 + 4 * v + 2] * scaleA * scaleB), __float_as_uint(sum[strip * 32 + 4 * v + 3] * scaleA * scaleB));
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0)
+                        auto stageAndStore = [&](const CUtensorMap* map)
                         {
-                            tmaStoreTile(&mapC, staging, static_cast<int32_t>(col0 + strip * 32), static_cast<int32_t>(row0), false);
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the buffer's previous slice has been read
+                            __syncwarp();
+                            uint8_t* rowPtr = staging + lane * 128u;
+                            const uint32_t swizzle = lane & 7u;
+                            #pragma unroll
+                            for (uint32_t v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(rowPtr + ((v ^ swizzle) << 4)) =
+                                    make_uint4(__float_as_uint(sum[strip * 32 + 4 * v]), __float_as_uint(sum[strip * 32 + 4 * v + 1]),
+                                               __float_as_uint(sum[strip * 32 + 4 * v + 2]), __float_as_uint(sum[strip * 32 + 4 * v + 3]));
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0)
+                            {
+                                tmaStoreTile(map, staging, static_cast<int32_t>(col0 + strip * 32), static_cast<int32_t>(row0), false);
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
+                        };
+                        if (outputs & 1u) stageAndStore(&mapC);
+                        if constexpr (Fold) if (outputs & 6u)
+                        {
+                            const uint32_t colS = col0 + strip * 32;
+                            #pragma unroll
+                            for (uint32_t v = 0; v < 8; ++v)
+                            {
+                                // every lane reads the same four bias values: one broadcast load; n is a multiple of 4
+                                const float4 bv = colS + 4 * v < p.n ? __ldg(reinterpret_cast<const float4*>(p.bias + colS + 4 * v)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                                sum[strip * 32 + 4 * v] += bv.x; sum[strip * 32 + 4 * v + 1] += bv.y;
+                                sum[strip * 32 + 4 * v + 2] += bv.z; sum[strip * 32 + 4 * v + 3] += bv.w;
+                            }
+                            if (outputs & 2u) stageAndStore(&mapC1);
+                            if (outputs & 4u)
+                            {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 32; ++i) sum[strip * 32 + i] = epilogueTanh(sum[strip * 32 + i]);
+                                stageAndStore(&mapC2);
+                            }
+                            if (p.maxSlot && row0 + lane < p.m)
+                            {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 32; ++i)
+                                    if (colS + (i & ~3u) < p.n) maxBits = max(maxBits, __float_as_uint(sum[strip * 32 + i]) & 0x7FFFFFFFu);
+                            }
                         }
                     }
                     else
@@ -1030,10 +1093,16 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                             for (uint32_t i = 0; i < 32; ++i)
                             {
                                 const uint32_t col = col0 + strip * 32 + i;
-                                if (col < p.n) out[col] = sum[strip * 32 + i] * scaleA * scaleB;
+                                if (col < p.n) out[col] = sum[strip * 32 + i];
                             }
                         }
                     }
+                }
+                if constexpr (Fold) if (p.maxSlot)
+                {
+                    // the bit patterns of non-negative floats order like the floats, and a NaN's lies above every number's
+                    maxBits = __reduce_max_sync(0xFFFFFFFFu, maxBits);
+                    if (lane == 0 && maxBits != 0) atomicMax(p.maxSlot, maxBits);
                 }
             }
             if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // staging buffers are read, C is written
@@ -1539,6 +1608,25 @@ void launchBoundedWaitSelfTest(const kernels::LaunchContext& ctx, uint64_t limit
     if (ctx.launches) ++*ctx.launches;
 }
 
+// The conditions under which launchTensorCore takes the three-fp16-pass CTA-pair kernel with TMA stores - the one whose
+// epilogue can fold a bias add and a tanh. Kept in step with the choices made there.
+bool canFoldEpilogue(const Problem& q)
+{
+    static const bool enabled = []{ const char* v = std::getenv("AIXB200_GEMM_EPILOGUE"); return !(v && v[0] == '0'); }();
+    static const bool tensorCoreOff = std::getenv("AIXB200_NO_TENSOR_CORE") != nullptr;
+    static const bool pairEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_PAIR"); return !(v && v[0] == '0'); }();
+    static const bool halfTerms = []{ const char* v = std::getenv("AIXB200_GEMM_F32"); return !(v && v[0] == 'h' && v[1] == 'y'); }();
+    static const bool tmaStoreEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_TMA_STORE"); return !(v && v[0] == '0'); }();
+    if (!enabled || tensorCoreOff || !pairEnabled || !halfTerms || !tmaStoreEnabled) return false;
+    if (q.dtype != F32 || !q.splitF32) return false;
+    if (q.m <= 128 || q.n < 64 || q.k < 32) return false;
+    if (q.m > 0x7FFFFF00ull || q.n > 0x7FFFFF00ull || q.k > 0x3FFFFF00ull) return false;
+    if ((q.n * 4) % 16 != 0) return false;
+    for (const void* ptr : {static_cast<const void*>(q.c), static_cast<const void*>(q.bias), static_cast<const void*>(q.biasOut), static_cast<const void*>(q.tanhOut)})
+        if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return false;
+    return encodeTiled() != nullptr;
+}
+
 bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& q)
 {
     if (q.dtype != F32 && q.dtype != BF16 && q.dtype != F16) return false;
@@ -1552,6 +1640,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     // CTA pairs (256 x 256 tiles) unless switched off or the problem has a single row of 128-row tiles.
     static const bool pairEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_PAIR"); return !(v && v[0] == '0'); }();
     const bool pair = pairEnabled && q.m > 128;
+    if (q.bias && !canFoldEpilogue(q)) return false;
     KernelParams p{};
     p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
     p.tilesM = pair ? (p.m + 255) / 256 : (p.m + kBlockM - 1) / kBlockM;
@@ -1807,6 +1896,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             cudaFuncSetAttribute(gemmPairKernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaFuncSetAttribute(gemmPairKernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaFuncSetAttribute(gemmPairKernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(static_cast<unsigned>(ctx.smCount) & ~1u);
             cfg.blockDim = dim3(kThreads);
@@ -1871,12 +1961,27 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             const size_t es = dtypeSize(q.dtype);
             p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 32) ? 1u : 0u;
         }
-        if (!tf32)            gemmPairKernel<0><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
-        else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
-        else                  gemmPairKernel<1><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, p);
+        CUtensorMap mapC1 = mapC, mapC2 = mapC;
+        p.outputs = 1;
+        if (q.bias)
+        {
+            // folded consumers: every output is a dense m x n f32 tensor that leaves through its own tensor map
+            if (!p.halfTerms || !p.tmaEpilogue) return false;
+            p.outputs = (q.storeC ? 1u : 0u) | (q.biasOut ? 2u : 0u) | (q.tanhOut ? 4u : 0u);
+            p.bias = q.bias;
+            p.maxSlot = q.maxSlot;
+            if (q.biasOut && !makeMap(&mapC1, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, q.biasOut, q.n, q.m, q.n * 4, 32, 32)) return false;
+            if (q.tanhOut && !makeMap(&mapC2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, q.tanhOut, q.n, q.m, q.n * 4, 32, 32)) return false;
+            if (q.maxSlot && cudaMemsetAsync(q.maxSlot, 0, 4, ctx.stream) != cudaSuccess) return false;
+        }
+        if (!tf32)            gemmPairKernel<0><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
+        else if (p.halfTerms && q.bias) gemmPairKernel<3><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
+        else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
+        else                  gemmPairKernel<1><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
         if (ctx.launches) ++*ctx.launches;
         return true;
     }
+    if (q.bias) return false;
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(ctx.smCount));
     if (tf32) gemmKernel<true><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);
     else      gemmKernel<false><<<grid, kThreads, smemBytes, ctx.stream>>>(mapA, mapB, mapA16, mapB16, p);

@@ -290,6 +290,41 @@ __global__ void __launch_bounds__(kBlock) transposeKernel(const S* __restrict__ 
     }
 }
 
+// The same permutation for the case that matters at size: both tensors dense, nothing behind the second swapped dimension.
+// The source is [A][X][B][Y], the result [A][Y][B][X]. A CTA moves a 32 x 32 tile of the (x, y) plane of one (a, b) through
+// shared memory: rows of y are read with consecutive threads along y, rows of x are written with consecutive threads along x,
+// so both sides of the copy touch whole 128-byte lines (for 4-byte elements) instead of one element per line.
+template <class S>
+__global__ void __launch_bounds__(256) transposeTiledKernel(const S* __restrict__ src, S* __restrict__ dst, uint32_t A, uint32_t X, uint32_t B, uint32_t Y,
+                                                            uint32_t tilesX, uint32_t tilesY, uint64_t tiles)
+{
+    __shared__ S tile[32][33];
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    for (uint64_t t = blockIdx.x; t < tiles; t += gridDim.x)
+    {
+        uint64_t rest = t;
+        const uint32_t tileY = static_cast<uint32_t>(rest % tilesY); rest /= tilesY;
+        const uint32_t tileX = static_cast<uint32_t>(rest % tilesX); rest /= tilesX;
+        const uint32_t b = static_cast<uint32_t>(rest % B);
+        const uint32_t a = static_cast<uint32_t>(rest / B);
+        const uint32_t x0 = tileX * 32, y0 = tileY * 32;
+        #pragma unroll
+        for (uint32_t r = 0; r < 4; ++r)
+        {
+            const uint32_t x = x0 + ty + r * 8, y = y0 + tx;
+            if (x < X && y < Y) tile[ty + r * 8][tx] = src[((static_cast<uint64_t>(a) * X + x) * B + b) * Y + y];
+        }
+        __syncthreads();
+        #pragma unroll
+        for (uint32_t r = 0; r < 4; ++r)
+        {
+            const uint32_t y = y0 + ty + r * 8, x = x0 + tx;
+            if (x < X && y < Y) dst[((static_cast<uint64_t>(a) * Y + y) * B + b) * X + x] = tile[tx][ty + r * 8];
+        }
+        __syncthreads();
+    }
+}
+
 // sliceSet (aixDeviceCPU.cpp:470-499)
 template <class S>
 __global__ void __launch_bounds__(kBlock) sliceSetKernel(const S* __restrict__ src, Layout srcLayout, S* __restrict__ dst, Layout dstLayout,
@@ -319,6 +354,33 @@ __global__ void __launch_bounds__(kBlock) triangleKernel(const S* __restrict__ s
         const int64_t row = static_cast<int64_t>((i / cols) % rows), col = static_cast<int64_t>(i % cols);
         const bool zero = lower ? (col > row + diagonal) : (col < row + diagonal);
         dst[layoutOffset(i, dstLayout)] = zero ? S(0) : src[layoutOffset(i, srcLayout)];
+    }
+}
+
+// tril / triu of dense tensors whose rows hold a whole number of 16-byte packs: one pack per thread and trip, the row and
+// column of its first element found with one division, elements on the wrong side of the diagonal replaced by zero.
+template <class S>
+__global__ void __launch_bounds__(kBlock) trianglePackedKernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint64_t packs, uint32_t rows,
+                                                               uint32_t packsPerRow, int64_t diagonal, bool lower)
+{
+    constexpr int kPer = 16 / sizeof(S);
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < packs; i += static_cast<uint64_t>(gridDim.x) * kBlock)
+    {
+        const uint64_t line = i / packsPerRow;
+        const int64_t row = static_cast<int64_t>(line % rows), col0 = static_cast<int64_t>(i - line * packsPerRow) * kPer;
+        // the pack's columns are col0 .. col0 + kPer - 1; kept when col <= row + diagonal (lower) or col >= row + diagonal (upper)
+        const int64_t edge = row + diagonal;
+        const bool allZero = lower ? (col0 > edge) : (col0 + kPer - 1 < edge);
+        uint4 pack = make_uint4(0, 0, 0, 0);
+        if (!allZero)
+        {
+            pack = src[i];
+            S* e = reinterpret_cast<S*>(&pack);
+            #pragma unroll
+            for (int q = 0; q < kPer; ++q)
+                if (lower ? (col0 + q > edge) : (col0 + q < edge)) e[q] = S(0);
+        }
+        dst[i] = pack;
     }
 }
 
@@ -435,9 +497,43 @@ __global__ void __launch_bounds__(kBlock) flushL2Kernel(uint4* buffer, uint64_t 
         buffer[i] = make_uint4(static_cast<unsigned>(i), 0u, 0u, 0u);
 }
 
+inline bool isCanonical(const Layout& l, const uint64_t* shape)
+{
+    uint64_t expect = 1;
+    for (int d = l.rank - 1; d >= 0; --d)
+    {
+        if (shape[d] != 1 && l.strides[d] != expect) return false;
+        expect *= shape[d];
+    }
+    return true;
+}
+
 template <int DT> void launchTranspose(const LaunchContext& ctx, const void* src, void* dst, uint64_t count, const Layout& sc, const Layout& ds, int d0, int d1)
 {
     typedef typename Elem<DT>::S S;
+    if (d0 > d1) std::swap(d0, d1);
+    if (d0 != d1 && count >= 4096 && count < (uint64_t(1) << 40))
+    {
+        // source dense in its own shape, result dense in the swapped shape, second swapped dimension innermost (or followed by
+        // dimensions of one element only): the tiled kernel
+        uint64_t swapped[MAX_RANK];
+        for (int d = 0; d < sc.rank; ++d) swapped[d] = sc.shape[d];
+        std::swap(swapped[d0], swapped[d1]);
+        uint64_t A = 1, B = 1, C = 1;
+        for (int d = 0; d < d0; ++d) A *= sc.shape[d];
+        for (int d = d0 + 1; d < d1; ++d) B *= sc.shape[d];
+        for (int d = d1 + 1; d < sc.rank; ++d) C *= sc.shape[d];
+        const uint64_t X = sc.shape[d0], Y = sc.shape[d1];
+        if (C == 1 && isCanonical(sc, sc.shape) && isCanonical(ds, swapped) && A < (1u << 31) && B < (1u << 31) && X < (1u << 31) && Y < (1u << 31) && X >= 8 && Y >= 8)
+        {
+            const uint64_t tilesX = (X + 31) / 32, tilesY = (Y + 31) / 32, tiles = A * B * tilesX * tilesY;
+            const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(tiles, static_cast<uint64_t>(ctx.smCount) * 32));
+            transposeTiledKernel<S><<<grid, 256, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), static_cast<uint32_t>(A), static_cast<uint32_t>(X),
+                                                                  static_cast<uint32_t>(B), static_cast<uint32_t>(Y), static_cast<uint32_t>(tilesX),
+                                                                  static_cast<uint32_t>(tilesY), tiles);
+            return;
+        }
+    }
     transposeKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), count, sc, ds, d0, d1);
 }
 template <int DT> void launchSliceSet(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
@@ -450,6 +546,15 @@ template <int DT> void launchTriangle(const LaunchContext& ctx, const void* src,
                                       uint64_t rows, uint64_t cols, int64_t diagonal, bool lower)
 {
     typedef typename Elem<DT>::S S;
+    constexpr uint64_t kPer = 16 / sizeof(S);
+    if (cols % kPer == 0 && count >= 4096 && rows < (1ull << 32) && cols / kPer < (1ull << 32) && isCanonical(sl, sl.shape) && isCanonical(dl, dl.shape) &&
+        reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0)
+    {
+        const uint64_t packs = count / kPer;
+        trianglePackedKernel<S><<<gridFor(packs, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), packs, static_cast<uint32_t>(rows),
+                                                                                       static_cast<uint32_t>(cols / kPer), diagonal, lower);
+        return;
+    }
     triangleKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, rows, cols, diagonal, lower);
 }
 template <int DT> void launchIndexSelect(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,

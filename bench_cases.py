@@ -295,6 +295,17 @@ def build_case(dev, case):
         k = 1024 if case.endswith("k1024") else 4096
         a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (k, 4096), dt, 1, 0.05)
         return lambda: a.matmul(b)
+    if case in ("linear_tanh_f32_k1024", "linear_tanh_f32_k4096"):
+        # one hidden layer of the MLP as the front end issues it: matmul(x, W) + b, then tanh, all three results kept
+        # (autograd holds them); with AIXB200_GEMM_EPILOGUE=0 the add and the tanh run as a generated kernel of their own
+        k = 1024 if case.endswith("k1024") else 4096
+        x, w, b = _rand(dev, (4096, k), C.F32, 0), _rand(dev, (k, 4096), C.F32, 1, 0.05), _rand(dev, (1, 4096), C.F32, 2, 0.1)
+
+        def layer():
+            mm = x.matmul(w)
+            s = mm + b
+            return mm, s, s.tanh()
+        return layer
     if case == "mlp_f32":
         from aix_b200.mlp import MlpTrainer
         trainer = MlpTrainer(dev)

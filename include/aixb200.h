@@ -172,7 +172,12 @@ int aixb200_argmax_indices_to(aixb200_device* dev, const aixb200_tensor* src, co
  * f32 on the tensor cores (tf32x3_matmul = 1) scales each operand by one power of two taken from its largest magnitude.
  * An operand that contains an infinity or a NaN is left unscaled; its finite elements above 65504 then overflow the fp16
  * terms, so rows and columns that the CPU device would still compute finitely can come out infinite or NaN as well.
- * Operands with non-finite elements that must keep their finite part exact need tf32x3_matmul = 0. */
+ * Operands with non-finite elements that must keep their finite part exact need tf32x3_matmul = 0.
+ * An f32 product on the tensor cores may be launched later than this call returns - at the latest by the next call that
+ * is not a recorded elementwise op: `result + row vector` (nn::Linear's bias, aixNeuralNetwork.hpp:150-153) and the tanh
+ * of that sum, when they are the next ops recorded and the values they consume are already deallocated, run inside the
+ * product's kernel, which then writes only the last of the three. Results and program order are those of separate
+ * launches; AIXB200_GEMM_EPILOGUE=0 in the environment launches every product from its own call. */
 int aixb200_matmul(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* result);
 
 /* ---- data movement (aixDevice.hpp:64-69, 74-81) ---- */
@@ -217,7 +222,8 @@ typedef struct aixb200_stats
     uint64_t prepared_operand_hits; /* f32 matmul operands whose two-term fp16 form was still cached */
     uint64_t prepared_operand_builds; /* ... and those that had to be prepared (max pass + split) */
     uint64_t prepared_operand_max_known; /* ... of which the max pass was skipped: the producing kernel had left max|x| */
-    uint64_t reserved[2];
+    uint64_t matmul_consumers_folded; /* recorded `product + row vector` and tanh ops that ran inside the product's kernel */
+    uint64_t reserved[1];
 } aixb200_stats;
 int aixb200_get_stats(aixb200_device* dev, aixb200_stats* out);
 /* CUDA C source of the most recently generated kernel (for inspection and tests); NULL if none yet. */

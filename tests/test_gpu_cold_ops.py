@@ -53,7 +53,8 @@ def test_argmax_family(b200, ref, dtype):
 @pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
 def test_transpose_materialised(b200, ref, dtype):
     rng = np.random.default_rng(400 + dtype)
-    for shape, (d0, d1) in [((4, 7), (0, 1)), ((3, 5, 6), (0, 2)), ((3, 5, 6), (1, 2)), ((2, 3, 4, 5), (1, 3)), ((65, 130), (0, 1))]:
+    for shape, (d0, d1) in [((4, 7), (0, 1)), ((3, 5, 6), (0, 2)), ((3, 5, 6), (1, 2)), ((2, 3, 4, 5), (1, 3)), ((65, 130), (0, 1)),
+                             ((257, 100), (0, 1)), ((3, 70, 50), (1, 2)), ((40, 5, 33), (0, 2)), ((2, 33, 3, 64), (1, 3)), ((64, 96, 2), (0, 1))]:
         x = values(rng, shape, dtype)
 
         def run(dev):
@@ -83,9 +84,9 @@ def test_slice_set_tril_triu(b200, ref, dtype):
             return d.raw()
         got, want = both(b200, ref, run)
         assert np.array_equal(got, want), f"sliceSet {DTYPE_NAMES[dtype]} {shape}"
-    for shape in [(5, 5), (4, 7), (3, 6, 4), (33, 65)]:
+    for shape in [(5, 5), (4, 7), (3, 6, 4), (33, 65), (70, 64), (3, 50, 48), (130, 32)]:      # the last three: whole 16-byte packs per row
         x = values(rng, shape, dtype)
-        for diagonal in (-2, 0, 1, 3):
+        for diagonal in (-2, 0, 1, 3, -40, 45):
             def run(dev):
                 t = TensorValue.from_numpy(x, dev, dtype)
                 lo, up = TensorValue.empty(shape, dev, dtype), TensorValue.empty(shape, dev, dtype)

@@ -1,0 +1,193 @@
+"""Consumers folded into the f32 matmul's epilogue: nn::Linear is matmul(x, W) + b (aixNeuralNetwork.hpp:150-153), usually
+followed by tanh. The device holds such a product back until it has seen the recorded ops that follow, and folds
+`+ row vector` and `tanh` into the product's kernel as far as the values they consume are dead (temporaries that were
+dropped): the kernel then writes one output instead of up to three. Every result must carry the bits the separate kernels
+give (same product, same add, same tanh routine), values that are kept alive must still be written, and program order
+must hold for ops recorded while the product waits.
+"""
+import numpy as np
+import pytest
+
+from aix_b200 import F32, TensorValue
+
+pytestmark = pytest.mark.gpu
+
+
+def folded(b200):
+    return b200.stats()["matmul_consumers_folded"]
+
+
+def operands(b200, m, k, n, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    w = (rng.normal(0, 1, (k, n)) / np.sqrt(k)).astype(np.float32)
+    b = rng.normal(0, 0.5, (1, n)).astype(np.float32)
+    return x, w, b, TensorValue.from_numpy(x, b200), TensorValue.from_numpy(w, b200), TensorValue.from_numpy(b, b200)
+
+
+def separate(b200, tx, tw, tb):
+    """The same three results from three launches: a synchronisation after each call keeps anything from being folded."""
+    mm = tx.matmul(tw)
+    b200.synchronize()
+    s = mm + tb
+    b200.synchronize()
+    t = s.tanh()
+    b200.synchronize()
+    return mm.numpy(), s.numpy(), t.numpy()
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 256, 384), (300, 100, 200), (1024, 1024, 1024), (257, 64, 68), (4096, 320, 512)])
+def test_linear_tanh_is_one_launch_with_the_bits_of_three(b200, ref, m, k, n):
+    x, w, b, tx, tw, tb = operands(b200, m, k, n, m + n)
+    want_mm, want_s, want_t = separate(b200, tx, tw, tb)
+    before, launches = folded(b200), b200.stats()["total_kernel_launches"]
+    t = (tx.matmul(tw) + tb).tanh()     # the product and the sum are temporaries: dead by the time the product is launched
+    b200.synchronize()
+    assert folded(b200) == before + 2, "the add and the tanh ran inside the product's kernel"
+    assert b200.stats()["total_kernel_launches"] - launches == 1, "one product, no elementwise kernel"
+    assert np.array_equal(t.numpy(), want_t)
+    exact = x.astype(np.float64) @ w.astype(np.float64) + b.astype(np.float64)
+    assert np.max(np.abs(want_s - exact)) <= 1e-5 * np.max(np.abs(exact))
+    assert np.max(np.abs(t.numpy() - np.tanh(exact))) <= 2e-5
+    # and against the reference's CPU device on a slab of rows
+    rows = slice(0, 8)
+    rx, rw, rb = TensorValue.from_numpy(x[rows], ref), TensorValue.from_numpy(w, ref), TensorValue.from_numpy(b, ref)
+    cpu = (rx.matmul(rw) + rb).tanh().numpy()
+    assert np.max(np.abs(t.numpy()[rows] - cpu)) <= 2e-5
+    # everything kept alive, as autograd keeps it: nothing is folded, every value is written
+    before = folded(b200)
+    mm = tx.matmul(tw)
+    s = mm + tb
+    t = s.tanh()
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(mm.numpy(), want_mm) and np.array_equal(s.numpy(), want_s) and np.array_equal(t.numpy(), want_t)
+
+
+def test_bias_on_the_left_and_bias_only(b200):
+    x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 5)
+    want_mm, want_s, want_t = separate(b200, tx, tw, tb)
+    before = folded(b200)
+    s = tb + tx.matmul(tw)              # row vector first
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(s.numpy(), want_s)
+    before = folded(b200)
+    s = tx.matmul(tw) + tb
+    u = s * 2.0                         # the sum's first consumer is not a tanh: the product is launched with the add folded
+    t = s.tanh()
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(s.numpy(), want_s)
+    assert np.array_equal(u.numpy(), want_s * np.float32(2.0))
+    assert np.array_equal(t.numpy(), want_t)
+    before = folded(b200)
+    s = tx.matmul(tw) + tb
+    t = s.tanh()                        # the sum stays alive: only the add is folded, the tanh runs as a kernel
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(s.numpy(), want_s) and np.array_equal(t.numpy(), want_t)
+
+
+def test_other_first_consumers_leave_the_product_alone(b200):
+    x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 6)
+    want_mm, want_s, want_t = separate(b200, tx, tw, tb)
+    before = folded(b200)
+    mm = tx.matmul(tw)
+    d = mm * mm                         # not `+ row vector`
+    s = mm + tb
+    del mm
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(d.numpy(), want_mm * want_mm)
+    assert np.array_equal(s.numpy(), want_s)
+    full = TensorValue.from_numpy(np.broadcast_to(b, (512, 256)).copy(), b200)
+    s = tx.matmul(tw) + full            # a full matrix, not a row vector
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(s.numpy(), want_s)
+    col = TensorValue.from_numpy(np.ones((512, 1), dtype=np.float32), b200)
+    s = tx.matmul(tw) + col             # a column vector
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(s.numpy(), want_mm + np.float32(1.0))
+    mm = tx.matmul(tw)
+    s = mm + tb
+    e = mm * 0.5                        # the product is read again after its add: it must be written
+    del mm
+    t = s.tanh()
+    del s
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(e.numpy(), want_mm * np.float32(0.5)) and np.array_equal(t.numpy(), want_t)
+
+
+def test_program_order_around_a_waiting_product(b200):
+    x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 7)
+    want_mm, want_s, want_t = separate(b200, tx, tw, tb)
+    bias = TensorValue.from_numpy(b, b200)
+    weights = TensorValue.from_numpy(w, b200)
+    before = folded(b200)
+    mm = tx.matmul(weights)
+    s = mm + bias
+    bias += 1.0                         # written after the add was recorded: the add still sees the old bias
+    weights *= 0.0                      # ... and the product the old weights
+    mm *= 2.0                           # ... and the add saw the product before this
+    t = s.tanh()
+    b200.synchronize()
+    assert folded(b200) == before
+    assert np.array_equal(s.numpy(), want_s)
+    assert np.array_equal(t.numpy(), want_t)
+    assert np.array_equal(mm.numpy(), want_mm * np.float32(2.0))
+    assert np.array_equal(bias.numpy(), b + np.float32(1.0))
+    assert not weights.numpy().any()
+    # the same with the product dropped: the add is folded and reads bias and weights as they were
+    bias = TensorValue.from_numpy(b, b200)
+    weights = TensorValue.from_numpy(w, b200)
+    before = folded(b200)
+    s = tx.matmul(weights) + bias
+    bias += 1.0
+    weights *= 0.0
+    t = s.tanh()
+    del s
+    z = TensorValue.full(3.0, (1000,), b200, F32)       # an unrelated fill does not end the wait
+    b200.synchronize()
+    assert folded(b200) == before + 2
+    assert np.array_equal(t.numpy(), want_t)
+    assert np.array_equal(bias.numpy(), b + np.float32(1.0))
+    assert not weights.numpy().any()
+    assert (z.numpy() == 3.0).all()
+    assert not tx.matmul(weights).numpy().any(), "the form prepared for the waiting product is not reused after the in-place update"
+    # a reduction recorded behind the folded add
+    before = folded(b200)
+    s = tx.matmul(tw) + tb
+    total = s.sum()
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(s.numpy(), want_s)
+    assert abs(float(total.numpy()) - want_s.astype(np.float64).sum()) <= 1e-5 * np.abs(want_s).sum()
+
+
+def test_the_next_product_finds_the_maximum_the_epilogue_left(b200):
+    """Two layers: the second product's left operand is the first one's tanh output; its max|x| comes from the first
+    product's epilogue once the size is known as an operand size (from the second step on)."""
+    rng = np.random.default_rng(9)
+    m, k = 1024, 1024
+    x = TensorValue.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32), b200)
+    w1 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), b200)
+    w2 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), b200)
+    b1 = TensorValue.from_numpy(rng.normal(0, 0.5, (1, k)).astype(np.float32), b200)
+    results = []
+    for step in range(3):
+        known = b200.stats()["prepared_operand_max_known"]
+        h = (x.matmul(w1) + b1).tanh()
+        y = h.matmul(w2)
+        b200.synchronize()
+        results.append((h.numpy(), y.numpy(), b200.stats()["prepared_operand_max_known"] - known))
+    assert results[2][2] >= 1, "the tanh output's maximum was left by the epilogue"
+    exact_h = np.tanh(x.numpy().astype(np.float64) @ w1.numpy().astype(np.float64) + b1.numpy().astype(np.float64))
+    exact_y = exact_h @ w2.numpy().astype(np.float64)
+    for h, y, _ in results:
+        assert np.array_equal(h, results[0][0])
+        assert np.max(np.abs(y - exact_y)) <= 1e-5 * np.max(np.abs(exact_y))
+        assert np.array_equal(y, results[0][1]), "the scale taken from the epilogue's maximum is the one the max pass finds"
