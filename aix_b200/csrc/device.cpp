@@ -1282,6 +1282,22 @@ void Device::contiguous(const aixb200_tensor* s, const aixb200_tensor* d)
     rec.in[0] = inputView(s, "contiguous");
     if (rec.in[0].dtype != rec.out.dtype) failInvalid("contiguous: element types differ");
     checkOperandSize(rec.in[0], rec.out, "contiguous");
+    // A large transposed matrix made contiguous: as a recorded op it would become a generated kernel whose loads walk down
+    // columns (one element per line); the tiled transpose kernel moves the same bytes through shared memory instead.
+    const View& in = rec.in[0];
+    if (!dryRun() && in.rank == 2 && in.strides[0] == 1 && in.strides[1] == in.shape[0] && in.shape[0] >= 64 && in.shape[1] >= 64 &&
+        in.size >= (uint64_t(1) << 16) && rec.out.isDense() && !in.overlaps(rec.out))
+    {
+        flush();
+        AIXB200_CTX();
+        kernels::Layout source{}, result{};
+        source.rank = result.rank = 2;
+        source.shape[0] = in.shape[1]; source.shape[1] = in.shape[0]; source.strides[0] = in.shape[0]; source.strides[1] = 1;
+        result.shape[0] = in.shape[0]; result.shape[1] = in.shape[1]; result.strides[0] = in.shape[1]; result.strides[1] = 1;
+        kernels::transposeGeneral(ctx, in.dtype, in.firstByte(), rec.out.firstByte(), in.size, source, result, 0, 1);
+        AIXB200_DONE("contiguous");
+        return;
+    }
     record(std::move(rec));
 }
 

@@ -291,15 +291,17 @@ __global__ void __launch_bounds__(kBlock) transposeKernel(const S* __restrict__ 
 }
 
 // The same permutation for the case that matters at size: both tensors dense, nothing behind the second swapped dimension.
-// The source is [A][X][B][Y], the result [A][Y][B][X]. A CTA moves a 32 x 32 tile of the (x, y) plane of one (a, b) through
+// The source is [A][X][B][Y], the result [A][Y][B][X]. A CTA moves a 64 x 64 tile of the (x, y) plane of one (a, b) through
 // shared memory: rows of y are read with consecutive threads along y, rows of x are written with consecutive threads along x,
-// so both sides of the copy touch whole 128-byte lines (for 4-byte elements) instead of one element per line.
+// so both sides of the copy touch whole lines instead of one element per line, and every thread has 16 independent loads
+// in flight before the barrier.
+constexpr uint32_t kTransposeTile = 64;
 template <class S>
 __global__ void __launch_bounds__(256) transposeTiledKernel(const S* __restrict__ src, S* __restrict__ dst, uint32_t A, uint32_t X, uint32_t B, uint32_t Y,
                                                             uint32_t tilesX, uint32_t tilesY, uint64_t tiles)
 {
-    __shared__ S tile[32][33];
-    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    __shared__ S tile[kTransposeTile][kTransposeTile + 1];
+    const uint32_t tx = threadIdx.x & 63u, ty = threadIdx.x >> 6;      // 64 x 4 threads
     for (uint64_t t = blockIdx.x; t < tiles; t += gridDim.x)
     {
         uint64_t rest = t;
@@ -307,19 +309,23 @@ __global__ void __launch_bounds__(256) transposeTiledKernel(const S* __restrict_
         const uint32_t tileX = static_cast<uint32_t>(rest % tilesX); rest /= tilesX;
         const uint32_t b = static_cast<uint32_t>(rest % B);
         const uint32_t a = static_cast<uint32_t>(rest / B);
-        const uint32_t x0 = tileX * 32, y0 = tileY * 32;
+        const uint32_t x0 = tileX * kTransposeTile, y0 = tileY * kTransposeTile;
+        const S* from = src + ((static_cast<uint64_t>(a) * X + x0) * B + b) * Y + y0;
+        S* to = dst + ((static_cast<uint64_t>(a) * Y + y0) * B + b) * X + x0;
+        const uint64_t fromPitch = static_cast<uint64_t>(B) * Y, toPitch = static_cast<uint64_t>(B) * X;
+        const uint32_t limitX = min(kTransposeTile, X - x0), limitY = min(kTransposeTile, Y - y0);
         #pragma unroll
-        for (uint32_t r = 0; r < 4; ++r)
+        for (uint32_t r = 0; r < kTransposeTile / 4; ++r)
         {
-            const uint32_t x = x0 + ty + r * 8, y = y0 + tx;
-            if (x < X && y < Y) tile[ty + r * 8][tx] = src[((static_cast<uint64_t>(a) * X + x) * B + b) * Y + y];
+            const uint32_t x = ty + r * 4;
+            if (x < limitX && tx < limitY) tile[x][tx] = from[x * fromPitch + tx];
         }
         __syncthreads();
         #pragma unroll
-        for (uint32_t r = 0; r < 4; ++r)
+        for (uint32_t r = 0; r < kTransposeTile / 4; ++r)
         {
-            const uint32_t y = y0 + ty + r * 8, x = x0 + tx;
-            if (x < X && y < Y) dst[((static_cast<uint64_t>(a) * Y + y) * B + b) * X + x] = tile[tx][ty + r * 8];
+            const uint32_t y = ty + r * 4;
+            if (tx < limitX && y < limitY) to[y * toPitch + tx] = tile[tx][y];
         }
         __syncthreads();
     }
@@ -526,8 +532,8 @@ template <int DT> void launchTranspose(const LaunchContext& ctx, const void* src
         const uint64_t X = sc.shape[d0], Y = sc.shape[d1];
         if (C == 1 && isCanonical(sc, sc.shape) && isCanonical(ds, swapped) && A < (1u << 31) && B < (1u << 31) && X < (1u << 31) && Y < (1u << 31) && X >= 8 && Y >= 8)
         {
-            const uint64_t tilesX = (X + 31) / 32, tilesY = (Y + 31) / 32, tiles = A * B * tilesX * tilesY;
-            const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(tiles, static_cast<uint64_t>(ctx.smCount) * 32));
+            const uint64_t tilesX = (X + kTransposeTile - 1) / kTransposeTile, tilesY = (Y + kTransposeTile - 1) / kTransposeTile, tiles = A * B * tilesX * tilesY;
+            const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(tiles, static_cast<uint64_t>(ctx.smCount) * 8));
             transposeTiledKernel<S><<<grid, 256, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), static_cast<uint32_t>(A), static_cast<uint32_t>(X),
                                                                   static_cast<uint32_t>(B), static_cast<uint32_t>(Y), static_cast<uint32_t>(tilesX),
                                                                   static_cast<uint32_t>(tilesY), tiles);

@@ -69,6 +69,26 @@ def test_transpose_materialised(b200, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
+def test_contiguous_of_a_large_transposed_matrix(b200, ref, dtype):
+    """Large enough for the tiled kernel (ragged tile edges, an offset view), followed and preceded by recorded ops."""
+    rng = np.random.default_rng(450 + dtype)
+    for rows, cols in [(300, 257), (64, 1030), (1000, 70)]:
+        x = values(rng, (rows + 1, cols), dtype)
+
+        def run(dev):
+            t = TensorValue.from_numpy(x, dev, dtype)
+            u = t + t                                       # a recorded producer
+            a = u.transpose(0, 1).contiguous()              # [cols, rows + 1]
+            below = TensorValue(t.storage, (rows, cols), t.strides, cols, dtype, dev)      # a view that starts one row in
+            b = below.transpose(0, 1).contiguous()          # [cols, rows]
+            c = b + b                                       # a recorded consumer
+            return a.raw(), b.raw(), c.raw()
+        got, want = both(b200, ref, run)
+        for g, w in zip(got, want):
+            assert np.array_equal(g, w), f"{DTYPE_NAMES[dtype]} {rows}x{cols}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
 def test_slice_set_tril_triu(b200, ref, dtype):
     rng = np.random.default_rng(500 + dtype)
     for shape, dim, start, end, step in [((8,), 0, 2, 7, 1), ((6, 9), 1, 1, 9, 3), ((6, 9), 0, 0, 6, 2), ((3, 4, 10), 2, 3, 10, 2), ((40, 70), 0, 5, 37, 4)]:
