@@ -33,6 +33,7 @@ struct NcclApi
     int (*commGetAsyncError)(NcclComm, int*) = nullptr;
     int (*commAbort)(NcclComm) = nullptr;
     int (*commDestroy)(NcclComm) = nullptr;
+    int (*commSplit)(NcclComm, int, int, NcclComm*, void*) = nullptr;      // NCCL >= 2.18; optional
     int (*allReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*reduceScatter)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*allGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
@@ -95,6 +96,7 @@ NcclApi& nccl()
     api.reduceScatter = reinterpret_cast<decltype(api.reduceScatter)>(sym("ncclReduceScatter"));
     api.allGather = reinterpret_cast<decltype(api.allGather)>(sym("ncclAllGather"));
     api.getErrorString = reinterpret_cast<decltype(api.getErrorString)>(sym("ncclGetErrorString"));
+    api.commSplit = reinterpret_cast<decltype(api.commSplit)>(dlsym(api.handle, "ncclCommSplit"));
     return api;
 }
 
@@ -155,15 +157,26 @@ Comm::Comm(int rank, int nranks, const void* id128, int ordinal) : m_rank(rank),
 #endif
     checkNccl(nccl().commInitRank(&comm, nranks, id, rank), "ncclCommInitRank");
     m_comm = comm;
+    // A second communicator over the same ranks for the all-gathers of a sharded optimizer (see allGather). Every rank
+    // decides the same way: same library, same environment.
+    const char* lane = std::getenv("AIXB200_COMM_GATHER_LANE");
+    if (nranks > 1 && !backendInjected() && nccl().commSplit && !(lane && lane[0] == '0'))
+    {
+        NcclComm second = nullptr;
+        checkNccl(nccl().commSplit(m_comm, 0, rank, &second, nullptr), "ncclCommSplit");
+        m_gatherComm = second;
+    }
 }
 
 Comm::~Comm()
 {
+    if (m_gatherComm && !m_aborted) nccl().commDestroy(m_gatherComm);
     if (m_comm && !m_aborted) nccl().commDestroy(m_comm);
 }
 
 void Comm::abortOnce()
 {
+    if (m_gatherComm && !m_aborted) nccl().commAbort(m_gatherComm);
     if (m_comm && !m_aborted) nccl().commAbort(m_comm);
     m_aborted = true;
 }
@@ -244,12 +257,12 @@ void Comm::reduceScatterSum(void* data, size_t count, uint32_t dtype, cudaStream
 }
 
 // In place: every rank contributes its own slice of `data` and receives all the others'.
-void Comm::allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream)
+void Comm::allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool ownLane)
 {
     const size_t slice = count / static_cast<size_t>(m_nranks);
     const char* own = static_cast<const char*>(data) + static_cast<size_t>(m_rank) * slice * dtypeSize(dtype);
     checkAsyncError("all_gather");
-    finishCall(nccl().allGather(own, data, slice, ncclType(dtype), m_comm, stream), "ncclAllGather");
+    finishCall(nccl().allGather(own, data, slice, ncclType(dtype), (ownLane && m_gatherComm) ? m_gatherComm : m_comm, stream), "ncclAllGather");
 }
 
 }   // namespace aixb200

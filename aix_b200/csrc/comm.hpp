@@ -19,7 +19,11 @@ public:
     // Sum over the ranks; with `average` the sum is divided by the number of ranks inside the collective.
     void allReduceSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average = false);
     void reduceScatterSum(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool average = false);
-    void allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream);
+    // With `ownLane` the all-gather runs on a second communicator (split off the first one when the library offers
+    // ncclCommSplit), so that on a stream of its own it does not queue behind reduce-scatters issued earlier: collectives of
+    // one communicator run one after the other whatever streams they are given.
+    void allGather(void* data, size_t count, uint32_t dtype, cudaStream_t stream, bool ownLane = false);
+    bool hasGatherLane() const { return m_gatherComm != nullptr; }
     int rank() const { return m_rank; }
     int size() const { return m_nranks; }
     // One query of the communicator's asynchronous state; an error aborts the communicator (once) and throws.
@@ -36,6 +40,7 @@ private:
     void finishCall(int result, const char* what);
     void abortOnce();
     void* m_comm = nullptr;
+    void* m_gatherComm = nullptr;   // second communicator over the same ranks, for all-gathers (AIXB200_COMM_GATHER_LANE=0: none)
     int   m_rank, m_nranks;
     long  m_timeoutMs = 0;
     bool  m_nonBlocking = false, m_aborted = false;

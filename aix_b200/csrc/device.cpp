@@ -189,7 +189,9 @@ Device::~Device()
     {
         cudaSetDevice(m_cfg.ordinal);
         if (m_commStream) cudaStreamSynchronize(m_commStream);
+        if (m_gatherStream) cudaStreamSynchronize(m_gatherStream);
         m_comm.reset();
+        if (m_gatherStream) { cudaStreamDestroy(m_gatherStream); m_gatherStream = nullptr; }
         if (m_commStream)
         {
             cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork);
@@ -1450,7 +1452,7 @@ void Device::allReduceAsync(void* data, size_t count, uint32_t dtype, double sca
 {
     if (!m_comm) failInvalid("all_reduce_async: aixb200_comm_init was not called");
     const bool average = ncclAverages(true) && isFloatType(dtype) && m_comm->size() > 1 && scale == 1.0 / m_comm->size();
-    startCollective(data, count, dtype, "all_reduce_async", [&]
+    startCollective(data, count, dtype, "all_reduce_async", [&](cudaStream_t)
     {
         m_comm->allReduceSum(data, count, dtype, m_commStream, average);
         if (scale != 1.0 && !average) scaleOnCommStream(data, count, dtype, scale);      // plain sum (the form in-switch reduction serves), then the pass
@@ -1466,7 +1468,7 @@ void Device::reduceScatterAsync(void* data, size_t count, uint32_t dtype, double
     const size_t ranks = static_cast<size_t>(m_comm->size());
     if (count % ranks != 0) failInvalid("reduce_scatter_async: the element count must be a multiple of the number of ranks");
     const bool average = ncclAverages(true) && isFloatType(dtype) && ranks > 1 && scale == 1.0 / m_comm->size();
-    startCollective(data, count, dtype, "reduce_scatter_async", [&]
+    startCollective(data, count, dtype, "reduce_scatter_async", [&](cudaStream_t)
     {
         if (ranks > 1) m_comm->reduceScatterSum(data, count, dtype, m_commStream, average);
         const size_t slice = count / ranks;
@@ -1480,7 +1482,10 @@ void Device::allGatherAsync(void* data, size_t count, uint32_t dtype)
     if (!m_comm) failInvalid("all_gather_async: aixb200_comm_init was not called");
     const size_t ranks = static_cast<size_t>(m_comm->size());
     if (count % ranks != 0) failInvalid("all_gather_async: the element count must be a multiple of the number of ranks");
-    startCollective(data, count, dtype, "all_gather_async", [&] { if (ranks > 1) m_comm->allGather(data, count, dtype, m_commStream); });
+    // On the gather lane when the communicator has one: the parameters' all-gathers then overtake the reduce-scatters of the
+    // last layers' gradients, which were issued earlier and are still running when the optimizer starts on the first layers.
+    const bool ownLane = m_comm->hasGatherLane();
+    startCollective(data, count, dtype, "all_gather_async", [&](cudaStream_t stream) { if (ranks > 1) m_comm->allGather(data, count, dtype, stream, ownLane); }, ownLane);
 }
 
 void Device::scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale)
@@ -1494,7 +1499,7 @@ void Device::scaleOnCommStream(void* data, size_t count, uint32_t dtype, double 
 
 // Common frame of the overlapped collectives: order the side stream after everything issued so far on the device's
 // stream, run `issue` there, and remember the buffer so that later ops touching it are ordered after the collective.
-void Device::startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue)
+void Device::startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void(cudaStream_t)>& issue, bool gatherLane)
 {
     aixb200_tensor whole{};
     whole.data = data; whole.size = count; whole.dtype = dtype; whole.rank = 1; whole.shape[0] = count; whole.strides[0] = 1;
@@ -1508,13 +1513,15 @@ void Device::startCollective(void* data, size_t count, uint32_t dtype, const cha
         check(cudaStreamCreateWithFlags(&m_commStream, cudaStreamNonBlocking), "cudaStreamCreate(comm)");
         check(cudaEventCreateWithFlags(&m_commFork, cudaEventDisableTiming), "cudaEventCreate(comm)");
     }
+    if (gatherLane && !m_gatherStream) check(cudaStreamCreateWithFlags(&m_gatherStream, cudaStreamNonBlocking), "cudaStreamCreate(gather)");
+    const cudaStream_t side = gatherLane ? m_gatherStream : m_commStream;
     check(cudaEventRecord(m_commFork, m_stream), "cudaEventRecord(comm fork)");
-    check(cudaStreamWaitEvent(m_commStream, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
-    issue();
+    check(cudaStreamWaitEvent(side, m_commFork, 0), "cudaStreamWaitEvent(comm fork)");
+    issue(side);
     cudaEvent_t done = nullptr;
     if (!m_commEventPool.empty()) { done = m_commEventPool.back(); m_commEventPool.pop_back(); }
     else check(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate(comm)");
-    check(cudaEventRecord(done, m_commStream), "cudaEventRecord(comm done)");
+    check(cudaEventRecord(done, side), "cudaEventRecord(comm done)");
     const char* begin = static_cast<const char*>(data);
     m_commInFlight.push_back({begin, begin + count * dtypeSize(dtype), done});
 }
@@ -1572,6 +1579,7 @@ void Device::commDestroy()
         cudaStreamSynchronize(m_stream);
         m_comm.reset();
     }
+    if (m_gatherStream) { cudaStreamDestroy(m_gatherStream); m_gatherStream = nullptr; }
     if (m_commStream)
     {
         cudaStreamDestroy(m_commStream); cudaEventDestroy(m_commFork);

@@ -216,12 +216,13 @@ private:
     aixb200_stats m_stats{};
     std::unique_ptr<Comm> m_comm;
     cudaStream_t   m_commStream = nullptr;      // side stream of overlapped all-reduces
+    cudaStream_t   m_gatherStream = nullptr;    // second side stream: all-gathers on the communicator's gather lane (comm.hpp)
     cudaEvent_t    m_commFork = nullptr;
     struct CommInFlight { const char* begin; const char* end; cudaEvent_t done; };
     std::vector<CommInFlight> m_commInFlight;   // collectives started on the side stream and not yet joined
     std::vector<cudaEvent_t>  m_commEventPool;
     void orderAfterCollectives(const View& v);
-    void startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void()>& issue);
+    void startCollective(void* data, size_t count, uint32_t dtype, const char* what, const std::function<void(cudaStream_t)>& issue, bool gatherLane = false);
     void scaleOnCommStream(void* data, size_t count, uint32_t dtype, double scale);  // the device's stream waits for in-flight collectives that touch the view
     struct OperandRegion { const char* lo; const char* hi; uint32_t slot; bool fresh; uint64_t stamp; bool operand; };   // operand: the tensor living there has been a matmul operand
     std::vector<OperandRegion> m_operandRegions;

@@ -409,6 +409,31 @@ class ShardedGradientExchange(GradientExchange):
             self.device.reduceScatterAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
         else:
             self.device.allReduceAsync(g.storage.data, g.size, g.dtype, 1.0 / self.world_size)
+        # Early updates (attach(optimizer, early=True)): the parameter whose collective was started two gradients ago has had
+        # a whole weight-gradient matmul to finish it; its slice is updated and its all-gather started now, inside backward().
+        early = getattr(self, "_early", None)
+        if early is not None:
+            self._order.append(early["index_of"].get(id(node)))
+            if len(self._order) >= 3 and self._order[-3] in early["allowed"]:
+                early["optimizer"].update_early(self._order[-3])
+
+    def attach(self, optimizer, early: bool = False):
+        """early=True (needs a ShardedAdam with a model attached): parameters of the modules the optimizer would update at
+        once in step() are instead updated inside backward(), two gradient-ready hooks after their own - their
+        reduce-scatter has finished under the matmul in between, and their all-gather then runs under the remaining
+        weight-gradient matmuls instead of after them. ONLY valid when no parameter value is read by backward() after the
+        first gradient is final: true for a feed-forward stack under the reference's recursion order (every dX is
+        computed on the way down, before any dW, aixCore.hpp:2192-2207)."""
+        super().attach(optimizer)
+        if early and self.world_size > 1 and hasattr(optimizer, "_owners"):
+            allowed = {i for j in optimizer._with_params[:optimizer._eager] for i in optimizer._owners[j]}
+            self._early = {"optimizer": optimizer, "allowed": allowed, "index_of": {id(p.node): i for i, p in enumerate(optimizer.parameters)}}
+            self._order = []
+
+    def finish(self):
+        super().finish()
+        if getattr(self, "_early", None) is not None:
+            self._order = []
 
 
 class ShardedAdam(Adam):
@@ -467,11 +492,21 @@ class ShardedAdam(Adam):
         if hasattr(self, "_due"):
             self._due.clear()
 
+    def update_early(self, i: int):
+        """Applies parameter i's update of the step that the next step() call counts, ahead of that call (from a
+        gradient-ready hook inside backward(): ShardedGradientExchange.attach(early=True))."""
+        done = self.__dict__.setdefault("_done_early", set())
+        if i not in done and self.parameters[i].isRequireGrad():
+            done.add(i)
+            self._update(i, self.timestep + 1)
+
     def step(self):
         self.finish()                                       # nothing of the previous step may be left when the gradients change
         self.timestep += 1
+        done = self.__dict__.setdefault("_done_early", set())
         if hasattr(self, "_owners"):
-            self._due = {i for i, p in enumerate(self.parameters) if p.isRequireGrad()}
+            self._due = {i for i, p in enumerate(self.parameters) if p.isRequireGrad() and i not in done}
+            done.clear()
             for j in self._with_params[:self._eager]:
                 for i in self._owners[j]:
                     if i in self._due:
@@ -479,10 +514,12 @@ class ShardedAdam(Adam):
                         self._update(i)
             return
         for i, p in enumerate(self.parameters):
-            if p.isRequireGrad():
+            if p.isRequireGrad() and i not in done:
                 self._update(i)
+        done.clear()
 
-    def _update(self, i: int):
+    def _update(self, i: int, timestep: Optional[int] = None):
+        timestep = self.timestep if timestep is None else timestep
         p = self.parameters[i]
         b1, b2 = float(np.float32(self.beta1)), float(np.float32(self.beta2))
         narrow = lambda x: float(np.float32(x))
@@ -494,8 +531,8 @@ class ShardedAdam(Adam):
         g = grad.to(C.F32)
         self.m[i] = self.beta1 * self.m[i] + narrow(1.0 - b1) * g
         self.v[i] = self.beta2 * self.v[i] + narrow(1.0 - b2) * g * g
-        mHat = self.m[i] / narrow(1.0 - math.pow(b1, self.timestep))
-        vHat = self.v[i] / narrow(1.0 - math.pow(b2, self.timestep))
+        mHat = self.m[i] / narrow(1.0 - math.pow(b1, timestep))
+        vHat = self.v[i] / narrow(1.0 - math.pow(b2, timestep))
         value -= (self.lr * mHat / (vHat.sqrt() + self.epsilon)).to(p.dtype)
         if self.sharded[i]:
             whole = p.value

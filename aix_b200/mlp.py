@@ -32,7 +32,7 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 class MlpTrainer:
     def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
-                 overlap=True, data=None, sharded=False, deferred=True):
+                 overlap=True, data=None, sharded=False, deferred=True, early=True):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -58,7 +58,11 @@ class MlpTrainer:
         exchange_type = ShardedGradientExchange if sharded else GradientExchange
         self.exchange = exchange_type(device, params, world_size) if overlap and world_size > 1 else None
         if self.exchange is not None:
-            self.exchange.attach(self.optimizer)
+            # early: the first layers' updates and all-gathers move into backward() (valid for this feed-forward stack)
+            if sharded and deferred and early:
+                self.exchange.attach(self.optimizer, early=True)
+            else:
+                self.exchange.attach(self.optimizer)
         self.flops_per_step = 2.0 * batch * sum(a * b for a, b in zip(dims[:-1], dims[1:])) * 3 \
             - 2.0 * batch * dims[0] * dims[1]                        # forward + dW + dX (no dX for the first layer)
 

@@ -361,6 +361,7 @@ def main():
                 # default form: sharded optimizer (reduce-scatter, 1/N of Adam per rank, all-gather); beside it the two
                 # all-reduce forms, to show what each step of the design buys
                 mlp_train = measure_mlp(dev, tensor_peak, sharded=True, **common)
+                mlp_train["ms_per_step_sharded_optimizer_no_early_updates"] = measure_mlp(dev, tensor_peak, sharded=True, early=False, **common)["ms_per_step"]
                 mlp_train["ms_per_step_sharded_optimizer_not_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=False, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_inside_backward"] = measure_mlp(dev, tensor_peak, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]

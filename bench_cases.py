@@ -123,11 +123,11 @@ def measure_matmul(dev, tensor_peak, size=4096):
 
 
 def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batch=4096, barrier=None, reduce_max=None, overlap=True,
-                sharded=False, deferred=True):
+                sharded=False, deferred=True, early=True):
     """MLP training configuration: device time of `steps` steps (forward, backward, gradient all-reduce when
     world_size > 1, Adam), loss not read inside the timed region."""
     from aix_b200.mlp import MlpTrainer
-    trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size, overlap=overlap, sharded=sharded, deferred=deferred)
+    trainer = MlpTrainer(dev, batch=batch, rank=rank, world_size=world_size, overlap=overlap, sharded=sharded, deferred=deferred, early=early)
     for _ in range(warmup):
         loss = trainer.step()
     first = float(loss.value.item())
@@ -156,7 +156,8 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
             "prepared_operand_hits_per_step": (s1["prepared_operand_hits"] - s0["prepared_operand_hits"]) / steps,
             "gradient_exchange": "none" if world_size == 1 else (
                 ("reduce-scatter per gradient started inside backward, each rank updates 1/N of every parameter, all-gather" +
-                 ("; later layers' updates deferred into the next forward pass" if deferred else "")) if sharded
+                 ("; later layers' updates deferred into the next forward pass" if deferred else "") +
+                 ("; first layers' updates and all-gathers moved into backward" if deferred and early else "")) if sharded
                 else ("all-reduce per parameter, started inside backward" if overlap else "all-reduce per parameter after backward")),
             "loss_after_warmup": first, "loss_at_end": last}
 
