@@ -541,7 +541,12 @@ void Device::checkLaunch(const char* what)
 {
     if (dryRun()) return;
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) failRuntime(std::string(what) + ": " + cudaGetErrorString(e));
+    if (e != cudaSuccess)
+    {
+        // a matmul that was not launched has not prepared its tile scheduler's next counter: start that area afresh
+        cudaMemsetAsync(static_cast<char*>(m_scratch) + m_scratchBytes, 0, kernels::kGemmCounterBytes, m_stream);
+        failRuntime(std::string(what) + ": " + cudaGetErrorString(e));
+    }
 }
 
 // ----------------------------------------------------------------------------------------------------------------
@@ -795,7 +800,7 @@ namespace
 
 kernels::LaunchContext makeContext(Device& d, uint64_t* launches)
 {
-    return kernels::LaunchContext{d.stream(), d.smCount(), d.scratch(), d.scratchBytes(), launches};
+    return kernels::LaunchContext{d.stream(), d.smCount(), d.scratch(), d.scratchBytes(), launches, d.gemmLaunchCounter()};
 }
 
 kernels::Layout layoutOf(const aixb200_tensor* t)

@@ -104,6 +104,7 @@ public:
 
     // Scratch for fixed kernels (reduction partials, counters); lives as long as the device.
     void* scratch() const { return m_scratch; }
+    uint32_t* gemmLaunchCounter() { return &m_gemmLaunches; }
     size_t scratchBytes() const { return m_scratchBytes; }
 
     std::string lastError;
@@ -237,6 +238,7 @@ private:
     uint64_t m_preparedBytes = 0, m_preparedStamp = 0;
     bool     m_termCacheEnabled = true;     // AIXB200_GEMM_TERM_CACHE=0: every matmul prepares its operands afresh
     bool m_inFlush = false;
+    uint32_t m_gemmLaunches = 0;            // numbers the launches that use the matmul's tile scheduler in this device's scratch
     bool m_checkErrorWord = false;
 };
 

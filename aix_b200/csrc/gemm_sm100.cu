@@ -93,6 +93,10 @@ struct KernelParams
     uint32_t* errorWord;
     float*   splitWorkspace;    // one 256 x 256 f32 partial accumulator per cluster
     uint32_t* splitCounters;    // per (split tile, CTA rank): partial accumulators published so far; left at zero
+    // Tiles handed out at run time (see WorkIterator): null = the static deal
+    uint32_t* tileCounters;     // eight counters, 16 words apart; launch e uses counter e % 8 and zeroes counter (e + 4) % 8
+    uint64_t* tileRing;         // per cluster kGemmRingSlots entries: (epoch << 40) | (iteration << 20) | tile
+    uint32_t tileEpoch;         // launch number on this device, 24 bits
     // Elementwise consumers folded into the epilogue of the three-fp16-pass f32 kernel (see Problem::bias):
     uint32_t outputs;           // bit 0: C itself, bit 1: C + bias (through mapC1), bit 2: tanh(C + bias) (through mapC2)
     const float* bias;          // n values, added to every row
@@ -527,16 +531,88 @@ struct WorkItem
     uint32_t tile, kbBegin, kbCount, kind;
     uint32_t partials;          // kWorkFinish: accumulators of the following `partials` clusters belong to this tile
 };
+// Which tiles a cluster computes. Static deal (tileCounters == null, and always for problems whose remainder wave is cut
+// along K): cluster c takes tiles c, c + clusters, ... Dynamic deal: one thread of the cluster - the leader CTA's TMA producer,
+// the first to need the answer - draws the next tile from a device-wide counter and publishes it, tagged with the launch and
+// the iteration, in the cluster's ring in global memory; every other role of both CTAs reads it there (a bounded spin; one
+// 8-byte load per tile and role). A cluster that starts late - because a collective's kernel held its SMs when the matmul
+// was launched - then simply draws fewer tiles, instead of finishing a fixed share late and the whole product with it. The
+// producer draws one tile ahead, so the counter's latency stays off its path.
+constexpr uint32_t kNoTile = 0xFFFFFu;
+enum : uint32_t { kRoleFetcher = 0, kRoleThread = 1, kRoleWarp = 2 };
 struct WorkIterator
 {
     uint32_t cluster, clusters, kBlocks, tiles, unit, unitEnd, units, next;
-    __device__ WorkIterator(const KernelParams& p, uint32_t clusterId, uint32_t clusterCount)
+    // dynamic deal
+    uint32_t* counter = nullptr;
+    uint64_t* ring = nullptr;
+    uint64_t  tagBase = 0;
+    uint32_t  role = kRoleThread, iteration = 0, drawn = kNoTile;
+    volatile uint32_t* abortFlag = nullptr;
+
+    __device__ WorkIterator(const KernelParams& p, uint32_t clusterId, uint32_t clusterCount, uint32_t roleOfCaller = kRoleThread,
+                            volatile uint32_t* abort = nullptr)
         : cluster(clusterId), clusters(clusterCount), kBlocks(p.kBlocks), tiles(p.tilesM * p.tilesN),
           unit(static_cast<uint32_t>(static_cast<uint64_t>(clusterId) * p.splitUnits / clusterCount)),
           unitEnd(static_cast<uint32_t>(static_cast<uint64_t>(clusterId + 1) * p.splitUnits / clusterCount)),
-          units(p.splitUnits), next(p.splitTiles + clusterId) {}
+          units(p.splitUnits), next(p.splitTiles + clusterId)
+    {
+        if (p.tileCounters)
+        {
+            counter = p.tileCounters + (p.tileEpoch & 7u) * 16u;
+            ring = p.tileRing + static_cast<size_t>(clusterId) * kernels::kGemmRingSlots;
+            tagBase = static_cast<uint64_t>(p.tileEpoch) << 40;
+            role = roleOfCaller;
+            abortFlag = abort;
+            if (role == kRoleFetcher)
+            {
+                if (clusterId == 0) p.tileCounters[((p.tileEpoch + 4u) & 7u) * 16u] = 0;     // ready for the launch four launches on
+                drawn = atomicAdd(counter, 1u);
+            }
+        }
+    }
+    __device__ uint32_t await(uint64_t tag)
+    {
+        const uint64_t* slot = ring + (iteration % kernels::kGemmRingSlots);
+        const uint64_t start = globalTimerNs();
+        uint32_t spins = 0;
+        for (;;)
+        {
+            uint64_t v;
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+            if ((v >> 20) == (tag >> 20)) return static_cast<uint32_t>(v & 0xFFFFFu);
+            if ((++spins & 63u) == 0)
+            {
+                if (*abortFlag) return kNoTile;
+                if (globalTimerNs() - start > kWaitLimitNs) { *abortFlag = 1; return kNoTile; }
+            }
+        }
+    }
     __device__ bool get(WorkItem& w)
     {
+        if (counter)
+        {
+            const uint64_t tag = tagBase | (static_cast<uint64_t>(iteration) << 20);
+            uint32_t tile;
+            if (role == kRoleFetcher)
+            {
+                tile = drawn < tiles ? drawn : kNoTile;
+                asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ring + (iteration % kernels::kGemmRingSlots)), "l"(tag | tile) : "memory");
+                if (tile != kNoTile) drawn = atomicAdd(counter, 1u);        // the next one, needed a whole tile from now
+            }
+            else if (role == kRoleThread) tile = await(tag);
+            else
+            {
+                // the lanes that are here together (all 32 unless a wait gave up in some of them): the first one reads
+                const uint32_t together = __activemask(), first = static_cast<uint32_t>(__ffs(static_cast<int>(together))) - 1u;
+                tile = (threadIdx.x & 31u) == first ? await(tag) : 0u;
+                tile = __shfl_sync(together, tile, static_cast<int>(first));
+            }
+            ++iteration;
+            if (tile == kNoTile) return false;
+            w.tile = tile; w.kbBegin = 0; w.kbCount = kBlocks; w.kind = kWorkWhole; w.partials = 0;
+            return true;
+        }
         if (unit < unitEnd)
         {
             w.tile = unit / kBlocks;
@@ -862,7 +938,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             bool ok = true;
             const uint32_t stageBytes = p.pairABytes + p.pairBBytes;
             const uint32_t leaderFull0 = mapToCta(smemAddr(&s.full[0]), 0);
-            WorkIterator work(p, clusterId, clusters);
+            WorkIterator work(p, clusterId, clusters, leader ? kRoleFetcher : kRoleThread, abortFlag);
             WorkItem w;
             while (ok && work.get(w))
             {
@@ -939,7 +1015,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int j = 0; j < 8; ++j) { aOff[j] = p.pairAOff[j]; bOff[j] = p.pairBOff[j]; }
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
-            WorkIterator work(p, clusterId, clusters);
+            WorkIterator work(p, clusterId, clusters, kRoleThread, abortFlag);
             WorkItem w;
             while (ok && work.get(w))
             for (uint32_t c = 0; c < p.chunks && ok; ++c)
@@ -991,7 +1067,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             float sum[128];
             uint32_t acc = 0, accPhase = 0;
             bool ok = true;
-            WorkIterator work(p, clusterId, clusters);
+            WorkIterator work(p, clusterId, clusters, kRoleWarp, abortFlag);
             WorkItem w;
             while (ok && work.get(w))
             {
@@ -1115,7 +1191,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const size_t slotStride = size_t(2) * 128 * 256;                 // floats per cluster slot of the workspace
         uint32_t acc = 0, accPhase = 0, sliceCounter = 0;
         bool ok = true;
-        WorkIterator work(p, clusterId, clusters);
+        WorkIterator work(p, clusterId, clusters, kRoleWarp, abortFlag);
         WorkItem w;
         while (ok && work.get(w))
         {
@@ -1960,6 +2036,20 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
                                             : (q.dtype == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
             const size_t es = dtypeSize(q.dtype);
             p.tmaEpilogue = makeMap(&mapC, ctype, q.c, q.n, q.m, q.n * es, static_cast<uint32_t>(128 / es), 32) ? 1u : 0u;
+        }
+        // Tiles are dealt out at run time while a collective is in flight on this device (its kernel may hold SMs when this
+        // one starts: see WorkIterator); alone on the GPU the static deal is 1-3 % faster (measured: 86.2 against 89.3 us at
+        // 4096 x 4096 x 1024 f32). AIXB200_GEMM_DYNAMIC=1 / 0: always / never.
+        static const int dynamicDeal = []{ const char* v = std::getenv("AIXB200_GEMM_DYNAMIC"); return v ? (v[0] == '0' ? 0 : 1) : -1; }();
+        if ((dynamicDeal > 0 || (dynamicDeal < 0 && q.shareDevice)) && ctx.gemmLaunches && p.splitTiles == 0 && tiles < kNoTile &&
+            kernels::kGemmRingOffset + static_cast<size_t>(clusters) * kernels::kGemmRingSlots * 8 <= kernels::kGemmCounterBytes)
+        {
+            char* area = static_cast<char*>(ctx.scratch) + ctx.scratchBytes;
+            p.tileCounters = reinterpret_cast<uint32_t*>(area + kernels::kGemmSchedulerOffset);
+            p.tileRing = reinterpret_cast<uint64_t*>(area + kernels::kGemmRingOffset);
+            // the launch number belongs to the scratch block: counter e % 8 was zeroed by launch e - 4 on the same block
+            *ctx.gemmLaunches = (*ctx.gemmLaunches + 1) & 0xFFFFFFu;
+            p.tileEpoch = *ctx.gemmLaunches;
         }
         CUtensorMap mapC1 = mapC, mapC2 = mapC;
         p.outputs = 1;

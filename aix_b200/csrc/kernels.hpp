@@ -15,6 +15,7 @@ struct LaunchContext
     void*        scratch;        // device scratch, zero-initialised once; kernels leave its counters at zero
     size_t       scratchBytes;
     uint64_t*    launches;       // incremented once per kernel launch
+    uint32_t*    gemmLaunches = nullptr;   // host counter of tensor-core matmul launches that used this scratch block's tile scheduler
 };
 
 // Layout of the scratch block shared by the reduction kernels.
@@ -23,7 +24,12 @@ constexpr size_t kScratchTimeoutOffset  = 128;      // raised by a kernel whose 
 constexpr size_t kScratchBadIndexOffset = 132;      // raised by indexSelect / indexAdd on an index outside the dimension
 constexpr size_t kMaxReduceBlocks     = 4096;       // upper bound of partials a full reduction may write
 // The device allocates this much beyond LaunchContext::scratchBytes: counters of the tensor-core matmul's split tiles.
-constexpr size_t kGemmCounterBytes    = 4096;
+constexpr size_t kGemmCounterBytes    = 4096 + 16384;
+// ... and, behind the first 4096 bytes, the tile scheduler of the CTA-pair matmul: eight rotating tile counters (64 bytes
+// apart) and, from kGemmRingOffset on, a ring of 16 published tile indices (8 bytes each) per cluster.
+constexpr size_t kGemmSchedulerOffset = 4096;
+constexpr size_t kGemmRingOffset      = 4096 + 512;
+constexpr size_t kGemmRingSlots       = 16;
 
 // ---- full reductions (Device::sum / Device::max, aixDevice.hpp:52,60) -----------------------------------------
 // dst[0] = sum or max of all elements of src, in src's element type.

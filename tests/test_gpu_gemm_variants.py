@@ -1,5 +1,6 @@
 """The tensor-core matmul has switches that select its fallback and experimental paths (single-CTA kernel, 2-D TMA boxes,
-row-per-thread epilogue, remainder wave shared along K, the TF32 + bf16 form of the f32 product). They are read once per process, so each variant runs in a child
+row-per-thread epilogue, remainder wave shared along K, the TF32 + bf16 form of the f32 product, tiles dealt out at run time,
+products launched by their own call). They are read once per process, so each variant runs in a child
 process on the same parity shapes (ragged M/N/K, transposed operands, bf16 and f32)."""
 import json
 import os
@@ -18,6 +19,8 @@ VARIANTS = {
     "shared_remainder_wave": {"AIXB200_GEMM_SPLITK": "1"},
     "narrow_tiles": {"AIXB200_GEMM_BLOCKN": "128"},
     "f32_tf32_hybrid": {"AIXB200_GEMM_F32": "hybrid"},
+    "tiles_dealt_at_run_time": {"AIXB200_GEMM_DYNAMIC": "1"},
+    "no_folded_epilogue": {"AIXB200_GEMM_EPILOGUE": "0"},
 }
 
 
