@@ -1039,9 +1039,10 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
     d.va = inputView(a, "matmul"); d.vb = inputView(b, "matmul");
     d.vr = outputView(r, "matmul");
     flush();
-    if (dryRun() || d.vr.size == 0) return;
+    if (d.vr.size == 0) return;
     // Products whose consumers the kernel can fold wait for the ops that follow (see DeferredMatmul). Operands staged from
-    // host memory live only until the next call, so those products are launched at once.
+    // host memory live only until the next call, so those products are launched at once. A dry-run device goes through
+    // the same decisions (and counts what it would have folded) without launching anything.
     if (m_foldMatmulEpilogue && m_staged.empty() && d.vr.isDense())
     {
         gemm::Problem probe{};
@@ -1049,13 +1050,21 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
         probe.m = a->shape[0]; probe.k = a->shape[1]; probe.n = b->shape[1];
         probe.c = d.vr.firstByte();
         probe.splitF32 = m_cfg.tf32x3_matmul != 0;
-        if (gemm::canFoldEpilogue(probe)) { m_deferred = d; m_deferred.active = true; return; }
+        if (gemm::canFoldEpilogue(probe, !dryRun())) { m_deferred = d; m_deferred.active = true; return; }
     }
+    if (dryRun()) return;
     launchMatmul(d, 0);
 }
 
 void Device::launchMatmul(const DeferredMatmul& d, int folded)
 {
+    if (dryRun())
+    {
+        if (folded == 2) m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(d.tanhIndex));
+        if (folded >= 1) m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(d.addIndex));
+        m_stats.matmul_consumers_folded += static_cast<uint64_t>(folded);
+        return;
+    }
     const uint64_t m = d.a.shape[0], k = d.a.shape[1], n = d.b.shape[1];
     AIXB200_CTX();
     gemm::Problem p{};

@@ -34,7 +34,8 @@ struct Problem
 };
 
 // Whether launchTensorCore would fold the problem's consumers (pointers, shape and element type decide; operands do not).
-bool canFoldEpilogue(const Problem& problem);
+// needDriver = false leaves out the check that the driver's tensor-map encoder can be reached (dry-run devices).
+bool canFoldEpilogue(const Problem& problem, bool needDriver = true);
 
 // Runs the problem on the tensor cores when its element type, shape and alignment allow it.
 // Returns false (having launched nothing) when the caller must use the CUDA-core kernel instead.

@@ -1686,7 +1686,7 @@ void launchBoundedWaitSelfTest(const kernels::LaunchContext& ctx, uint64_t limit
 
 // The conditions under which launchTensorCore takes the three-fp16-pass CTA-pair kernel with TMA stores - the one whose
 // epilogue can fold a bias add and a tanh. Kept in step with the choices made there.
-bool canFoldEpilogue(const Problem& q)
+bool canFoldEpilogue(const Problem& q, bool needDriver)
 {
     static const bool enabled = []{ const char* v = std::getenv("AIXB200_GEMM_EPILOGUE"); return !(v && v[0] == '0'); }();
     static const bool tensorCoreOff = std::getenv("AIXB200_NO_TENSOR_CORE") != nullptr;
@@ -1700,7 +1700,7 @@ bool canFoldEpilogue(const Problem& q)
     if ((q.n * 4) % 16 != 0) return false;
     for (const void* ptr : {static_cast<const void*>(q.c), static_cast<const void*>(q.bias), static_cast<const void*>(q.biasOut), static_cast<const void*>(q.tanhOut)})
         if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return false;
-    return encodeTiled() != nullptr;
+    return !needDriver || encodeTiled() != nullptr;
 }
 
 bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const Problem& q)
@@ -1716,7 +1716,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
     // CTA pairs (256 x 256 tiles) unless switched off or the problem has a single row of 128-row tiles.
     static const bool pairEnabled = []{ const char* v = std::getenv("AIXB200_GEMM_PAIR"); return !(v && v[0] == '0'); }();
     const bool pair = pairEnabled && q.m > 128;
-    if (q.bias && !canFoldEpilogue(q)) return false;
+    if (q.bias && !canFoldEpilogue(q, true)) return false;
     KernelParams p{};
     p.m = static_cast<uint32_t>(q.m); p.n = static_cast<uint32_t>(q.n); p.k = static_cast<uint32_t>(q.k);
     p.tilesM = pair ? (p.m + 255) / 256 : (p.m + kBlockM - 1) / kBlockM;
