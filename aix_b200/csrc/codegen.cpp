@@ -408,7 +408,7 @@ std::string kernelKey(const KernelSpec& spec, const KernelVariant& variant, cons
     std::string key;
     key.reserve(64 + spec.nodes.size() * 12);
     auto put = [&](unsigned x) { key += std::to_string(x); key += '.'; };
-    key += "E"; put(variant.vec); put(variant.packed16); put(variant.index64); put(options.block); put(options.unroll); put(options.strictMath);
+    key += "E"; put(variant.vec); put(variant.packed16); put(variant.index64); put(options.block); put(options.unroll); put(options.strictMath); put(options.rowMinBlocks);
     key += "L";
     for (size_t i = 0; i < spec.loads.size(); ++i)
     {
@@ -613,7 +613,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         }
     };
 
-    o << "extern \"C\" __global__ void __launch_bounds__(" << B << ") " << entryName
+    o << "extern \"C\" __global__ void __launch_bounds__(" << B << ((variant.rowMode && options.rowMinBlocks > 0) ? ", " + std::to_string(options.rowMinBlocks) : std::string()) << ") " << entryName
       << "(const __grid_constant__ Params p)\n{\n";
     o << "    const idx_t n = (idx_t)" << arg(slotCount) << ";\n";
     for (size_t i = 0; i < nL; ++i)

@@ -21,6 +21,7 @@ struct CodegenOptions
     bool strictMath = true;   // reported in the key only; the compile flags are chosen by the caller
     int  block      = 256;    // threads per CTA
     int  unroll     = 2;      // packs in flight per thread
+    int  rowMinBlocks = 0;    // row-form kernels: CTAs per SM asked for in __launch_bounds__ (0: left to the compiler)
 };
 
 // Everything that selects a distinct kernel for one KernelSpec at launch time.

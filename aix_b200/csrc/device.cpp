@@ -93,13 +93,17 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_codegen.strictMath = m_cfg.strict_math != 0;
     m_codegen.block = envInt("AIXB200_EW_BLOCK", 256);
     m_codegen.unroll = std::max(1, std::min(8, envInt("AIXB200_EW_UNROLL", 2)));
+    m_codegen.rowMinBlocks = std::max(0, std::min(8, envInt("AIXB200_ROW_MIN_BLOCKS", 0)));
     m_wavesPerSm = std::max(1, envInt("AIXB200_EW_WAVES", 8));
     m_fuseReductions = envInt("AIXB200_FUSE_REDUCTIONS", 1) != 0;
     m_fuseRowReductions = envInt("AIXB200_FUSE_ROW_REDUCTIONS", 1) != 0;
     m_termCacheEnabled = envInt("AIXB200_GEMM_TERM_CACHE", 1) != 0;
     m_keepIdleFills = envInt("AIXB200_KEEP_IDLE_FILLS", 1) != 0;
     m_fuseOperandMax = envInt("AIXB200_FUSE_OPERAND_MAX", 1) != 0;
-    m_foldMatmulEpilogue = envInt("AIXB200_GEMM_EPILOGUE", 1) != 0 && m_cfg.strict_math == 0 && m_cfg.fusion != 0;
+    // 0: every product is launched by its own call; 1 (default): `+ row vector` may be folded; 2: its tanh as well (measured
+    // slower than the separate kernel: see launchDeferredMatmul)
+    m_foldDepth = std::max(0, std::min(2, envInt("AIXB200_GEMM_EPILOGUE", 1)));
+    m_foldMatmulEpilogue = m_foldDepth != 0 && m_cfg.strict_math == 0 && m_cfg.fusion != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -1105,7 +1109,7 @@ void Device::launchMatmul(const DeferredMatmul& d, int folded)
     }
 }
 
-void Device::launchDeferredMatmul()
+void Device::launchDeferredMatmul(bool consumerRecorded)
 {
     const DeferredMatmul d = m_deferred;
     m_deferred = DeferredMatmul{};
@@ -1113,7 +1117,9 @@ void Device::launchDeferredMatmul()
     // deallocated and no other recorded op touching it. Measured on B200 (4096 x 4096 outputs): the product alone 83 us (K =
     // 1024); product, then add + tanh as a generated kernel 117 us; all three results written by the product's epilogue 135 us -
     // every CTA finishes its tile at the same moment, and a burst of three tiles per CTA cannot drain while the tensor
-    // cores run the two chunks of K ahead that TMEM has room for. With one output the epilogue costs what it always did.
+    // cores run the two chunks of K ahead that TMEM has room for. The tanh is not folded by default either (m_foldDepth):
+    // with product and sum dead the separate kernel only reads one matrix and writes one (106.6 us for both launches),
+    // while eight epilogue warps need about 5000 instructions per thread and tile for bias, tanh and the maximum (117.3 us).
     auto dead = [&](const View& v, size_t skipA, size_t skipB)
     {
         if (!m_released.count(v.base)) return false;
@@ -1126,7 +1132,11 @@ void Device::launchDeferredMatmul()
         }
         return true;
     };
+    // And the add alone is folded only when nothing recorded consumes the sum: a recorded consumer would run in one generated
+    // kernel together with the add anyway, so folding saves no pass over memory there, while the folding instantiation is a
+    // few microseconds slower than the plain one (98 against 83 us at K = 1024; 105 us for product + add kernel).
     int folded = d.folded;
+    if (m_foldDepth < 2 && (folded == 2 || consumerRecorded)) folded = 0;
     if (folded == 2 && !dead(d.biasOut, d.addIndex, d.tanhIndex)) folded = 1;
     if (folded >= 1 && !dead(d.vr, d.addIndex, d.addIndex)) folded = 0;
     launchMatmul(d, folded);
@@ -1193,7 +1203,7 @@ void Device::advanceDeferredMatmul(size_t index)
     {
         // both consumers are candidates; the call that recorded the tanh still held the sum, which is why the product was not
         // launched there and then: whether the sum is dead shows once that call has returned
-        if (touches(op, d.tanhOut) || touches(op, d.biasOut)) launchDeferredMatmul();
+        if (touches(op, d.tanhOut) || touches(op, d.biasOut)) launchDeferredMatmul(true);
         return;
     }
     if (!touches(op, d.biasOut)) return;
@@ -1205,7 +1215,7 @@ void Device::advanceDeferredMatmul(size_t index)
         d.tanhOut = op.out;
         return;
     }
-    launchDeferredMatmul();
+    launchDeferredMatmul(true);
 }
 
 void Device::transpose(const aixb200_tensor* a, const aixb200_tensor* r, size_t dim0, size_t dim1)

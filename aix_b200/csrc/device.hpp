@@ -176,8 +176,9 @@ private:
     };
     DeferredMatmul m_deferred;
     bool m_foldMatmulEpilogue = true;           // AIXB200_GEMM_EPILOGUE=0: every product is launched by its own call
+    int  m_foldDepth = 1;                       // consumers folded at most: 1 = the add, 2 = the add and its tanh (AIXB200_GEMM_EPILOGUE=2)
     void advanceDeferredMatmul(size_t index);   // looks at the op just recorded at m_pending[index]
-    void launchDeferredMatmul();
+    void launchDeferredMatmul(bool consumerRecorded = false);   // consumerRecorded: a recorded op that reads the sum ended the wait
     void launchMatmul(const DeferredMatmul& d, int folded);
     void launchSpec(const KernelSpec& spec);
     CompiledKernel& getKernel(const KernelSpec& spec, const KernelVariant& variant, const std::string& key);

@@ -892,8 +892,8 @@ __device__ __forceinline__ float epilogueTanh(float x)
 
 // Mode 0: 16-bit operands, one pass. Mode 1: f32 as a TF32 main pass plus two bf16 cross-term passes. Mode 2: f32 as three
 // fp16 passes over two-term operands - every pass is a 16-bit pass, so nothing in the issue loops depends on the pass.
-// Mode 3: mode 2 with elementwise consumers folded into the epilogue (an instantiation of its own, so that the plain
-// product keeps its register allocation).
+// Modes 3 and 4: mode 2 with elementwise consumers folded into the epilogue - the bias add (3), and its tanh as well (4);
+// instantiations of their own, so that the plain product and the add-only form keep their register allocation.
 template <int Mode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Mode >= 2 ? kThreadsHalfTerms : kThreads, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA16,
@@ -902,7 +902,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 {
     constexpr bool Tf32 = Mode != 0;
     constexpr bool HalfTerms = Mode >= 2;
-    constexpr bool Fold = Mode == 3;             // bias / tanh consumers folded into the epilogue
+    constexpr bool Fold = Mode >= 3;             // consumers folded into the epilogue: the bias add (3), and its tanh (4)
+    constexpr bool FoldTanh = Mode == 4;
     extern __shared__ uint8_t rawSmem[];
     PairStorage& s = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1145,7 +1146,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                                 sum[strip * 32 + 4 * v + 2] += bv.z; sum[strip * 32 + 4 * v + 3] += bv.w;
                             }
                             if (outputs & 2u) stageAndStore(&mapC1);
-                            if (outputs & 4u)
+                            if constexpr (FoldTanh) if (outputs & 4u)
                             {
                                 #pragma unroll
                                 for (uint32_t i = 0; i < 32; ++i) sum[strip * 32 + i] = epilogueTanh(sum[strip * 32 + i]);
@@ -1973,6 +1974,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             cudaFuncSetAttribute(gemmPairKernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaFuncSetAttribute(gemmPairKernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaFuncSetAttribute(gemmPairKernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
+            cudaFuncSetAttribute(gemmPairKernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairSmem));
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(static_cast<unsigned>(ctx.smCount) & ~1u);
             cfg.blockDim = dim3(kThreads);
@@ -2065,6 +2067,7 @@ bool launchTensorCore(Device& device, const kernels::LaunchContext& ctx, const P
             if (q.maxSlot && cudaMemsetAsync(q.maxSlot, 0, 4, ctx.stream) != cudaSuccess) return false;
         }
         if (!tf32)            gemmPairKernel<0><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
+        else if (p.halfTerms && q.tanhOut) gemmPairKernel<4><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
         else if (p.halfTerms && q.bias) gemmPairKernel<3><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
         else if (p.halfTerms) gemmPairKernel<2><<<2 * clusters, kThreadsHalfTerms, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);
         else                  gemmPairKernel<1><<<2 * clusters, kThreads, pairSmem, ctx.stream>>>(mapA, mapB, mapA16, mapB16, mapC, mapC1, mapC2, p);

@@ -296,6 +296,17 @@ def build_case(dev, case):
         k = 1024 if case.endswith("k1024") else 4096
         a, b = _rand(dev, (4096, k), dt, 0, 0.05), _rand(dev, (k, 4096), dt, 1, 0.05)
         return lambda: a.matmul(b)
+    if case in ("linear_values_f32_k1024", "linear_values_f32_k4096"):
+        # matmul(x, W) + b on tensor values: the product is a temporary, so the add runs in its epilogue and only the sum is written
+        k = 1024 if case.endswith("k1024") else 4096
+        x, w, b = _rand(dev, (4096, k), C.F32, 0), _rand(dev, (k, 4096), C.F32, 1, 0.05), _rand(dev, (1, 4096), C.F32, 2, 0.1)
+        return lambda: x.matmul(w) + b
+    if case in ("linear_tanh_values_f32_k1024", "linear_tanh_values_f32_k4096"):
+        # the same layer on tensor values, product and sum dropped as temporaries: the add runs in the product's epilogue, and
+        # with AIXB200_GEMM_EPILOGUE=2 the tanh too
+        k = 1024 if case.endswith("k1024") else 4096
+        x, w, b = _rand(dev, (4096, k), C.F32, 0), _rand(dev, (k, 4096), C.F32, 1, 0.05), _rand(dev, (1, 4096), C.F32, 2, 0.1)
+        return lambda: (x.matmul(w) + b).tanh()
     if case in ("linear_tanh_f32_k1024", "linear_tanh_f32_k4096"):
         # one hidden layer of the MLP as the front end issues it: matmul(x, W) + b, then tanh, all three results kept
         # (autograd holds them); with AIXB200_GEMM_EPILOGUE=0 the add and the tanh run as a generated kernel of their own
@@ -318,6 +329,13 @@ def build_case(dev, case):
         if case.endswith("_nt"): return lambda: a.matmul(b.transpose(0, 1))
         if case.endswith("_tn"): return lambda: a.transpose(0, 1).matmul(b)
         return lambda: a.matmul(b)
+    if case in ("transpose_f32_5000", "tril_f32_5000"):
+        # two of the data-movement virtuals at the size of the reference's device benchmarks
+        sq = _rand(dev, (5000, 5000), C.F32, 0)
+        out = TensorValue.empty((5000, 5000), dev)
+        if case.startswith("transpose"):
+            return lambda: dev.transpose(sq.deviceParams(), out.deviceParams(), 0, 1)
+        return lambda: dev.tril(sq.deviceParams(), out.deviceParams(), 0)
     if case == "adam_f32":
         p, g, m, v = (_rand(dev, (1 << 16, 1024), C.F32, s) for s in range(4))
 

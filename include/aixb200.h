@@ -174,10 +174,10 @@ int aixb200_argmax_indices_to(aixb200_device* dev, const aixb200_tensor* src, co
  * terms, so rows and columns that the CPU device would still compute finitely can come out infinite or NaN as well.
  * Operands with non-finite elements that must keep their finite part exact need tf32x3_matmul = 0.
  * An f32 product on the tensor cores may be launched later than this call returns - at the latest by the next call that
- * is not a recorded elementwise op: `result + row vector` (nn::Linear's bias, aixNeuralNetwork.hpp:150-153) and the tanh
- * of that sum, when they are the next ops recorded and the values they consume are already deallocated, run inside the
- * product's kernel, which then writes only the last of the three. Results and program order are those of separate
- * launches; AIXB200_GEMM_EPILOGUE=0 in the environment launches every product from its own call. */
+ * is not a recorded elementwise op: `result + row vector` (nn::Linear's bias, aixNeuralNetwork.hpp:150-153), when it is
+ * the next op recorded, `result` is already deallocated and no recorded op consumes the sum, runs inside the product's
+ * kernel, which then writes only the sum. Results and program order are those of separate launches;
+ * AIXB200_GEMM_EPILOGUE=0 in the environment launches every product from its own call, =2 folds a following tanh too. */
 int aixb200_matmul(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* result);
 
 /* ---- data movement (aixDevice.hpp:64-69, 74-81) ---- */

@@ -5,12 +5,30 @@ dropped): the kernel then writes one output instead of up to three. Every result
 give (same product, same add, same tanh routine), values that are kept alive must still be written, and program order
 must hold for ops recorded while the product waits.
 """
+import os
+
 import numpy as np
 import pytest
 
-from aix_b200 import F32, TensorValue
+from aix_b200 import F32, DeviceB200, TensorValue
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def deep():
+    """A second handle on the same GPU that folds the tanh as well: AIXB200_GEMM_EPILOGUE=2, read when a device is created.
+    The default (1) folds the add only - measured, the tanh is cheaper as a kernel of its own."""
+    old = os.environ.get("AIXB200_GEMM_EPILOGUE")
+    os.environ["AIXB200_GEMM_EPILOGUE"] = "2"
+    try:
+        dev = DeviceB200(0)
+    finally:
+        if old is None: os.environ.pop("AIXB200_GEMM_EPILOGUE")
+        else: os.environ["AIXB200_GEMM_EPILOGUE"] = old
+    yield dev
+    dev.synchronize()
+    dev.close()
 
 
 def folded(b200):
@@ -37,7 +55,8 @@ def separate(b200, tx, tw, tb):
 
 
 @pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 256, 384), (300, 100, 200), (1024, 1024, 1024), (257, 64, 68), (4096, 320, 512)])
-def test_linear_tanh_is_one_launch_with_the_bits_of_three(b200, ref, m, k, n):
+def test_linear_tanh_is_one_launch_with_the_bits_of_three(deep, ref, m, k, n):
+    b200 = deep
     x, w, b, tx, tw, tb = operands(b200, m, k, n, m + n)
     want_mm, want_s, want_t = separate(b200, tx, tw, tb)
     before, launches = folded(b200), b200.stats()["total_kernel_launches"]
@@ -64,7 +83,31 @@ def test_linear_tanh_is_one_launch_with_the_bits_of_three(b200, ref, m, k, n):
     assert np.array_equal(mm.numpy(), want_mm) and np.array_equal(s.numpy(), want_s) and np.array_equal(t.numpy(), want_t)
 
 
-def test_bias_on_the_left_and_bias_only(b200):
+def test_by_default_the_add_is_folded_when_no_recorded_op_consumes_the_sum(b200):
+    """Measured: a recorded consumer runs in one generated kernel together with the add, so folding the add there saves no
+    pass over memory; folding pays when the sum goes straight to a matmul, a reduction kernel or the host."""
+    x, w, b, tx, tw, tb = operands(b200, 512, 256, 384, 11)
+    want_mm, want_s, want_t = separate(b200, tx, tw, tb)
+    before, launches = folded(b200), b200.stats()["total_kernel_launches"]
+    t = (tx.matmul(tw) + tb).tanh()
+    b200.synchronize()
+    assert folded(b200) == before
+    assert b200.stats()["total_kernel_launches"] - launches == 2, "the product, then add + tanh as one generated kernel"
+    assert np.array_equal(t.numpy(), want_t)
+    before, launches = folded(b200), b200.stats()["total_kernel_launches"]
+    s = tx.matmul(tw) + tb
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert b200.stats()["total_kernel_launches"] - launches == 1
+    assert np.array_equal(s.numpy(), want_s)
+    before = folded(b200)
+    y = (tx.matmul(tw) + tb).matmul(TensorValue.from_numpy(np.eye(384, dtype=np.float32), b200))      # straight into the next product
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.max(np.abs(y.numpy() - want_s)) <= 1e-5 * np.max(np.abs(want_s))
+
+
+def test_bias_on_the_left_and_bias_only(b200, deep):
     x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 5)
     want_mm, want_s, want_t = separate(b200, tx, tw, tb)
     before = folded(b200)
@@ -72,6 +115,8 @@ def test_bias_on_the_left_and_bias_only(b200):
     b200.synchronize()
     assert folded(b200) == before + 1
     assert np.array_equal(s.numpy(), want_s)
+    b200 = deep
+    x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 5)
     before = folded(b200)
     s = tx.matmul(tw) + tb
     u = s * 2.0                         # the sum's first consumer is not a tanh: the product is launched with the add folded
@@ -122,7 +167,8 @@ def test_other_first_consumers_leave_the_product_alone(b200):
     assert np.array_equal(e.numpy(), want_mm * np.float32(0.5)) and np.array_equal(t.numpy(), want_t)
 
 
-def test_program_order_around_a_waiting_product(b200):
+def test_program_order_around_a_waiting_product(deep):
+    b200 = deep
     x, w, b, tx, tw, tb = operands(b200, 512, 128, 256, 7)
     want_mm, want_s, want_t = separate(b200, tx, tw, tb)
     bias = TensorValue.from_numpy(b, b200)
@@ -168,24 +214,28 @@ def test_program_order_around_a_waiting_product(b200):
     assert abs(float(total.numpy()) - want_s.astype(np.float64).sum()) <= 1e-5 * np.abs(want_s).sum()
 
 
-def test_the_next_product_finds_the_maximum_the_epilogue_left(b200):
-    """Two layers: the second product's left operand is the first one's tanh output; its max|x| comes from the first
+@pytest.mark.parametrize("with_tanh", [False, True], ids=["sum", "tanh"])
+def test_the_next_product_finds_the_maximum_the_epilogue_left(b200, deep, with_tanh):
+    """Two layers: the second product's left operand is the first one's folded output; its max|x| comes from the first
     product's epilogue once the size is known as an operand size (from the second step on)."""
+    dev = deep if with_tanh else b200
     rng = np.random.default_rng(9)
     m, k = 1024, 1024
-    x = TensorValue.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32), b200)
-    w1 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), b200)
-    w2 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), b200)
-    b1 = TensorValue.from_numpy(rng.normal(0, 0.5, (1, k)).astype(np.float32), b200)
+    x = TensorValue.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32), dev)
+    w1 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), dev)
+    w2 = TensorValue.from_numpy((rng.normal(0, 1, (k, k)) / 32).astype(np.float32), dev)
+    b1 = TensorValue.from_numpy(rng.normal(0, 0.5, (1, k)).astype(np.float32), dev)
     results = []
     for step in range(3):
-        known = b200.stats()["prepared_operand_max_known"]
-        h = (x.matmul(w1) + b1).tanh()
+        known, before = dev.stats()["prepared_operand_max_known"], folded(dev)
+        h = (x.matmul(w1) + b1).tanh() if with_tanh else x.matmul(w1) + b1
         y = h.matmul(w2)
-        b200.synchronize()
-        results.append((h.numpy(), y.numpy(), b200.stats()["prepared_operand_max_known"] - known))
-    assert results[2][2] >= 1, "the tanh output's maximum was left by the epilogue"
-    exact_h = np.tanh(x.numpy().astype(np.float64) @ w1.numpy().astype(np.float64) + b1.numpy().astype(np.float64))
+        dev.synchronize()
+        assert folded(dev) == before + (2 if with_tanh else 1)
+        results.append((h.numpy(), y.numpy(), dev.stats()["prepared_operand_max_known"] - known))
+    assert results[2][2] >= 1, "the folded output's maximum was left by the epilogue"
+    exact_h = x.numpy().astype(np.float64) @ w1.numpy().astype(np.float64) + b1.numpy().astype(np.float64)
+    if with_tanh: exact_h = np.tanh(exact_h)
     exact_y = exact_h @ w2.numpy().astype(np.float64)
     for h, y, _ in results:
         assert np.array_equal(h, results[0][0])

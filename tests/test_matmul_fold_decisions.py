@@ -2,9 +2,27 @@
 launched; the device counts what it would have folded). nn::Linear is matmul(x, W) + b followed by tanh
 (aixNeuralNetwork.hpp:150-153): the add and the tanh are folded as far as the values they consume are dead, so that the
 product's kernel is left with one output; values that stay alive keep their own kernels."""
-import numpy as np
+import os
 
-from aix_b200 import F32, TensorValue
+import numpy as np
+import pytest
+
+from aix_b200 import F32, DeviceB200, TensorValue
+
+
+@pytest.fixture(scope="module")
+def deep():
+    """A dry-run device that folds the tanh as well (AIXB200_GEMM_EPILOGUE=2, read when a device is created; the default
+    folds the add only)."""
+    old = os.environ.get("AIXB200_GEMM_EPILOGUE")
+    os.environ["AIXB200_GEMM_EPILOGUE"] = "2"
+    try:
+        dev = DeviceB200(0, dry_run=1, disk_cache=0)
+    finally:
+        if old is None: os.environ.pop("AIXB200_GEMM_EPILOGUE")
+        else: os.environ["AIXB200_GEMM_EPILOGUE"] = old
+    yield dev
+    dev.close()
 
 
 def run(dry, body):
@@ -23,7 +41,18 @@ def operands(dry, m=256, k=128, n=256):
     return x, w, b
 
 
-def test_dead_intermediates_are_folded_and_live_ones_are_not(dry):
+def test_by_default_the_add_is_folded_when_no_recorded_op_consumes_the_sum(dry):
+    x, w, b = operands(dry)
+    d = run(dry, lambda: (x.matmul(w) + b).tanh())
+    assert d["matmul_consumers_folded"] == 0 and d["fused_kernels"] == 1, d        # the product, then add + tanh as one kernel
+    d = run(dry, lambda: x.matmul(w) + b)
+    assert d["matmul_consumers_folded"] == 1 and d["fused_kernels"] == 0, d        # nothing recorded consumes the sum
+    d = run(dry, lambda: (x.matmul(w) + b).matmul(w.transpose(0, 1)))
+    assert d["matmul_consumers_folded"] == 1 and d["fused_kernels"] == 0, d        # straight into the next product
+
+
+def test_dead_intermediates_are_folded_and_live_ones_are_not(deep):
+    dry = deep
     x, w, b = operands(dry)
     d = run(dry, lambda: (x.matmul(w) + b).tanh())
     assert d["matmul_consumers_folded"] == 2 and d["fused_kernels"] == 0, d        # one product, nothing else
@@ -42,7 +71,8 @@ def test_dead_intermediates_are_folded_and_live_ones_are_not(dry):
     assert d["matmul_consumers_folded"] == 1 and d["fused_kernels"] == 1, d        # the tanh keeps its kernel
 
 
-def test_what_does_not_match_is_left_alone(dry):
+def test_what_does_not_match_is_left_alone(deep):
+    dry = deep
     x, w, b = operands(dry)
     full = TensorValue.full(0.1, (256, 256), dry)
     column = TensorValue.full(0.1, (256, 1), dry)
@@ -68,7 +98,8 @@ def test_what_does_not_match_is_left_alone(dry):
     assert run(dry, product_read_again)["matmul_consumers_folded"] == 0
 
 
-def test_ops_recorded_while_the_product_waits_do_not_end_the_wait(dry):
+def test_ops_recorded_while_the_product_waits_do_not_end_the_wait(deep):
+    dry = deep
     x, w, b = operands(dry)
 
     def with_bystanders():
