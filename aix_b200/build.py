@@ -53,8 +53,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("compilation failed")
     if procs or force or not os.path.isfile(OUT):
-        cmd = [NVCC, "-shared", "-o", OUT] + objects + ["-cudart", "static", "-lnvrtc", "-ldl", "-lpthread"]
+        # linked beside the target and renamed into place: a reader never sees a half-written library
+        cmd = [NVCC, "-shared", "-o", OUT + ".tmp"] + objects + ["-cudart", "static", "-lnvrtc", "-ldl", "-lpthread"]
         subprocess.run(cmd, check=True)
+        os.replace(OUT + ".tmp", OUT)
     return OUT
 
 

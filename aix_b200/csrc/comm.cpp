@@ -25,6 +25,8 @@ enum { kNcclSum = 0, kNcclAvg = 4 };
 enum { kNcclSuccess = 0, kNcclRemoteError = 6, kNcclInProgress = 7 };
 enum { kNcclInt32 = 2, kNcclInt64 = 4, kNcclHalf = 6, kNcclFloat = 7, kNcclDouble = 8, kNcclBfloat16 = 9 };
 
+constexpr int kDefaultMaxCtas = 0;       // see Comm::Comm
+
 struct NcclApi
 {
     int (*getUniqueId)(NcclUniqueId*) = nullptr;
@@ -155,12 +157,28 @@ Comm::Comm(int rank, int nranks, const void* id128, int ordinal) : m_rank(rank),
         return;
     }
 #endif
+#ifdef AIXB200_HAVE_NCCL_CONFIG
+    // AIXB200_COMM_MAX_CTAS: upper bound on the CTAs a collective's kernel may use. The collectives of the overlapped
+    // exchange share the GPU with the matmuls of backward(); every SM they hold is one the persistent matmul grid cannot
+    // start a CTA on. 0 leaves NCCL's own choice.
+    const char* ctas = std::getenv("AIXB200_COMM_MAX_CTAS");
+    const int maxCtas = (ctas && *ctas) ? std::atoi(ctas) : kDefaultMaxCtas;
+    if (maxCtas > 0 && nccl().commInitRankConfig && !backendInjected())
+    {
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.blocking = 1;
+        config.maxCTAs = maxCtas;
+        config.minCTAs = 1;
+        checkNccl(nccl().commInitRankConfig(&comm, nranks, id, rank, &config), "ncclCommInitRankConfig");
+    }
+    else
+#endif
     checkNccl(nccl().commInitRank(&comm, nranks, id, rank), "ncclCommInitRank");
     m_comm = comm;
-    // A second communicator over the same ranks for the all-gathers of a sharded optimizer (see allGather). Every rank
-    // decides the same way: same library, same environment.
+    // AIXB200_COMM_GATHER_LANE=1: a second communicator over the same ranks for the all-gathers of a sharded optimizer (see
+    // allGather). Every rank decides the same way: same library, same environment.
     const char* lane = std::getenv("AIXB200_COMM_GATHER_LANE");
-    if (nranks > 1 && !backendInjected() && nccl().commSplit && !(lane && lane[0] == '0'))
+    if (nranks > 1 && !backendInjected() && nccl().commSplit && lane && lane[0] == '1')
     {
         NcclComm second = nullptr;
         checkNccl(nccl().commSplit(m_comm, 0, rank, &second, nullptr), "ncclCommSplit");

@@ -542,10 +542,37 @@ template <int DT> void launchTranspose(const LaunchContext& ctx, const void* src
     }
     transposeKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), count, sc, ds, d0, d1);
 }
+// sliceSet between dense tensors: element i of the source is (outer, j, w) with w running over the dimensions behind the
+// sliced one; it lands at ((outer * extent + start + j * step) * inner + w) - two divisions in the narrowest index type
+// instead of a mixed-radix walk over both layouts.
+template <class S, class I>
+__global__ void __launch_bounds__(kBlock) sliceSetDenseKernel(const S* __restrict__ src, S* __restrict__ dst, I count, I inner, I sliceExtent,
+                                                              uint64_t dimExtent, uint64_t start, uint64_t step)
+{
+    for (I i = static_cast<I>(blockIdx.x) * kBlock + threadIdx.x; i < count; i += static_cast<I>(gridDim.x) * kBlock)
+    {
+        const I q = i / inner, w = i - q * inner, outer = q / sliceExtent, j = q - outer * sliceExtent;
+        dst[(static_cast<uint64_t>(outer) * dimExtent + start + static_cast<uint64_t>(j) * step) * inner + w] = src[i];
+    }
+}
+
 template <int DT> void launchSliceSet(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
                                       int dim, uint64_t start, uint64_t step, uint64_t sliceExtent)
 {
     typedef typename Elem<DT>::S S;
+    if (count >= 4096 && sliceExtent > 0 && isCanonical(sl, sl.shape) && isCanonical(dl, dl.shape))
+    {
+        uint64_t inner = 1;
+        for (int d = dim + 1; d < dl.rank; ++d) inner *= dl.shape[d];
+        const unsigned grid = static_cast<unsigned>(std::min<uint64_t>((count + kBlock - 1) / kBlock, static_cast<uint64_t>(ctx.smCount) * 32));
+        if (count < (uint64_t(1) << 32))
+            sliceSetDenseKernel<S, uint32_t><<<grid, kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), static_cast<uint32_t>(count),
+                                                                             static_cast<uint32_t>(inner), static_cast<uint32_t>(sliceExtent), dl.shape[dim], start, step);
+        else
+            sliceSetDenseKernel<S, uint64_t><<<grid, kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), count, inner, sliceExtent,
+                                                                             dl.shape[dim], start, step);
+        return;
+    }
     sliceSetKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, dim, start, step, sliceExtent);
 }
 template <int DT> void launchTriangle(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const Layout& dl, uint64_t count,
@@ -563,10 +590,48 @@ template <int DT> void launchTriangle(const LaunchContext& ctx, const void* src,
     }
     triangleKernel<S><<<gridFor(count, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), dl, count, rows, cols, diagonal, lower);
 }
+// indexSelect from a dense source with a dense index list: every selected slice is one contiguous run of `runLength` units
+// (16-byte packs when the slices allow it, elements otherwise), copied by the threads of a CTA side by side; a CTA takes
+// the runs blockIdx.y, blockIdx.y + gridDim.y, ... One index load per run instead of two mixed-radix decompositions per element.
+template <class V>
+__global__ void __launch_bounds__(kBlock) indexSelectRunsKernel(const V* __restrict__ src, V* __restrict__ dst, const int32_t* __restrict__ indices,
+                                                                uint64_t indexCount, uint64_t runLength, uint64_t extent, uint64_t runs, uint32_t* badIndex)
+{
+    for (uint64_t run = blockIdx.y; run < runs; run += gridDim.y)
+    {
+        const uint64_t outer = run / indexCount;
+        const int64_t index = indices[run - outer * indexCount];
+        if (index < 0 || static_cast<uint64_t>(index) >= extent)
+        {
+            if (threadIdx.x == 0 && blockIdx.x == 0) *badIndex = 1u;
+            continue;
+        }
+        const V* from = src + (outer * extent + static_cast<uint64_t>(index)) * runLength;
+        V* to = dst + run * runLength;
+        for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBlock + threadIdx.x; i < runLength; i += static_cast<uint64_t>(gridDim.x) * kBlock) to[i] = from[i];
+    }
+}
+
 template <int DT> void launchIndexSelect(const LaunchContext& ctx, const void* src, const Layout& sl, void* dst, const int32_t* indices,
                                          const Layout& il, uint64_t indexCount, uint64_t sliceSize, uint64_t dimSize, uint64_t dstCount)
 {
     typedef typename Elem<DT>::S S;
+    const bool denseIndices = il.rank == 0 || (il.rank == 1 && (il.strides[0] == 1 || il.shape[0] == 1));
+    if (denseIndices && sliceSize >= 32 && indexCount > 0 && dstCount >= 4096 && isCanonical(sl, sl.shape))
+    {
+        const uint64_t extent = dimSize / sliceSize, runs = dstCount / sliceSize;
+        const bool packs = (sliceSize * sizeof(S)) % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+        const uint64_t runLength = packs ? sliceSize * sizeof(S) / 16 : sliceSize;
+        const dim3 grid(static_cast<unsigned>(std::min<uint64_t>((runLength + kBlock - 1) / kBlock, 16)),
+                        static_cast<unsigned>(std::min<uint64_t>(runs, static_cast<uint64_t>(ctx.smCount) * 32)));
+        if (packs)
+            indexSelectRunsKernel<uint4><<<grid, kBlock, 0, ctx.stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), indices, indexCount,
+                                                                         runLength, extent, runs, badIndexWord(ctx));
+        else
+            indexSelectRunsKernel<S><<<grid, kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), static_cast<S*>(dst), indices, indexCount, runLength, extent,
+                                                                     runs, badIndexWord(ctx));
+        return;
+    }
     indexSelectKernel<S><<<gridFor(dstCount, ctx.smCount), kBlock, 0, ctx.stream>>>(static_cast<const S*>(src), sl, static_cast<S*>(dst), indices, il,
                                                                                    indexCount, sliceSize, dimSize, dstCount, badIndexWord(ctx));
 }

@@ -32,7 +32,7 @@ def synthetic_batch(dims, batch, rank=0, seed=0):
 
 class MlpTrainer:
     def __init__(self, device, dims=DEFAULT_DIMS, batch=4096, rank=0, world_size=1, lr=1e-3, seed=0, weights=None, biases=None,
-                 overlap=True, data=None, sharded=False, deferred=True, early=True):
+                 overlap=True, data=None, sharded=False, deferred=False, early=False):
         self.device, self.dims, self.world_size = device, tuple(dims), world_size
         if weights is None:
             weights, biases = xavier_parameters(dims, seed)
@@ -47,7 +47,10 @@ class MlpTrainer:
         self.x = Tensor(TensorValue.from_numpy(x, device))
         self.y = Tensor(TensorValue.from_numpy(y, device))
         # sharded=True: reduce-scatter the gradients, update 1/world_size of every parameter (and keep that share of the
-        # Adam state) per rank, all-gather the parameters; needs the overlapped exchange
+        # Adam state) per rank, all-gather the parameters; needs the overlapped exchange. deferred / early move the updates
+        # of the late / early layers into the next forward pass / into backward() (ShardedAdam.attach_model,
+        # ShardedGradientExchange.attach): they want the all-gathers on a lane of their own (AIXB200_COMM_GATHER_LANE=1).
+        # Measured on 8 B200 the plain sharded form is the fastest of those that could be measured there, so it is the default.
         sharded = sharded and overlap and world_size > 1
         params = self.model.parameters()
         self.optimizer = ShardedAdam(params, rank, world_size, lr=lr) if sharded else Adam(params, lr=lr)   # after the parameters live on the device

@@ -361,10 +361,24 @@ def main():
                 # default form: sharded optimizer (reduce-scatter, 1/N of Adam per rank, all-gather); beside it the two
                 # all-reduce forms, to show what each step of the design buys
                 mlp_train = measure_mlp(dev, tensor_peak, sharded=True, **common)
-                mlp_train["ms_per_step_sharded_optimizer_no_early_updates"] = measure_mlp(dev, tensor_peak, sharded=True, early=False, **common)["ms_per_step"]
-                mlp_train["ms_per_step_sharded_optimizer_not_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=False, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_inside_backward"] = measure_mlp(dev, tensor_peak, **common)["ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]
+                # ... and the optional forms of the sharded optimizer on a communicator whose all-gathers have a lane of their
+                # own (read when the communicator is created, hence a second one): late layers' updates deferred into the next
+                # forward pass, early layers' moved into backward
+                try:
+                    dev.commDestroy()
+                    os.environ["AIXB200_COMM_GATHER_LANE"] = "1"
+                    ids = [DeviceB200.commUniqueId() if rank == 0 else None]
+                    dist.broadcast_object_list(ids, src=0)
+                    dev.commInit(rank, world, ids[0])
+                    mlp_train["ms_per_step_gather_lane"] = measure_mlp(dev, tensor_peak, sharded=True, **common)["ms_per_step"]
+                    mlp_train["ms_per_step_gather_lane_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, **common)["ms_per_step"]
+                    mlp_train["ms_per_step_gather_lane_deferred_early"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, early=True, **common)["ms_per_step"]
+                except Exception as exc:
+                    mlp_train["gather_lane_error"] = str(exc)
+                finally:
+                    os.environ.pop("AIXB200_COMM_GATHER_LANE", None)
                 # the broadcast + reduction configuration with its rows split over the ranks (one scalar all-reduce for the mean)
                 from bench_cases import measure_config1_sharded
                 line["config1_sharded"] = measure_config1_sharded(dev, hbm_peak, rank, world, barrier=barrier, reduce_max=max_over_ranks)

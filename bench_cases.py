@@ -123,7 +123,7 @@ def measure_matmul(dev, tensor_peak, size=4096):
 
 
 def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batch=4096, barrier=None, reduce_max=None, overlap=True,
-                sharded=False, deferred=True, early=True):
+                sharded=False, deferred=False, early=False):
     """MLP training configuration: device time of `steps` steps (forward, backward, gradient all-reduce when
     world_size > 1, Adam), loss not read inside the timed region."""
     from aix_b200.mlp import MlpTrainer

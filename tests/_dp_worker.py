@@ -1,9 +1,10 @@
 """Child process of tests/test_gpu_comm.py: one data-parallel rank on its own GPU.
 
-    python tests/_dp_worker.py <rank> <world> <dir> <exchange 0|1|2> <steps> [<ranks whose batches one process concatenates>]
+    python tests/_dp_worker.py <rank> <world> <dir> <exchange 0|1|2|3> <steps> [<ranks whose batches one process concatenates>]
 
 exchange: 0 = all-reduces after backward, 1 = all-reduces started inside backward, 2 = sharded optimizer (reduce-scatter,
-per-rank slice of Adam, all-gather).
+per-rank slice of Adam, all-gather), 3 = the same with the late layers' updates deferred into the next forward pass, the
+early layers' moved into backward, and the all-gathers on a communicator of their own.
 
 Rank 0 publishes the communicator id through a file in <dir>; every rank trains the small MLP and writes its parameters
 and losses to <dir>/rank<r>_<overlap>.npz. With world = 1 and the last argument R, the single process trains on the
@@ -26,7 +27,9 @@ BATCH = 384
 
 def main():
     rank, world, out_dir, mode, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4]), int(sys.argv[5])
-    overlap, sharded = mode >= 1, mode == 2
+    overlap, sharded, deferred = mode >= 1, mode >= 2, mode == 3
+    if deferred:
+        os.environ["AIXB200_COMM_GATHER_LANE"] = "1"        # all-gathers on a communicator and stream of their own
     concat = int(sys.argv[6]) if len(sys.argv) > 6 else 0
     if world == 1 and concat > 1:
         parts = [synthetic_batch(DIMS, BATCH, r) for r in range(concat)]
@@ -54,7 +57,7 @@ def main():
             unique = f.read()
     dev = DeviceB200(rank)
     dev.commInit(rank, world, unique)
-    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, overlap=overlap, sharded=sharded)
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, overlap=overlap, sharded=sharded, deferred=deferred, early=deferred)
     losses = []
     for _ in range(steps):
         losses.append(float(trainer.step().value.numpy()))

@@ -82,15 +82,18 @@ def worker(rank, world, port, out_dir, overlap=True, sharded=False):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     dev = GlooDevice()
     weights, biases = xavier_parameters(DIMS, seed=0)
-    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases, overlap=overlap, sharded=sharded)
+    deferred = sharded == "deferred"               # updates of the late layers inside the next forward pass, of the early ones inside backward
+    trainer = MlpTrainer(dev, DIMS, BATCH, rank=rank, world_size=world, weights=weights, biases=biases, overlap=overlap, sharded=bool(sharded),
+                         deferred=deferred, early=deferred)
     x, y = synthetic_batch(DIMS, BATCH, rank)
     set_batch(trainer, dev, x, y)
     for _ in range(STEPS):
         trainer.step()
     if sharded:
-        # the deferred optimizer owes the last step's updates of the later half of the modules until the next forward pass or finish()
-        owed = sum(len(m.parameters()) for m in [m for m in trainer.model.modules if m.parameters()][trainer.optimizer._eager:])
-        assert dev.gather_calls == STEPS * len(trainer.model.parameters()) - owed
+        if deferred:
+            # the deferred optimizer owes the last step's updates of the later half of the modules until the next forward pass or finish()
+            owed = sum(len(m.parameters()) for m in [m for m in trainer.model.modules if m.parameters()][trainer.optimizer._eager:])
+            assert dev.gather_calls == STEPS * len(trainer.model.parameters()) - owed
         trainer.optimizer.finish()
         # one reduce-scatter, one join and one all-gather per parameter and step; the optimizer state is 1/world of a replica's
         count = STEPS * len(trainer.model.parameters())
@@ -105,7 +108,8 @@ def worker(rank, world, port, out_dir, overlap=True, sharded=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("overlap,sharded", [(True, False), (False, False), (True, True)], ids=["overlapped", "after_backward", "sharded_optimizer"])
+@pytest.mark.parametrize("overlap,sharded", [(True, False), (False, False), (True, "eager"), (True, "deferred")],
+                         ids=["overlapped", "after_backward", "sharded_optimizer", "sharded_optimizer_deferred_and_early"])
 def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path, overlap, sharded):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -91,7 +91,8 @@ def test_contiguous_of_a_large_transposed_matrix(b200, ref, dtype):
 @pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
 def test_slice_set_tril_triu(b200, ref, dtype):
     rng = np.random.default_rng(500 + dtype)
-    for shape, dim, start, end, step in [((8,), 0, 2, 7, 1), ((6, 9), 1, 1, 9, 3), ((6, 9), 0, 0, 6, 2), ((3, 4, 10), 2, 3, 10, 2), ((40, 70), 0, 5, 37, 4)]:
+    for shape, dim, start, end, step in [((8,), 0, 2, 7, 1), ((6, 9), 1, 1, 9, 3), ((6, 9), 0, 0, 6, 2), ((3, 4, 10), 2, 3, 10, 2), ((40, 70), 0, 5, 37, 4),
+                                          ((100, 120), 1, 0, 120, 2), ((9, 50, 40), 1, 3, 47, 5), ((200, 64), 0, 10, 190, 1)]:      # large enough for the dense kernel
         extent = (end - start + step - 1) // step
         src_shape = list(shape)
         src_shape[dim] = extent
@@ -120,7 +121,11 @@ def test_slice_set_tril_triu(b200, ref, dtype):
 @pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: DTYPE_NAMES[d])
 def test_index_select_and_index_add(b200, ref, dtype):
     rng = np.random.default_rng(600 + dtype)
-    for shape, dim, idx in [((9,), 0, [3, 0, 8, 3]), ((5, 6), 0, [4, 4, 1]), ((5, 6), 1, [0, 5, 2, 2, 3]), ((3, 4, 5), 1, [3, 1]), ((40, 33), 1, list(range(0, 33, 3)))]:
+    # whole slices as contiguous runs; distinct indices (colliding additions have a test of their own below)
+    long_runs = [((200, 64), 0, list(rng.permutation(200)[:100])), ((10, 50, 40), 1, list(rng.permutation(50)[:30])),
+                 ((300, 33), 0, list(rng.permutation(300)[:150]))]
+    for shape, dim, idx in [((9,), 0, [3, 0, 8, 3]), ((5, 6), 0, [4, 4, 1]), ((5, 6), 1, [0, 5, 2, 2, 3]), ((3, 4, 5), 1, [3, 1]),
+                            ((40, 33), 1, list(range(0, 33, 3)))] + long_runs:
         x = values(rng, shape, dtype)
         src_shape = list(shape)
         src_shape[dim] = len(idx)

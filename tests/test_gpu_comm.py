@@ -149,7 +149,7 @@ def test_two_ranks_reproduce_the_single_process_run_on_the_concatenated_batch(tm
     single = subprocess.Popen([sys.executable, worker, "0", "1", str(tmp_path), "0", str(steps), "2"], env=env)
     assert single.wait(timeout=600) == 0
     want = np.load(tmp_path / "single.npz")
-    for mode in ("1", "2"):                               # overlapped all-reduce; sharded optimizer
+    for mode in ("1", "2", "3"):                          # overlapped all-reduce; sharded optimizer; ... deferred / early updates, gather lane
         procs = [subprocess.Popen([sys.executable, worker, str(r), "2", str(tmp_path), mode, str(steps)], env=env) for r in range(2)]
         assert [p.wait(timeout=600) for p in procs] == [0, 0]
         ranks = [np.load(tmp_path / f"rank{r}_{mode}.npz") for r in range(2)]

@@ -292,3 +292,21 @@ def test_index_ops_skip_and_report_out_of_range_indices(b200):
     source = TensorValue.from_numpy(x, b200)
     b200.indexSelect(source.deviceParams(), sel.deviceParams(), view.deviceParams(), 0)
     assert np.array_equal(sel.numpy(), x[[0, 2, 4]])
+
+
+def test_index_select_by_whole_runs_skips_out_of_range_indices_too(b200):
+    """Slices long enough to be copied as contiguous runs take another kernel: same rule, same report."""
+    from aix_b200 import I32
+    x = np.arange(100 * 64, dtype=np.float32).reshape(100, 64)
+    bad = np.arange(80) % 100
+    bad[7], bad[50] = 100, -3
+    t = TensorValue.from_numpy(x, b200)
+    idx = TensorValue.from_numpy(bad, b200, I32)
+    sel = TensorValue.full(-7.0, (80, 64), b200)
+    b200.synchronize()
+    b200.indexSelect(t.deviceParams(), sel.deviceParams(), idx.deviceParams(), 0)
+    with pytest.raises(ValueError, match="outside the indexed dimension"):
+        b200.synchronize()
+    got = sel.numpy()
+    for row, v in enumerate(bad):
+        assert (np.array_equal(got[row], x[v]) if 0 <= v < 100 else np.all(got[row] == -7.0)), row
