@@ -486,7 +486,9 @@ std::vector<uint64_t> packKernelArguments(const KernelSpec& spec, const KernelVa
 std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& variant, const CodegenOptions& options,
                                  const std::string& entryName)
 {
-    const int E = variant.vec, U = options.unroll, B = options.block;
+    const bool tunedRows16 = variant.rowMode && variant.packed16 && options.rowMinBlocks < 0;
+    const int E = variant.vec, U = tunedRows16 ? 1 : options.unroll, B = options.block;
+    const int rowMinBlocks = tunedRows16 ? 8 : std::max(0, options.rowMinBlocks);
     const size_t nL = spec.loads.size(), nS = spec.stores.size();
     std::ostringstream o;
     o << "#define AIX_FAST " << (options.strictMath ? 0 : 1) << "\n" << kPrelude << "\n";
@@ -613,7 +615,7 @@ std::string generateKernelSource(const KernelSpec& spec, const KernelVariant& va
         }
     };
 
-    o << "extern \"C\" __global__ void __launch_bounds__(" << B << ((variant.rowMode && options.rowMinBlocks > 0) ? ", " + std::to_string(options.rowMinBlocks) : std::string()) << ") " << entryName
+    o << "extern \"C\" __global__ void __launch_bounds__(" << B << ((variant.rowMode && rowMinBlocks > 0) ? ", " + std::to_string(rowMinBlocks) : std::string()) << ") " << entryName
       << "(const __grid_constant__ Params p)\n{\n";
     o << "    const idx_t n = (idx_t)" << arg(slotCount) << ";\n";
     for (size_t i = 0; i < nL; ++i)

@@ -21,7 +21,9 @@ struct CodegenOptions
     bool strictMath = true;   // reported in the key only; the compile flags are chosen by the caller
     int  block      = 256;    // threads per CTA
     int  unroll     = 2;      // packs in flight per thread
-    int  rowMinBlocks = 0;    // row-form kernels: CTAs per SM asked for in __launch_bounds__ (0: left to the compiler)
+    int  rowMinBlocks = -1;   // row-form kernels: CTAs per SM asked for in __launch_bounds__ (0: left to the compiler). -1: automatic -
+                              // 16-bit row-form kernels ask for 8 and keep one pack in flight per thread (measured on the
+                              // broadcast + reduction configuration, bf16 8192 x 8192: 63 us against 68 us), others ask for nothing
 };
 
 // Everything that selects a distinct kernel for one KernelSpec at launch time.

@@ -93,7 +93,7 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     m_codegen.strictMath = m_cfg.strict_math != 0;
     m_codegen.block = envInt("AIXB200_EW_BLOCK", 256);
     m_codegen.unroll = std::max(1, std::min(8, envInt("AIXB200_EW_UNROLL", 2)));
-    m_codegen.rowMinBlocks = std::max(0, std::min(8, envInt("AIXB200_ROW_MIN_BLOCKS", 0)));
+    m_codegen.rowMinBlocks = std::max(-1, std::min(8, envInt("AIXB200_ROW_MIN_BLOCKS", -1)));
     m_wavesPerSm = std::max(1, envInt("AIXB200_EW_WAVES", 8));
     m_fuseReductions = envInt("AIXB200_FUSE_REDUCTIONS", 1) != 0;
     m_fuseRowReductions = envInt("AIXB200_FUSE_ROW_REDUCTIONS", 1) != 0;
