@@ -358,19 +358,24 @@ void Device::appendOperandMaxEpilogues(std::vector<KernelSpec>& kernels, std::ve
             const size_t bytes = static_cast<size_t>(st.view.endByte() - st.view.firstByte());
             return std::find(m_operandSizes.begin(), m_operandSizes.end(), bytes) != m_operandSizes.end();
         };
-        size_t candidates = 0;
-        for (const KernelStore& st : spec.stores) candidates += qualifies(st) ? 1 : 0;
+        size_t candidates = 0, known = 0;
+        int lastNode = -1;
+        auto livesThere = [&](const KernelStore& st)
+        {
+            for (const OperandRegion& r : m_operandRegions)
+                if (r.operand && r.lo == st.view.firstByte() && r.hi == st.view.endByte()) return true;
+            return false;
+        };
+        for (const KernelStore& st : spec.stores)
+            if (qualifies(st)) { ++candidates; known += livesThere(st) ? 1 : 0; lastNode = std::max(lastNode, static_cast<int>(st.node)); }
         for (const KernelStore& st : spec.stores)
         {
             if (!qualifies(st)) continue;
             if (spec.reductions.size() >= m_limits.maxReductionsPerKernel) break;
-            if (candidates > 1)
-            {
-                bool operandLivesThere = false;
-                for (const OperandRegion& r : m_operandRegions)
-                    operandLivesThere = operandLivesThere || (r.operand && r.lo == st.view.firstByte() && r.hi == st.view.endByte());
-                if (!operandLivesThere) continue;
-            }
+            // Several candidates: those where an operand is known to live; if none is, the value computed last - the end of
+            // the chain is what the next matmul reads (bias + tanh stores the sum and its tanh; the tanh is the operand).
+            // Both choices depend on the recorded ops and on sizes only, not on the addresses of fresh allocations.
+            if (candidates > 1 && (known > 0 ? !livesThere(st) : static_cast<int>(st.node) != lastNode)) continue;
             const int region = rememberOperandRegion(st.view.firstByte(), st.view.endByte(), false);
             View slot;
             slot.base = reinterpret_cast<char*>(preparedSlot(region >= 0 ? m_operandRegions[static_cast<size_t>(region)].slot : m_dummySlot));
