@@ -104,6 +104,7 @@ Device::Device(const aixb200_config& cfg) : m_cfg(cfg)
     // slower than the separate kernel: see launchDeferredMatmul)
     m_foldDepth = std::max(0, std::min(2, envInt("AIXB200_GEMM_EPILOGUE", 1)));
     m_foldMatmulEpilogue = m_foldDepth != 0 && m_cfg.strict_math == 0 && m_cfg.fusion != 0;
+    m_redirectMatmul = envInt("AIXB200_GEMM_REDIRECT", 1) != 0;
 
     if (m_cfg.disk_cache)
     {
@@ -1065,8 +1066,16 @@ void Device::matmul(const aixb200_tensor* a, const aixb200_tensor* b, const aixb
     launchMatmul(d, 0);
 }
 
-void Device::launchMatmul(const DeferredMatmul& d, int folded)
+void Device::launchMatmul(const DeferredMatmul& d, int folded, void* redirectTo)
 {
+    if (redirectTo)
+    {
+        // the zero-fill and the accumulation disappear: the product lands where their result would have
+        m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(std::max(d.addIndex, d.fillIndex)));
+        m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(std::min(d.addIndex, d.fillIndex)));
+        m_stats.matmul_consumers_folded += 1;
+        ++m_stats.fills_absorbed;
+    }
     if (dryRun())
     {
         if (folded == 2) m_pending.erase(m_pending.begin() + static_cast<std::ptrdiff_t>(d.tanhIndex));
@@ -1081,7 +1090,7 @@ void Device::launchMatmul(const DeferredMatmul& d, int folded)
     p.m = m; p.n = n; p.k = k;
     p.a = d.va.firstByte(); p.aRowStride = d.a.strides[0]; p.aColStride = d.a.strides[1];
     p.b = d.vb.firstByte(); p.bRowStride = d.b.strides[0]; p.bColStride = d.b.strides[1];
-    p.c = d.vr.firstByte();
+    p.c = redirectTo ? redirectTo : d.vr.firstByte();
     p.splitF32 = m_cfg.tf32x3_matmul != 0;
     p.shareDevice = !m_commInFlight.empty();
     int region = -1;
@@ -1103,6 +1112,7 @@ void Device::launchMatmul(const DeferredMatmul& d, int folded)
     if (tensorCore) m_checkErrorWord = true;
     else if (folded == 0)
         kernels::matmulSimt(ctx, d.r.dtype, p.a, p.aRowStride, p.aColStride, p.b, p.bRowStride, p.bColStride, p.c, m, n, k);
+    (void)redirectTo;
     AIXB200_DONE("matmul");
     if (folded > 0 && !tensorCore) { launchMatmul(d, 0); return; }       // the consumers stay recorded and run as kernels
     if (folded > 0)
@@ -1140,6 +1150,15 @@ void Device::launchDeferredMatmul(bool consumerRecorded)
     // And the add alone is folded only when nothing recorded consumes the sum: a recorded consumer would run in one generated
     // kernel together with the add anyway, so folding saves no pass over memory there, while the folding instantiation is a
     // few microseconds slower than the plain one (98 against 83 us at K = 1024; 105 us for product + add kernel).
+    if (d.redirect)
+    {
+        // `target = 0 + product` with the product dead: the product is written into the target itself (0 + x is x)
+        const bool productDead = dead(d.vr, d.addIndex, d.addIndex);
+        launchMatmul(d, 0, productDead ? d.biasOut.firstByte() : nullptr);
+        for (const OpRecord& op : m_pending)
+            if (op.out.overlaps(d.va) || op.out.overlaps(d.vb)) invalidatePreparedTerms(op.out.firstByte(), op.out.endByte());
+        return;
+    }
     int folded = d.folded;
     if (m_foldDepth < 2 && (folded == 2 || consumerRecorded)) folded = 0;
     if (folded == 2 && !dead(d.biasOut, d.addIndex, d.tanhIndex)) folded = 1;
@@ -1175,6 +1194,11 @@ void Device::advanceDeferredMatmul(size_t index)
         return v.dtype == F32 && v.isDense() && v.size == d.vr.size && reinterpret_cast<uintptr_t>(v.firstByte()) % 16 == 0 &&
                !v.overlaps(d.vr) && !v.overlaps(d.va) && !v.overlaps(d.vb);
     };
+    if (d.redirect)
+    {
+        if (touches(op, d.biasOut) || touches(op, d.vr)) launchDeferredMatmul(true);
+        return;
+    }
     if (d.folded == 0)
     {
         if (!touches(op, d.vr)) return;                         // unrelated (a fill of some gradient, say): keep waiting
@@ -1196,6 +1220,32 @@ void Device::advanceDeferredMatmul(size_t index)
                     d.folded = 1;
                     d.addIndex = index;
                     d.bias = op.in[1 - product];
+                    d.biasOut = op.out;
+                    return;
+                }
+            }
+        }
+        // `target += result` where the target's zero-fill is still recorded and nothing else recorded touches the target:
+        // a candidate for writing the product into the target directly (decided when the wait ends: the result must be dead)
+        if (m_redirectMatmul && op.op == Op::Add && op.numInputs == 2 && denseLikeResult(op.out))
+        {
+            const int product = op.in[0].sameElements(d.vr) ? 0 : (op.in[1].sameElements(d.vr) ? 1 : -1);
+            if (product >= 0 && op.in[1 - product].sameElements(op.out))
+            {
+                size_t fill = index;
+                bool clean = true;
+                for (size_t i = 0; i < index && clean; ++i)
+                {
+                    const OpRecord& other = m_pending[i];
+                    if (!touches(other, op.out)) continue;
+                    if (fill == index && other.op == Op::Fill && other.out.sameElements(op.out) && other.scalar.raw == 0) fill = i;
+                    else clean = false;
+                }
+                if (clean && fill != index)
+                {
+                    d.redirect = true;
+                    d.addIndex = index;
+                    d.fillIndex = fill;
                     d.biasOut = op.out;
                     return;
                 }

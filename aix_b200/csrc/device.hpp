@@ -173,13 +173,18 @@ private:
         int folded = 0;                         // recorded consumers matched so far: 0, 1 (the add), 2 (add and tanh)
         size_t addIndex = 0, tanhIndex = 0;     // their positions in m_pending
         View bias, biasOut, tanhOut;
+        // Accumulation into a buffer whose zero-fill is still recorded (`grad += dW` after zeroGrad()): the product can be
+        // written straight into that buffer, and the fill and the add dropped, if the product itself is dead by then.
+        bool   redirect = false;
+        size_t fillIndex = 0;                   // position of the zero-fill in m_pending; the add sits at addIndex, its result in biasOut
     };
     DeferredMatmul m_deferred;
     bool m_foldMatmulEpilogue = true;           // AIXB200_GEMM_EPILOGUE=0: every product is launched by its own call
     int  m_foldDepth = 1;                       // consumers folded at most: 1 = the add, 2 = the add and its tanh (AIXB200_GEMM_EPILOGUE=2)
     void advanceDeferredMatmul(size_t index);   // looks at the op just recorded at m_pending[index]
     void launchDeferredMatmul(bool consumerRecorded = false);   // consumerRecorded: a recorded op that reads the sum ended the wait
-    void launchMatmul(const DeferredMatmul& d, int folded);
+    void launchMatmul(const DeferredMatmul& d, int folded, void* redirectTo = nullptr);
+    bool m_redirectMatmul = true;               // AIXB200_GEMM_REDIRECT=0: accumulations into zero-filled buffers stay kernels of their own
     void launchSpec(const KernelSpec& spec);
     CompiledKernel& getKernel(const KernelSpec& spec, const KernelVariant& variant, const std::string& key);
     std::vector<char> compile(const std::string& source, const std::string& entry);

@@ -241,3 +241,36 @@ def test_the_next_product_finds_the_maximum_the_epilogue_left(b200, deep, with_t
         assert np.array_equal(h, results[0][0])
         assert np.max(np.abs(y - exact_y)) <= 1e-5 * np.max(np.abs(exact_y))
         assert np.array_equal(y, results[0][1]), "the scale taken from the epilogue's maximum is the one the max pass finds"
+
+
+def test_a_dead_product_lands_in_the_zero_filled_buffer_it_is_accumulated_into(b200):
+    """`grad += x^T . G` after zeroGrad(): the fill and the add disappear, the product is written into the gradient buffer."""
+    x, w, b, tx, tw, tb = operands(b200, 512, 256, 384, 21)
+    want_mm, _, _ = separate(b200, tx, tw, tb)
+    before, launches = folded(b200), b200.stats()["total_kernel_launches"]
+    g = TensorValue.full(0.0, (512, 384), b200)
+    g += tx.matmul(tw)
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert b200.stats()["total_kernel_launches"] - launches == 1, "the product alone: no fill kernel, no add kernel"
+    assert np.array_equal(g.numpy(), want_mm)
+    g += tx.matmul(tw)                  # no fill recorded any more: an ordinary accumulation
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(g.numpy(), want_mm + want_mm)
+    g = TensorValue.full(0.5, (512, 384), b200)     # not zero
+    g += tx.matmul(tw)
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(g.numpy(), np.float32(0.5) + want_mm)
+    g = TensorValue.full(0.0, (512, 384), b200)
+    mm = tx.matmul(tw)                  # the product stays alive: it must be written itself
+    g += mm
+    b200.synchronize()
+    assert folded(b200) == before + 1
+    assert np.array_equal(g.numpy(), want_mm) and np.array_equal(mm.numpy(), want_mm)
+    g = TensorValue.full(0.0, (512, 384), b200)
+    g += tx.matmul(tw)
+    h = g * 2.0                         # a reader of the target recorded while the product waits
+    b200.synchronize()
+    assert np.array_equal(g.numpy(), want_mm) and np.array_equal(h.numpy(), want_mm * np.float32(2.0))

@@ -122,3 +122,40 @@ def test_strict_math_and_the_switch_keep_every_product_in_its_own_call():
         del x, w, b
     finally:
         strict.close()
+
+
+def test_a_dead_product_is_written_straight_into_a_zero_filled_accumulation_target(dry):
+    """zeroGrad() fills every gradient, backward() then does `grad += x^T . G` (aixCore.hpp:2014-2021, 2192-2207): the zero-fill is
+    still recorded and the product is a temporary, so the product lands in the gradient buffer and neither the fill nor the
+    add runs."""
+    x, w, b = operands(dry)
+
+    def accumulate():
+        g = TensorValue.full(0.0, (256, 256), dry)
+        g += x.matmul(w)
+        return g
+    d = run(dry, accumulate)
+    assert d["matmul_consumers_folded"] == 1 and d["fused_kernels"] == 0, d
+
+    def product_kept():
+        g = TensorValue.full(0.0, (256, 256), dry)
+        mm = x.matmul(w)
+        g += mm
+        return g, mm
+    d = run(dry, product_kept)
+    assert d["matmul_consumers_folded"] == 0 and d["fused_kernels"] == 1, d
+
+    def target_not_zero():
+        g = TensorValue.full(1.0, (256, 256), dry)
+        g += x.matmul(w)
+        return g
+    d = run(dry, target_not_zero)
+    assert d["matmul_consumers_folded"] == 0 and d["fused_kernels"] == 1, d
+
+    def target_read_in_between():
+        g = TensorValue.full(0.0, (256, 256), dry)
+        h = g * 2.0
+        g += x.matmul(w)
+        return g, h
+    d = run(dry, target_read_in_between)
+    assert d["matmul_consumers_folded"] == 0, d
