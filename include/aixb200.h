@@ -176,7 +176,9 @@ int aixb200_argmax_indices_to(aixb200_device* dev, const aixb200_tensor* src, co
  * An f32 product on the tensor cores may be launched later than this call returns - at the latest by the next call that
  * is not a recorded elementwise op: `result + row vector` (nn::Linear's bias, aixNeuralNetwork.hpp:150-153), when it is
  * the next op recorded, `result` is already deallocated and no recorded op consumes the sum, runs inside the product's
- * kernel, which then writes only the sum. Results and program order are those of separate launches;
+ * kernel, which then writes only the sum; and `target += result` into a buffer whose zero-fill is still recorded (the
+ * gradient accumulation after zeroGrad) makes a deallocated `result` land in `target` directly. Results and program order
+ * are those of separate launches;
  * AIXB200_GEMM_EPILOGUE=0 in the environment launches every product from its own call, =2 folds a following tanh too. */
 int aixb200_matmul(aixb200_device* dev, const aixb200_tensor* a, const aixb200_tensor* b, const aixb200_tensor* result);
 
