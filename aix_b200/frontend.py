@@ -37,6 +37,8 @@ class TensorNode:
         return self._grad
 
     def backward(self, seed: TensorValue):
+        if _readyNodes:
+            _callReadyHooks()
         if self.retainGrad:
             g = self.grad()
             g += seed
@@ -58,6 +60,21 @@ def defaultBackward(node: TensorNode, seed: TensorValue):
     if node.requireGrad and not node.retainGrad:
         g = node.grad()
         g += seed                                  # in-place Device::add into the gradient buffer
+        if node.gradReadyHook is not None:
+            _readyNodes.append(node)
+
+
+# Gradient-ready hooks (no counterpart in the reference) are not called from inside defaultBackward but at the next step of the
+# backward pass - the next TensorNode.backward call, or the end of Tensor.backward. By then the caller has dropped the
+# temporary it accumulated (`W.backward(x^T . G)`), so a device that holds the product back can still write it straight into
+# the gradient buffer; a hook called at once would start a collective, which launches everything recorded, while the
+# temporary is still referenced.
+_readyNodes: List[TensorNode] = []
+
+
+def _callReadyHooks():
+    while _readyNodes:
+        node = _readyNodes.pop(0)
         if node.gradReadyHook is not None:
             node.gradReadyHook(node)
 
@@ -163,6 +180,7 @@ class Tensor:
         v = self.node.value
         seed = TensorValue.full(1, v.shape, v.device, v.dtype)
         self.node.backward(seed)
+        _callReadyHooks()
 
     # views / conversions
     def broadcastTo(self, shape) -> "Tensor":
@@ -325,9 +343,9 @@ def all_reduce_gradients(device, parameters: Sequence[Tensor], world_size: int):
 
 
 class GradientExchange:
-    """The same exchange, overlapped with the rest of backward() and with the optimizer step: as soon as a parameter's
-    gradient has been accumulated (defaultBackward, aixCore.hpp:2014-2021) its all-reduce starts on the device's side
-    stream, so that the collectives of some layers run under the matmuls of the others. `attach(optimizer)` makes the
+    """The same exchange, overlapped with the rest of backward() and with the optimizer step: once a parameter's
+    gradient has been accumulated (defaultBackward, aixCore.hpp:2014-2021; the hook runs at the backward pass's next
+    step, see _callReadyHooks) its all-reduce starts on the device's side stream, so that the collectives of some layers run under the matmuls of the others. `attach(optimizer)` makes the
     optimizer join, before it starts on a parameter, only that parameter's collective: the front end produces the
     weight gradients first-layer-first, so the largest exchanges are the last to start, and Adam already runs on the
     first parameters while they finish. Without an attached optimizer, `finish()` joins everything at once; it goes

@@ -372,6 +372,7 @@ def main():
                     ids = [DeviceB200.commUniqueId() if rank == 0 else None]
                     dist.broadcast_object_list(ids, src=0)
                     dev.commInit(rank, world, ids[0])
+                    measure_mlp(dev, tensor_peak, sharded=True, **dict(common, steps=5))      # the new communicators set up their connections
                     mlp_train["ms_per_step_gather_lane"] = measure_mlp(dev, tensor_peak, sharded=True, **common)["ms_per_step"]
                     mlp_train["ms_per_step_gather_lane_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, **common)["ms_per_step"]
                     mlp_train["ms_per_step_gather_lane_deferred_early"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, early=True, **common)["ms_per_step"]
