@@ -136,9 +136,12 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
     dev.synchronize()
     s0 = dev.stats()
     dev.recordEvent(e0)
+    import time
+    issue_start = time.perf_counter()
     for _ in range(steps):
         loss = trainer.step()
     dev.recordEvent(e1)
+    host_ms = (time.perf_counter() - issue_start) * 1e3 / steps        # time the host needs to issue a step (no wait for the device in it)
     ms = dev.elapsedMs(e0, e1)
     if barrier: barrier()
     if reduce_max: ms = reduce_max(ms)
@@ -147,7 +150,7 @@ def measure_mlp(dev, tensor_peak, steps=10, warmup=3, rank=0, world_size=1, batc
     per_step = ms / steps
     tf = trainer.flops_per_step / (per_step * 1e-3) / 1e12
     return {"config": "4 Linear 1024-4096-4096-4096-1024, tanh, f32, batch %d per GPU, MSE, Adam(1e-3)" % batch,
-            "ms_per_step": per_step, "steps_per_s": 1e3 / per_step, "samples_per_s": world_size * batch * 1e3 / per_step,
+            "ms_per_step": per_step, "host_issue_ms_per_step": host_ms, "steps_per_s": 1e3 / per_step, "samples_per_s": world_size * batch * 1e3 / per_step,
             "gemm_TFLOP/s_per_gpu": tf, "frac_of_measured_bf16_peak": tf / tensor_peak, "world_size": world_size,
             "kernel_launches_per_step": (s1["total_kernel_launches"] - s0["total_kernel_launches"]) / steps,
             "fused_kernels_per_step": (s1["fused_kernels"] - s0["fused_kernels"]) / steps,
@@ -347,9 +350,29 @@ def build_case(dev, case):
     raise SystemExit(f"unknown case {case}")
 
 
+def run_dp_machinery(steps=30):
+    """What the data-parallel forms of the MLP step cost WITHOUT any communication: one GPU, a communicator of one rank (its
+    collectives move nothing), the front end told that there are two ranks. The difference to the plain step is GPU work of
+    the exchange's machinery itself - scaling passes, per-parameter optimizer kernels that no longer merge, weights whose
+    maximum no producer leaves - not NVLink time and not contention with a collective's kernel."""
+    dev = DeviceB200(0)
+    dev.commInit(0, 1, DeviceB200.commUniqueId())
+    forms = {"sharded optimizer": dict(sharded=True), "sharded, deferred": dict(sharded=True, deferred=True),
+             "all-reduce inside backward": dict(), "all-reduce after backward": dict(overlap=False)}
+    for name, kw in forms.items():
+        r = measure_mlp(dev, 1.0, steps=steps, warmup=3, rank=0, world_size=2, **kw)
+        print(f"{name}: {r['ms_per_step']:.3f} ms per step, host {r['host_issue_ms_per_step']:.3f} ms, {r['kernel_launches_per_step']:.0f} launches")
+    r = measure_mlp(dev, 1.0, steps=steps, warmup=3)
+    print(f"plain step: {r['ms_per_step']:.3f} ms per step, host {r['host_issue_ms_per_step']:.3f} ms, {r['kernel_launches_per_step']:.0f} launches")
+    dev.commDestroy()
+    dev.close()
+
+
 def run_case(argv):
     case = argv[0] if argv else "chain_f32"
     repeats = int(argv[1]) if len(argv) > 1 else 4
+    if case == "mlp_f32_dp_machinery":
+        return run_dp_machinery(repeats if len(argv) > 1 else 30)
     dev = DeviceB200(0)
     fn = build_case(dev, case)
     dev.synchronize()
