@@ -175,10 +175,10 @@ Comm::Comm(int rank, int nranks, const void* id128, int ordinal) : m_rank(rank),
 #endif
     checkNccl(nccl().commInitRank(&comm, nranks, id, rank), "ncclCommInitRank");
     m_comm = comm;
-    // AIXB200_COMM_GATHER_LANE=1: a second communicator over the same ranks for the all-gathers of a sharded optimizer (see
-    // allGather). Every rank decides the same way: same library, same environment.
+    // A second communicator over the same ranks for the all-gathers of a sharded optimizer (see allGather;
+    // AIXB200_COMM_GATHER_LANE=0: none). Every rank decides the same way: same library, same environment.
     const char* lane = std::getenv("AIXB200_COMM_GATHER_LANE");
-    if (nranks > 1 && !backendInjected() && nccl().commSplit && lane && lane[0] == '1')
+    if (nranks > 1 && !backendInjected() && nccl().commSplit && !(lane && lane[0] == '0'))
     {
         NcclComm second = nullptr;
         checkNccl(nccl().commSplit(m_comm, 0, rank, &second, nullptr), "ncclCommSplit");

@@ -40,7 +40,7 @@ private:
     void finishCall(int result, const char* what);
     void abortOnce();
     void* m_comm = nullptr;
-    void* m_gatherComm = nullptr;   // second communicator over the same ranks, for all-gathers (AIXB200_COMM_GATHER_LANE=1)
+    void* m_gatherComm = nullptr;   // second communicator over the same ranks, for all-gathers (AIXB200_COMM_GATHER_LANE=0: none)
     int   m_rank, m_nranks;
     long  m_timeoutMs = 0;
     bool  m_nonBlocking = false, m_aborted = false;

@@ -49,8 +49,8 @@ class MlpTrainer:
         # sharded=True: reduce-scatter the gradients, update 1/world_size of every parameter (and keep that share of the
         # Adam state) per rank, all-gather the parameters; needs the overlapped exchange. deferred / early move the updates
         # of the late / early layers into the next forward pass / into backward() (ShardedAdam.attach_model,
-        # ShardedGradientExchange.attach): they want the all-gathers on a lane of their own (AIXB200_COMM_GATHER_LANE=1).
-        # Measured on 8 B200 the plain sharded form is the fastest of those that could be measured there, so it is the default.
+        # ShardedGradientExchange.attach). Measured on 8 B200 they are within 1 % of the plain sharded form (all with the
+        # all-gathers on a communicator of their own, the device's default), so the plain form is the default.
         sharded = sharded and overlap and world_size > 1
         params = self.model.parameters()
         self.optimizer = ShardedAdam(params, rank, world_size, lr=lr) if sharded else Adam(params, lr=lr)   # after the parameters live on the device

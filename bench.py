@@ -358,28 +358,28 @@ def main():
             if world == 1:
                 mlp_train = measure_mlp(dev, tensor_peak, **common)
             else:
-                # default form: sharded optimizer (reduce-scatter, 1/N of Adam per rank, all-gather); beside it the two
-                # all-reduce forms, to show what each step of the design buys
+                # default form: sharded optimizer (reduce-scatter, 1/N of Adam per rank, all-gather on a communicator of its own);
+                # beside it the two all-reduce forms and the optional forms of the sharded optimizer (late layers' updates deferred
+                # into the next forward pass, early layers' moved into backward), to show what each step of the design buys
                 mlp_train = measure_mlp(dev, tensor_peak, sharded=True, **common)
                 inside = measure_mlp(dev, tensor_peak, **common)
                 mlp_train["ms_per_step_all_reduce_inside_backward"] = inside["ms_per_step"]
                 mlp_train["host_issue_ms_per_step_all_reduce_inside_backward"] = inside["host_issue_ms_per_step"]
                 mlp_train["ms_per_step_all_reduce_after_backward"] = measure_mlp(dev, tensor_peak, overlap=False, **common)["ms_per_step"]
-                # ... and the optional forms of the sharded optimizer on a communicator whose all-gathers have a lane of their
-                # own (read when the communicator is created, hence a second one): late layers' updates deferred into the next
-                # forward pass, early layers' moved into backward
+                mlp_train["ms_per_step_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, **common)["ms_per_step"]
+                mlp_train["ms_per_step_deferred_early"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, early=True, **common)["ms_per_step"]
+                # ... and the sharded optimizer with every collective on ONE communicator (read when the communicator is created,
+                # hence a second one)
                 try:
                     dev.commDestroy()
-                    os.environ["AIXB200_COMM_GATHER_LANE"] = "1"
+                    os.environ["AIXB200_COMM_GATHER_LANE"] = "0"
                     ids = [DeviceB200.commUniqueId() if rank == 0 else None]
                     dist.broadcast_object_list(ids, src=0)
                     dev.commInit(rank, world, ids[0])
-                    measure_mlp(dev, tensor_peak, sharded=True, **dict(common, steps=5))      # the new communicators set up their connections
-                    mlp_train["ms_per_step_gather_lane"] = measure_mlp(dev, tensor_peak, sharded=True, **common)["ms_per_step"]
-                    mlp_train["ms_per_step_gather_lane_deferred"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, **common)["ms_per_step"]
-                    mlp_train["ms_per_step_gather_lane_deferred_early"] = measure_mlp(dev, tensor_peak, sharded=True, deferred=True, early=True, **common)["ms_per_step"]
+                    measure_mlp(dev, tensor_peak, sharded=True, **dict(common, steps=5))      # the new communicator sets up its connections
+                    mlp_train["ms_per_step_one_communicator"] = measure_mlp(dev, tensor_peak, sharded=True, **common)["ms_per_step"]
                 except Exception as exc:
-                    mlp_train["gather_lane_error"] = str(exc)
+                    mlp_train["one_communicator_error"] = str(exc)
                 finally:
                     os.environ.pop("AIXB200_COMM_GATHER_LANE", None)
                 # the broadcast + reduction configuration with its rows split over the ranks (one scalar all-reduce for the mean)

@@ -3,8 +3,8 @@
     python tests/_dp_worker.py <rank> <world> <dir> <exchange 0|1|2|3> <steps> [<ranks whose batches one process concatenates>]
 
 exchange: 0 = all-reduces after backward, 1 = all-reduces started inside backward, 2 = sharded optimizer (reduce-scatter,
-per-rank slice of Adam, all-gather), 3 = the same with the late layers' updates deferred into the next forward pass, the
-early layers' moved into backward, and the all-gathers on a communicator of their own.
+per-rank slice of Adam, all-gather; all collectives on one communicator), 3 = the same with the all-gathers on a communicator
+of their own (the default), the late layers' updates deferred into the next forward pass and the early layers' moved into backward.
 
 Rank 0 publishes the communicator id through a file in <dir>; every rank trains the small MLP and writes its parameters
 and losses to <dir>/rank<r>_<overlap>.npz. With world = 1 and the last argument R, the single process trains on the
@@ -28,8 +28,8 @@ BATCH = 384
 def main():
     rank, world, out_dir, mode, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4]), int(sys.argv[5])
     overlap, sharded, deferred = mode >= 1, mode >= 2, mode == 3
-    if deferred:
-        os.environ["AIXB200_COMM_GATHER_LANE"] = "1"        # all-gathers on a communicator and stream of their own
+    if mode == 2:
+        os.environ["AIXB200_COMM_GATHER_LANE"] = "0"        # mode 2: every collective on one communicator; mode 3: all-gathers on their own (default)
     concat = int(sys.argv[6]) if len(sys.argv) > 6 else 0
     if world == 1 and concat > 1:
         parts = [synthetic_batch(DIMS, BATCH, r) for r in range(concat)]
