@@ -191,8 +191,8 @@ def measure_cold_ops(dev, hbm_peak, n=10_000_000):
         "contiguous of a transposed 5000x5000 view": (lambda: holder.__setitem__("c", sq.transpose(0, 1).contiguous()), 8 * 25_000_000),
         "tril 5000x5000 f32": (lambda: dev.tril(sq.deviceParams(), tri.deviceParams(), 0), 8 * 25_000_000),
         "indexSelect 10000 rows of 1000 f32": (lambda: dev.indexSelect(rows.deviceParams(), sel.deviceParams(), idx.deviceParams(), 0), 8 * n),
-        "indexAdd 10000 rows of 1000 f32 into 10000 (lane-parallel form)": (lambda: dev.indexAdd(sel.deviceParams(), rows.deviceParams(), idx.deviceParams(), 0), 12 * n),
-        "indexAdd 10000 rows of 1000 f32 into 64 (atomic form)": (lambda: dev.indexAdd(sel.deviceParams(), few.deviceParams(), idx_few.deviceParams(), 0), 4 * n),
+        "indexAdd 10000 rows of 1000 f32 into 10000 rows (atomics, whole slices as runs)": (lambda: dev.indexAdd(sel.deviceParams(), rows.deviceParams(), idx.deviceParams(), 0), 12 * n),
+        "indexAdd 10000 rows of 1000 f32 into 64 rows (the same, ~156 additions per element)": (lambda: dev.indexAdd(sel.deviceParams(), few.deviceParams(), idx_few.deviceParams(), 0), 4 * n),
         "sliceSet 5000x2500 into every other column": (lambda: dev.sliceSet(TensorValue(sq.storage, (5000, 2500), (2500, 1), 0, C.F32, dev).deviceParams(),
                                                                               tri.deviceParams(), 1, 0, 5000, 2), 8 * 12_500_000),
     }

@@ -180,7 +180,7 @@ def test_index_add_with_a_long_index_list_and_collisions(b200, ref, dtype):
     """Few lanes and a long index list take the atomic form: integer results must equal the sequential ones bit for
     bit (wrapping sums commute); floating results within the type's tolerance of the per-add rounding."""
     rng = np.random.default_rng(950 + dtype)
-    for shape, dim, count in [((50, 8), 0, 4000), ((3, 64, 4), 1, 1000), ((257,), 0, 5000)]:
+    for shape, dim, count in [((50, 8), 0, 4000), ((3, 64, 4), 1, 1000), ((257,), 0, 5000), ((40, 64), 0, 3000), ((2, 30, 48), 1, 500)]:
         idx = rng.integers(0, shape[dim], count)
         src_shape = list(shape)
         src_shape[dim] = count
