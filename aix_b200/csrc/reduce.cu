@@ -156,7 +156,7 @@ void launchReduceAll(const LaunchContext& ctx, bool isMax, const View& src, void
 // dst[k] (+)= fold over r of src[k * keptStride + r]: one CTA (long rows) or one warp (short rows) per output.
 // ------------------------------------------------------------------------------------------------------------
 template <int DT, bool IsMax, bool WarpPerRow>
-__global__ void __launch_bounds__(kBlock) reduceRowsKernel(const typename Elem<DT>::S* __restrict__ src, uint64_t rows, uint64_t cols,
+__global__ void __launch_bounds__(kBlock, 8) reduceRowsKernel(const typename Elem<DT>::S* __restrict__ src, uint64_t rows, uint64_t cols,
                                                            uint64_t rowStride, typename Elem<DT>::S* dst)
 {
     typedef Reduce<DT, IsMax> R;
