@@ -136,7 +136,20 @@ void launchReduceAll(const LaunchContext& ctx, bool isMax, const View& src, void
     for (int d = 0; d < src.rank; ++d) { layout.shape[d] = src.shape[d]; layout.strides[d] = src.strides[d]; }
     const uint64_t perBlock = static_cast<uint64_t>(kBlock) * (dense ? 4 * (16 / sizeof(S)) : 1);
     uint64_t blocks = (src.size + perBlock - 1) / perBlock;
-    blocks = std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::min<uint64_t>(maxBlocks, static_cast<uint64_t>(ctx.smCount) * 8)));
+    // A grid-stride kernel: no more CTAs than are resident at once (what the kernel's registers allow, at most 8 per SM) -
+    // a partial second wave would run at a fraction of the bandwidth while everything else has finished.
+    auto residentPerSm = [](const void* kernel)
+    {
+        int perSm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, kBlock, 0) != cudaSuccess || perSm <= 0) { cudaGetLastError(); perSm = 8; }
+        return std::min(perSm, 8);
+    };
+    static const int resident[4] = {residentPerSm(reinterpret_cast<const void*>(&reduceAllKernel<DT, false, false>)),
+                                    residentPerSm(reinterpret_cast<const void*>(&reduceAllKernel<DT, false, true>)),
+                                    residentPerSm(reinterpret_cast<const void*>(&reduceAllKernel<DT, true, false>)),
+                                    residentPerSm(reinterpret_cast<const void*>(&reduceAllKernel<DT, true, true>))};
+    const int perSm = resident[(isMax ? 2 : 0) + (dense ? 1 : 0)];
+    blocks = std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::min<uint64_t>(maxBlocks, static_cast<uint64_t>(ctx.smCount) * perSm)));
     auto out = static_cast<S*>(dst);
     const unsigned int grid = static_cast<unsigned int>(blocks);
     if (isMax)
