@@ -30,6 +30,7 @@ struct CompiledKernel
 {
     CUmodule   module = nullptr;
     CUfunction function = nullptr;
+    int        residentPerSm = 0;     // CTAs of this kernel that fit on one SM at once (0: unknown)
     std::string source;
 };
 
@@ -244,6 +245,7 @@ private:
     uint64_t m_preparedBytes = 0, m_preparedStamp = 0;
     bool     m_termCacheEnabled = true;     // AIXB200_GEMM_TERM_CACHE=0: every matmul prepares its operands afresh
     bool m_inFlush = false;
+    int  m_residentGrid = 2;                // generated kernels get SMs x resident CTAs x this many CTAs; 0: always SMs x 8 (AIXB200_RESIDENT_GRID)
     uint32_t m_gemmLaunches = 0;            // numbers the launches that use the matmul's tile scheduler in this device's scratch
     bool m_checkErrorWord = false;
 };
