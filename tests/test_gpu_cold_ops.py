@@ -54,7 +54,8 @@ def test_argmax_family(b200, ref, dtype):
 def test_transpose_materialised(b200, ref, dtype):
     rng = np.random.default_rng(400 + dtype)
     for shape, (d0, d1) in [((4, 7), (0, 1)), ((3, 5, 6), (0, 2)), ((3, 5, 6), (1, 2)), ((2, 3, 4, 5), (1, 3)), ((65, 130), (0, 1)),
-                             ((257, 100), (0, 1)), ((3, 70, 50), (1, 2)), ((40, 5, 33), (0, 2)), ((2, 33, 3, 64), (1, 3)), ((64, 96, 2), (0, 1))]:
+                             ((257, 100), (0, 1)), ((3, 70, 50), (1, 2)), ((40, 5, 33), (0, 2)), ((2, 33, 3, 64), (1, 3)), ((64, 96, 2), (0, 1)),
+                             ((128, 260), (0, 1)), ((3, 68, 72), (1, 2)), ((8, 64, 100), (0, 2))]:      # the last three: rows of whole 16-byte packs
         x = values(rng, shape, dtype)
 
         def run(dev):
